@@ -1,0 +1,242 @@
+/*
+ * nomos_attn.h -- C ABI of libnomos_attn.so: B200 (sm_100a) quantized-KV attention
+ * for the Nomos kernel (lightofbaldr/nomos-nvfp4).
+ *
+ * The library is a drop-in for ONE path of the reference: the KV-cache
+ * quantize-on-write codecs, the single-token GQA decode attention and the
+ * multi-row speculative-verify attention.  Each "thin" entry point keeps the
+ * argument order of the internal Mojo operator it replaces (cited per function,
+ * paths relative to the reference root); the DeviceContext argument becomes a
+ * `stream` (a cudaStream_t passed as void*; NULL = the legacy default stream).
+ *
+ * Conventions (those of the reference's own C ABI, nomos_ffi.mojo:18-23):
+ *   - every device pointer is a uint64_t address, every dimension an int32_t;
+ *   - the return value is an int32_t status: 0 ok, negative = error;
+ *   - calls are asynchronous on `stream`; the library never synchronises,
+ *     never allocates device memory and never touches another stream;
+ *   - the caller owns every buffer, including scratch/workspace;
+ *   - early-return no-ops follow the reference (nh <= 0 or seq_len <= 0 -> 0).
+ *
+ * Status codes:
+ *    0  NOMOS_ATTN_OK
+ *   -1  bad argument (null pointer, non-positive dimension, misalignment,
+ *       nh != nkv*kvg, window longer than the ring, ...)
+ *   -2  unsupported configuration (head_dim other than 128/256/512, ...)
+ *   -3  capacity (workspace too small, position beyond a linear cache)
+ *   -4  output not produced
+ *  -99  CUDA runtime error reported by the launch
+ * nomos_attn_last_error() returns a thread-local message for the last failure.
+ *
+ * Alignment: cache rows, scale buffers and Q/out rows must be 16-byte aligned;
+ * cache_hd must be a multiple of 16 (int8) or 32 (int4) elements.
+ */
+#ifndef NOMOS_ATTN_H
+#define NOMOS_ATTN_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NOMOS_ATTN_OK 0
+#define NOMOS_ATTN_EBADARG (-1)
+#define NOMOS_ATTN_EUNSUPPORTED (-2)
+#define NOMOS_ATTN_ECAPACITY (-3)
+#define NOMOS_ATTN_ENOTWRITTEN (-4)
+#define NOMOS_ATTN_ECUDA (-99)
+
+/* KV cache formats of the fused entry points */
+#define NOMOS_KV_I8 0     /* int8 rows + one fp32 scale per (head, slot)              */
+#define NOMOS_KV_I4 1     /* packed int4 rows + one fp32 scale per (head, slot)       */
+#define NOMOS_KV_I4B32 2  /* packed int4 rows + one fp16 scale per 32 values, followed
+                             by one cached fp32 "q8" scale per (head, slot)           */
+/* element types of Q and of the output */
+#define NOMOS_F32 0
+#define NOMOS_BF16 1
+
+/* Library version (cf. nomos_version, nomos_ffi.mojo:117-120). */
+int32_t nomos_attn_version(void);
+/* Message describing the last non-zero status returned on this thread. */
+const char *nomos_attn_last_error(void);
+
+/* ------------------------------------------------------------------------- *
+ *  KV cache codecs (thin, call-for-call)                                     *
+ * ------------------------------------------------------------------------- */
+
+/* gpu_quant_kv_i8, lib/kv_cache_quant.mojo:100-113: bf16 [n_rows, dim] -> int8 +
+ * fp32 row scale (amax/127, 0 -> 1). */
+int32_t nomos_kv_quant_i8(void *stream, uint64_t in_bf16, uint64_t out_i8, uint64_t out_scales,
+                          int32_t n_rows, int32_t dim);
+
+/* gpu_dequant_kv_i8, lib/kv_cache_quant.mojo:116-131. */
+int32_t nomos_kv_dequant_i8(void *stream, uint64_t in_i8, uint64_t in_scales, uint64_t out_bf16,
+                            int32_t n_rows, int32_t dim);
+
+/* gpu_append_quant_kv_i8, lib/kv_cache_quant.mojo:252-271: quantize n_s new
+ * tokens' K/V (fp32 [n_s, nkv, l_hd], token stride l_kvd) into ring slots
+ * (base_pos + s) % cache_cap of the int8 cache [nkv, cache_cap, cache_hd]. */
+int32_t nomos_kv_append_quant_i8(void *stream, uint64_t src_k, uint64_t src_v,
+                                 uint64_t dst_k_i8, uint64_t dst_v_i8, uint64_t k_scales, uint64_t v_scales,
+                                 int32_t n_s, int32_t nkv, int32_t l_hd, int32_t l_kvd, int32_t cache_cap,
+                                 int32_t cache_hd, int32_t base_pos);
+
+/* gpu_dequant_kv_i8_layer, lib/kv_cache_quant.mojo:274-290: ring window
+ * [win_start, win_start+klen) -> linear bf16 scratch [nkv, max_seq, cache_hd]. */
+int32_t nomos_kv_dequant_i8_layer(void *stream, uint64_t src_i8, uint64_t scales, uint64_t dst_bf16,
+                                  int32_t nkv, int32_t klen, int32_t cache_hd, int32_t max_seq,
+                                  int32_t cache_cap, int32_t win_start);
+
+/* gpu_append_quant_kv_i4, lib/kv_cache_quant.mojo:803-836.  scale_blocks == 1:
+ * one fp32 scale per row (amax/7); scale_blocks > 1: block-32 layout, the scale
+ * buffer holds [nkv, cache_cap, nblocks] fp16 then [nkv, cache_cap] fp32. */
+int32_t nomos_kv_append_quant_i4(void *stream, uint64_t src_k, uint64_t src_v,
+                                 uint64_t dst_k_i4, uint64_t dst_v_i4, uint64_t k_scales, uint64_t v_scales,
+                                 int32_t n_s, int32_t nkv, int32_t l_hd, int32_t l_kvd, int32_t cache_cap,
+                                 int32_t cache_hd, int32_t base_pos, int32_t scale_blocks);
+
+/* gpu_append_quant_kv_i4_with_q8, lib/kv_cache_quant.mojo:839-882: as above and
+ * publishes each row as int8 at ABSOLUTE row h*q8_pitch + base_pos + s of a linear
+ * view [nkv, q8_pitch, cache_hd] with its fp32 scale [nkv, q8_pitch]. */
+int32_t nomos_kv_append_quant_i4_with_q8(void *stream, uint64_t src_k, uint64_t src_v,
+                                         uint64_t dst_k_i4, uint64_t dst_v_i4, uint64_t k_scales, uint64_t v_scales,
+                                         uint64_t dst_k_q8, uint64_t dst_v_q8, uint64_t k_q8_scales, uint64_t v_q8_scales,
+                                         int32_t n_s, int32_t nkv, int32_t l_hd, int32_t l_kvd, int32_t cache_cap,
+                                         int32_t cache_hd, int32_t base_pos, int32_t q8_pitch, int32_t scale_blocks);
+
+/* gpu_dequant_kv_i4_layer, lib/kv_cache_quant.mojo:885-918: int4 ring window ->
+ * linear bf16 scratch (row-scale or block-32). */
+int32_t nomos_kv_dequant_i4_layer(void *stream, uint64_t src_i4, uint64_t scales, uint64_t dst_bf16,
+                                  int32_t nkv, int32_t klen, int32_t cache_hd, int32_t max_seq,
+                                  int32_t cache_cap, int32_t win_start, int32_t scale_blocks);
+
+/* gpu_dequant_kv_i4_to_q8_layer, lib/kv_cache_quant.mojo:956-989: int4 ring window
+ * -> linear int8 scratch + linear fp32 row scales. */
+int32_t nomos_kv_dequant_i4_to_q8_layer(void *stream, uint64_t src_i4, uint64_t scales, uint64_t dst_i8,
+                                        uint64_t dst_scale, int32_t nkv, int32_t klen, int32_t cache_hd,
+                                        int32_t max_seq, int32_t cache_cap, int32_t win_start, int32_t scale_blocks);
+
+/* append_kv_gpu_dev / append_kv_gpu_dev_async, lib/attention_gpu.mojo:87-133:
+ * one token's fp32 K,V [nkv, l_hd] -> fp32 cache [nkv, max_seq, cache_hd] at cl. */
+int32_t nomos_kv_append_fp32(void *stream, uint64_t k_cache, uint64_t v_cache, uint64_t k_new, uint64_t v_new,
+                             int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq, int32_t cl);
+
+/* append_kv_gpu_bf16_dev, lib/attention_gpu.mojo:136-162: same into a bf16 cache
+ * (the two bf16 scratch arguments of the reference are accepted and unused). */
+int32_t nomos_kv_append_bf16(void *stream, uint64_t k_cache, uint64_t v_cache, uint64_t k_new, uint64_t v_new,
+                             uint64_t k_bf16_scratch, uint64_t v_bf16_scratch,
+                             int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq, int32_t cl);
+
+/* gpu_append_kv_batched_bf16, lib/batched_attn_gpu.mojo:87-102. */
+int32_t nomos_kv_append_batched_bf16(void *stream, uint64_t src_k, uint64_t src_v, uint64_t dst_k, uint64_t dst_v,
+                                     int32_t n_s, int32_t nkv, int32_t l_hd, int32_t l_kvd, int32_t max_seq,
+                                     int32_t cache_hd, int32_t base_pos);
+
+/* ------------------------------------------------------------------------- *
+ *  Attention (thin, call-for-call)                                           *
+ * ------------------------------------------------------------------------- *
+ * In all of these `max_seq` is the row pitch per head of the K/V/scale arrays
+ * handed in (the caller may pre-offset the base pointers), `seq_len` counts keys
+ * from that base, and no softmax scale or softcap is applied
+ * (lib/attention_gpu_int8.mojo:8-9).  Q and the output are fp32.  The scratch
+ * arguments keep the reference's sizes and are used only as split-K workspace.
+ */
+
+/* attention_gpu_int8_dev, lib/attention_gpu_int8.mojo:598-631.
+ * scores_scratch: >= nh*seq_len floats. */
+int32_t nomos_attn_decode_i8(void *stream, uint64_t q, uint64_t k_i8, uint64_t v_i8, uint64_t k_scale,
+                             uint64_t v_scale, uint64_t scores_scratch, uint64_t out,
+                             int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
+                             int32_t seq_len, int32_t kvg);
+
+/* attention_decode_order_multirow_int8, lib/attention_gpu_int8.mojo:634-708:
+ * S query rows [S, nh, l_hd]; row r attends absolute keys
+ * [max(0, apos-window+1) if window>0 else 0, apos], apos = query_base_pos + r.
+ * scores: >= S*nh*score_stride floats. */
+int32_t nomos_attn_decode_multirow_i8(void *stream, uint64_t q_b, uint64_t scores, uint64_t attn_b,
+                                      uint64_t k_i8, uint64_t v_i8, uint64_t k_scale, uint64_t v_scale,
+                                      int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
+                                      int32_t S, int32_t score_stride, int32_t kvg, int32_t window,
+                                      int32_t query_base_pos);
+
+/* attention_prefill_prefix_batched_int8, lib/attention_gpu_int8.mojo:844-887.
+ * q_t / attn_t are the reference's transpose scratches (accepted, unused). */
+int32_t nomos_attn_prefix_batched_i8(void *stream, uint64_t q_b, uint64_t q_t, uint64_t scores, uint64_t attn_t,
+                                     uint64_t attn_b, uint64_t k_i8, uint64_t v_i8, uint64_t k_scale, uint64_t v_scale,
+                                     int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
+                                     int32_t S, int32_t key_len, int32_t kvg, int32_t window,
+                                     int32_t query_base_pos, int32_t key_base_pos);
+
+/* attention_gpu_fp32_dev, lib/attention_gpu.mojo:165-204 (cuBLAS handle dropped). */
+int32_t nomos_attn_decode_fp32(void *stream, uint64_t q, uint64_t k_cache, uint64_t v_cache, uint64_t scores_scratch,
+                               uint64_t out, int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd,
+                               int32_t max_seq, int32_t seq_len, int32_t kvg);
+
+/* attention_gpu_bf16_dev, lib/attention_gpu.mojo:207-248 (q_bf16 / scores_bf16
+ * scratches accepted, unused). */
+int32_t nomos_attn_decode_bf16(void *stream, uint64_t q, uint64_t k_cache, uint64_t v_cache, uint64_t scores_scratch,
+                               uint64_t q_bf16, uint64_t scores_bf16, uint64_t out,
+                               int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
+                               int32_t seq_len, int32_t kvg);
+
+/* attention_prefill_prefix_batched_fp32 / _bf16, lib/batched_attn_gpu.mojo:499-548,
+ * 613-666.  kv_is_bf16 selects the cache element type. */
+int32_t nomos_attn_prefix_batched_dense(void *stream, uint64_t q_b, uint64_t scores, uint64_t attn_b,
+                                        uint64_t k_cache, uint64_t v_cache,
+                                        int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
+                                        int32_t S, int32_t key_len, int32_t kvg, int32_t window,
+                                        int32_t query_base_pos, int32_t key_base_pos, int32_t kv_is_bf16);
+
+/* ------------------------------------------------------------------------- *
+ *  Fused superset: attention straight off the packed ring cache              *
+ * ------------------------------------------------------------------------- *
+ * One call = (optional) quantize-on-write of the new rows + attention of S query
+ * rows over the window, with no dequant scratch and no score matrix.  It stands
+ * for the reference's per-layer sequence append -> window reader -> attention
+ * (lib/engine_decode.mojo:356-389, 445-460, 527-554; verify:
+ * lib/engine_prefill.mojo:547-726).
+ *
+ * All fields are 8 bytes wide so a caller without C structs can fill an int64
+ * array.  Zero-initialise, then set what you need.
+ */
+typedef struct nomos_attn_args {
+    uint64_t struct_bytes;      /* sizeof(nomos_attn_args_t), for versioning              */
+    uint64_t q;                 /* [batch][S][nh][l_hd], q_type                           */
+    uint64_t k_cache, v_cache;  /* [batch][nkv][cache_cap][cache_hd] int8, or /2 bytes int4*/
+    uint64_t k_scales, v_scales;/* per kv_fmt, see NOMOS_KV_*                             */
+    uint64_t out;               /* [batch][S][nh][l_hd], out_type (may be 0 if partial_out)*/
+    uint64_t partial_out;       /* 0, or fp32 [batch][S][nh][l_hd+2] = un-normalised o,
+                                   then m (natural log), then l: for cross-GPU merging     */
+    uint64_t workspace;         /* split-K scratch                                        */
+    int64_t ws_bytes;           /* >= nomos_attn_workspace_bytes(args)                     */
+    uint64_t new_k, new_v;      /* 0, or fp32 [n_new][nkv][l_hd] rows to quantize+append   */
+    int64_t n_new, new_stride;  /* rows, and elements between consecutive rows            */
+    int64_t new_base_pos;       /* absolute position of the first new row                 */
+    int64_t kv_fmt, q_type, out_type;
+    int64_t batch, S, nh, nkv, kvg, l_hd, cache_hd, cache_cap;
+    int64_t win_start;          /* absolute position of the first attended key            */
+    int64_t klen;               /* attended keys INCLUDING the new rows; the S query rows
+                                   are the last S keys, causal among themselves           */
+    int64_t window;             /* per-row sliding window (0 = none)                      */
+    double softmax_scale;       /* multiplies QK before the softmax; 1.0 = the reference  */
+    int64_t q_batch_stride, out_batch_stride;      /* elements; 0 = dense                 */
+    int64_t kv_batch_stride, scale_batch_stride;   /* bytes;    0 = dense                 */
+    int64_t force_splits;       /* 0 = library chooses the sequence split                 */
+} nomos_attn_args_t;
+
+/* Bytes of workspace the call needs (>= 0), or a negative status. */
+int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args);
+/* Run it. */
+int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *args);
+
+/* Merge G partial triples (as written through partial_out, gathered from G
+ * sequence shards) into a normalised output.  partials: fp32 [G][rows][l_hd+2];
+ * out: [rows][l_hd] of out_type.  No counterpart in the reference (which is
+ * single-GPU); it is the on-device tail of the sequence-sharded decode. */
+int32_t nomos_attn_merge_partials(void *stream, uint64_t partials, int32_t G, int32_t rows, int32_t l_hd,
+                                  uint64_t out, int32_t out_type);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NOMOS_ATTN_H */

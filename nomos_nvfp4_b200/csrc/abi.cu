@@ -1,0 +1,407 @@
+// extern "C" surface of libnomos_attn.so: argument validation + forwarding.
+// Declarations and per-function reference citations live in include/nomos_attn.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/nomos_attn.h"
+#include "common.cuh"
+#include "launch.h"
+
+namespace nomos {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+}  // namespace nomos
+
+using namespace nomos;
+
+#define NOMOS_EXPORT extern "C" __attribute__((visibility("default")))
+
+#define REQUIRE(cond, ...)                      \
+    do {                                        \
+        if (!(cond)) {                          \
+            set_error(__VA_ARGS__);             \
+            return NOMOS_EBADARG;               \
+        }                                       \
+    } while (0)
+
+static inline bool aligned(uint64_t p, uint64_t a) { return (p & (a - 1)) == 0; }
+static inline void *ptr(uint64_t a) { return reinterpret_cast<void *>(a); }
+static inline cudaStream_t as_stream(void *s) { return static_cast<cudaStream_t>(s); }
+static inline bool hd_ok(int hd) { return hd == 128 || hd == 256 || hd == 512; }
+
+NOMOS_EXPORT int32_t nomos_attn_version(void) { return 100; }
+NOMOS_EXPORT const char *nomos_attn_last_error(void) { return g_err; }
+
+// ------------------------------------------------------------------- codecs
+
+NOMOS_EXPORT int32_t nomos_kv_quant_i8(void *stream, uint64_t in_bf16, uint64_t out_i8, uint64_t out_scales,
+                                       int32_t n_rows, int32_t dim) {
+    if (n_rows <= 0) return NOMOS_OK;
+    REQUIRE(in_bf16 && out_i8 && out_scales, "nomos_kv_quant_i8: null pointer");
+    REQUIRE(dim > 0, "nomos_kv_quant_i8: dim %d", dim);
+    return launch_quant_i8(as_stream(stream), ptr(in_bf16), ptr(out_i8), ptr(out_scales), n_rows, dim);
+}
+
+NOMOS_EXPORT int32_t nomos_kv_dequant_i8(void *stream, uint64_t in_i8, uint64_t in_scales, uint64_t out_bf16,
+                                         int32_t n_rows, int32_t dim) {
+    if (n_rows <= 0) return NOMOS_OK;
+    REQUIRE(in_i8 && in_scales && out_bf16, "nomos_kv_dequant_i8: null pointer");
+    REQUIRE(dim > 0, "nomos_kv_dequant_i8: dim %d", dim);
+    return launch_dequant_i8(as_stream(stream), ptr(in_i8), ptr(in_scales), ptr(out_bf16), n_rows, dim);
+}
+
+static int check_append(const char *who, uint64_t a, uint64_t b, uint64_t c, uint64_t d, uint64_t e, uint64_t f,
+                        int n_s, int nkv, int l_hd, int l_kvd, int cache_cap, int cache_hd, int base_pos) {
+    REQUIRE(a && b && c && d && e && f, "%s: null pointer", who);
+    REQUIRE(nkv > 0 && l_hd > 0 && cache_cap > 0 && cache_hd >= l_hd, "%s: bad geometry nkv=%d l_hd=%d cache_cap=%d cache_hd=%d",
+            who, nkv, l_hd, cache_cap, cache_hd);
+    REQUIRE(l_kvd >= nkv * l_hd || n_s == 1, "%s: token stride l_kvd=%d < nkv*l_hd", who, l_kvd);
+    REQUIRE(base_pos >= 0, "%s: base_pos %d", who, base_pos);
+    REQUIRE(n_s <= cache_cap, "%s: n_s=%d rows would overwrite each other in a ring of %d", who, n_s, cache_cap);
+    return NOMOS_OK;
+}
+
+NOMOS_EXPORT int32_t nomos_kv_append_quant_i8(void *stream, uint64_t src_k, uint64_t src_v, uint64_t dst_k_i8,
+                                              uint64_t dst_v_i8, uint64_t k_scales, uint64_t v_scales, int32_t n_s,
+                                              int32_t nkv, int32_t l_hd, int32_t l_kvd, int32_t cache_cap,
+                                              int32_t cache_hd, int32_t base_pos) {
+    if (n_s <= 0) return NOMOS_OK;
+    int rc = check_append("nomos_kv_append_quant_i8", src_k, src_v, dst_k_i8, dst_v_i8, k_scales, v_scales, n_s, nkv, l_hd,
+                          l_kvd, cache_cap, cache_hd, base_pos);
+    if (rc) return rc;
+    return launch_append_i8(as_stream(stream), ptr(src_k), ptr(src_v), ptr(dst_k_i8), ptr(dst_v_i8), ptr(k_scales),
+                            ptr(v_scales), n_s, nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos);
+}
+
+static int check_scale_blocks(const char *who, int l_hd, int scale_blocks) {
+    REQUIRE(scale_blocks >= 1, "%s: scale_blocks %d", who, scale_blocks);
+    if (scale_blocks > 1 && scale_blocks != (l_hd + 31) / 32) {
+        set_error("%s: scale_blocks=%d but head_dim %d has %d blocks of 32", who, scale_blocks, l_hd, (l_hd + 31) / 32);
+        return NOMOS_EUNSUPPORTED;
+    }
+    return NOMOS_OK;
+}
+
+NOMOS_EXPORT int32_t nomos_kv_append_quant_i4(void *stream, uint64_t src_k, uint64_t src_v, uint64_t dst_k_i4,
+                                              uint64_t dst_v_i4, uint64_t k_scales, uint64_t v_scales, int32_t n_s,
+                                              int32_t nkv, int32_t l_hd, int32_t l_kvd, int32_t cache_cap,
+                                              int32_t cache_hd, int32_t base_pos, int32_t scale_blocks) {
+    if (n_s <= 0) return NOMOS_OK;
+    int rc = check_append("nomos_kv_append_quant_i4", src_k, src_v, dst_k_i4, dst_v_i4, k_scales, v_scales, n_s, nkv, l_hd,
+                          l_kvd, cache_cap, cache_hd, base_pos);
+    if (rc) return rc;
+    REQUIRE(cache_hd % 2 == 0, "nomos_kv_append_quant_i4: odd cache_hd %d", cache_hd);
+    if ((rc = check_scale_blocks("nomos_kv_append_quant_i4", l_hd, scale_blocks))) return rc;
+    return launch_append_i4(as_stream(stream), ptr(src_k), ptr(src_v), ptr(dst_k_i4), ptr(dst_v_i4), ptr(k_scales),
+                            ptr(v_scales), nullptr, nullptr, nullptr, nullptr, n_s, nkv, l_hd, l_kvd, cache_cap, cache_hd,
+                            base_pos, 0, scale_blocks);
+}
+
+NOMOS_EXPORT int32_t nomos_kv_append_quant_i4_with_q8(void *stream, uint64_t src_k, uint64_t src_v, uint64_t dst_k_i4,
+                                                      uint64_t dst_v_i4, uint64_t k_scales, uint64_t v_scales,
+                                                      uint64_t dst_k_q8, uint64_t dst_v_q8, uint64_t k_q8_scales,
+                                                      uint64_t v_q8_scales, int32_t n_s, int32_t nkv, int32_t l_hd,
+                                                      int32_t l_kvd, int32_t cache_cap, int32_t cache_hd, int32_t base_pos,
+                                                      int32_t q8_pitch, int32_t scale_blocks) {
+    if (n_s <= 0) return NOMOS_OK;
+    int rc = check_append("nomos_kv_append_quant_i4_with_q8", src_k, src_v, dst_k_i4, dst_v_i4, k_scales, v_scales, n_s,
+                          nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos);
+    if (rc) return rc;
+    REQUIRE(dst_k_q8 && dst_v_q8 && k_q8_scales && v_q8_scales, "nomos_kv_append_quant_i4_with_q8: null view pointer");
+    REQUIRE(cache_hd % 2 == 0, "nomos_kv_append_quant_i4_with_q8: odd cache_hd %d", cache_hd);
+    if (base_pos + n_s > q8_pitch) {
+        set_error("nomos_kv_append_quant_i4_with_q8: rows [%d,%d) beyond the view pitch %d", base_pos, base_pos + n_s, q8_pitch);
+        return NOMOS_ECAPACITY;
+    }
+    if ((rc = check_scale_blocks("nomos_kv_append_quant_i4_with_q8", l_hd, scale_blocks))) return rc;
+    return launch_append_i4(as_stream(stream), ptr(src_k), ptr(src_v), ptr(dst_k_i4), ptr(dst_v_i4), ptr(k_scales),
+                            ptr(v_scales), ptr(dst_k_q8), ptr(dst_v_q8), ptr(k_q8_scales), ptr(v_q8_scales), n_s, nkv, l_hd,
+                            l_kvd, cache_cap, cache_hd, base_pos, q8_pitch, scale_blocks);
+}
+
+static int check_reader(const char *who, uint64_t src, uint64_t scales, uint64_t dst, int nkv, int klen, int cache_hd,
+                        int max_seq, int cache_cap, int win_start) {
+    REQUIRE(src && scales && dst, "%s: null pointer", who);
+    REQUIRE(nkv > 0 && cache_hd > 0 && cache_cap > 0 && win_start >= 0, "%s: bad geometry", who);
+    REQUIRE(cache_hd % 8 == 0, "%s: cache_hd %d must be a multiple of 8", who, cache_hd);
+    REQUIRE(aligned(src, 8) && aligned(dst, 16), "%s: misaligned buffer", who);
+    if (klen > max_seq) { set_error("%s: klen %d exceeds the scratch pitch %d", who, klen, max_seq); return NOMOS_ECAPACITY; }
+    if (klen > cache_cap) { set_error("%s: klen %d exceeds the ring capacity %d", who, klen, cache_cap); return NOMOS_ECAPACITY; }
+    return NOMOS_OK;
+}
+
+NOMOS_EXPORT int32_t nomos_kv_dequant_i8_layer(void *stream, uint64_t src_i8, uint64_t scales, uint64_t dst_bf16,
+                                               int32_t nkv, int32_t klen, int32_t cache_hd, int32_t max_seq,
+                                               int32_t cache_cap, int32_t win_start) {
+    if (klen <= 0) return NOMOS_OK;
+    int rc = check_reader("nomos_kv_dequant_i8_layer", src_i8, scales, dst_bf16, nkv, klen, cache_hd, max_seq, cache_cap, win_start);
+    if (rc) return rc;
+    return launch_window_reader(as_stream(stream), 0, ptr(src_i8), ptr(scales), ptr(dst_bf16), nullptr, nkv, klen, cache_hd,
+                                max_seq, cache_cap, win_start, 1);
+}
+
+NOMOS_EXPORT int32_t nomos_kv_dequant_i4_layer(void *stream, uint64_t src_i4, uint64_t scales, uint64_t dst_bf16,
+                                               int32_t nkv, int32_t klen, int32_t cache_hd, int32_t max_seq,
+                                               int32_t cache_cap, int32_t win_start, int32_t scale_blocks) {
+    if (klen <= 0) return NOMOS_OK;
+    int rc = check_reader("nomos_kv_dequant_i4_layer", src_i4, scales, dst_bf16, nkv, klen, cache_hd, max_seq, cache_cap, win_start);
+    if (rc) return rc;
+    REQUIRE(scale_blocks >= 1, "nomos_kv_dequant_i4_layer: scale_blocks %d", scale_blocks);
+    return launch_window_reader(as_stream(stream), scale_blocks > 1 ? 2 : 1, ptr(src_i4), ptr(scales), ptr(dst_bf16), nullptr,
+                                nkv, klen, cache_hd, max_seq, cache_cap, win_start, scale_blocks);
+}
+
+NOMOS_EXPORT int32_t nomos_kv_dequant_i4_to_q8_layer(void *stream, uint64_t src_i4, uint64_t scales, uint64_t dst_i8,
+                                                     uint64_t dst_scale, int32_t nkv, int32_t klen, int32_t cache_hd,
+                                                     int32_t max_seq, int32_t cache_cap, int32_t win_start,
+                                                     int32_t scale_blocks) {
+    if (klen <= 0) return NOMOS_OK;
+    int rc = check_reader("nomos_kv_dequant_i4_to_q8_layer", src_i4, scales, dst_i8, nkv, klen, cache_hd, max_seq, cache_cap, win_start);
+    if (rc) return rc;
+    REQUIRE(dst_scale, "nomos_kv_dequant_i4_to_q8_layer: null dst_scale");
+    REQUIRE(scale_blocks >= 1, "nomos_kv_dequant_i4_to_q8_layer: scale_blocks %d", scale_blocks);
+    return launch_window_reader(as_stream(stream), scale_blocks > 1 ? 4 : 3, ptr(src_i4), ptr(scales), ptr(dst_i8),
+                                ptr(dst_scale), nkv, klen, cache_hd, max_seq, cache_cap, win_start, scale_blocks);
+}
+
+static int check_dense_append(const char *who, uint64_t a, uint64_t b, uint64_t c, uint64_t d, int nkv, int l_hd,
+                              int cache_hd, int max_seq, int pos, int n_s) {
+    REQUIRE(a && b && c && d, "%s: null pointer", who);
+    REQUIRE(nkv > 0 && l_hd > 0 && cache_hd >= l_hd && max_seq > 0 && pos >= 0, "%s: bad geometry", who);
+    if (pos + n_s > max_seq) { set_error("%s: rows [%d,%d) beyond max_seq %d", who, pos, pos + n_s, max_seq); return NOMOS_ECAPACITY; }
+    return NOMOS_OK;
+}
+
+NOMOS_EXPORT int32_t nomos_kv_append_fp32(void *stream, uint64_t k_cache, uint64_t v_cache, uint64_t k_new, uint64_t v_new,
+                                          int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq, int32_t cl) {
+    int rc = check_dense_append("nomos_kv_append_fp32", k_cache, v_cache, k_new, v_new, nkv, l_hd, cache_hd, max_seq, cl, 1);
+    if (rc) return rc;
+    return launch_append_dense(as_stream(stream), 0, ptr(k_new), ptr(v_new), ptr(k_cache), ptr(v_cache), 1, nkv, l_hd,
+                               nkv * l_hd, max_seq, cache_hd, cl);
+}
+
+NOMOS_EXPORT int32_t nomos_kv_append_bf16(void *stream, uint64_t k_cache, uint64_t v_cache, uint64_t k_new, uint64_t v_new,
+                                          uint64_t, uint64_t, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
+                                          int32_t cl) {
+    int rc = check_dense_append("nomos_kv_append_bf16", k_cache, v_cache, k_new, v_new, nkv, l_hd, cache_hd, max_seq, cl, 1);
+    if (rc) return rc;
+    return launch_append_dense(as_stream(stream), 1, ptr(k_new), ptr(v_new), ptr(k_cache), ptr(v_cache), 1, nkv, l_hd,
+                               nkv * l_hd, max_seq, cache_hd, cl);
+}
+
+NOMOS_EXPORT int32_t nomos_kv_append_batched_bf16(void *stream, uint64_t src_k, uint64_t src_v, uint64_t dst_k,
+                                                  uint64_t dst_v, int32_t n_s, int32_t nkv, int32_t l_hd, int32_t l_kvd,
+                                                  int32_t max_seq, int32_t cache_hd, int32_t base_pos) {
+    if (n_s <= 0) return NOMOS_OK;
+    int rc = check_dense_append("nomos_kv_append_batched_bf16", dst_k, dst_v, src_k, src_v, nkv, l_hd, cache_hd, max_seq, base_pos, n_s);
+    if (rc) return rc;
+    return launch_append_dense(as_stream(stream), 1, ptr(src_k), ptr(src_v), ptr(dst_k), ptr(dst_v), n_s, nkv, l_hd, l_kvd,
+                               max_seq, cache_hd, base_pos);
+}
+
+// ---------------------------------------------------------------- attention
+
+static int check_attn_geometry(const char *who, int nh, int nkv, int l_hd, int cache_hd, int kvg) {
+    REQUIRE(nkv > 0 && kvg > 0 && nh == nkv * kvg, "%s: nh=%d must equal nkv=%d * kvg=%d", who, nh, nkv, kvg);
+    if (!hd_ok(l_hd)) { set_error("%s: head_dim %d unsupported (128, 256, 512)", who, l_hd); return NOMOS_EUNSUPPORTED; }
+    REQUIRE(cache_hd >= l_hd, "%s: cache_hd %d < l_hd %d", who, cache_hd, l_hd);
+    return NOMOS_OK;
+}
+
+static int run_fused(cudaStream_t st, AttnArgs &a, const char *who) {
+    int rc = check_attn_geometry(who, a.nh, a.nkv, a.l_hd, a.cache_hd, a.kvg);
+    if (rc) return rc;
+    REQUIRE(a.q && a.k_cache && a.v_cache && a.k_scales && a.v_scales, "%s: null pointer", who);
+    REQUIRE(a.out || a.partial_out, "%s: no output buffer", who);
+    REQUIRE(a.batch > 0 && a.S > 0 && a.cache_cap > 0 && a.win_start >= 0, "%s: bad batch/S/cache_cap/win_start", who);
+    REQUIRE(a.kv_fmt >= KV_I8 && a.kv_fmt <= KV_I4B32, "%s: kv_fmt %d", who, a.kv_fmt);
+    REQUIRE((a.q_type == ET_F32 || a.q_type == ET_BF16) && (a.out_type == ET_F32 || a.out_type == ET_BF16), "%s: element type", who);
+    const int row_bytes = a.kv_fmt == KV_I8 ? a.cache_hd : a.cache_hd / 2;
+    REQUIRE(row_bytes % 16 == 0, "%s: cache rows must be a multiple of 16 bytes (cache_hd=%d)", who, a.cache_hd);
+    REQUIRE(aligned((uint64_t)a.k_cache, 16) && aligned((uint64_t)a.v_cache, 16) && aligned((uint64_t)a.k_scales, 4) &&
+                aligned((uint64_t)a.v_scales, 4) && aligned((uint64_t)a.q, 4),
+            "%s: misaligned buffer", who);
+    REQUIRE(a.kv_batch_stride % 16 == 0 && a.scale_batch_stride % 4 == 0, "%s: misaligned batch stride", who);
+    REQUIRE(a.window >= 0, "%s: window %d", who, a.window);
+    if (a.klen > a.cache_cap) { set_error("%s: klen %d exceeds the cache capacity %d", who, a.klen, a.cache_cap); return NOMOS_ECAPACITY; }
+    REQUIRE(a.klen >= a.S, "%s: klen %d < S %d (the query rows are the last S keys)", who, a.klen, a.S);
+    return launch_attn_fused(st, a);
+}
+
+static void fill_thin(AttnArgs &a, uint64_t q, uint64_t k, uint64_t v, uint64_t ks, uint64_t vs, uint64_t scratch,
+                      long scratch_floats, uint64_t out, int nh, int nkv, int l_hd, int cache_hd, int max_seq, int kvg) {
+    memset(&a, 0, sizeof(a));
+    a.q = ptr(q); a.k_cache = ptr(k); a.v_cache = ptr(v); a.k_scales = ptr(ks); a.v_scales = ptr(vs);
+    a.out = ptr(out); a.workspace = ptr(scratch); a.ws_bytes = scratch ? scratch_floats * 4 : 0;
+    a.kv_fmt = KV_I8; a.q_type = ET_F32; a.out_type = ET_F32;
+    a.batch = 1; a.S = 1; a.nh = nh; a.nkv = nkv; a.kvg = kvg; a.l_hd = l_hd; a.cache_hd = cache_hd; a.cache_cap = max_seq;
+    a.softmax_scale = 1.0f;
+    a.fit_splits_to_ws = 1;
+}
+
+NOMOS_EXPORT int32_t nomos_attn_decode_i8(void *stream, uint64_t q, uint64_t k_i8, uint64_t v_i8, uint64_t k_scale,
+                                          uint64_t v_scale, uint64_t scores_scratch, uint64_t out, int32_t nh, int32_t nkv,
+                                          int32_t l_hd, int32_t cache_hd, int32_t max_seq, int32_t seq_len, int32_t kvg) {
+    if (nh <= 0 || seq_len <= 0) return NOMOS_OK;
+    AttnArgs a;
+    fill_thin(a, q, k_i8, v_i8, k_scale, v_scale, scores_scratch, (long)nh * seq_len, out, nh, nkv, l_hd, cache_hd, max_seq, kvg);
+    a.klen = seq_len;
+    return run_fused(as_stream(stream), a, "nomos_attn_decode_i8");
+}
+
+NOMOS_EXPORT int32_t nomos_attn_decode_multirow_i8(void *stream, uint64_t q_b, uint64_t scores, uint64_t attn_b,
+                                                   uint64_t k_i8, uint64_t v_i8, uint64_t k_scale, uint64_t v_scale,
+                                                   int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
+                                                   int32_t S, int32_t score_stride, int32_t kvg, int32_t window,
+                                                   int32_t query_base_pos) {
+    if (nh <= 0 || S <= 0 || score_stride <= 0) return NOMOS_OK;
+    REQUIRE(query_base_pos >= 0, "nomos_attn_decode_multirow_i8: query_base_pos %d", query_base_pos);
+    AttnArgs a;
+    fill_thin(a, q_b, k_i8, v_i8, k_scale, v_scale, scores, (long)S * nh * score_stride, attn_b, nh, nkv, l_hd, cache_hd, max_seq, kvg);
+    a.S = S; a.klen = query_base_pos + S; a.window = window;
+    return run_fused(as_stream(stream), a, "nomos_attn_decode_multirow_i8");
+}
+
+NOMOS_EXPORT int32_t nomos_attn_prefix_batched_i8(void *stream, uint64_t q_b, uint64_t, uint64_t scores, uint64_t,
+                                                  uint64_t attn_b, uint64_t k_i8, uint64_t v_i8, uint64_t k_scale,
+                                                  uint64_t v_scale, int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd,
+                                                  int32_t max_seq, int32_t S, int32_t key_len, int32_t kvg, int32_t window,
+                                                  int32_t query_base_pos, int32_t key_base_pos) {
+    if (nh <= 0 || S <= 0 || key_len <= 0) return NOMOS_OK;
+    // The fused kernel expresses "row s sees keys up to its own position": the key
+    // range handed in must end exactly at the last query row.
+    if (key_base_pos != 0 || key_len != query_base_pos + S) {
+        set_error("nomos_attn_prefix_batched_i8: only key_base_pos=0 and key_len=query_base_pos+S are supported");
+        return NOMOS_EUNSUPPORTED;
+    }
+    AttnArgs a;
+    fill_thin(a, q_b, k_i8, v_i8, k_scale, v_scale, scores, (long)S * nh * key_len, attn_b, nh, nkv, l_hd, cache_hd, max_seq, kvg);
+    a.S = S; a.klen = key_len; a.window = window;
+    return run_fused(as_stream(stream), a, "nomos_attn_prefix_batched_i8");
+}
+
+static int run_dense(cudaStream_t st, const char *who, uint64_t q, uint64_t k, uint64_t v, uint64_t scratch, long scratch_floats,
+                     uint64_t out, int nh, int nkv, int l_hd, int cache_hd, int max_seq, int S, int key_len, int kvg,
+                     int window, int qbase, int kbase, int kv_is_bf16) {
+    int rc = check_attn_geometry(who, nh, nkv, l_hd, cache_hd, kvg);
+    if (rc) return rc;
+    REQUIRE(q && k && v && out, "%s: null pointer", who);
+    REQUIRE(aligned(k, 16) && aligned(v, 16) && aligned(q, 4) && (cache_hd * (kv_is_bf16 ? 2 : 4)) % 16 == 0, "%s: misaligned cache", who);
+    if (key_len > max_seq) { set_error("%s: key_len %d exceeds max_seq %d", who, key_len, max_seq); return NOMOS_ECAPACITY; }
+    DenseAttnArgs a;
+    a.q = static_cast<const float *>(ptr(q)); a.k_cache = ptr(k); a.v_cache = ptr(v); a.out = static_cast<float *>(ptr(out));
+    a.workspace = ptr(scratch); a.ws_bytes = scratch ? scratch_floats * 4 : 0;
+    a.kv_is_bf16 = kv_is_bf16; a.S = S; a.nh = nh; a.nkv = nkv; a.kvg = kvg; a.l_hd = l_hd; a.cache_hd = cache_hd;
+    a.max_seq = max_seq; a.key_len = key_len; a.window = window; a.query_base_pos = qbase; a.key_base_pos = kbase;
+    return launch_attn_dense(st, a);
+}
+
+NOMOS_EXPORT int32_t nomos_attn_decode_fp32(void *stream, uint64_t q, uint64_t k_cache, uint64_t v_cache,
+                                            uint64_t scores_scratch, uint64_t out, int32_t nh, int32_t nkv, int32_t l_hd,
+                                            int32_t cache_hd, int32_t max_seq, int32_t seq_len, int32_t kvg) {
+    if (nh <= 0 || seq_len <= 0) return NOMOS_OK;
+    return run_dense(as_stream(stream), "nomos_attn_decode_fp32", q, k_cache, v_cache, scores_scratch, (long)nh * seq_len, out, nh,
+                     nkv, l_hd, cache_hd, max_seq, 1, seq_len, kvg, 0, seq_len - 1, 0, 0);
+}
+
+NOMOS_EXPORT int32_t nomos_attn_decode_bf16(void *stream, uint64_t q, uint64_t k_cache, uint64_t v_cache,
+                                            uint64_t scores_scratch, uint64_t, uint64_t, uint64_t out, int32_t nh,
+                                            int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq, int32_t seq_len,
+                                            int32_t kvg) {
+    if (nh <= 0 || seq_len <= 0) return NOMOS_OK;
+    return run_dense(as_stream(stream), "nomos_attn_decode_bf16", q, k_cache, v_cache, scores_scratch, (long)nh * seq_len, out, nh,
+                     nkv, l_hd, cache_hd, max_seq, 1, seq_len, kvg, 0, seq_len - 1, 0, 1);
+}
+
+NOMOS_EXPORT int32_t nomos_attn_prefix_batched_dense(void *stream, uint64_t q_b, uint64_t scores, uint64_t attn_b,
+                                                     uint64_t k_cache, uint64_t v_cache, int32_t nh, int32_t nkv,
+                                                     int32_t l_hd, int32_t cache_hd, int32_t max_seq, int32_t S,
+                                                     int32_t key_len, int32_t kvg, int32_t window, int32_t query_base_pos,
+                                                     int32_t key_base_pos, int32_t kv_is_bf16) {
+    if (nh <= 0 || S <= 0 || key_len <= 0) return NOMOS_OK;
+    return run_dense(as_stream(stream), "nomos_attn_prefix_batched_dense", q_b, k_cache, v_cache, scores, (long)S * nh * key_len,
+                     attn_b, nh, nkv, l_hd, cache_hd, max_seq, S, key_len, kvg, window, query_base_pos, key_base_pos,
+                     kv_is_bf16 != 0);
+}
+
+// -------------------------------------------------------------------- fused
+
+static int unpack_args(const nomos_attn_args_t *u, AttnArgs &a, const char *who) {
+    REQUIRE(u != nullptr, "%s: null args", who);
+    REQUIRE(u->struct_bytes == sizeof(nomos_attn_args_t), "%s: struct_bytes %llu != %zu", who,
+            (unsigned long long)u->struct_bytes, sizeof(nomos_attn_args_t));
+    memset(&a, 0, sizeof(a));
+    a.q = ptr(u->q); a.k_cache = ptr(u->k_cache); a.v_cache = ptr(u->v_cache);
+    a.k_scales = ptr(u->k_scales); a.v_scales = ptr(u->v_scales);
+    a.out = ptr(u->out); a.partial_out = static_cast<float *>(ptr(u->partial_out));
+    a.workspace = ptr(u->workspace); a.ws_bytes = u->ws_bytes;
+    a.new_k = static_cast<const float *>(ptr(u->new_k)); a.new_v = static_cast<const float *>(ptr(u->new_v));
+    a.n_new = (int)u->n_new; a.new_stride = (int)u->new_stride; a.new_base_pos = (int)u->new_base_pos;
+    a.kv_fmt = (int)u->kv_fmt; a.q_type = (int)u->q_type; a.out_type = (int)u->out_type;
+    a.batch = (int)u->batch; a.S = (int)u->S; a.nh = (int)u->nh; a.nkv = (int)u->nkv; a.kvg = (int)u->kvg;
+    a.l_hd = (int)u->l_hd; a.cache_hd = (int)u->cache_hd; a.cache_cap = (int)u->cache_cap;
+    a.win_start = (int)u->win_start; a.klen = (int)u->klen; a.window = (int)u->window;
+    a.softmax_scale = (float)u->softmax_scale;
+    const long row_bytes = a.kv_fmt == KV_I8 ? a.cache_hd : a.cache_hd / 2;
+    const long rows = (long)a.nkv * a.cache_cap;
+    long scale_bytes = rows * 4;
+    if (a.kv_fmt == KV_I4B32) scale_bytes = rows * ((a.l_hd + 31) / 32) * 2 + rows * 4;
+    a.q_batch_stride = u->q_batch_stride ? u->q_batch_stride : (long)a.S * a.nh * a.l_hd;
+    a.out_batch_stride = u->out_batch_stride ? u->out_batch_stride : (long)a.S * a.nh * a.l_hd;
+    a.kv_batch_stride = u->kv_batch_stride ? u->kv_batch_stride : rows * row_bytes;
+    a.scale_batch_stride = u->scale_batch_stride ? u->scale_batch_stride : scale_bytes;
+    a.force_splits = (int)u->force_splits;
+    return NOMOS_OK;
+}
+
+NOMOS_EXPORT int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args) {
+    AttnArgs a;
+    int rc = unpack_args(args, a, "nomos_attn_workspace_bytes");
+    if (rc) return rc;
+    if ((rc = check_attn_geometry("nomos_attn_workspace_bytes", a.nh, a.nkv, a.l_hd, a.cache_hd, a.kvg))) return rc;
+    if (a.batch <= 0 || a.S <= 0 || a.klen <= 0) { set_error("nomos_attn_workspace_bytes: bad batch/S/klen"); return NOMOS_EBADARG; }
+    return attn_workspace_bytes(a);
+}
+
+NOMOS_EXPORT int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *args) {
+    AttnArgs a;
+    int rc = unpack_args(args, a, "nomos_attn_fused");
+    if (rc) return rc;
+    if (a.nh <= 0 || a.klen <= 0) return NOMOS_OK;
+    if (a.new_k || a.new_v) {
+        REQUIRE(a.new_k && a.new_v && a.n_new > 0, "nomos_attn_fused: new_k/new_v/n_new inconsistent");
+        REQUIRE(a.batch == 1, "nomos_attn_fused: fused append supports batch 1");
+        REQUIRE(a.new_base_pos + a.n_new == a.win_start + a.klen, "nomos_attn_fused: the new rows must be the last keys of the window");
+        // Quantize-on-write runs first on the same stream; the attention launch that
+        // follows reads the rows it stored.
+        const int stride = a.new_stride ? a.new_stride : a.nkv * a.l_hd;
+        if (a.kv_fmt == KV_I8)
+            rc = launch_append_i8(as_stream(stream), a.new_k, a.new_v, const_cast<void *>(a.k_cache), const_cast<void *>(a.v_cache),
+                                  const_cast<void *>(a.k_scales), const_cast<void *>(a.v_scales), a.n_new, a.nkv, a.l_hd, stride,
+                                  a.cache_cap, a.cache_hd, a.new_base_pos);
+        else
+            rc = launch_append_i4(as_stream(stream), a.new_k, a.new_v, const_cast<void *>(a.k_cache), const_cast<void *>(a.v_cache),
+                                  const_cast<void *>(a.k_scales), const_cast<void *>(a.v_scales), nullptr, nullptr, nullptr, nullptr,
+                                  a.n_new, a.nkv, a.l_hd, stride, a.cache_cap, a.cache_hd, a.new_base_pos, 0,
+                                  a.kv_fmt == KV_I4B32 ? (a.l_hd + 31) / 32 : 1);
+        if (rc) return rc;
+    }
+    return run_fused(as_stream(stream), a, "nomos_attn_fused");
+}
+
+NOMOS_EXPORT int32_t nomos_attn_merge_partials(void *stream, uint64_t partials, int32_t G, int32_t rows, int32_t l_hd,
+                                               uint64_t out, int32_t out_type) {
+    if (rows <= 0) return NOMOS_OK;
+    REQUIRE(partials && out && G > 0 && l_hd > 0, "nomos_attn_merge_partials: bad argument");
+    REQUIRE(out_type == ET_F32 || out_type == ET_BF16, "nomos_attn_merge_partials: out_type %d", out_type);
+    return launch_merge_partials(as_stream(stream), static_cast<const float *>(ptr(partials)), G, rows, l_hd, ptr(out), out_type);
+}

@@ -1,0 +1,76 @@
+// Internal host-side launch interface between the C-ABI layer (abi.cu) and the
+// kernel translation units.  Every function enqueues on `st`, never synchronises,
+// never allocates, and returns a NOMOS_* status.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nomos {
+
+// ---- kv_quant.cu
+int launch_quant_i8(cudaStream_t st, const void *in_bf16, void *out_i8, void *out_scales, int n_rows, int dim);
+int launch_dequant_i8(cudaStream_t st, const void *in_i8, const void *in_scales, void *out_bf16, int n_rows, int dim);
+int launch_append_i8(cudaStream_t st, const void *src_k, const void *src_v, void *dst_k, void *dst_v, void *k_scales,
+                     void *v_scales, int n_s, int nkv, int l_hd, int l_kvd, int cache_cap, int cache_hd, int base_pos);
+int launch_append_i4(cudaStream_t st, const void *src_k, const void *src_v, void *dst_k, void *dst_v, void *k_scales,
+                     void *v_scales, void *k_q8, void *v_q8, void *k_q8_scales, void *v_q8_scales, int n_s, int nkv,
+                     int l_hd, int l_kvd, int cache_cap, int cache_hd, int base_pos, int q8_pitch, int scale_blocks);
+// mode: 0 i8->bf16, 1 i4->bf16, 2 i4 block-32->bf16, 3 i4->q8, 4 i4 block-32->q8
+int launch_window_reader(cudaStream_t st, int mode, const void *src, const void *scales, void *dst, void *dst_scale, int nkv,
+                         int klen, int cache_hd, int pitch, int cache_cap, int win_start, int scale_blocks);
+int launch_append_dense(cudaStream_t st, int dst_is_bf16, const void *src_k, const void *src_v, void *dst_k, void *dst_v,
+                        int n_s, int nkv, int l_hd, int l_kvd, int max_seq, int cache_hd, int base_pos);
+
+// ---- attn_fused.cu : split-K attention over the packed (quantised) ring cache
+
+enum KvFmt { KV_I8 = 0, KV_I4 = 1, KV_I4B32 = 2 };
+enum ElemType { ET_F32 = 0, ET_BF16 = 1 };
+
+struct AttnArgs {
+    // tensors (device pointers)
+    const void *q;          // [batch][S][nh][l_hd]  fp32 or bf16
+    const void *k_cache;    // [batch][nkv][cache_cap][cache_hd (/2 for int4)]
+    const void *v_cache;
+    const void *k_scales;   // [batch][nkv][cache_cap] fp32, or the block-32 buffer
+    const void *v_scales;
+    void *out;              // [batch][S][nh][l_hd]  fp32 or bf16 (ignored when partial_out is set)
+    float *partial_out;     // optional [batch][S][nh][l_hd+2] un-normalised (o.., m, l); m in natural-log units
+    void *workspace;        // split-K scratch, ws_bytes long
+    long ws_bytes;
+    // optional fused quantize-on-write of n_new rows at positions new_base_pos.. (decode: n_new = 1)
+    const float *new_k;     // [n_new][nkv][l_hd] fp32, row stride new_stride (elements); nullptr = none
+    const float *new_v;
+    int n_new, new_stride, new_base_pos;
+    // geometry
+    int kv_fmt, q_type, out_type;
+    int batch, S, nh, nkv, kvg, l_hd, cache_hd, cache_cap;
+    int win_start;          // absolute position of window index 0
+    int klen;               // keys in the window; query row r sees window indices [lo_r, klen - (S-1-r))
+    int window;             // sliding window per row (0 = none): lo_r = max(0, hi_r - window)
+    float softmax_scale;
+    long q_batch_stride, kv_batch_stride, scale_batch_stride, out_batch_stride;   // elements (q/out), bytes (kv, scales)
+    int force_splits;       // 0 = choose; >0 = use exactly this many splits (tests)
+    int fit_splits_to_ws;   // 1: use fewer splits rather than fail when the workspace is small (thin entry points)
+};
+
+long attn_workspace_bytes(const AttnArgs &a);
+int launch_attn_fused(cudaStream_t st, const AttnArgs &a);
+// partials [G][rows][l_hd+2] = (o.., m, l) with m in natural-log units (the exported form)
+int launch_merge_partials(cudaStream_t st, const float *partials, int G, int rows, int l_hd, void *out, int out_type);
+// same, m in log2 units (in-library split partials), fp32 output
+int launch_merge_partials_log2(cudaStream_t st, const float *partials, int G, int rows, int l_hd, float *out);
+
+// ---- attn_dense.cu : fp32 / bf16 KV decode + prefix-batched attention
+struct DenseAttnArgs {
+    const float *q;          // [S][nh][l_hd] fp32
+    const void *k_cache;     // [nkv][max_seq][cache_hd] fp32 or bf16
+    const void *v_cache;
+    float *out;              // [S][nh][l_hd] fp32
+    void *workspace; long ws_bytes;
+    int kv_is_bf16;
+    int S, nh, nkv, kvg, l_hd, cache_hd, max_seq, key_len, window, query_base_pos, key_base_pos;
+};
+int launch_attn_dense(cudaStream_t st, const DenseAttnArgs &a);
+
+}  // namespace nomos

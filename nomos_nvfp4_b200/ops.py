@@ -1,0 +1,231 @@
+"""Host-side mirror of the reference's operator interface for the attention path.
+
+Function names, argument order and argument meaning are those of the reference's
+Mojo operators (cited per function, paths relative to the reference root); the
+leading ``ctx`` becomes ``stream``: a raw ``cudaStream_t`` value, a
+``torch.cuda.Stream``, or ``None`` for torch's current stream.  Buffer arguments
+may be torch CUDA tensors or integer device addresses.  The reference's operators
+``raise`` on failure; so do these (``NomosError`` carrying the library's status).
+
+torch is used for nothing but device memory and streams; all compute is in
+``libnomos_attn.so`` and there is no fallback if it is missing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import _lib
+from ._lib import AttnArgs
+
+KV_I8, KV_I4, KV_I4B32 = 0, 1, 2
+F32, BF16 = 0, 1
+
+
+class NomosError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"libnomos_attn status {status}: {message}")
+        self.status = status
+
+
+def _addr(x) -> int:
+    if x is None:
+        return 0
+    if isinstance(x, int):
+        return x
+    return x.data_ptr()            # torch tensor
+
+
+def _stream(stream) -> C.c_void_p:
+    if stream is None:
+        import torch
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    if isinstance(stream, int):
+        return C.c_void_p(stream)
+    return C.c_void_p(stream.cuda_stream)
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        raise NomosError(status, _lib.lib().nomos_attn_last_error().decode("utf-8", "replace"))
+
+
+def version() -> int:
+    return _lib.lib().nomos_attn_version()
+
+
+# ---------------------------------------------------------------------- codecs
+
+def gpu_quant_kv_i8(stream, in_bf16, out_i8, out_scales, n_rows, dim):
+    """lib/kv_cache_quant.mojo:100"""
+    _check(_lib.lib().nomos_kv_quant_i8(_stream(stream), _addr(in_bf16), _addr(out_i8), _addr(out_scales), n_rows, dim))
+
+
+def gpu_dequant_kv_i8(stream, in_i8, in_scales, out_bf16, n_rows, dim):
+    """lib/kv_cache_quant.mojo:116"""
+    _check(_lib.lib().nomos_kv_dequant_i8(_stream(stream), _addr(in_i8), _addr(in_scales), _addr(out_bf16), n_rows, dim))
+
+
+def gpu_append_quant_kv_i8(stream, src_k, src_v, dst_k_i8, dst_v_i8, k_scales, v_scales,
+                           n_s, nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos):
+    """lib/kv_cache_quant.mojo:252"""
+    _check(_lib.lib().nomos_kv_append_quant_i8(
+        _stream(stream), _addr(src_k), _addr(src_v), _addr(dst_k_i8), _addr(dst_v_i8), _addr(k_scales), _addr(v_scales),
+        n_s, nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos))
+
+
+def gpu_dequant_kv_i8_layer(stream, src_i8, scales, dst_bf16, nkv, klen, cache_hd, max_seq, cache_cap, win_start):
+    """lib/kv_cache_quant.mojo:274"""
+    _check(_lib.lib().nomos_kv_dequant_i8_layer(
+        _stream(stream), _addr(src_i8), _addr(scales), _addr(dst_bf16), nkv, klen, cache_hd, max_seq, cache_cap, win_start))
+
+
+def gpu_append_quant_kv_i4(stream, src_k, src_v, dst_k_i4, dst_v_i4, k_scales, v_scales,
+                           n_s, nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos, scale_blocks=1):
+    """lib/kv_cache_quant.mojo:803"""
+    _check(_lib.lib().nomos_kv_append_quant_i4(
+        _stream(stream), _addr(src_k), _addr(src_v), _addr(dst_k_i4), _addr(dst_v_i4), _addr(k_scales), _addr(v_scales),
+        n_s, nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos, scale_blocks))
+
+
+def gpu_append_quant_kv_i4_with_q8(stream, src_k, src_v, dst_k_i4, dst_v_i4, k_scales, v_scales,
+                                   dst_k_q8, dst_v_q8, k_q8_scales, v_q8_scales,
+                                   n_s, nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos, q8_pitch, scale_blocks=1):
+    """lib/kv_cache_quant.mojo:839"""
+    _check(_lib.lib().nomos_kv_append_quant_i4_with_q8(
+        _stream(stream), _addr(src_k), _addr(src_v), _addr(dst_k_i4), _addr(dst_v_i4), _addr(k_scales), _addr(v_scales),
+        _addr(dst_k_q8), _addr(dst_v_q8), _addr(k_q8_scales), _addr(v_q8_scales),
+        n_s, nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos, q8_pitch, scale_blocks))
+
+
+def gpu_dequant_kv_i4_layer(stream, src_i4, scales, dst_bf16, nkv, klen, cache_hd, max_seq, cache_cap, win_start,
+                            scale_blocks=1):
+    """lib/kv_cache_quant.mojo:885"""
+    _check(_lib.lib().nomos_kv_dequant_i4_layer(
+        _stream(stream), _addr(src_i4), _addr(scales), _addr(dst_bf16), nkv, klen, cache_hd, max_seq, cache_cap,
+        win_start, scale_blocks))
+
+
+def gpu_dequant_kv_i4_to_q8_layer(stream, src_i4, scales, dst_i8, dst_scale, nkv, klen, cache_hd, max_seq, cache_cap,
+                                  win_start, scale_blocks=1):
+    """lib/kv_cache_quant.mojo:956"""
+    _check(_lib.lib().nomos_kv_dequant_i4_to_q8_layer(
+        _stream(stream), _addr(src_i4), _addr(scales), _addr(dst_i8), _addr(dst_scale), nkv, klen, cache_hd, max_seq,
+        cache_cap, win_start, scale_blocks))
+
+
+def append_kv_gpu_dev_async(stream, d_k_cache_layer, d_v_cache_layer, d_k_new, d_v_new, nkv, l_hd, cache_hd, max_seq, cl):
+    """lib/attention_gpu.mojo:109 (and the synchronous twin at :87)"""
+    _check(_lib.lib().nomos_kv_append_fp32(
+        _stream(stream), _addr(d_k_cache_layer), _addr(d_v_cache_layer), _addr(d_k_new), _addr(d_v_new),
+        nkv, l_hd, cache_hd, max_seq, cl))
+
+
+def append_kv_gpu_bf16_dev(stream, d_k_cache_layer, d_v_cache_layer, d_k_new, d_v_new, d_k_bf16, d_v_bf16,
+                           nkv, l_hd, cache_hd, max_seq, cl):
+    """lib/attention_gpu.mojo:136"""
+    _check(_lib.lib().nomos_kv_append_bf16(
+        _stream(stream), _addr(d_k_cache_layer), _addr(d_v_cache_layer), _addr(d_k_new), _addr(d_v_new),
+        _addr(d_k_bf16), _addr(d_v_bf16), nkv, l_hd, cache_hd, max_seq, cl))
+
+
+def gpu_append_kv_batched_bf16(stream, d_src_k, d_src_v, d_dst_k_cache, d_dst_v_cache,
+                               n_s, nkv, l_hd, l_kvd, max_seq, cache_hd, base_pos=0):
+    """lib/batched_attn_gpu.mojo:87"""
+    _check(_lib.lib().nomos_kv_append_batched_bf16(
+        _stream(stream), _addr(d_src_k), _addr(d_src_v), _addr(d_dst_k_cache), _addr(d_dst_v_cache),
+        n_s, nkv, l_hd, l_kvd, max_seq, cache_hd, base_pos))
+
+
+# ------------------------------------------------------------------- attention
+
+def attention_gpu_int8_dev(stream, d_q_gpu, d_k_i8, d_v_i8, d_k_scale, d_v_scale, d_scores_scratch, d_attn_out_scratch,
+                           nh, nkv, l_hd, cache_hd, max_seq, seq_len, kvg):
+    """lib/attention_gpu_int8.mojo:598"""
+    _check(_lib.lib().nomos_attn_decode_i8(
+        _stream(stream), _addr(d_q_gpu), _addr(d_k_i8), _addr(d_v_i8), _addr(d_k_scale), _addr(d_v_scale),
+        _addr(d_scores_scratch), _addr(d_attn_out_scratch), nh, nkv, l_hd, cache_hd, max_seq, seq_len, kvg))
+
+
+def attention_decode_order_multirow_int8(stream, d_q_b, d_scores, d_attn_b, d_k_i8, d_v_i8, d_k_scale, d_v_scale,
+                                         nh, nkv, l_hd, cache_hd, max_seq, S, score_stride, kvg, window, query_base_pos):
+    """lib/attention_gpu_int8.mojo:634"""
+    _check(_lib.lib().nomos_attn_decode_multirow_i8(
+        _stream(stream), _addr(d_q_b), _addr(d_scores), _addr(d_attn_b), _addr(d_k_i8), _addr(d_v_i8),
+        _addr(d_k_scale), _addr(d_v_scale), nh, nkv, l_hd, cache_hd, max_seq, S, score_stride, kvg, window, query_base_pos))
+
+
+def attention_prefill_prefix_batched_int8(stream, d_q_b, d_q_t, d_scores, d_attn_t, d_attn_b, d_k_i8, d_v_i8,
+                                          d_k_scale, d_v_scale, nh, nkv, l_hd, cache_hd, max_seq, S, key_len, kvg,
+                                          window, query_base_pos, key_base_pos):
+    """lib/attention_gpu_int8.mojo:844"""
+    _check(_lib.lib().nomos_attn_prefix_batched_i8(
+        _stream(stream), _addr(d_q_b), _addr(d_q_t), _addr(d_scores), _addr(d_attn_t), _addr(d_attn_b),
+        _addr(d_k_i8), _addr(d_v_i8), _addr(d_k_scale), _addr(d_v_scale),
+        nh, nkv, l_hd, cache_hd, max_seq, S, key_len, kvg, window, query_base_pos, key_base_pos))
+
+
+def attention_gpu_fp32_dev(stream, handle, d_q_gpu, d_k_cache_layer, d_v_cache_layer, d_scores_scratch,
+                           d_attn_out_scratch, nh, nkv, l_hd, cache_hd, max_seq, seq_len, kvg):
+    """lib/attention_gpu.mojo:165 (the cuBLAS ``handle`` is accepted and ignored)"""
+    _check(_lib.lib().nomos_attn_decode_fp32(
+        _stream(stream), _addr(d_q_gpu), _addr(d_k_cache_layer), _addr(d_v_cache_layer), _addr(d_scores_scratch),
+        _addr(d_attn_out_scratch), nh, nkv, l_hd, cache_hd, max_seq, seq_len, kvg))
+
+
+def attention_gpu_bf16_dev(stream, handle, d_q_gpu, d_k_cache_layer, d_v_cache_layer, d_scores_scratch, d_q_bf16,
+                           d_scores_bf16, d_attn_out_scratch, nh, nkv, l_hd, cache_hd, max_seq, seq_len, kvg):
+    """lib/attention_gpu.mojo:207"""
+    _check(_lib.lib().nomos_attn_decode_bf16(
+        _stream(stream), _addr(d_q_gpu), _addr(d_k_cache_layer), _addr(d_v_cache_layer), _addr(d_scores_scratch),
+        _addr(d_q_bf16), _addr(d_scores_bf16), _addr(d_attn_out_scratch), nh, nkv, l_hd, cache_hd, max_seq, seq_len, kvg))
+
+
+def attention_prefill_prefix_batched_fp32(stream, handle, d_q_b, d_q_t, d_scores, d_attn_t, d_attn_b,
+                                          d_k_cache_layer, d_v_cache_layer, nh, nkv, l_hd, cache_hd, max_seq, S,
+                                          key_len, kvg, window, query_base_pos, key_base_pos):
+    """lib/batched_attn_gpu.mojo:499"""
+    _check(_lib.lib().nomos_attn_prefix_batched_dense(
+        _stream(stream), _addr(d_q_b), _addr(d_scores), _addr(d_attn_b), _addr(d_k_cache_layer), _addr(d_v_cache_layer),
+        nh, nkv, l_hd, cache_hd, max_seq, S, key_len, kvg, window, query_base_pos, key_base_pos, 0))
+
+
+def attention_prefill_prefix_batched_bf16(stream, handle, d_q_b, d_q_t, d_q_t_bf16, d_scores, d_scores_bf16, d_attn_t,
+                                          d_attn_b, d_k_cache_layer, d_v_cache_layer, nh, nkv, l_hd, cache_hd, max_seq,
+                                          S, key_len, kvg, window, query_base_pos, key_base_pos):
+    """lib/batched_attn_gpu.mojo:613"""
+    _check(_lib.lib().nomos_attn_prefix_batched_dense(
+        _stream(stream), _addr(d_q_b), _addr(d_scores), _addr(d_attn_b), _addr(d_k_cache_layer), _addr(d_v_cache_layer),
+        nh, nkv, l_hd, cache_hd, max_seq, S, key_len, kvg, window, query_base_pos, key_base_pos, 1))
+
+
+# ----------------------------------------------------------------------- fused
+
+def make_args(**kw) -> AttnArgs:
+    """Zero-initialised ``nomos_attn_args_t`` with the given fields set (tensors or addresses)."""
+    a = AttnArgs()
+    a.struct_bytes = C.sizeof(AttnArgs)
+    a.batch, a.S, a.softmax_scale = 1, 1, 1.0
+    ptr_fields = {"q", "k_cache", "v_cache", "k_scales", "v_scales", "out", "partial_out", "workspace", "new_k", "new_v"}
+    for k, v in kw.items():
+        if not hasattr(a, k):
+            raise TypeError(f"nomos_attn_args_t has no field {k}")
+        setattr(a, k, _addr(v) if k in ptr_fields else v)
+    return a
+
+
+def attn_workspace_bytes(args: AttnArgs) -> int:
+    n = _lib.lib().nomos_attn_workspace_bytes(C.byref(args))
+    if n < 0:
+        _check(int(n))
+    return int(n)
+
+
+def attn_fused(stream, args: AttnArgs) -> None:
+    """Append (optional) + attention over the packed ring in one call; replaces the
+    reference's per-layer append -> window reader -> attention sequence
+    (lib/engine_decode.mojo:356-389, 445-460, 527-554)."""
+    _check(_lib.lib().nomos_attn_fused(_stream(stream), C.byref(args)))
+
+
+def attn_merge_partials(stream, partials, G, rows, l_hd, out, out_type=F32) -> None:
+    _check(_lib.lib().nomos_attn_merge_partials(_stream(stream), _addr(partials), G, rows, l_hd, _addr(out), out_type))

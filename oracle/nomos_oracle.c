@@ -269,6 +269,7 @@ ORC_API void orc_append_quant_kv_i4_with_q8(const float *src_k, const float *src
 /* lib/kv_cache_quant.mojo:221-249,274-290 */
 ORC_API void orc_dequant_kv_i8_layer(const int8_t *src, const float *scales, uint16_t *dst_bf16,
                                      int nkv, int klen, int cache_hd, int pitch, int cache_cap, int win_start) {
+#pragma omp parallel for collapse(2) schedule(static)
     for (int h = 0; h < nkv; ++h)
         for (int j = 0; j < klen; ++j) {
             size_t sr = (size_t)h * cache_cap + (size_t)((win_start + j) % cache_cap);
@@ -530,25 +531,26 @@ ORC_API void orc_attn_decode_dense(const float *q, const void *k_cache, const vo
     for (int h = 0; h < nh; ++h) {
         size_t row0 = (size_t)(h / kvg) * max_seq;
         float *sc = scores + (size_t)h * seq_len;
+        float qb[2048];
+        for (int d = 0; d < l_hd; ++d) {
+            float qv = q[(size_t)h * l_hd + d];
+            qb[d] = kv_is_bf16 ? bf16_to_f32(f32_to_bf16(qv)) : qv;     /* Q narrowed once (lib/attention_gpu.mojo:230) */
+        }
         for (int t = 0; t < seq_len; ++t) {
             float acc = 0.0f;
-            for (int d = 0; d < l_hd; ++d) {
-                size_t ki = (row0 + t) * cache_hd + d;
-                float qv = q[(size_t)h * l_hd + d];
-                if (kv_is_bf16) acc += bf16_to_f32(f32_to_bf16(qv)) * bf16_to_f32(((const uint16_t *)k_cache)[ki]);
-                else acc += qv * ((const float *)k_cache)[ki];
-            }
+            size_t base = (row0 + t) * cache_hd;
+            if (kv_is_bf16) { const uint16_t *kr = (const uint16_t *)k_cache + base; for (int d = 0; d < l_hd; ++d) acc += qb[d] * bf16_to_f32(kr[d]); }
+            else { const float *kr = (const float *)k_cache + base; for (int d = 0; d < l_hd; ++d) acc += qb[d] * kr[d]; }
             sc[t] = acc;
         }
         softmax_row(sc, seq_len);
-        for (int d = 0; d < l_hd; ++d) {
-            float acc = 0.0f;
-            for (int t = 0; t < seq_len; ++t) {
-                size_t vi = (row0 + t) * cache_hd + d;
-                if (kv_is_bf16) acc += bf16_to_f32(f32_to_bf16(sc[t])) * bf16_to_f32(((const uint16_t *)v_cache)[vi]);
-                else acc += sc[t] * ((const float *)v_cache)[vi];
-            }
-            out[(size_t)h * l_hd + d] = acc;
+        float *o = out + (size_t)h * l_hd;
+        for (int d = 0; d < l_hd; ++d) o[d] = 0.0f;
+        for (int t = 0; t < seq_len; ++t) {                              /* per output element: keys in order */
+            size_t base = (row0 + t) * cache_hd;
+            float pt = kv_is_bf16 ? bf16_to_f32(f32_to_bf16(sc[t])) : sc[t];   /* P narrowed (:240) */
+            if (kv_is_bf16) { const uint16_t *vr = (const uint16_t *)v_cache + base; for (int d = 0; d < l_hd; ++d) o[d] += pt * bf16_to_f32(vr[d]); }
+            else { const float *vr = (const float *)v_cache + base; for (int d = 0; d < l_hd; ++d) o[d] += pt * vr[d]; }
         }
     }
 }
