@@ -9,8 +9,12 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
+import os
+
 PKG = Path(__file__).resolve().parent
-LIB_PATH = PKG / "libnomos_attn.so"
+# NOMOS_ATTN_LIB points at another build of the same library (e.g. one compiled with
+# different tile parameters); the default is the in-tree build.
+LIB_PATH = Path(os.environ.get("NOMOS_ATTN_LIB", PKG / "libnomos_attn.so"))
 
 u64, i32, i64, vp = C.c_uint64, C.c_int32, C.c_int64, C.c_void_p
 

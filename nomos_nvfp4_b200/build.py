@@ -42,8 +42,13 @@ def _stale(target: Path, deps) -> bool:
     return any(Path(d).stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose_ptxas: bool = False) -> Path:
-    OBJ.mkdir(exist_ok=True)
+def build(force: bool = False, verbose_ptxas: bool = False, extra_flags=(), out: Path | None = None,
+          obj_dir: Path | None = None) -> Path:
+    """Compile and link.  `extra_flags` (e.g. -DNOMOS_NWARP=3) with `out`/`obj_dir` build a variant
+    beside the default library without touching it."""
+    global OBJ, LIB
+    OBJ, LIB = (obj_dir or PKG / "_obj"), (out or PKG / "libnomos_attn.so")
+    OBJ.mkdir(exist_ok=True, parents=True)
     headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "nomos_attn.h", Path(__file__)]
     objs = []
     procs = []
@@ -52,15 +57,15 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> Path:
         obj = OBJ / (name + ".o")
         objs.append(obj)
         if force or _stale(obj, [src, *headers]):
-            cmd = [nvcc(), *ARCH, *COMMON, *EXTRA.get(name, []), "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc(), *ARCH, *COMMON, *EXTRA.get(name, []), *extra_flags, "-c", str(src), "-o", str(obj)]
             if verbose_ptxas:
                 cmd += ["-Xptxas", "-v"]
             procs.append((name, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = []
     for name, p in procs:
-        out, _ = p.communicate()
+        log, _ = p.communicate()
         if verbose_ptxas or p.returncode != 0:
-            sys.stderr.write(f"--- {name}\n{out}\n")
+            sys.stderr.write(f"--- {name}\n{log}\n")
         if p.returncode != 0:
             failed.append(name)
     if failed:

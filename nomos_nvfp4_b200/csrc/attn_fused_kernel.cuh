@@ -1,0 +1,633 @@
+// Device side of the fused split-K attention over the packed quantised KV ring
+// (sm_100a).  See attn_fused.cu for the host side and the overall description.
+#pragma once
+
+#include <math_constants.h>
+
+#include "common.cuh"
+#include "launch.h"
+
+namespace nomos {
+namespace fused {
+
+// Tile parameters (overridable at build time for tuning).  One query-row tile (decode, up to 8
+// rows of a GQA group) needs ~130 registers per thread and runs 12 warps per SM; three tiles
+// (verify, up to 24 rows) keep 96 fp32 accumulators per thread and run 8.
+#ifndef NOMOS_NWARP
+#define NOMOS_NWARP 12
+#endif
+#ifndef NOMOS_NWARP_MULTI
+#define NOMOS_NWARP_MULTI 8
+#endif
+#ifndef NOMOS_NSTAGE
+#define NOMOS_NSTAGE 2
+#endif
+
+constexpr int TILE = 32;                 // tokens per warp tile
+constexpr int NSTAGE = NOMOS_NSTAGE;     // cp.async stages per warp
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+constexpr float M_INIT = -1.0e30f;       // finite "minus infinity" for the running max
+constexpr int Q_FIX_MAX = 16256;         // 127 * 128: two int8 limbs, hi in [-127,127], lo in [-64,63]
+constexpr float P_FIX = 65535.0f;        // probabilities reach the tensor core as 16-bit fixed point (two u8 limbs)
+constexpr float RND_MAGIC = 8388608.0f;  // 2^23: adding it leaves round-to-nearest(x) in the low mantissa bits
+
+template <int FMT, int HD, int MT>
+struct Cfg {
+    static constexpr int NW = (MT == 1) ? NOMOS_NWARP : NOMOS_NWARP_MULTI;    // warps per CTA
+    static constexpr int ROWB = (FMT == KV_I8) ? HD : HD / 2;                 // cache bytes per token row
+    static constexpr int CHUNKS = ROWB / 16;                                  // 16-byte chunks per row
+    static constexpr int NBLK = HD / 32;
+    static constexpr int SCB = (FMT == KV_I4B32) ? NBLK * 2 : 4;              // scale bytes per token
+    static constexpr int KV_BYTES = TILE * ROWB;
+    static constexpr int SC_BYTES = TILE * SCB;
+    static constexpr int STAGE_BYTES = 2 * KV_BYTES + 2 * SC_BYTES;
+    static constexpr int NSLOT = 8 * MT;                                      // query rows (row x group head) per CTA
+    static constexpr int NT = HD / 8;                                         // PV N tiles (8 output dims each)
+    static constexpr int Q_BYTES = 2 * NSLOT * HD;                            // two limbs
+    static constexpr int SLOT_BYTES = NSLOT * 16;                             // qscale, lo, hi, pad
+    static constexpr int PIPE_BYTES = NW * NSTAGE * STAGE_BYTES;
+    static constexpr int MERGE_BYTES = NW * NSLOT * (HD + 2) * 4;
+    static constexpr int SMEM_BYTES = Q_BYTES + SLOT_BYTES + (PIPE_BYTES > MERGE_BYTES ? PIPE_BYTES : MERGE_BYTES);
+};
+
+struct KParams {
+    const uint8_t *q;
+    const uint8_t *k_cache, *v_cache, *k_scales, *v_scales;
+    uint8_t *out;
+    float *partial;          // workspace partials or exported partials: [split][grow][HD+2]
+    int write_partial;       // 1: write (o, M, l) to partial; 0: write normalised out
+    int export_nat;          // 1: partial m is exported in natural-log units
+    int q_type, out_type;
+    int S, nh, nkv, kvg, cache_hd, cache_cap, win_start, klen, window;
+    int tile0, ntiles, tiles_per_split, row_groups, grows;
+    float qk_scale_log2;     // softmax_scale * log2(e)
+    // in-kernel split merge: the last CTA of a (batch, kv head, row group) unit to finish merges
+    unsigned long long *counters;   // one word per unit: (epoch << 16) | arrivals; nullptr = no in-kernel merge
+    unsigned long long epoch;       // unique per launch, so stale or uninitialised words read as "0 arrivals"
+    int splits;
+    float *partial_export;          // optional exported (o, m, l) per row, m in natural-log units
+    long q_batch_stride, kv_batch_stride, scale_batch_stride, out_batch_stride;
+};
+
+__device__ __forceinline__ float load_q(const uint8_t *q, int q_type, long idx) {
+    return q_type == ET_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(q)[idx])
+                             : reinterpret_cast<const float *>(q)[idx];
+}
+
+// D(16x8,s32) = A(16x32,u8,row) * B(32x8,s8,col), no accumulator input.
+__device__ __forceinline__ void mma_u8s8_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+    const int z = 0;
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
+}
+
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+}  // namespace fused
+}  // namespace nomos
+
+namespace nomos {
+namespace fused {
+
+template <int FMT, int HD, int MT>
+__global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(const KParams p) {
+    using C = Cfg<FMT, HD, MT>;
+    constexpr int NWARP = C::NW;
+    static_assert(FMT == KV_I8, "int4 tiles are handled by a separate code path");
+    extern __shared__ __align__(128) uint8_t smem[];
+    int8_t *q_limbs = reinterpret_cast<int8_t *>(smem);                        // [2][NSLOT][HD]
+    float *slot_qscale = reinterpret_cast<float *>(smem + C::Q_BYTES);         // [NSLOT]
+    int *slot_lo = reinterpret_cast<int *>(smem + C::Q_BYTES + C::NSLOT * 4);
+    int *slot_hi = reinterpret_cast<int *>(smem + C::Q_BYTES + C::NSLOT * 8);
+    uint8_t *pipe = smem + C::Q_BYTES + C::SLOT_BYTES;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x, kvh = blockIdx.y;
+    const int b = blockIdx.z / p.row_groups, rg = blockIdx.z % p.row_groups;
+
+    // ------------------------------------------------------------ tile schedule
+    const int tile_begin = p.tile0 + split * p.tiles_per_split;
+    const int tile_end = min(p.tile0 + p.ntiles, tile_begin + p.tiles_per_split);
+    const int my_first = tile_begin + warp;
+    const int my_count = my_first < tile_end ? (tile_end - my_first + NWARP - 1) / NWARP : 0;
+
+    const int row_stride = p.cache_hd;                       // bytes between consecutive token rows (int8)
+    const uint8_t *kbase = p.k_cache + b * p.kv_batch_stride + (size_t)kvh * p.cache_cap * (size_t)row_stride;
+    const uint8_t *vbase = p.v_cache + b * p.kv_batch_stride + (size_t)kvh * p.cache_cap * (size_t)row_stride;
+    const uint8_t *ksbase = p.k_scales + b * p.scale_batch_stride + (size_t)kvh * p.cache_cap * C::SCB;
+    const uint8_t *vsbase = p.v_scales + b * p.scale_batch_stride + (size_t)kvh * p.cache_cap * C::SCB;
+
+    uint8_t *my_pipe = pipe + warp * NSTAGE * C::STAGE_BYTES;
+    const uint32_t my_pipe_u32 = smem_u32(my_pipe);
+    const int ring0 = p.win_start % p.cache_cap;
+
+    // Copy geometry: per cp.async instruction the warp covers 8 rows x 64 bytes; lane = (row r, chunk c0).
+    constexpr int HPASS = C::CHUNKS / 4;                     // 64-byte column groups per row
+    const int cr = lane >> 2, cc0 = lane & 3;
+    const size_t lane_goff = (size_t)cr * row_stride + cc0 * 16;
+    uint32_t lane_soff[HPASS];
+#pragma unroll
+    for (int h = 0; h < HPASS; ++h) lane_soff[h] = cr * C::ROWB + swz_chunk<C::ROWB>(cr, cc0 + 4 * h) * 16;
+
+    auto issue = [&](int it) {
+        if (it < my_count) {
+            const int tok0 = (my_first + it * NWARP) * TILE;
+            const uint32_t st = my_pipe_u32 + (it % NSTAGE) * C::STAGE_BYTES;
+            int slot0 = ring0 + tok0;
+            slot0 = slot0 >= p.cache_cap ? slot0 - p.cache_cap : slot0;          // klen <= cache_cap (host-checked)
+            if (slot0 + TILE <= p.cache_cap && tok0 + TILE <= p.klen) {
+                // fast path: the 32 rows are contiguous in the ring and all inside the window
+                const uint8_t *gk = kbase + (size_t)slot0 * row_stride + lane_goff;
+                const uint8_t *gv = vbase + (size_t)slot0 * row_stride + lane_goff;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int h = 0; h < HPASS; ++h) {
+                        const size_t go = (size_t)(8 * i) * row_stride + 64 * h;
+                        const uint32_t so = st + lane_soff[h] + 8 * i * C::ROWB;
+                        cp_async16(so, gk + go, 16);
+                        cp_async16(so + C::KV_BYTES, gv + go, 16);
+                    }
+                const size_t sg = (size_t)(slot0 + lane) * C::SCB;
+                cp_async4(st + 2 * C::KV_BYTES + lane * 4, ksbase + sg, 4);
+                cp_async4(st + 2 * C::KV_BYTES + C::SC_BYTES + lane * 4, vsbase + sg, 4);
+            } else {
+                // ragged tile: wraps the ring or runs past the window; rows past the end are zero-filled
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int tok = tok0 + cr + 8 * i;
+                    int slot = ring0 + tok;
+                    slot = slot >= p.cache_cap ? slot - p.cache_cap : slot;
+                    const bool ok = tok < p.klen;
+                    const size_t go = (size_t)(ok ? slot : 0) * row_stride + cc0 * 16;
+#pragma unroll
+                    for (int h = 0; h < HPASS; ++h) {
+                        const uint32_t so = st + lane_soff[h] + 8 * i * C::ROWB;
+                        cp_async16(so, kbase + go + 64 * h, ok ? 16 : 0);
+                        cp_async16(so + C::KV_BYTES, vbase + go + 64 * h, ok ? 16 : 0);
+                    }
+                }
+                const int tok = tok0 + lane;
+                int slot = ring0 + tok;
+                slot = slot >= p.cache_cap ? slot - p.cache_cap : slot;
+                const bool ok = tok < p.klen;
+                const size_t sg = (size_t)(ok ? slot : 0) * C::SCB;
+                cp_async4(st + 2 * C::KV_BYTES + lane * 4, ksbase + sg, ok ? 4 : 0);
+                cp_async4(st + 2 * C::KV_BYTES + C::SC_BYTES + lane * 4, vsbase + sg, ok ? 4 : 0);
+            }
+        }
+        cp_async_commit();
+    };
+
+    // Programmatic dependent launch.  This grid may have been set up while its predecessor in
+    // the stream was still running: wait for the predecessor's memory (the query, freshly
+    // appended cache rows, the shared split workspace) before the first global access.  Then let
+    // the split-merge grid be set up right away; it blocks the same way until this grid is done.
+    pdl_wait();
+    pdl_launch_dependents();
+
+    // The first tiles are requested before the query rows are prepared, so the
+    // DRAM latency of the pipeline fill overlaps the prologue.
+#pragma unroll
+    for (int s = 0; s < NSTAGE - 1; ++s) issue(s);
+
+    // ------------------------------------------------------------ Q prologue
+    // Slot sl of this CTA = local row index rg*NSLOT + sl = (query row r, group head j).
+    // Each row becomes 15-bit fixed point: q ~= sq * (128*hi + lo), hi/lo int8.
+    for (int sl = warp; sl < C::NSLOT; sl += NWARP) {
+        const int idx = rg * C::NSLOT + sl;
+        const int r = idx / p.kvg, j = idx % p.kvg;
+        const bool valid = r < p.S;
+        float x[HD / 32];
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < HD / 32; ++i) {
+            x[i] = valid ? load_q(p.q, p.q_type, b * p.q_batch_stride + ((long)r * p.nh + kvh * p.kvg + j) * HD + lane + 32 * i) : 0.0f;
+            amax = fmaxf(amax, fabsf(x[i]));
+        }
+        amax = warp_max(amax);
+        const float sq = amax > 0.0f ? amax / (float)Q_FIX_MAX : 1.0f;
+        const float inv = 1.0f / sq;
+#pragma unroll
+        for (int i = 0; i < HD / 32; ++i) {
+            int qf = __float2int_rn(x[i] * inv);
+            qf = max(-Q_FIX_MAX, min(Q_FIX_MAX, qf));
+            const int hi = (qf + 64) >> 7;
+            const int lo = qf - (hi << 7);
+            q_limbs[sl * HD + lane + 32 * i] = (int8_t)hi;
+            q_limbs[(C::NSLOT + sl) * HD + lane + 32 * i] = (int8_t)lo;
+        }
+        if (lane == 0) {
+            const int hi_b = valid ? p.klen - (p.S - 1 - r) : 0;
+            slot_qscale[sl] = valid ? sq * p.qk_scale_log2 : 0.0f;
+            slot_hi[sl] = hi_b;
+            slot_lo[sl] = (valid && p.window > 0) ? max(0, hi_b - p.window) : 0;
+        }
+    }
+    __syncthreads();
+
+    float qscale[MT];
+    int lo_b[MT], hi_b[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        qscale[mt] = slot_qscale[mt * 8 + g];
+        lo_b[mt] = slot_lo[mt * 8 + g];
+        hi_b[mt] = slot_hi[mt * 8 + g];
+    }
+    // Q A-fragments (rows g = high limb, rows g+8 = low limb of slot g): registers for
+    // one M tile, re-read from shared memory otherwise.
+    constexpr bool Q_IN_REGS = (MT == 1) && (HD <= 256);
+    uint32_t qa[Q_IN_REGS ? HD / 32 : 1][4];
+    auto load_qa = [&](uint32_t(&a)[4], int mt, int ks) {
+        const int8_t *hi_row = q_limbs + (mt * 8 + g) * HD + ks * 32 + 4 * t;
+        const int8_t *lo_row = hi_row + C::NSLOT * HD;
+        a[0] = *reinterpret_cast<const uint32_t *>(hi_row);
+        a[1] = *reinterpret_cast<const uint32_t *>(lo_row);
+        a[2] = *reinterpret_cast<const uint32_t *>(hi_row + 16);
+        a[3] = *reinterpret_cast<const uint32_t *>(lo_row + 16);
+    };
+    if constexpr (Q_IN_REGS) {
+#pragma unroll
+        for (int ks = 0; ks < HD / 32; ++ks) load_qa(qa[ks], 0, ks);
+    }
+
+    // ------------------------------------------------------------ running state
+    float M[MT], l[MT];
+    float acc[MT][C::NT][2];              // [slot tile][8-dim tile][2 dims] of slot g
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        M[mt] = M_INIT; l[mt] = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < C::NT; ++nt) { acc[mt][nt][0] = 0.0f; acc[mt][nt][1] = 0.0f; }
+    }
+    int lo_max = 0, hi_min = 0x7fffffff;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+        if (hi_b[mt] > 0) { lo_max = max(lo_max, lo_b[mt]); hi_min = min(hi_min, hi_b[mt]); }
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, o));
+        hi_min = min(hi_min, __shfl_xor_sync(0xffffffffu, hi_min, o));
+    }
+
+    for (int it = 0; it < my_count; ++it) {
+        issue(it + NSTAGE - 1);
+        cp_async_wait<NSTAGE - 1>();
+        __syncwarp();
+
+        const int tok0 = (my_first + it * NWARP) * TILE;
+        const uint32_t st = my_pipe_u32 + (it % NSTAGE) * C::STAGE_BYTES;
+        const uint8_t *stp = my_pipe + (it % NSTAGE) * C::STAGE_BYTES;
+        const bool need_mask = (tok0 + TILE > hi_min) || (tok0 < lo_max);
+
+        // --------------------------------------------------------------- QK
+        // c[mt][n]: rows g / g+8 = high / low limb of slot (mt, g); columns = tokens 8n+2t, 8n+2t+1.
+        int c[MT][4][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) c[mt][n][i] = 0;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+#pragma unroll
+            for (int half = 0; half < HD / 64; ++half) {
+                uint32_t kb[4];
+                const int row = 8 * n + (lane & 7);
+                const int ch = 4 * half + (lane >> 3);
+                ldmatrix_x4(kb, st + row * C::ROWB + swz_chunk<C::ROWB>(row, ch) * 16);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    if constexpr (Q_IN_REGS) {
+                        mma_s8s8(c[mt][n], qa[2 * half], kb[0], kb[1]);
+                        mma_s8s8(c[mt][n], qa[2 * half + 1], kb[2], kb[3]);
+                    } else {
+                        uint32_t a[4];
+                        load_qa(a, mt, 2 * half);
+                        mma_s8s8(c[mt][n], a, kb[0], kb[1]);
+                        load_qa(a, mt, 2 * half + 1);
+                        mma_s8s8(c[mt][n], a, kb[2], kb[3]);
+                    }
+                }
+            }
+        }
+        const float *ksm = reinterpret_cast<const float *>(stp + 2 * C::KV_BYTES);
+        const float *vsm = reinterpret_cast<const float *>(stp + 2 * C::KV_BYTES + C::SC_BYTES);
+        float s2[MT][4][2];               // base-2 logits of my 8 tokens
+        float vs[4][2];                   // their V scales
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const float2 kk = *reinterpret_cast<const float2 *>(ksm + 8 * n + 2 * t);
+            const float2 vv = *reinterpret_cast<const float2 *>(vsm + 8 * n + 2 * t);
+            vs[n][0] = vv.x; vs[n][1] = vv.y;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                s2[mt][n][0] = (float)(c[mt][n][0] * 128 + c[mt][n][2]) * (qscale[mt] * kk.x);
+                s2[mt][n][1] = (float)(c[mt][n][1] * 128 + c[mt][n][3]) * (qscale[mt] * kk.y);
+            }
+        }
+        if (need_mask) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int n = 0; n < 4; ++n)
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int tok = tok0 + 8 * n + 2 * t + j;
+                        if (tok < lo_b[mt] || tok >= hi_b[mt]) s2[mt][n][j] = -CUDART_INF_F;
+                    }
+        }
+
+        // ------------------------------------------------ softmax weights, 16-bit fixed point
+        // w_t = 2^(s_t - tile max) * v_scale_t / (largest v_scale of the tile) lies in [0,1] and is
+        // rounded to u16; the softmax denominator is accumulated from the ROUNDED values, so the
+        // rounding perturbs normalised weights instead of the output's absolute value.
+        float vmax = 0.0f;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) vmax = fmaxf(vmax, fmaxf(vs[n][0], vs[n][1]));
+        vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1));
+        vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 2));
+        const float vnorm = vmax > 0.0f ? P_FIX * rcpf(vmax) : 0.0f;
+        const float tile_unit = vmax * (1.0f / P_FIX);
+        float vsn[4][2], rvs[4][2];
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                vsn[n][j] = vs[n][j] * vnorm;
+                rvs[n][j] = rcpf(vs[n][j]);
+            }
+        if (need_mask) {                  // zero-filled rows past the end of the window carry scale 0
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) rvs[n][j] = vs[n][j] > 0.0f ? rvs[n][j] : 0.0f;
+        }
+
+        uint32_t pa[MT][4];               // A fragment of the PV MMA: a0/a2 = high limbs, a1/a3 = low limbs
+        float F[MT];                      // weight of this tile's integer sums in the running accumulators
+        bool rescale = false;
+        float alpha[MT];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            float mx = -CUDART_INF_F;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) mx = fmaxf(mx, fmaxf(s2[mt][n][0], s2[mt][n][1]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(M[mt], mx);
+            const float mx_safe = mx == -CUDART_INF_F ? 0.0f : mx;
+            alpha[mt] = ex2f(M[mt] - m_new);
+            rescale |= (m_new != M[mt]);
+            M[mt] = m_new;
+            F[mt] = mx == -CUDART_INF_F ? 0.0f : ex2f(mx - m_new) * tile_unit;
+            uint32_t pk[4];
+            float lsum = 0.0f;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const float f0 = fmaf(ex2f(s2[mt][n][0] - mx_safe), vsn[n][0], RND_MAGIC);
+                const float f1 = fmaf(ex2f(s2[mt][n][1] - mx_safe), vsn[n][1], RND_MAGIC);
+                lsum = fmaf(f0 - RND_MAGIC, rvs[n][0], lsum);
+                lsum = fmaf(f1 - RND_MAGIC, rvs[n][1], lsum);
+                pk[n] = prmt(__float_as_uint(f0), __float_as_uint(f1), 0x5410u);     // two u16
+            }
+            l[mt] = fmaf(F[mt], lsum, l[mt] * alpha[mt]);
+            pa[mt][0] = prmt(pk[0], pk[1], 0x7531u);
+            pa[mt][1] = prmt(pk[0], pk[1], 0x6420u);
+            pa[mt][2] = prmt(pk[2], pk[3], 0x7531u);
+            pa[mt][3] = prmt(pk[2], pk[3], 0x6420u);
+        }
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < C::NT; ++nt) { acc[mt][nt][0] *= alpha[mt]; acc[mt][nt][1] *= alpha[mt]; }
+        }
+
+        // --------------------------------------------------------------- PV
+        // u8 x s8 MMA over all 32 tokens at once: A = weight limbs (rows g / g+8 = high / low),
+        // B = V bytes transposed by ldmatrix.trans + one byte permute, exact int32 result.
+        const uint32_t vst = st + C::KV_BYTES;
+#pragma unroll
+        for (int ch = 0; ch < HD / 16; ++ch) {
+            uint32_t vr[4];               // vr[o]: tokens 8o+2t, 8o+2t+1 x dims 16ch+2g, 16ch+2g+1
+            ldmatrix_x4_trans(vr, vst + lane * C::ROWB + swz_chunk<C::ROWB>(lane, ch) * 16);
+            const uint32_t be0 = prmt(vr[0], vr[1], 0x6420u), bo0 = prmt(vr[0], vr[1], 0x7531u);
+            const uint32_t be1 = prmt(vr[2], vr[3], 0x6420u), bo1 = prmt(vr[2], vr[3], 0x7531u);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                int d4[4];
+                mma_u8s8_zero(d4, pa[mt][0], pa[mt][1], pa[mt][2], pa[mt][3], be0, be1);
+                acc[mt][2 * ch][0] = fmaf((float)(d4[0] * 256 + d4[2]), F[mt], acc[mt][2 * ch][0]);
+                acc[mt][2 * ch][1] = fmaf((float)(d4[1] * 256 + d4[3]), F[mt], acc[mt][2 * ch][1]);
+                mma_u8s8_zero(d4, pa[mt][0], pa[mt][1], pa[mt][2], pa[mt][3], bo0, bo1);
+                acc[mt][2 * ch + 1][0] = fmaf((float)(d4[0] * 256 + d4[2]), F[mt], acc[mt][2 * ch + 1][0]);
+                acc[mt][2 * ch + 1][1] = fmaf((float)(d4[1] * 256 + d4[3]), F[mt], acc[mt][2 * ch + 1][1]);
+            }
+        }
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+
+    // ---------------------------------------------------- merge warps in shared
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        l[mt] += __shfl_xor_sync(0xffffffffu, l[mt], 1);
+        l[mt] += __shfl_xor_sync(0xffffffffu, l[mt], 2);
+    }
+    __syncthreads();                      // every warp is done with its pipeline memory
+    float *mbuf = reinterpret_cast<float *>(pipe);          // [NWARP][NSLOT][HD+2]
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        float *r0 = mbuf + ((size_t)warp * C::NSLOT + mt * 8 + g) * (HD + 2);
+#pragma unroll
+        for (int nt = 0; nt < C::NT; ++nt) {
+            // n tile nt holds d = 16*(nt/2) + 2*col + (nt&1); this thread has cols 2t, 2t+1
+            const int d0 = 16 * (nt >> 1) + 4 * t + (nt & 1);
+            r0[d0] = acc[mt][nt][0];
+            r0[d0 + 2] = acc[mt][nt][1];
+        }
+        if (t == 0) { r0[HD] = M[mt]; r0[HD + 1] = l[mt]; }
+    }
+    __syncthreads();
+
+    for (int sl = 0; sl < C::NSLOT; ++sl) {
+        const int idx = rg * C::NSLOT + sl;
+        const int r = idx / p.kvg, j = idx % p.kvg;
+        if (r >= p.S) break;
+        float mstar = M_INIT;
+#pragma unroll
+        for (int w = 0; w < NWARP; ++w) mstar = fmaxf(mstar, mbuf[((size_t)w * C::NSLOT + sl) * (HD + 2) + HD]);
+        float wgt[NWARP], lstar = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NWARP; ++w) {
+            const float *rw = mbuf + ((size_t)w * C::NSLOT + sl) * (HD + 2);
+            wgt[w] = ex2f(rw[HD] - mstar);
+            lstar += wgt[w] * rw[HD + 1];
+        }
+        const long grow = ((long)b * p.S + r) * p.nh + kvh * p.kvg + j;
+        for (int d = threadIdx.x; d < HD; d += NWARP * 32) {
+            float o = 0.0f;
+#pragma unroll
+            for (int w = 0; w < NWARP; ++w) o += wgt[w] * mbuf[((size_t)w * C::NSLOT + sl) * (HD + 2) + d];
+            if (p.write_partial) {
+                p.partial[((size_t)split * p.grows + grow) * (HD + 2) + d] = o;
+            } else {
+                const float v = lstar > 0.0f ? o / lstar : 0.0f;
+                const long oi = b * p.out_batch_stride + ((long)r * p.nh + kvh * p.kvg + j) * HD + d;
+                if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
+                else reinterpret_cast<float *>(p.out)[oi] = v;
+            }
+        }
+        if (p.write_partial && threadIdx.x == 0) {
+            float *pr = p.partial + ((size_t)split * p.grows + grow) * (HD + 2);
+            pr[HD] = p.export_nat ? mstar * LN2 : mstar;
+            pr[HD + 1] = lstar;
+        }
+    }
+    if (p.counters == nullptr) return;
+
+    // ------------------------------------------- in-kernel merge across the splits
+    // Arrival counting without a zeroed workspace: the counter word carries the launch's
+    // epoch, so whatever an earlier launch (or nobody) left there counts as zero arrivals.
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long *ctr = p.counters + ((size_t)blockIdx.z * gridDim.y + blockIdx.y);
+        unsigned long long old = *reinterpret_cast<volatile unsigned long long *>(ctr);
+        int arrived = -1;
+        for (int tries = 0; tries < (1 << 20); ++tries) {        // bounded: gives up rather than spin forever
+            const unsigned long long cnt = (old >> 16) == p.epoch ? (old & 0xffffull) : 0ull;
+            const unsigned long long prev = atomicCAS(ctr, old, (p.epoch << 16) | (cnt + 1));
+            if (prev == old) { arrived = (int)cnt + 1; break; }
+            old = prev;
+        }
+        s_last = (arrived == p.splits);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+
+    // The last CTA of the unit merges its rows.  Phase A stages every split's (m, l) in shared
+    // memory; phase B gives each thread one (row, dim) and streams the splits' partial outputs
+    // from L2 with independent loads in flight.
+    constexpr int NTHR = NWARP * 32;
+    const int G = p.splits;
+    float *ms = reinterpret_cast<float *>(pipe);            // [NSLOT][G]  m of each split (-inf if empty)
+    float *ls = ms + C::NSLOT * G;                          // [NSLOT][G]  l of each split
+    const int first = rg * C::NSLOT;
+    const int nrows = min(C::NSLOT, p.S * p.kvg - first);   // valid slots of this row group
+    const size_t rstride = (size_t)p.grows * (HD + 2);
+    auto grow_of = [&](int sl) {
+        const int idx = first + sl;
+        return ((long)b * p.S + idx / p.kvg) * p.nh + kvh * p.kvg + idx % p.kvg;
+    };
+    for (int e = threadIdx.x; e < nrows * G; e += NTHR) {
+        const int sl = e / G, i = e - sl * G;
+        const float *pr = p.partial + (size_t)i * rstride + (size_t)grow_of(sl) * (HD + 2);
+        const float li = __ldcg(pr + HD + 1);
+        ls[sl * G + i] = li;
+        ms[sl * G + i] = li > 0.0f ? __ldcg(pr + HD) : -CUDART_INF_F;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < nrows * HD; e += NTHR) {
+        const int sl = e / HD, d = e - sl * HD;
+        const long grow = grow_of(sl);
+        const float *base = p.partial + (size_t)grow * (HD + 2) + d;
+        float mstar = -CUDART_INF_F;
+        for (int i = 0; i < G; ++i) mstar = fmaxf(mstar, ms[sl * G + i]);
+        if (mstar == -CUDART_INF_F) mstar = 0.0f;           // no split saw a key for this row: weights are all 0
+        float lstar = 0.0f, o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+        int i = 0;
+        for (; i + 4 <= G; i += 4) {
+            const float v0 = __ldcg(base + (size_t)i * rstride), v1 = __ldcg(base + (size_t)(i + 1) * rstride);
+            const float v2 = __ldcg(base + (size_t)(i + 2) * rstride), v3 = __ldcg(base + (size_t)(i + 3) * rstride);
+            const float w0 = ex2f(ms[sl * G + i] - mstar), w1 = ex2f(ms[sl * G + i + 1] - mstar);
+            const float w2 = ex2f(ms[sl * G + i + 2] - mstar), w3 = ex2f(ms[sl * G + i + 3] - mstar);
+            lstar += w0 * ls[sl * G + i] + w1 * ls[sl * G + i + 1] + w2 * ls[sl * G + i + 2] + w3 * ls[sl * G + i + 3];
+            o0 = fmaf(w0, v0, o0); o1 = fmaf(w1, v1, o1); o2 = fmaf(w2, v2, o2); o3 = fmaf(w3, v3, o3);
+        }
+        for (; i < G; ++i) {
+            const float w = ex2f(ms[sl * G + i] - mstar);
+            lstar += w * ls[sl * G + i];
+            o0 = fmaf(w, __ldcg(base + (size_t)i * rstride), o0);
+        }
+        const float o = (o0 + o1) + (o2 + o3);
+        if (p.partial_export) {
+            p.partial_export[(size_t)grow * (HD + 2) + d] = o;
+            if (d == 0) {
+                p.partial_export[(size_t)grow * (HD + 2) + HD] = lstar > 0.0f ? mstar * LN2 : 0.0f;
+                p.partial_export[(size_t)grow * (HD + 2) + HD + 1] = lstar;
+            }
+        } else {
+            const float v = lstar > 0.0f ? o / lstar : 0.0f;
+            const int idx = first + sl;
+            const long oi = b * p.out_batch_stride + ((long)(idx / p.kvg) * p.nh + kvh * p.kvg + idx % p.kvg) * HD + d;
+            if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
+            else reinterpret_cast<float *>(p.out)[oi] = v;
+        }
+    }
+}
+
+// Merge G partial triples per row.  partials [G][rows][hd+2] = (o.., m, l); m in log2
+// units when nat == 0 (in-library split partials), natural-log units when nat == 1.
+// One CTA per row: the weights 2^(m_i - m*) are computed once into shared memory.
+constexpr int MERGE_MAX_G = 1024;
+__global__ void __launch_bounds__(128) merge_kernel(const float *partials, int G, int rows, int hd, void *out, int out_type,
+                                                     int nat, float *partial_out) {
+    __shared__ float wgt[MERGE_MAX_G];
+    __shared__ float red[8];
+    pdl_wait();                           // no-op unless launched as a programmatic dependent
+    pdl_launch_dependents();              // a following attention grid may start streaming its cache now
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float unit = nat ? LOG2E : 1.0f;
+    const size_t rstride = (size_t)rows * (hd + 2);
+    const float *base = partials + (size_t)row * (hd + 2);
+    float mloc = -CUDART_INF_F;
+    for (int i = tid; i < G; i += 128) {
+        const float li = base[i * rstride + hd + 1];
+        const float mi = base[i * rstride + hd] * unit;
+        wgt[i] = li > 0.0f ? mi : -CUDART_INF_F;
+        mloc = fmaxf(mloc, wgt[i]);
+    }
+    mloc = warp_max(mloc);
+    if ((tid & 31) == 0) red[tid >> 5] = mloc;
+    __syncthreads();
+    const float mstar = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    float lloc = 0.0f;
+    for (int i = tid; i < G; i += 128) {
+        const float w = wgt[i] == -CUDART_INF_F ? 0.0f : ex2f(wgt[i] - mstar);
+        lloc += w * base[i * rstride + hd + 1];
+        wgt[i] = w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lloc += __shfl_xor_sync(0xffffffffu, lloc, o);
+    if ((tid & 31) == 0) red[4 + (tid >> 5)] = lloc;
+    __syncthreads();
+    const float lstar = red[4] + red[5] + red[6] + red[7];
+    for (int d = tid; d < hd; d += 128) {
+        float o = 0.0f;
+        for (int i = 0; i < G; ++i) o = fmaf(wgt[i], base[i * rstride + d], o);
+        if (partial_out) {
+            partial_out[(size_t)row * (hd + 2) + d] = o;
+        } else {
+            const float v = lstar > 0.0f ? o / lstar : 0.0f;
+            if (out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(out)[(size_t)row * hd + d] = __float2bfloat16_rn(v);
+            else reinterpret_cast<float *>(out)[(size_t)row * hd + d] = v;
+        }
+    }
+    if (partial_out && tid == 0) {
+        partial_out[(size_t)row * (hd + 2) + hd] = lstar > 0.0f ? mstar * LN2 : 0.0f;   // exported m: natural log
+        partial_out[(size_t)row * (hd + 2) + hd + 1] = lstar;
+    }
+}
+
+}  // namespace fused
+}  // namespace nomos

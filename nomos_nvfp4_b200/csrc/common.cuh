@@ -116,6 +116,11 @@ __device__ __forceinline__ float ex2f(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(x));
     return r;
 }
+__device__ __forceinline__ float rcpf(float x) {      // one MUFU instruction, ~1 ulp
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(x));
+    return r;
+}
 __device__ __forceinline__ float lg2f(float x) {
     float r;
     asm("lg2.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(x));
