@@ -202,6 +202,12 @@ long attn_workspace_bytes(const AttnArgs &a) {
 
 int launch_attn_fused(cudaStream_t st, const AttnArgs &a) { return dispatch(st, a, false, nullptr); }
 
+#ifdef NOMOS_TIMELINE
+extern "C" __attribute__((visibility("default"))) int nomos_debug_timeline(unsigned long long *host_out, int n_ctas) {
+    return (int)cudaMemcpyFromSymbol(host_out, fused::g_timeline, sizeof(unsigned long long) * 6 * n_ctas);
+}
+#endif
+
 int launch_merge_partials(cudaStream_t st, const float *partials, int G, int rows, int l_hd, void *out, int out_type) {
     merge_kernel<<<rows, 128, 0, st>>>(partials, G, rows, l_hd, out, out_type, 1, nullptr);
     cudaError_t e = cudaGetLastError();

@@ -84,6 +84,25 @@ __device__ __forceinline__ void mma_u8s8_zero(int (&d)[4], uint32_t a0, uint32_t
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
 }
 
+#ifdef NOMOS_TIMELINE
+// Debug builds only: per-CTA wall-clock marks (ns) read back by nomos_debug_timeline().
+__device__ unsigned long long g_timeline[4096][6];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define NOMOS_MARK(slot)                                                                                    \
+    do {                                                                                                    \
+        if (threadIdx.x == 0) {                                                                             \
+            const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                 \
+            if (cta < 4096) g_timeline[cta][slot] = gtime();                                                \
+        }                                                                                                   \
+    } while (0)
+#else
+#define NOMOS_MARK(slot) do {} while (0)
+#endif
+
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
@@ -188,34 +207,47 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
     // the stream was still running: wait for the predecessor's memory (the query, freshly
     // appended cache rows, the shared split workspace) before the first global access.  Then let
     // the split-merge grid be set up right away; it blocks the same way until this grid is done.
+    NOMOS_MARK(0);
     pdl_wait();
     pdl_launch_dependents();
-
-    // The first tiles are requested before the query rows are prepared, so the
-    // DRAM latency of the pipeline fill overlaps the prologue.
-#pragma unroll
-    for (int s = 0; s < NSTAGE - 1; ++s) issue(s);
+    NOMOS_MARK(1);
 
     // ------------------------------------------------------------ Q prologue
     // Slot sl of this CTA = local row index rg*NSLOT + sl = (query row r, group head j).
-    // Each row becomes 15-bit fixed point: q ~= sq * (128*hi + lo), hi/lo int8.
-    for (int sl = warp; sl < C::NSLOT; sl += NWARP) {
+    // The query loads go out first, then the first cache tiles are requested, so the (tiny) query
+    // is not queued behind megabytes of prefetch and the pipeline fill overlaps its preparation.
+    constexpr int QITER = (C::NSLOT + NWARP - 1) / NWARP;
+    float qx[QITER][HD / 32];
+#pragma unroll
+    for (int qi = 0; qi < QITER; ++qi) {
+        const int sl = warp + qi * NWARP;
         const int idx = rg * C::NSLOT + sl;
         const int r = idx / p.kvg, j = idx % p.kvg;
+        const bool valid = sl < C::NSLOT && r < p.S;
+#pragma unroll
+        for (int i = 0; i < HD / 32; ++i)
+            qx[qi][i] = valid ? load_q(p.q, p.q_type, b * p.q_batch_stride + ((long)r * p.nh + kvh * p.kvg + j) * HD + lane + 32 * i) : 0.0f;
+    }
+#pragma unroll
+    for (int s = 0; s < NSTAGE - 1; ++s) issue(s);
+
+    // Each row becomes 15-bit fixed point: q ~= sq * (128*hi + lo), hi/lo int8.
+#pragma unroll
+    for (int qi = 0; qi < QITER; ++qi) {
+        const int sl = warp + qi * NWARP;
+        if (sl >= C::NSLOT) break;
+        const int idx = rg * C::NSLOT + sl;
+        const int r = idx / p.kvg;
         const bool valid = r < p.S;
-        float x[HD / 32];
         float amax = 0.0f;
 #pragma unroll
-        for (int i = 0; i < HD / 32; ++i) {
-            x[i] = valid ? load_q(p.q, p.q_type, b * p.q_batch_stride + ((long)r * p.nh + kvh * p.kvg + j) * HD + lane + 32 * i) : 0.0f;
-            amax = fmaxf(amax, fabsf(x[i]));
-        }
+        for (int i = 0; i < HD / 32; ++i) amax = fmaxf(amax, fabsf(qx[qi][i]));
         amax = warp_max(amax);
-        const float sq = amax > 0.0f ? amax / (float)Q_FIX_MAX : 1.0f;
-        const float inv = 1.0f / sq;
+        const float sq = amax > 0.0f ? amax * (1.0f / (float)Q_FIX_MAX) : 1.0f;
+        const float inv = rcpf(sq);
 #pragma unroll
         for (int i = 0; i < HD / 32; ++i) {
-            int qf = __float2int_rn(x[i] * inv);
+            int qf = __float2int_rn(qx[qi][i] * inv);
             qf = max(-Q_FIX_MAX, min(Q_FIX_MAX, qf));
             const int hi = (qf + 64) >> 7;
             const int lo = qf - (hi << 7);
@@ -256,6 +288,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         for (int ks = 0; ks < HD / 32; ++ks) load_qa(qa[ks], 0, ks);
     }
 
+    NOMOS_MARK(2);
     // ------------------------------------------------------------ running state
     float M[MT], l[MT];
     float acc[MT][C::NT][2];              // [slot tile][8-dim tile][2 dims] of slot g
@@ -434,6 +467,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         __syncwarp();
     }
     cp_async_wait<0>();
+    if (warp == 0) NOMOS_MARK(3);
 
     // ---------------------------------------------------- merge warps in shared
 #pragma unroll
@@ -491,15 +525,16 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
             pr[HD + 1] = lstar;
         }
     }
+    NOMOS_MARK(4);
     if (p.counters == nullptr) return;
 
     // ------------------------------------------- in-kernel merge across the splits
     // Arrival counting without a zeroed workspace: the counter word carries the launch's
     // epoch, so whatever an earlier launch (or nobody) left there counts as zero arrivals.
     __shared__ int s_last;
-    __threadfence();
-    __syncthreads();
+    __syncthreads();                      // all partial stores of this CTA are issued
     if (threadIdx.x == 0) {
+        __threadfence();                  // cumulative: orders the whole CTA's stores before the arrival
         unsigned long long *ctr = p.counters + ((size_t)blockIdx.z * gridDim.y + blockIdx.y);
         unsigned long long old = *reinterpret_cast<volatile unsigned long long *>(ctr);
         int arrived = -1;
@@ -514,6 +549,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    NOMOS_MARK(5);
 
     // The last CTA of the unit merges its rows.  Phase A stages every split's (m, l) in shared
     // memory; phase B gives each thread one (row, dim) and streams the splits' partial outputs
@@ -529,6 +565,18 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         const int idx = first + sl;
         return ((long)b * p.S + idx / p.kvg) * p.nh + kvh * p.kvg + idx % p.kvg;
     };
+    // Small merges (the common decode case): every thread owns one (row, dim) and requests its
+    // G partial outputs BEFORE the (m, l) staging barrier, so both sets of L2 loads are in flight
+    // together (one round trip instead of two).
+    constexpr int GFAST = 16;
+    const bool fast = (G <= GFAST) && (nrows * HD <= NTHR);
+    float pre[GFAST];
+    if (fast && (int)threadIdx.x < nrows * HD) {
+        const int sl = threadIdx.x / HD, d = threadIdx.x - sl * HD;
+        const float *base = p.partial + (size_t)grow_of(sl) * (HD + 2) + d;
+#pragma unroll
+        for (int i = 0; i < GFAST; ++i) pre[i] = i < G ? __ldcg(base + (size_t)i * rstride) : 0.0f;
+    }
     for (int e = threadIdx.x; e < nrows * G; e += NTHR) {
         const int sl = e / G, i = e - sl * G;
         const float *pr = p.partial + (size_t)i * rstride + (size_t)grow_of(sl) * (HD + 2);
@@ -546,6 +594,16 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         if (mstar == -CUDART_INF_F) mstar = 0.0f;           // no split saw a key for this row: weights are all 0
         float lstar = 0.0f, o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
         int i = 0;
+        if (fast) {
+#pragma unroll
+            for (int k = 0; k < GFAST; ++k)
+                if (k < G) {
+                    const float w = ex2f(ms[sl * G + k] - mstar);
+                    lstar = fmaf(w, ls[sl * G + k], lstar);
+                    o0 = fmaf(w, pre[k], o0);
+                }
+            i = G;
+        }
         for (; i + 4 <= G; i += 4) {
             const float v0 = __ldcg(base + (size_t)i * rstride), v1 = __ldcg(base + (size_t)(i + 1) * rstride);
             const float v2 = __ldcg(base + (size_t)(i + 2) * rstride), v3 = __ldcg(base + (size_t)(i + 3) * rstride);
