@@ -83,12 +83,12 @@ static int kernel_occupancy() {
     return occ[dev];
 }
 
-static int pick_mt(int slots) { return slots <= 8 ? 1 : 3; }
+static int pick_mt(int slots, int hd = 128) { return (slots <= 8 || hd > 128) ? 1 : 3; }
 
 static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp) {
     Plan pl;
     const int slots = a.S * a.kvg;
-    pl.mt = pick_mt(slots);
+    pl.mt = pick_mt(slots, hd);
     pl.row_groups = (slots + 8 * pl.mt - 1) / (8 * pl.mt);
     // first window index any row needs
     int j_begin = 0;
@@ -184,11 +184,24 @@ static int dispatch_mt(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
     return pick_mt(a.S * a.kvg) == 1 ? launch_inst<FMT, HD, 1>(st, a, q, ws) : launch_inst<FMT, HD, 3>(st, a, q, ws);
 }
 
-static int dispatch(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
-    if (a.kv_fmt != KV_I8) { set_error("kv_fmt %d not built yet", a.kv_fmt); return NOMOS_EUNSUPPORTED; }
+template <int FMT>
+static int dispatch_hd(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
     switch (a.l_hd) {
-        case 128: return dispatch_mt<KV_I8, 128>(st, a, q, ws);
-        default: set_error("head_dim %d unsupported (128)", a.l_hd); return NOMOS_EUNSUPPORTED;
+        case 128: return dispatch_mt<FMT, 128>(st, a, q, ws);
+        // wider heads keep 64 / 128 fp32 sums per thread for one 8-row tile: more query rows are
+        // covered by row groups (extra CTAs over the same cache bytes, served from L2)
+        case 256: return launch_inst<FMT, 256, 1>(st, a, q, ws);
+        case 512: return launch_inst<FMT, 512, 1>(st, a, q, ws);
+        default: set_error("head_dim %d unsupported (128, 256, 512)", a.l_hd); return NOMOS_EUNSUPPORTED;
+    }
+}
+
+static int dispatch(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
+    switch (a.kv_fmt) {
+        case KV_I8: return dispatch_hd<KV_I8>(st, a, q, ws);
+        case KV_I4: return dispatch_hd<KV_I4>(st, a, q, ws);
+        case KV_I4B32: return dispatch_hd<KV_I4B32>(st, a, q, ws);
+        default: set_error("kv_fmt %d unknown", a.kv_fmt); return NOMOS_EBADARG;
     }
 }
 

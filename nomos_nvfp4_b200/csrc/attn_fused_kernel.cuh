@@ -34,7 +34,6 @@ constexpr float RND_MAGIC = 8388608.0f;  // 2^23: adding it leaves round-to-near
 
 template <int FMT, int HD, int MT>
 struct Cfg {
-    static constexpr int NW = (MT == 1) ? NOMOS_NWARP : NOMOS_NWARP_MULTI;    // warps per CTA
     static constexpr int ROWB = (FMT == KV_I8) ? HD : HD / 2;                 // cache bytes per token row
     static constexpr int CHUNKS = ROWB / 16;                                  // 16-byte chunks per row
     static constexpr int NBLK = HD / 32;
@@ -45,7 +44,11 @@ struct Cfg {
     static constexpr int NSLOT = 8 * MT;                                      // query rows (row x group head) per CTA
     static constexpr int NT = HD / 8;                                         // PV N tiles (8 output dims each)
     static constexpr int Q_BYTES = 2 * NSLOT * HD;                            // two limbs
-    static constexpr int SLOT_BYTES = NSLOT * 16;                             // qscale, lo, hi, pad
+    static constexpr int SLOT_BYTES = NSLOT * 16 + NSLOT * NBLK * 4;          // qscale, lo, hi, pad; 8*sum(q) per block
+    // warps per CTA: as many as the register file and ~200 KB of pipeline memory allow
+    static constexpr int NW_REG = (MT == 1 && HD <= 256) ? NOMOS_NWARP : NOMOS_NWARP_MULTI;
+    static constexpr int NW_MEM = (200 * 1024) / (NSTAGE * STAGE_BYTES);
+    static constexpr int NW = NW_REG < NW_MEM ? NW_REG : (NW_MEM < 1 ? 1 : NW_MEM);
     static constexpr int PIPE_BYTES = NW * NSTAGE * STAGE_BYTES;
     static constexpr int MERGE_BYTES = NW * NSLOT * (HD + 2) * 4;
     static constexpr int SMEM_BYTES = Q_BYTES + SLOT_BYTES + (PIPE_BYTES > MERGE_BYTES ? PIPE_BYTES : MERGE_BYTES);
@@ -103,6 +106,14 @@ __device__ __forceinline__ unsigned long long gtime() {
 #define NOMOS_MARK(slot) do {} while (0)
 #endif
 
+__device__ __forceinline__ void mma_u8u8_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+    const int z = 0;
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
+}
+
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
@@ -116,12 +127,12 @@ template <int FMT, int HD, int MT>
 __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(const KParams p) {
     using C = Cfg<FMT, HD, MT>;
     constexpr int NWARP = C::NW;
-    static_assert(FMT == KV_I8, "int4 tiles are handled by a separate code path");
     extern __shared__ __align__(128) uint8_t smem[];
     int8_t *q_limbs = reinterpret_cast<int8_t *>(smem);                        // [2][NSLOT][HD]
     float *slot_qscale = reinterpret_cast<float *>(smem + C::Q_BYTES);         // [NSLOT]
     int *slot_lo = reinterpret_cast<int *>(smem + C::Q_BYTES + C::NSLOT * 4);
     int *slot_hi = reinterpret_cast<int *>(smem + C::Q_BYTES + C::NSLOT * 8);
+    int *slot_qsum = reinterpret_cast<int *>(smem + C::Q_BYTES + C::NSLOT * 16);   // [NSLOT][NBLK]
     uint8_t *pipe = smem + C::Q_BYTES + C::SLOT_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -135,7 +146,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
     const int my_first = tile_begin + warp;
     const int my_count = my_first < tile_end ? (tile_end - my_first + NWARP - 1) / NWARP : 0;
 
-    const int row_stride = p.cache_hd;                       // bytes between consecutive token rows (int8)
+    const int row_stride = (FMT == KV_I8) ? p.cache_hd : p.cache_hd / 2;   // bytes between consecutive token rows
     const uint8_t *kbase = p.k_cache + b * p.kv_batch_stride + (size_t)kvh * p.cache_cap * (size_t)row_stride;
     const uint8_t *vbase = p.v_cache + b * p.kv_batch_stride + (size_t)kvh * p.cache_cap * (size_t)row_stride;
     const uint8_t *ksbase = p.k_scales + b * p.scale_batch_stride + (size_t)kvh * p.cache_cap * C::SCB;
@@ -153,6 +164,15 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
 #pragma unroll
     for (int h = 0; h < HPASS; ++h) lane_soff[h] = cr * C::ROWB + swz_chunk<C::ROWB>(cr, cc0 + 4 * h) * 16;
 
+    // one token's scale bytes (4: fp32 row scale; 2 per block of 32 for the block-32 layout)
+    auto copy_scales = [&](uint32_t dst, const uint8_t *src, bool ok) {
+        if constexpr (C::SCB == 4) cp_async4(dst, src, ok ? 4 : 0);
+        else if constexpr (C::SCB == 8) cp_async8(dst, src, ok ? 8 : 0);
+        else {
+#pragma unroll
+            for (int o = 0; o < C::SCB; o += 16) cp_async16(dst + o, src + o, ok ? 16 : 0);
+        }
+    };
     auto issue = [&](int it) {
         if (it < my_count) {
             const int tok0 = (my_first + it * NWARP) * TILE;
@@ -173,8 +193,8 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
                         cp_async16(so + C::KV_BYTES, gv + go, 16);
                     }
                 const size_t sg = (size_t)(slot0 + lane) * C::SCB;
-                cp_async4(st + 2 * C::KV_BYTES + lane * 4, ksbase + sg, 4);
-                cp_async4(st + 2 * C::KV_BYTES + C::SC_BYTES + lane * 4, vsbase + sg, 4);
+                copy_scales(st + 2 * C::KV_BYTES + lane * C::SCB, ksbase + sg, true);
+                copy_scales(st + 2 * C::KV_BYTES + C::SC_BYTES + lane * C::SCB, vsbase + sg, true);
             } else {
                 // ragged tile: wraps the ring or runs past the window; rows past the end are zero-filled
 #pragma unroll
@@ -196,8 +216,8 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
                 slot = slot >= p.cache_cap ? slot - p.cache_cap : slot;
                 const bool ok = tok < p.klen;
                 const size_t sg = (size_t)(ok ? slot : 0) * C::SCB;
-                cp_async4(st + 2 * C::KV_BYTES + lane * 4, ksbase + sg, ok ? 4 : 0);
-                cp_async4(st + 2 * C::KV_BYTES + C::SC_BYTES + lane * 4, vsbase + sg, ok ? 4 : 0);
+                copy_scales(st + 2 * C::KV_BYTES + lane * C::SCB, ksbase + sg, ok);
+                copy_scales(st + 2 * C::KV_BYTES + C::SC_BYTES + lane * C::SCB, vsbase + sg, ok);
             }
         }
         cp_async_commit();
@@ -245,14 +265,34 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         amax = warp_max(amax);
         const float sq = amax > 0.0f ? amax * (1.0f / (float)Q_FIX_MAX) : 1.0f;
         const float inv = rcpf(sq);
+        int qblk[HD / 32];
 #pragma unroll
         for (int i = 0; i < HD / 32; ++i) {
+            qblk[i] = 0;
             int qf = __float2int_rn(qx[qi][i] * inv);
             qf = max(-Q_FIX_MAX, min(Q_FIX_MAX, qf));
             const int hi = (qf + 64) >> 7;
             const int lo = qf - (hi << 7);
-            q_limbs[sl * HD + lane + 32 * i] = (int8_t)hi;
-            q_limbs[(C::NSLOT + sl) * HD + lane + 32 * i] = (int8_t)lo;
+            int pos = lane + 32 * i;
+            if constexpr (FMT != KV_I8) {
+                // int4 tiles hand element 32b+8t+2j+par of a row to MMA k slot 16*par+4t+j of step b
+                pos = 32 * i + ((lane & 1) << 4) + ((lane >> 3) << 2) + ((lane >> 1) & 3);
+                int bs = qf;                                        // sum of the block's fixed-point values
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
+                qblk[i] = bs;
+            }
+            q_limbs[sl * HD + pos] = (int8_t)hi;
+            q_limbs[(C::NSLOT + sl) * HD + pos] = (int8_t)lo;
+        }
+        if constexpr (FMT != KV_I8) {
+            if (lane == 0) {
+                int tot = 0;
+#pragma unroll
+                for (int i = 0; i < HD / 32; ++i) tot += qblk[i];
+#pragma unroll
+                for (int i = 0; i < HD / 32; ++i) slot_qsum[sl * C::NBLK + i] = 8 * (FMT == KV_I4 ? tot : qblk[i]);
+            }
         }
         if (lane == 0) {
             const int hi_b = valid ? p.klen - (p.S - 1 - r) : 0;
@@ -287,6 +327,14 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
 #pragma unroll
         for (int ks = 0; ks < HD / 32; ++ks) load_qa(qa[ks], 0, ks);
     }
+    auto get_qa = [&](uint32_t(&a)[4], int mt, int ks) {
+        if constexpr (Q_IN_REGS) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = qa[ks][i];
+        } else {
+            load_qa(a, mt, ks);
+        }
+    };
 
     NOMOS_MARK(2);
     // ------------------------------------------------------------ running state
@@ -317,52 +365,102 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         const uint32_t st = my_pipe_u32 + (it % NSTAGE) * C::STAGE_BYTES;
         const uint8_t *stp = my_pipe + (it % NSTAGE) * C::STAGE_BYTES;
         const bool need_mask = (tok0 + TILE > hi_min) || (tok0 < lo_max);
+        const uint8_t *ksm = stp + 2 * C::KV_BYTES;                 // K scales of the tile, token-major
+        const uint8_t *vsm = ksm + C::SC_BYTES;                     // V scales
 
         // --------------------------------------------------------------- QK
-        // c[mt][n]: rows g / g+8 = high / low limb of slot (mt, g); columns = tokens 8n+2t, 8n+2t+1.
-        int c[MT][4][4];
+        // Base-2 logits s2[mt][n][e] of slot (mt, g) against token 8n+2t+e.  The MMA rows g / g+8
+        // carry the high / low limb of the slot's query, the columns 2t, 2t+1 the two tokens.
+        float s2[MT][4][2];
+        if constexpr (FMT == KV_I8) {
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
+            for (int n = 0; n < 4; ++n) {
+                int c[MT][4];
 #pragma unroll
-            for (int n = 0; n < 4; ++n)
+                for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) c[mt][n][i] = 0;
+                    for (int i = 0; i < 4; ++i) c[mt][i] = 0;
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
+                for (int half = 0; half < HD / 64; ++half) {
+                    uint32_t kb[4];
+                    const int row = 8 * n + (lane & 7);
+                    const int ch = 4 * half + (lane >> 3);
+                    ldmatrix_x4(kb, st + row * C::ROWB + swz_chunk<C::ROWB>(row, ch) * 16);
 #pragma unroll
-            for (int half = 0; half < HD / 64; ++half) {
-                uint32_t kb[4];
-                const int row = 8 * n + (lane & 7);
-                const int ch = 4 * half + (lane >> 3);
-                ldmatrix_x4(kb, st + row * C::ROWB + swz_chunk<C::ROWB>(row, ch) * 16);
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    if constexpr (Q_IN_REGS) {
-                        mma_s8s8(c[mt][n], qa[2 * half], kb[0], kb[1]);
-                        mma_s8s8(c[mt][n], qa[2 * half + 1], kb[2], kb[3]);
-                    } else {
+                    for (int mt = 0; mt < MT; ++mt) {
                         uint32_t a[4];
-                        load_qa(a, mt, 2 * half);
-                        mma_s8s8(c[mt][n], a, kb[0], kb[1]);
-                        load_qa(a, mt, 2 * half + 1);
-                        mma_s8s8(c[mt][n], a, kb[2], kb[3]);
+                        get_qa(a, mt, 2 * half);
+                        mma_s8s8(c[mt], a, kb[0], kb[1]);
+                        get_qa(a, mt, 2 * half + 1);
+                        mma_s8s8(c[mt], a, kb[2], kb[3]);
                     }
                 }
+                const float2 kk = *reinterpret_cast<const float2 *>(ksm + (8 * n + 2 * t) * 4);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    s2[mt][n][0] = (float)(c[mt][0] * 128 + c[mt][2]) * (qscale[mt] * kk.x);
+                    s2[mt][n][1] = (float)(c[mt][1] * 128 + c[mt][3]) * (qscale[mt] * kk.y);
+                }
             }
-        }
-        const float *ksm = reinterpret_cast<const float *>(stp + 2 * C::KV_BYTES);
-        const float *vsm = reinterpret_cast<const float *>(stp + 2 * C::KV_BYTES + C::SC_BYTES);
-        float s2[MT][4][2];               // base-2 logits of my 8 tokens
-        float vs[4][2];                   // their V scales
+        } else {
+            // int4: a 16-byte chunk holds one block of 32 values; low nibbles (even elements) feed
+            // MMA k slots 0-15, high nibbles k slots 16-31, both as biased unsigned bytes q+8.  The
+            // bias is removed exactly with 8 * sum(q limbs), precomputed per slot (and block).
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const float2 kk = *reinterpret_cast<const float2 *>(ksm + 8 * n + 2 * t);
-            const float2 vv = *reinterpret_cast<const float2 *>(vsm + 8 * n + 2 * t);
-            vs[n][0] = vv.x; vs[n][1] = vv.y;
+            for (int n = 0; n < 4; ++n) {
+                int c[MT][4];
+                float sblk[MT][2];
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                s2[mt][n][0] = (float)(c[mt][n][0] * 128 + c[mt][n][2]) * (qscale[mt] * kk.x);
-                s2[mt][n][1] = (float)(c[mt][n][1] * 128 + c[mt][n][3]) * (qscale[mt] * kk.y);
+                for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) c[mt][i] = 0;
+                    sblk[mt][0] = 0.0f; sblk[mt][1] = 0.0f;
+                }
+#pragma unroll
+                for (int grp = 0; grp < HD / 128; ++grp) {
+                    uint32_t kr[4];
+                    const int row = 8 * n + (lane & 7);
+                    const int ch = 4 * grp + (lane >> 3);
+                    ldmatrix_x4(kr, st + row * C::ROWB + swz_chunk<C::ROWB>(row, ch) * 16);
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        const int blk = 4 * grp + m;
+                        const uint32_t lo = lop3_and_xor(kr[m], 0x0f0f0f0fu, 0x08080808u);
+                        const uint32_t hi = lop3_and_xor(kr[m] >> 4, 0x0f0f0f0fu, 0x08080808u);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            uint32_t a[4];
+                            get_qa(a, mt, blk);
+                            if constexpr (FMT == KV_I4) {
+                                mma_s8u8(c[mt], a, lo, hi);
+                            } else {
+                                int cb[4] = {0, 0, 0, 0};
+                                mma_s8u8(cb, a, lo, hi);
+                                // fp16 block scales of tokens 8n+2t and 8n+2t+1
+                                const int bias = slot_qsum[(mt * 8 + g) * C::NBLK + blk];
+                                const float f0 = __half2float(*reinterpret_cast<const __half *>(ksm + ((8 * n + 2 * t) * C::NBLK + blk) * 2));
+                                const float f1 = __half2float(*reinterpret_cast<const __half *>(ksm + ((8 * n + 2 * t + 1) * C::NBLK + blk) * 2));
+                                sblk[mt][0] = fmaf((float)(cb[0] * 128 + cb[2] - bias), f0, sblk[mt][0]);
+                                sblk[mt][1] = fmaf((float)(cb[1] * 128 + cb[3] - bias), f1, sblk[mt][1]);
+                            }
+                        }
+                    }
+                }
+                if constexpr (FMT == KV_I4) {
+                    const float2 kk = *reinterpret_cast<const float2 *>(ksm + (8 * n + 2 * t) * 4);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const int bias = slot_qsum[(mt * 8 + g) * C::NBLK];          // 8 * sum over the whole row
+                        s2[mt][n][0] = (float)(c[mt][0] * 128 + c[mt][2] - bias) * (qscale[mt] * kk.x);
+                        s2[mt][n][1] = (float)(c[mt][1] * 128 + c[mt][3] - bias) * (qscale[mt] * kk.y);
+                    }
+                } else {
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        s2[mt][n][0] = sblk[mt][0] * qscale[mt];
+                        s2[mt][n][1] = sblk[mt][1] * qscale[mt];
+                    }
+                }
             }
         }
         if (need_mask) {
@@ -378,33 +476,27 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         }
 
         // ------------------------------------------------ softmax weights, 16-bit fixed point
-        // w_t = 2^(s_t - tile max) * v_scale_t / (largest v_scale of the tile) lies in [0,1] and is
-        // rounded to u16; the softmax denominator is accumulated from the ROUNDED values, so the
-        // rounding perturbs normalised weights instead of the output's absolute value.
-        float vmax = 0.0f;
+        // w = 2^(s - tile max) * v_scale, divided by the tile's largest w, is rounded to u16 and
+        // split into two u8 limbs for the tensor core; F carries the tile's weight into the fp32
+        // running sums.  Block-32 caches have one v_scale per (token, block of 32 dims).
+        constexpr int NVB = (FMT == KV_I4B32) ? C::NBLK : 1;
+        float vsc[4][2][NVB];
 #pragma unroll
-        for (int n = 0; n < 4; ++n) vmax = fmaxf(vmax, fmaxf(vs[n][0], vs[n][1]));
-        vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1));
-        vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 2));
-        const float vnorm = vmax > 0.0f ? P_FIX * rcpf(vmax) : 0.0f;
-        const float tile_unit = vmax * (1.0f / P_FIX);
-        float vsn[4][2], rvs[4][2];
+        for (int n = 0; n < 4; ++n) {
+            if constexpr (FMT == KV_I4B32) {
 #pragma unroll
-        for (int n = 0; n < 4; ++n)
+                for (int e = 0; e < 2; ++e)
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                vsn[n][j] = vs[n][j] * vnorm;
-                rvs[n][j] = rcpf(vs[n][j]);
+                    for (int vb = 0; vb < NVB; ++vb)
+                        vsc[n][e][vb] = __half2float(*reinterpret_cast<const __half *>(vsm + ((8 * n + 2 * t + e) * C::NBLK + vb) * 2));
+            } else {
+                const float2 vv = *reinterpret_cast<const float2 *>(vsm + (8 * n + 2 * t) * 4);
+                vsc[n][0][0] = vv.x; vsc[n][1][0] = vv.y;
             }
-        if (need_mask) {                  // zero-filled rows past the end of the window carry scale 0
-#pragma unroll
-            for (int n = 0; n < 4; ++n)
-#pragma unroll
-                for (int j = 0; j < 2; ++j) rvs[n][j] = vs[n][j] > 0.0f ? rvs[n][j] : 0.0f;
         }
-
-        uint32_t pa[MT][4];               // A fragment of the PV MMA: a0/a2 = high limbs, a1/a3 = low limbs
-        float F[MT];                      // weight of this tile's integer sums in the running accumulators
+        uint32_t pa[MT][NVB][4];          // A fragments of the PV MMA: a0/a2 = high limbs, a1/a3 = low limbs
+        int ubias[MT][NVB];               // int4 only: 8 * sum of the u16 weights (removes the +8 nibble bias)
+        float F[MT];
         bool rescale = false;
         float alpha[MT];
 #pragma unroll
@@ -415,26 +507,51 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float m_new = fmaxf(M[mt], mx);
-            const float mx_safe = mx == -CUDART_INF_F ? 0.0f : mx;
+            const bool empty = mx == -CUDART_INF_F;                 // every token of the tile is masked for this slot
+            const float mx_safe = empty ? 0.0f : mx;
+            const float tile_w = empty ? 0.0f : ex2f(mx - m_new);
             alpha[mt] = ex2f(M[mt] - m_new);
             rescale |= (m_new != M[mt]);
             M[mt] = m_new;
-            F[mt] = mx == -CUDART_INF_F ? 0.0f : ex2f(mx - m_new) * tile_unit;
-            uint32_t pk[4];
-            float lsum = 0.0f;
+            float pe[4][2];
+            float lsum = 0.0f, wmax = 0.0f;
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
-                const float f0 = fmaf(ex2f(s2[mt][n][0] - mx_safe), vsn[n][0], RND_MAGIC);
-                const float f1 = fmaf(ex2f(s2[mt][n][1] - mx_safe), vsn[n][1], RND_MAGIC);
-                lsum = fmaf(f0 - RND_MAGIC, rvs[n][0], lsum);
-                lsum = fmaf(f1 - RND_MAGIC, rvs[n][1], lsum);
-                pk[n] = prmt(__float_as_uint(f0), __float_as_uint(f1), 0x5410u);     // two u16
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    pe[n][e] = ex2f(s2[mt][n][e] - mx_safe);
+                    lsum += pe[n][e];
+#pragma unroll
+                    for (int vb = 0; vb < NVB; ++vb) wmax = fmaxf(wmax, pe[n][e] * vsc[n][e][vb]);
+                }
+            wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, 1));
+            wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, 2));
+            const float inv = wmax > 0.0f ? P_FIX * rcpf(wmax) : 0.0f;
+            F[mt] = tile_w * wmax * (1.0f / P_FIX);
+            l[mt] = fmaf(tile_w, lsum, l[mt] * alpha[mt]);
+#pragma unroll
+            for (int vb = 0; vb < NVB; ++vb) {
+                uint32_t pk[4];
+                int usum = 0;
+#pragma unroll
+                for (int n = 0; n < 4; ++n) {
+                    const uint32_t f0 = __float_as_uint(fmaf(pe[n][0] * vsc[n][0][vb], inv, RND_MAGIC));
+                    const uint32_t f1 = __float_as_uint(fmaf(pe[n][1] * vsc[n][1][vb], inv, RND_MAGIC));
+                    pk[n] = prmt(f0, f1, 0x5410u);                  // two u16
+                    if constexpr (FMT != KV_I8) usum += (int)(f0 & 0xffffu) + (int)(f1 & 0xffffu);
+                }
+                pa[mt][vb][0] = prmt(pk[0], pk[1], 0x7531u);
+                pa[mt][vb][1] = prmt(pk[0], pk[1], 0x6420u);
+                pa[mt][vb][2] = prmt(pk[2], pk[3], 0x7531u);
+                pa[mt][vb][3] = prmt(pk[2], pk[3], 0x6420u);
+                if constexpr (FMT != KV_I8) {
+                    usum += __shfl_xor_sync(0xffffffffu, usum, 1);
+                    usum += __shfl_xor_sync(0xffffffffu, usum, 2);
+                    ubias[mt][vb] = 8 * usum;
+                } else {
+                    ubias[mt][vb] = 0;
+                }
             }
-            l[mt] = fmaf(F[mt], lsum, l[mt] * alpha[mt]);
-            pa[mt][0] = prmt(pk[0], pk[1], 0x7531u);
-            pa[mt][1] = prmt(pk[0], pk[1], 0x6420u);
-            pa[mt][2] = prmt(pk[2], pk[3], 0x7531u);
-            pa[mt][3] = prmt(pk[2], pk[3], 0x6420u);
         }
         if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
@@ -444,24 +561,50 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         }
 
         // --------------------------------------------------------------- PV
-        // u8 x s8 MMA over all 32 tokens at once: A = weight limbs (rows g / g+8 = high / low),
-        // B = V bytes transposed by ldmatrix.trans + one byte permute, exact int32 result.
+        // One MMA spans the whole 32-token tile: A = weight limbs (rows g / g+8 = high / low),
+        // B = V bytes transposed by ldmatrix.trans + byte permutes; the int32 result is exact.
         const uint32_t vst = st + C::KV_BYTES;
+        if constexpr (FMT == KV_I8) {
 #pragma unroll
-        for (int ch = 0; ch < HD / 16; ++ch) {
-            uint32_t vr[4];               // vr[o]: tokens 8o+2t, 8o+2t+1 x dims 16ch+2g, 16ch+2g+1
-            ldmatrix_x4_trans(vr, vst + lane * C::ROWB + swz_chunk<C::ROWB>(lane, ch) * 16);
-            const uint32_t be0 = prmt(vr[0], vr[1], 0x6420u), bo0 = prmt(vr[0], vr[1], 0x7531u);
-            const uint32_t be1 = prmt(vr[2], vr[3], 0x6420u), bo1 = prmt(vr[2], vr[3], 0x7531u);
+            for (int ch = 0; ch < HD / 16; ++ch) {
+                uint32_t vr[4];           // vr[o]: tokens 8o+2t, 8o+2t+1 x dims 16ch+2g, 16ch+2g+1
+                ldmatrix_x4_trans(vr, vst + lane * C::ROWB + swz_chunk<C::ROWB>(lane, ch) * 16);
+                const uint32_t be0 = prmt(vr[0], vr[1], 0x6420u), bo0 = prmt(vr[0], vr[1], 0x7531u);
+                const uint32_t be1 = prmt(vr[2], vr[3], 0x6420u), bo1 = prmt(vr[2], vr[3], 0x7531u);
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                int d4[4];
-                mma_u8s8_zero(d4, pa[mt][0], pa[mt][1], pa[mt][2], pa[mt][3], be0, be1);
-                acc[mt][2 * ch][0] = fmaf((float)(d4[0] * 256 + d4[2]), F[mt], acc[mt][2 * ch][0]);
-                acc[mt][2 * ch][1] = fmaf((float)(d4[1] * 256 + d4[3]), F[mt], acc[mt][2 * ch][1]);
-                mma_u8s8_zero(d4, pa[mt][0], pa[mt][1], pa[mt][2], pa[mt][3], bo0, bo1);
-                acc[mt][2 * ch + 1][0] = fmaf((float)(d4[0] * 256 + d4[2]), F[mt], acc[mt][2 * ch + 1][0]);
-                acc[mt][2 * ch + 1][1] = fmaf((float)(d4[1] * 256 + d4[3]), F[mt], acc[mt][2 * ch + 1][1]);
+                for (int mt = 0; mt < MT; ++mt) {
+                    int d4[4];
+                    mma_u8s8_zero(d4, pa[mt][0][0], pa[mt][0][1], pa[mt][0][2], pa[mt][0][3], be0, be1);
+                    acc[mt][2 * ch][0] = fmaf((float)(d4[0] * 256 + d4[2]), F[mt], acc[mt][2 * ch][0]);
+                    acc[mt][2 * ch][1] = fmaf((float)(d4[1] * 256 + d4[3]), F[mt], acc[mt][2 * ch][1]);
+                    mma_u8s8_zero(d4, pa[mt][0][0], pa[mt][0][1], pa[mt][0][2], pa[mt][0][3], bo0, bo1);
+                    acc[mt][2 * ch + 1][0] = fmaf((float)(d4[0] * 256 + d4[2]), F[mt], acc[mt][2 * ch + 1][0]);
+                    acc[mt][2 * ch + 1][1] = fmaf((float)(d4[1] * 256 + d4[3]), F[mt], acc[mt][2 * ch + 1][1]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int ch = 0; ch < HD / 32; ++ch) {          // packed chunk ch = block ch = dims 32ch..32ch+31
+                uint32_t vr[4];           // vr[o]: tokens 8o+2t, 8o+2t+1 x packed bytes 16ch+2g, 16ch+2g+1
+                ldmatrix_x4_trans(vr, vst + lane * C::ROWB + swz_chunk<C::ROWB>(lane, ch) * 16);
+                uint32_t pb[2][2];        // [byte 2g | 2g+1][tokens 0-15 | 16-31]: one packed byte of four tokens
+                pb[0][0] = prmt(vr[0], vr[1], 0x6420u); pb[1][0] = prmt(vr[0], vr[1], 0x7531u);
+                pb[0][1] = prmt(vr[2], vr[3], 0x6420u); pb[1][1] = prmt(vr[2], vr[3], 0x7531u);
+                constexpr int VBI = (FMT == KV_I4B32) ? 1 : 0;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {               // element 4g+e of the block: byte e/2, nibble e%2
+                    const uint32_t b0 = lop3_and_xor((e & 1) ? pb[e >> 1][0] >> 4 : pb[e >> 1][0], 0x0f0f0f0fu, 0x08080808u);
+                    const uint32_t b1 = lop3_and_xor((e & 1) ? pb[e >> 1][1] >> 4 : pb[e >> 1][1], 0x0f0f0f0fu, 0x08080808u);
+                    const int nt = 4 * ch + e;
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const int vb = VBI * ch;
+                        int d4[4];
+                        mma_u8u8_zero(d4, pa[mt][vb][0], pa[mt][vb][1], pa[mt][vb][2], pa[mt][vb][3], b0, b1);
+                        acc[mt][nt][0] = fmaf((float)(d4[0] * 256 + d4[2] - ubias[mt][vb]), F[mt], acc[mt][nt][0]);
+                        acc[mt][nt][1] = fmaf((float)(d4[1] * 256 + d4[3] - ubias[mt][vb]), F[mt], acc[mt][nt][1]);
+                    }
+                }
             }
         }
         __syncwarp();
@@ -482,10 +625,17 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         float *r0 = mbuf + ((size_t)warp * C::NSLOT + mt * 8 + g) * (HD + 2);
 #pragma unroll
         for (int nt = 0; nt < C::NT; ++nt) {
-            // n tile nt holds d = 16*(nt/2) + 2*col + (nt&1); this thread has cols 2t, 2t+1
-            const int d0 = 16 * (nt >> 1) + 4 * t + (nt & 1);
-            r0[d0] = acc[mt][nt][0];
-            r0[d0 + 2] = acc[mt][nt][1];
+            // this thread has MMA columns 2t, 2t+1 of n tile nt.  int8: column c of tile nt is
+            // dim 16*(nt/2) + 2c + (nt&1); int4: dim 32*(nt/4) + 4c + (nt&3).
+            if constexpr (FMT == KV_I8) {
+                const int d0 = 16 * (nt >> 1) + 4 * t + (nt & 1);
+                r0[d0] = acc[mt][nt][0];
+                r0[d0 + 2] = acc[mt][nt][1];
+            } else {
+                const int d0 = 32 * (nt >> 2) + 8 * t + (nt & 3);
+                r0[d0] = acc[mt][nt][0];
+                r0[d0 + 4] = acc[mt][nt][1];
+            }
         }
         if (t == 0) { r0[HD] = M[mt]; r0[HD + 1] = l[mt]; }
     }
