@@ -229,6 +229,20 @@ int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args);
 /* Run it. */
 int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *args);
 
+/* nomos_attn_fused for callers that cannot pass a workspace.  No counterpart in the
+ * reference (its engine allocates every scratch buffer itself at start-up).  The Nomos
+ * engine commits its whole device-memory budget when it starts and treats a failed
+ * cudaMalloc as fatal, and a decode loop must not call the allocator (it synchronises the
+ * device); such callers have no spare buffer to hand in.  Here the split scratch is a
+ * fixed 4 MiB array inside the library image (held by every GPU that loads the library
+ * until exit); the call allocates nothing.  args->workspace / ws_bytes / new_k / new_v
+ * are not used (new_k, new_v must be 0).  Returns NOMOS_ATTN_ECAPACITY when the call would
+ * need more than 4 MiB of split scratch.  All calls on a device share the array: keep them
+ * ordered (one stream); calls that overlap on the GPU corrupt each other.  The first call
+ * on each device resolves the array's address and should be made before any stream
+ * capture begins. */
+int32_t nomos_attn_fused_static_ws(void *stream, const nomos_attn_args_t *args);
+
 /* Merge G partial triples (as written through partial_out, gathered from G
  * sequence shards) into a normalised output.  partials: fp32 [G][rows][l_hd+2];
  * out: [rows][l_hd] of out_type.  No counterpart in the reference (which is

@@ -405,3 +405,70 @@ NOMOS_EXPORT int32_t nomos_attn_merge_partials(void *stream, uint64_t partials, 
     REQUIRE(out_type == ET_F32 || out_type == ET_BF16, "nomos_attn_merge_partials: out_type %d", out_type);
     return launch_merge_partials(as_stream(stream), static_cast<const float *>(ptr(partials)), G, rows, l_hd, ptr(out), out_type);
 }
+
+// ------------------------------------------------- fused call without a caller workspace
+//
+// Some callers of this library cannot give it a workspace: the Nomos engine hands its whole
+// device-memory budget out once at start-up (the KV cache is sized to fill the card, and a
+// failed cudaMalloc is fatal to the serving daemon), and a decode loop must not call the
+// allocator at all because cudaMalloc/cudaFree synchronise the device.  For them the split
+// scratch below is part of the library image: a fixed array in device memory, so this entry
+// point never calls cudaMalloc, cudaFree or any allocating routine.
+//
+// Cost and limits, all deliberate:
+//   * every GPU that loads the library holds NOMOS_STATIC_WS_BYTES (4 MiB) until the process exits;
+//   * a call whose split scratch would be larger is refused with NOMOS_ECAPACITY;
+//   * all calls on one device share the array, which keeps the previous call's contents.  Nothing in
+//     it has to start at zero: the arrival counters carry a per-launch tag and the partial results are
+//     fully rewritten before they are read, so no clearing pass is needed.  Two calls that overlap
+//     on the GPU (different streams) would overwrite each other's partial results: callers must
+//     keep calls to this entry point ordered on a device, e.g. by using one stream.
+//   * the first call on each device looks the array's device address up (cudaGetSymbolAddress);
+//     make that first call before starting any stream capture.
+#define NOMOS_STATIC_WS_BYTES (4 << 20)
+static __device__ __align__(256) unsigned char g_static_ws[NOMOS_STATIC_WS_BYTES];
+
+// In host code `g_static_ws` is only a handle for the runtime, not a device address; the address
+// the kernels need is resolved here, once per device, with that device current.
+static int static_ws_address(void **out) {
+    static void *cached[64] = {nullptr};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        set_error("nomos_attn_fused_static_ws: cannot identify the current device (%s)", cudaGetErrorString(e));
+        return NOMOS_ECUDA;
+    }
+    if (cached[dev] == nullptr) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_ws);
+        if (e != cudaSuccess || p == nullptr) {
+            set_error("nomos_attn_fused_static_ws: cudaGetSymbolAddress failed on device %d (%s)", dev, cudaGetErrorString(e));
+            return NOMOS_ECUDA;
+        }
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return NOMOS_OK;
+}
+
+NOMOS_EXPORT int32_t nomos_attn_fused_static_ws(void *stream, const nomos_attn_args_t *args) {
+    AttnArgs a;
+    int rc = unpack_args(args, a, "nomos_attn_fused_static_ws");
+    if (rc) return rc;
+    if (a.nh <= 0 || a.klen <= 0) return NOMOS_OK;
+    REQUIRE(a.new_k == nullptr && a.new_v == nullptr, "nomos_attn_fused_static_ws: fused append is not offered here; append first");
+    if ((rc = check_attn_geometry("nomos_attn_fused_static_ws", a.nh, a.nkv, a.l_hd, a.cache_hd, a.kvg))) return rc;
+    REQUIRE(a.batch > 0 && a.S > 0, "nomos_attn_fused_static_ws: bad batch/S");
+    const long need = attn_workspace_bytes(a);
+    if (need < 0) return (int32_t)need;
+    if (need > NOMOS_STATIC_WS_BYTES) {
+        set_error("nomos_attn_fused_static_ws: this call needs %ld bytes of split scratch, the built-in array holds %d; "
+                  "use nomos_attn_fused with a caller workspace", need, NOMOS_STATIC_WS_BYTES);
+        return NOMOS_ECAPACITY;
+    }
+    void *ws = nullptr;
+    if ((rc = static_ws_address(&ws))) return rc;
+    a.workspace = ws;                       // the resolved device address, never the host-side symbol
+    a.ws_bytes = NOMOS_STATIC_WS_BYTES;
+    return run_fused(as_stream(stream), a, "nomos_attn_fused_static_ws");
+}

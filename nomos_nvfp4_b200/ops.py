@@ -227,5 +227,15 @@ def attn_fused(stream, args: AttnArgs) -> None:
     _check(_lib.lib().nomos_attn_fused(_stream(stream), C.byref(args)))
 
 
+def attn_fused_static_ws(stream, args: AttnArgs) -> None:
+    """``attn_fused`` for callers that cannot provide a workspace (an engine whose memory budget
+    is fully committed at start-up, a decode loop that must never call the allocator): the split
+    scratch is a fixed 4 MiB array inside the library, nothing is allocated, ``args.workspace`` is
+    ignored.  Raises with status -3 if the call would need more scratch than that.  Calls on one
+    device share the array, so issue them in order (one stream); make the first call on a device
+    before any stream capture."""
+    _check(_lib.lib().nomos_attn_fused_static_ws(_stream(stream), C.byref(args)))
+
+
 def attn_merge_partials(stream, partials, G, rows, l_hd, out, out_type=F32) -> None:
     _check(_lib.lib().nomos_attn_merge_partials(_stream(stream), _addr(partials), G, rows, l_hd, _addr(out), out_type))
