@@ -130,7 +130,8 @@ def decode_args(ops, q, cache, out, nh, nkv, hd, t, seqs, **kw):
     k, v, ks, vs = cache
     return ops.make_args(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=out, kv_fmt=ops.KV_I8,
                          q_type=ops.BF16, out_type=ops.BF16, batch=seqs, nh=nh, nkv=nkv, kvg=nh // nkv, l_hd=hd,
-                         cache_hd=hd, cache_cap=t, klen=t, softmax_scale=SOFTMAX_SCALE, **kw)
+                         cache_hd=hd, cache_cap=t, klen=t, softmax_scale=SOFTMAX_SCALE,
+                         flags=ops.SETTLED_CACHE, **kw)   # decode loop: only the newest row is written per step
 
 
 def run_ours(args) -> dict:

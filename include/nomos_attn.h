@@ -222,7 +222,16 @@ typedef struct nomos_attn_args {
     int64_t q_batch_stride, out_batch_stride;      /* elements; 0 = dense                 */
     int64_t kv_batch_stride, scale_batch_stride;   /* bytes;    0 = dense                 */
     int64_t force_splits;       /* 0 = library chooses the sequence split                 */
+    int64_t flags;              /* NOMOS_ATTN_* bits below                                */
 } nomos_attn_args_t;
+
+/* flags bit: the caller guarantees that every cache row (and scale) OLDER than the S query
+ * rows was written by work that completed before the kernel immediately preceding this call
+ * in the stream was launched -- true for a decode/verify loop, where only the append of the
+ * current rows touches the cache.  The library may then start streaming those older rows
+ * while that preceding kernel is still finishing (the query, the S newest rows and every
+ * output are still ordered after it). */
+#define NOMOS_ATTN_SETTLED_CACHE 1
 
 /* Bytes of workspace the call needs (>= 0), or a negative status. */
 int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args);

@@ -32,7 +32,7 @@ class AttnArgs(C.Structure):
         ("win_start", i64), ("klen", i64), ("window", i64),
         ("softmax_scale", C.c_double),
         ("q_batch_stride", i64), ("out_batch_stride", i64), ("kv_batch_stride", i64), ("scale_batch_stride", i64),
-        ("force_splits", i64),
+        ("force_splits", i64), ("flags", i64),
     ]
 
 

@@ -360,6 +360,7 @@ static int unpack_args(const nomos_attn_args_t *u, AttnArgs &a, const char *who)
     a.kv_batch_stride = u->kv_batch_stride ? u->kv_batch_stride : rows * row_bytes;
     a.scale_batch_stride = u->scale_batch_stride ? u->scale_batch_stride : scale_bytes;
     a.force_splits = (int)u->force_splits;
+    a.settled_cache = (u->flags & NOMOS_ATTN_SETTLED_CACHE) ? 1 : 0;
     return NOMOS_OK;
 }
 

@@ -154,6 +154,7 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     p.epoch = next_epoch();
     p.splits = pl.splits;
     p.partial_export = a.partial_out;
+    p.early_rows = a.settled_cache ? std::max(0, a.klen - std::max(a.S, a.n_new)) : 0;
     if (pl.splits > MERGE_MAX_G) { set_error("too many splits (%d)", pl.splits); return NOMOS_EUNSUPPORTED; }
     p.q_type = a.q_type; p.out_type = a.out_type;
     p.S = a.S; p.nh = a.nh; p.nkv = a.nkv; p.kvg = a.kvg; p.cache_hd = a.cache_hd; p.cache_cap = a.cache_cap;

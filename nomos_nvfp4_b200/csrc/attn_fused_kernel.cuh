@@ -70,6 +70,7 @@ struct KParams {
     unsigned long long epoch;       // unique per launch, so stale or uninitialised words read as "0 arrivals"
     int splits;
     float *partial_export;          // optional exported (o, m, l) per row, m in natural-log units
+    int early_rows;                 // window rows [0, early_rows) may be read before griddepcontrol.wait
     long q_batch_stride, kv_batch_stride, scale_batch_stride, out_batch_stride;
 };
 
@@ -228,6 +229,10 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
     // appended cache rows, the shared split workspace) before the first global access.  Then let
     // the split-merge grid be set up right away; it blocks the same way until this grid is done.
     NOMOS_MARK(0);
+    // Cache rows the caller declared settled (not written by the stream predecessor) are requested
+    // before that wait, so the pipeline fill overlaps the predecessor's tail.
+    int early_n = 0;
+    while (early_n < NSTAGE - 1 && early_n < my_count && (my_first + early_n * NWARP + 1) * TILE <= p.early_rows) issue(early_n++);
     pdl_wait();
     pdl_launch_dependents();
     NOMOS_MARK(1);
@@ -248,8 +253,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         for (int i = 0; i < HD / 32; ++i)
             qx[qi][i] = valid ? load_q(p.q, p.q_type, b * p.q_batch_stride + ((long)r * p.nh + kvh * p.kvg + j) * HD + lane + 32 * i) : 0.0f;
     }
-#pragma unroll
-    for (int s = 0; s < NSTAGE - 1; ++s) issue(s);
+    for (int s = early_n; s < NSTAGE - 1; ++s) issue(s);
 
     // Each row becomes 15-bit fixed point: q ~= sq * (128*hi + lo), hi/lo int8.
 #pragma unroll

@@ -19,6 +19,7 @@ from ._lib import AttnArgs
 
 KV_I8, KV_I4, KV_I4B32 = 0, 1, 2
 F32, BF16 = 0, 1
+SETTLED_CACHE = 1            # nomos_attn_args_t.flags bit, see include/nomos_attn.h
 
 
 class NomosError(RuntimeError):
