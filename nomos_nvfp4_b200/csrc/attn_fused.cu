@@ -83,7 +83,11 @@ static int kernel_occupancy() {
     return occ[dev];
 }
 
-static int pick_mt(int slots, int hd = 128) { return (slots <= 8 || hd > 128) ? 1 : 3; }
+// Query-row tiles per CTA.  Up to 24 rows (e.g. 9 verify tokens x 2 group heads) run as up to three
+// 8-row groups of the 12-warp kernel: the groups stream the same cache bytes concurrently (one DRAM
+// read, served to the other groups from L2), which measured faster than one 24-row CTA with 8 warps
+// and 255 registers.  Beyond that the 24-row kernel keeps the number of L2 re-reads down.
+static int pick_mt(int slots, int hd = 128) { return (slots <= 24 || hd > 128) ? 1 : 3; }
 
 static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp) {
     Plan pl;

@@ -30,6 +30,7 @@ constexpr float LN2 = 0.6931471805599453f;
 constexpr float M_INIT = -1.0e30f;       // finite "minus infinity" for the running max
 constexpr int Q_FIX_MAX = 16256;         // 127 * 128: two int8 limbs, hi in [-127,127], lo in [-64,63]
 constexpr float P_FIX = 65535.0f;        // probabilities reach the tensor core as 16-bit fixed point (two u8 limbs)
+constexpr float LAZY_MAX = 8.0f;         // base-2 slack before the running softmax reference is moved
 constexpr float RND_MAGIC = 8388608.0f;  // 2^23: adding it leaves round-to-nearest(x) in the low mantissa bits
 
 template <int FMT, int HD, int MT>
@@ -286,8 +287,11 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
                 for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
                 qblk[i] = bs;
             }
-            q_limbs[sl * HD + pos] = (int8_t)hi;
-            q_limbs[(C::NSLOT + sl) * HD + pos] = (int8_t)lo;
+            // rows are stored with their 16-byte chunks XOR-swizzled by the slot index, so that the
+            // ldmatrix that builds an A fragment (8 slots x one chunk) is free of bank conflicts
+            const int spos = ((((pos >> 4) ^ (sl & 7)) << 4) | (pos & 15));
+            q_limbs[sl * HD + spos] = (int8_t)hi;
+            q_limbs[(C::NSLOT + sl) * HD + spos] = (int8_t)lo;
         }
         if constexpr (FMT != KV_I8) {
             if (lane == 0) {
@@ -319,13 +323,14 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
     // one M tile, re-read from shared memory otherwise.
     constexpr bool Q_IN_REGS = (MT == 1) && (HD <= 256);
     uint32_t qa[Q_IN_REGS ? HD / 32 : 1][4];
+    // A fragment of k step ks for M tile mt in one ldmatrix.x4: matrices = (high limb, chunk 2ks),
+    // (low limb, chunk 2ks), (high, 2ks+1), (low, 2ks+1) of slots 8mt..8mt+7  ->  a0, a1, a2, a3.
+    const uint32_t q_u32 = smem_u32(q_limbs);
     auto load_qa = [&](uint32_t(&a)[4], int mt, int ks) {
-        const int8_t *hi_row = q_limbs + (mt * 8 + g) * HD + ks * 32 + 4 * t;
-        const int8_t *lo_row = hi_row + C::NSLOT * HD;
-        a[0] = *reinterpret_cast<const uint32_t *>(hi_row);
-        a[1] = *reinterpret_cast<const uint32_t *>(lo_row);
-        a[2] = *reinterpret_cast<const uint32_t *>(hi_row + 16);
-        a[3] = *reinterpret_cast<const uint32_t *>(lo_row + 16);
+        const int slot = mt * 8 + (lane & 7);
+        const int limb = (lane >> 3) & 1;
+        const int ch = 2 * ks + (lane >> 4);
+        ldmatrix_x4(a, q_u32 + (limb * C::NSLOT + slot) * HD + ((ch ^ (slot & 7)) << 4));
     };
     if constexpr (Q_IN_REGS) {
 #pragma unroll
@@ -377,33 +382,39 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         // carry the high / low limb of the slot's query, the columns 2t, 2t+1 the two tokens.
         float s2[MT][4][2];
         if constexpr (FMT == KV_I8) {
+            int c[MT][4][4];
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
-                int c[MT][4];
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int n = 0; n < 4; ++n)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) c[mt][n][i] = 0;
+#pragma unroll
+            for (int half = 0; half < HD / 64; ++half) {
+                uint32_t kb[4][4];        // K bytes of the four 8-token groups, chunks 4half..4half+3
+#pragma unroll
+                for (int n = 0; n < 4; ++n) {
+                    const int row = 8 * n + (lane & 7);
+                    const int ch = 4 * half + (lane >> 3);
+                    ldmatrix_x4(kb[n], st + row * C::ROWB + swz_chunk<C::ROWB>(row, ch) * 16);
+                }
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) c[mt][i] = 0;
-#pragma unroll
-                for (int half = 0; half < HD / 64; ++half) {
-                    uint32_t kb[4];
-                    const int row = 8 * n + (lane & 7);
-                    const int ch = 4 * half + (lane >> 3);
-                    ldmatrix_x4(kb, st + row * C::ROWB + swz_chunk<C::ROWB>(row, ch) * 16);
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
+                    for (int k2 = 0; k2 < 2; ++k2) {
                         uint32_t a[4];
-                        get_qa(a, mt, 2 * half);
-                        mma_s8s8(c[mt], a, kb[0], kb[1]);
-                        get_qa(a, mt, 2 * half + 1);
-                        mma_s8s8(c[mt], a, kb[2], kb[3]);
+                        get_qa(a, mt, 2 * half + k2);
+#pragma unroll
+                        for (int n = 0; n < 4; ++n) mma_s8s8(c[mt][n], a, kb[n][2 * k2], kb[n][2 * k2 + 1]);
                     }
-                }
+            }
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
                 const float2 kk = *reinterpret_cast<const float2 *>(ksm + (8 * n + 2 * t) * 4);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    s2[mt][n][0] = (float)(c[mt][0] * 128 + c[mt][2]) * (qscale[mt] * kk.x);
-                    s2[mt][n][1] = (float)(c[mt][1] * 128 + c[mt][3]) * (qscale[mt] * kk.y);
+                    s2[mt][n][0] = (float)(c[mt][n][0] * 128 + c[mt][n][2]) * (qscale[mt] * kk.x);
+                    s2[mt][n][1] = (float)(c[mt][n][1] * 128 + c[mt][n][3]) * (qscale[mt] * kk.y);
                 }
             }
         } else {
@@ -501,7 +512,6 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         uint32_t pa[MT][NVB][4];          // A fragments of the PV MMA: a0/a2 = high limbs, a1/a3 = low limbs
         int ubias[MT][NVB];               // int4 only: 8 * sum of the u16 weights (removes the +8 nibble bias)
         float F[MT];
-        bool rescale = false;
         float alpha[MT];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
@@ -510,12 +520,19 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
             for (int n = 0; n < 4; ++n) mx = fmaxf(mx, fmaxf(s2[mt][n][0], s2[mt][n][1]));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(M[mt], mx);
+            // The running reference only moves when the tile maximum exceeds it by more than 2^8:
+            // weights are normalised per tile anyway, so a stale reference costs no precision (the
+            // tile weight is at most 2^8 larger) and the fp32 sums are rescaled a handful of times
+            // per call instead of once per tile.
+            const float m_new = mx > M[mt] + LAZY_MAX ? mx : M[mt];
             const bool empty = mx == -CUDART_INF_F;                 // every token of the tile is masked for this slot
             const float mx_safe = empty ? 0.0f : mx;
             const float tile_w = empty ? 0.0f : ex2f(mx - m_new);
             alpha[mt] = ex2f(M[mt] - m_new);
-            rescale |= (m_new != M[mt]);
+            if (__any_sync(0xffffffffu, m_new != M[mt])) {
+#pragma unroll
+                for (int nt = 0; nt < C::NT; ++nt) { acc[mt][nt][0] *= alpha[mt]; acc[mt][nt][1] *= alpha[mt]; }
+            }
             M[mt] = m_new;
             float pe[4][2];
             float lsum = 0.0f, wmax = 0.0f;
@@ -557,13 +574,6 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
                 }
             }
         }
-        if (__any_sync(0xffffffffu, rescale)) {
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                for (int nt = 0; nt < C::NT; ++nt) { acc[mt][nt][0] *= alpha[mt]; acc[mt][nt][1] *= alpha[mt]; }
-        }
-
         // --------------------------------------------------------------- PV
         // One MMA spans the whole 32-token tile: A = weight limbs (rows g / g+8 = high / low),
         // B = V bytes transposed by ldmatrix.trans + byte permutes; the int32 result is exact.

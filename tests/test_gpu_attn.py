@@ -306,3 +306,42 @@ def test_bad_arguments_return_status_not_fault():
     ops.attention_gpu_int8_dev(None, t, t, t, t, t, t, t, 0, 4, 128, 128, 64, 16, 2)        # nh <= 0: no-op, ok
     ops.attention_gpu_int8_dev(None, t, t, t, t, t, t, t, 8, 4, 128, 128, 64, 0, 2)         # seq_len <= 0: no-op
     torch.cuda.synchronize()
+
+
+def test_settled_cache_flag_gives_identical_output(oracle):
+    """The flag only moves the first cache reads ahead of the stream-order wait; results are the same."""
+    rng = np.random.default_rng(61)
+    nh, nkv, hd, T = 32, 16, 128, 5000
+    c = build_cache("i8", rng, T, nkv, hd)
+    q = bf16_normal(rng, (1, nh, hd))
+    keep = [dev(q), dev(c.k), dev(c.v), dev(c.ks), dev(c.vs)]
+    outs = []
+    for flags in (0, ops.SETTLED_CACHE):
+        out = torch.full((1, nh, hd), SENTINEL, dtype=torch.float32, device=DEV)
+        a = ops.make_args(q=keep[0], k_cache=keep[1], v_cache=keep[2], k_scales=keep[3], v_scales=keep[4], out=out,
+                          kv_fmt=ops.KV_I8, nh=nh, nkv=nkv, kvg=2, l_hd=hd, cache_hd=hd, cache_cap=T, klen=T,
+                          softmax_scale=0.1, flags=flags)
+        ws = torch.empty(max(ops.attn_workspace_bytes(a), 16), dtype=torch.uint8, device=DEV)
+        a.workspace, a.ws_bytes = ws.data_ptr(), ws.numel()
+        for _ in range(3):                      # back-to-back launches exercise the programmatic dependency chain
+            ops.attn_fused(None, a)
+        torch.cuda.synchronize()
+        outs.append(host(out))
+    assert np.array_equal(outs[0], outs[1])
+    want = exact(oracle, c, q, klen=T, scale=0.1)
+    assert within(outs[1], want, TOL)[0]
+
+
+@pytest.mark.parametrize("S,kvg", [(17, 2), (9, 8), (4, 8)])
+def test_many_verify_rows(oracle, S, kvg):
+    """More than 24 query rows per KV head (the 24-row CTA path) and wide GQA groups."""
+    rng = np.random.default_rng(S * 10 + kvg)
+    nkv, hd, T = 2, 128, 900
+    nh = nkv * kvg
+    c = build_cache("i8", rng, T, nkv, hd)
+    q = bf16_normal(rng, (S, nh, hd)) * np.float32(0.5)
+    want = exact(oracle, c, q, S=S, klen=T, scale=0.2)
+    got, _ = fused(c, q, S=S, klen=T, scale=0.2)
+    for r in range(S):
+        ok, rel = within(got[r], want[r], TOL)
+        assert ok, f"row {r}: {rel:.2e} x RMS"
