@@ -218,24 +218,29 @@ def run_ours(args) -> dict:
         return {"metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": N, "steps": args.steps,
                 "ms_per_step": round(ms_per_step, 6), "quick": True} if rank == 0 else {}
 
-    # end to end through the C ABI with HOST buffers: per step, H2D of the bf16 query and of the new token's
-    # fp32 K/V rows from pinned memory, quantize-on-write + attention, D2H of the bf16 output.
-    T_e = T
-    host_q = [torch.randn((seqs, 1, nh_l, HD)).to(torch.bfloat16).pin_memory() for _ in range(NLAYERS)]
-    host_k = torch.randn((seqs, nkv_l, HD)).pin_memory(); host_v = torch.randn((seqs, nkv_l, HD)).pin_memory()
+    # end to end through the C ABI with HOST buffers: per step one H2D copy (pinned) of the bf16 query and
+    # the new token's fp32 K/V rows, ONE library call (quantize-on-write fused into the attention kernel),
+    # one D2H copy of the bf16 output, host synchronisation.
+    q_bytes, kv_bytes = seqs * nh_l * HD * 2, seqs * nkv_l * HD * 4
+    stage_h = torch.empty(q_bytes + 2 * kv_bytes, dtype=torch.uint8).pin_memory()
+    stage_h[:q_bytes].view(torch.bfloat16).copy_(torch.randn(seqs * nh_l * HD).to(torch.bfloat16))
+    stage_h[q_bytes:].view(torch.float32).copy_(torch.randn(2 * seqs * nkv_l * HD))
+    stage_d = torch.empty_like(stage_h, device=dev)
     host_out = torch.empty((seqs, 1, nh_l, HD), dtype=torch.bfloat16).pin_memory()
-    d_newk = torch.empty((seqs, nkv_l, HD), device=dev); d_newv = torch.empty_like(d_newk)
-    h2d = host_q[0].numel() * 2 + host_k.numel() * 4 * 2
-    d2h = host_out.numel() * 2
+    e2e_args = []
+    for i in range(NLAYERS):
+        k, v, ks, vs = caches[i]
+        e2e_args.append(ops.make_args(
+            q=stage_d.data_ptr(), k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=outs[i], kv_fmt=ops.KV_I8,
+            q_type=ops.BF16, out_type=ops.BF16, batch=seqs, nh=nh_l, nkv=nkv_l, kvg=nh_l // nkv_l, l_hd=HD, cache_hd=HD,
+            cache_cap=T, klen=T, softmax_scale=SOFTMAX_SCALE, flags=ops.SETTLED_CACHE, workspace=ws, ws_bytes=ws_bytes,
+            new_k=stage_d.data_ptr() + q_bytes, new_v=stage_d.data_ptr() + q_bytes + kv_bytes, n_new=1, new_base_pos=T - 1))
+    h2d, d2h = stage_h.numel(), host_out.numel() * 2
 
     def e2e_step(i):
         j = i % NLAYERS
-        qs[j].copy_(host_q[j], non_blocking=True)
-        d_newk.copy_(host_k, non_blocking=True); d_newv.copy_(host_v, non_blocking=True)
-        k, v, ks, vs = caches[j]
-        for s in range(seqs):       # quantize-on-write of the new token at position T-1 (per sequence)
-            ops.gpu_append_quant_kv_i8(stream, d_newk[s], d_newv[s], k[s], v[s], ks[s], vs[s], 1, nkv_l, HD, nkv_l * HD, T_e, HD, T_e - 1)
-        ops.attn_fused(stream, layer_args[j])
+        stage_d.copy_(stage_h, non_blocking=True)
+        ops.attn_fused(stream, e2e_args[j])
         host_out.copy_(outs[j], non_blocking=True)
         torch.cuda.synchronize()
 

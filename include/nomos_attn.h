@@ -209,7 +209,7 @@ typedef struct nomos_attn_args {
                                    then m (natural log), then l: for cross-GPU merging     */
     uint64_t workspace;         /* split-K scratch                                        */
     int64_t ws_bytes;           /* >= nomos_attn_workspace_bytes(args)                     */
-    uint64_t new_k, new_v;      /* 0, or fp32 [n_new][nkv][l_hd] rows to quantize+append   */
+    uint64_t new_k, new_v;      /* 0, or fp32 [batch][n_new][nkv][l_hd] rows to quantize+append */
     int64_t n_new, new_stride;  /* rows, and elements between consecutive rows            */
     int64_t new_base_pos;       /* absolute position of the first new row                 */
     int64_t kv_fmt, q_type, out_type;

@@ -380,21 +380,11 @@ NOMOS_EXPORT int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *arg
     if (a.nh <= 0 || a.klen <= 0) return NOMOS_OK;
     if (a.new_k || a.new_v) {
         REQUIRE(a.new_k && a.new_v && a.n_new > 0, "nomos_attn_fused: new_k/new_v/n_new inconsistent");
-        REQUIRE(a.batch == 1, "nomos_attn_fused: fused append supports batch 1");
         REQUIRE(a.new_base_pos + a.n_new == a.win_start + a.klen, "nomos_attn_fused: the new rows must be the last keys of the window");
-        // Quantize-on-write runs first on the same stream; the attention launch that
-        // follows reads the rows it stored.
-        const int stride = a.new_stride ? a.new_stride : a.nkv * a.l_hd;
-        if (a.kv_fmt == KV_I8)
-            rc = launch_append_i8(as_stream(stream), a.new_k, a.new_v, const_cast<void *>(a.k_cache), const_cast<void *>(a.v_cache),
-                                  const_cast<void *>(a.k_scales), const_cast<void *>(a.v_scales), a.n_new, a.nkv, a.l_hd, stride,
-                                  a.cache_cap, a.cache_hd, a.new_base_pos);
-        else
-            rc = launch_append_i4(as_stream(stream), a.new_k, a.new_v, const_cast<void *>(a.k_cache), const_cast<void *>(a.v_cache),
-                                  const_cast<void *>(a.k_scales), const_cast<void *>(a.v_scales), nullptr, nullptr, nullptr, nullptr,
-                                  a.n_new, a.nkv, a.l_hd, stride, a.cache_cap, a.cache_hd, a.new_base_pos, 0,
-                                  a.kv_fmt == KV_I4B32 ? (a.l_hd + 31) / 32 : 1);
-        if (rc) return rc;
+        // Quantize-on-write happens inside the attention kernel: the warp that owns the newest tile
+        // quantises the rows, uses them, and stores them into the ring.
+        if (a.new_stride == 0) a.new_stride = a.nkv * a.l_hd;
+        REQUIRE(a.n_new <= a.klen && a.n_new <= a.cache_cap, "nomos_attn_fused: n_new %d exceeds the window", a.n_new);
     }
     return run_fused(as_stream(stream), a, "nomos_attn_fused");
 }

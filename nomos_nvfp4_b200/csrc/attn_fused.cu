@@ -121,7 +121,9 @@ static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp) {
             const int per_warp = (tps + nwarp - 1) / nwarp;
             const long ctas = (long)units * n;
             const long waves = (ctas + slots_gpu - 1) / slots_gpu;
-            const double cost = (double)waves * (per_warp + 1.5) + 0.02 * n;
+            // in units of one warp-tile (~1.7 us on B200): streaming rounds plus ~1.5 of CTA start-up per wave, and what a split costs at the
+            // end (partial store, fence, arrival, merge by the last CTA) when there is more than one
+            const double cost = (double)waves * (per_warp + 1.5) + (n > 1 ? 2.0 + 0.02 * n : 0.0);
             if (cost < best_cost) { best_cost = cost; best = n; }
         }
     }
@@ -159,6 +161,10 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     p.splits = pl.splits;
     p.partial_export = a.partial_out;
     p.early_rows = a.settled_cache ? std::max(0, a.klen - std::max(a.S, a.n_new)) : 0;
+    p.new_k = a.new_k; p.new_v = a.new_v;
+    p.n_new = a.new_k ? a.n_new : 0; p.new_stride = a.new_stride; p.new_base_pos = a.new_base_pos;
+    p.k_cache_w = const_cast<uint8_t *>(p.k_cache); p.v_cache_w = const_cast<uint8_t *>(p.v_cache);
+    p.k_scales_w = const_cast<uint8_t *>(p.k_scales); p.v_scales_w = const_cast<uint8_t *>(p.v_scales);
     if (pl.splits > MERGE_MAX_G) { set_error("too many splits (%d)", pl.splits); return NOMOS_EUNSUPPORTED; }
     p.q_type = a.q_type; p.out_type = a.out_type;
     p.S = a.S; p.nh = a.nh; p.nkv = a.nkv; p.kvg = a.kvg; p.cache_hd = a.cache_hd; p.cache_cap = a.cache_cap;

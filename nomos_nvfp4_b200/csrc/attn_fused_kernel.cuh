@@ -5,6 +5,7 @@
 #include <math_constants.h>
 
 #include "common.cuh"
+#include "kv_rows.cuh"
 #include "launch.h"
 
 namespace nomos {
@@ -50,9 +51,10 @@ struct Cfg {
     static constexpr int NW_REG = (MT == 1 && HD <= 256) ? NOMOS_NWARP : NOMOS_NWARP_MULTI;
     static constexpr int NW_MEM = (200 * 1024) / (NSTAGE * STAGE_BYTES);
     static constexpr int NW = NW_REG < NW_MEM ? NW_REG : (NW_MEM < 1 ? 1 : NW_MEM);
+    static constexpr int APPEND_BYTES = NW * (ROWB + 64);                     // per warp: one quantised row + its scales
     static constexpr int PIPE_BYTES = NW * NSTAGE * STAGE_BYTES;
     static constexpr int MERGE_BYTES = NW * NSLOT * (HD + 2) * 4;
-    static constexpr int SMEM_BYTES = Q_BYTES + SLOT_BYTES + (PIPE_BYTES > MERGE_BYTES ? PIPE_BYTES : MERGE_BYTES);
+    static constexpr int SMEM_BYTES = Q_BYTES + SLOT_BYTES + APPEND_BYTES + (PIPE_BYTES > MERGE_BYTES ? PIPE_BYTES : MERGE_BYTES);
 };
 
 struct KParams {
@@ -72,6 +74,10 @@ struct KParams {
     int splits;
     float *partial_export;          // optional exported (o, m, l) per row, m in natural-log units
     int early_rows;                 // window rows [0, early_rows) may be read before griddepcontrol.wait
+    // fused quantize-on-write: the last n_new keys of the window are given as fp32 rows
+    const float *new_k, *new_v;     // [n_new][nkv][HD], row stride new_stride elements; nullptr = none
+    uint8_t *k_cache_w, *v_cache_w, *k_scales_w, *v_scales_w;   // writable aliases of the cache
+    int n_new, new_stride, new_base_pos;
     long q_batch_stride, kv_batch_stride, scale_batch_stride, out_batch_stride;
 };
 
@@ -135,7 +141,8 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
     int *slot_lo = reinterpret_cast<int *>(smem + C::Q_BYTES + C::NSLOT * 4);
     int *slot_hi = reinterpret_cast<int *>(smem + C::Q_BYTES + C::NSLOT * 8);
     int *slot_qsum = reinterpret_cast<int *>(smem + C::Q_BYTES + C::NSLOT * 16);   // [NSLOT][NBLK]
-    uint8_t *pipe = smem + C::Q_BYTES + C::SLOT_BYTES;
+    uint8_t *append_scratch = smem + C::Q_BYTES + C::SLOT_BYTES;                  // [NW][ROWB + 64]
+    uint8_t *pipe = append_scratch + C::APPEND_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -376,6 +383,56 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
         const bool need_mask = (tok0 + TILE > hi_min) || (tok0 < lo_max);
         const uint8_t *ksm = stp + 2 * C::KV_BYTES;                 // K scales of the tile, token-major
         const uint8_t *vsm = ksm + C::SC_BYTES;                     // V scales
+
+        // ------------------------------------------- fused quantize-on-write of the new keys
+        // The newest n_new keys arrive as fp32 rows.  The warp that owns their tile quantises them
+        // (same row codec as the append kernels, bit for bit), overwrites the rows the copy engine
+        // fetched for those slots in shared memory, and -- for row group 0, so exactly once per KV
+        // head -- stores bytes and scales into the ring for later calls.
+        if (p.new_k != nullptr && tok0 + TILE > p.klen - p.n_new) {
+            uint8_t *scr = append_scratch + warp * (C::ROWB + 64);
+            for (int i = 0; i < p.n_new; ++i) {
+                const int wi = p.klen - p.n_new + i;                 // window index of new key i
+                if (wi < tok0 || wi >= tok0 + TILE) continue;
+                const int r = wi - tok0;
+                const int slot = (p.new_base_pos + i) % p.cache_cap;
+                const size_t crow = (size_t)kvh * p.cache_cap + slot;
+#pragma unroll
+                for (int kv = 0; kv < 2; ++kv) {
+                    const float *src = (kv ? p.new_v : p.new_k) + ((size_t)b * p.n_new + i) * p.new_stride + kvh * HD;
+                    uint8_t *tile_rows = my_pipe + (it % NSTAGE) * C::STAGE_BYTES + kv * C::KV_BYTES;
+                    uint8_t *tile_sc = my_pipe + (it % NSTAGE) * C::STAGE_BYTES + 2 * C::KV_BYTES + kv * C::SC_BYTES + r * C::SCB;
+                    uint8_t *g_rows = (kv ? p.v_cache_w : p.k_cache_w) + b * p.kv_batch_stride + crow * row_stride;
+                    uint8_t *g_sc = (kv ? p.v_scales_w : p.k_scales_w) + b * p.scale_batch_stride;
+                    const bool writer = (rg == 0);
+                    if constexpr (FMT == KV_I8) {
+                        quant_row_i8(src, HD, HD, reinterpret_cast<int8_t *>(scr), reinterpret_cast<float *>(scr + C::ROWB), lane);
+                        if (writer) quant_row_i8(src, HD, p.cache_hd, reinterpret_cast<int8_t *>(g_rows), reinterpret_cast<float *>(g_sc) + crow, lane);
+                    } else if constexpr (FMT == KV_I4) {
+                        const float sc = quant_row_i4(src, HD, HD, scr, nullptr, lane);
+                        if (lane == 0) *reinterpret_cast<float *>(scr + C::ROWB) = sc;
+                        if (writer) {
+                            const float sg = quant_row_i4(src, HD, p.cache_hd, g_rows, nullptr, lane);
+                            if (lane == 0) reinterpret_cast<float *>(g_sc)[crow] = sg;
+                        }
+                    } else {
+                        quant_row_i4_block32(src, HD, scr, reinterpret_cast<__half *>(scr + C::ROWB), lane);
+                        if (writer) {
+                            const float q8s = quant_row_i4_block32(src, HD, g_rows, reinterpret_cast<__half *>(g_sc) + crow * C::NBLK, lane);
+                            if (lane == 0)
+                                reinterpret_cast<float *>(g_sc + (size_t)p.nkv * p.cache_cap * C::NBLK * 2)[crow] = q8s;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane < C::CHUNKS)
+                        *reinterpret_cast<uint4 *>(tile_rows + r * C::ROWB + swz_chunk<C::ROWB>(r, lane) * 16) =
+                            *reinterpret_cast<const uint4 *>(scr + lane * 16);
+                    if (lane < C::SCB / 2)
+                        reinterpret_cast<uint16_t *>(tile_sc)[lane] = reinterpret_cast<const uint16_t *>(scr + C::ROWB)[lane];
+                    __syncwarp();
+                }
+            }
+        }
 
         // --------------------------------------------------------------- QK
         // Base-2 logits s2[mt][n][e] of slot (mt, g) against token 8n+2t+e.  The MMA rows g / g+8
