@@ -400,6 +400,44 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
                                                  "note": "2.4 MB per call: launch-latency-bound, L2-resident"}
     except Exception as e:
         out["c3_swa_ring_i4b32_fused_append"] = {"error": str(e)}
+    # the reference model's real layer geometry (Gemma-4-31B, lib/gemma4_engine.mojo:371-392), int4 block-32 KV:
+    # sliding layers 32q/16kv x 256 with a 1024-slot ring, full layers 32q/4kv x 512 at 32768 keys
+    for name, nkv_g, hd_g, t_g, cap_g in (("g4_sliding_hd256_i4b32_w1024", 16, 256, 1024, 1024),
+                                          ("g4_full_hd512_i4b32_32k", 4, 512, 32768, 32768)):
+        try:
+            nb = hd_g // 32
+            rows = nkv_g * cap_g
+            cs = []
+            for li in range(2 if t_g > 4096 else 1):
+                k = torch.zeros((nkv_g, cap_g, hd_g // 2), dtype=torch.uint8, device=dev); v = torch.zeros_like(k)
+                ks = torch.zeros(rows * nb * 2 + rows * 4, dtype=torch.uint8, device=dev); vs = torch.zeros_like(ks)
+                g = torch.Generator(device=dev); g.manual_seed(77 + li)
+                for base in range(0, t_g, 2048):
+                    n = min(2048, t_g - base)
+                    kk = torch.randn((n, nkv_g, hd_g), generator=g, device=dev).to(torch.bfloat16).float().contiguous()
+                    vv = torch.randn((n, nkv_g, hd_g), generator=g, device=dev).to(torch.bfloat16).float().contiguous()
+                    ops.gpu_append_quant_kv_i4(None, kk, vv, k, v, ks, vs, n, nkv_g, hd_g, nkv_g * hd_g, cap_g, hd_g, base, nb)
+                cs.append((k, v, ks, vs))
+            q = torch.randn((1, 1, NH, hd_g), device=dev).to(torch.bfloat16)
+            o = torch.zeros((1, 1, NH, hd_g), dtype=torch.bfloat16, device=dev)
+            al = [ops.make_args(q=q, k_cache=c[0], v_cache=c[1], k_scales=c[2], v_scales=c[3], out=o, kv_fmt=ops.KV_I4B32,
+                                q_type=ops.BF16, out_type=ops.BF16, nh=NH, nkv=nkv_g, kvg=NH // nkv_g, l_hd=hd_g, cache_hd=hd_g,
+                                cache_cap=cap_g, klen=t_g, softmax_scale=1.0 / np.sqrt(hd_g), flags=ops.SETTLED_CACHE) for c in cs]
+            wsb = ops.attn_workspace_bytes(al[0])
+            ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+            for a_ in al:
+                a_.workspace, a_.ws_bytes = ws.data_ptr(), wsb
+            cnt = [0]
+
+            def fng():
+                ops.attn_fused(stream, al[cnt[0] % len(al)]); cnt[0] += 1
+
+            us = time_call(torch, fng, iters)
+            by = 2 * nkv_g * t_g * (hd_g // 2) + 2 * nkv_g * t_g * nb * 2 + NH * hd_g * 4
+            out[name] = {"us_per_layer": round(us, 2), "GBps": round(by / us / 1e3, 1), "bytes": by}
+            del cs, ws
+        except Exception as e:
+            out[name] = {"error": str(e)}
     # configuration 5b: batch 1 x 524288 keys, sharded by sequence chunks, (o, m, l) all-gathered and merged
     try:
         T5 = 524288 // world
