@@ -59,6 +59,13 @@ extern "C" {
 int32_t nomos_attn_version(void);
 /* Message describing the last non-zero status returned on this thread. */
 const char *nomos_attn_last_error(void);
+/* Device-side fault bits of the current device, accumulated since the last clearing read.
+ * The kernels never wait without a limit; a wait that ran out ORs a bit in here and the
+ * launch carries on (its output is then undefined).  Bit 0: a tile requested from the cache
+ * did not arrive within about two seconds.  Synchronises the device; a health check between
+ * steps, not a per-call status.  `clear` != 0 resets the word after reading.
+ * No counterpart in the reference (its kernels have no waits). */
+int32_t nomos_attn_device_faults(uint32_t *out_bits, int32_t clear);
 
 /* ------------------------------------------------------------------------- *
  *  KV cache codecs (thin, call-for-call)                                     *
@@ -232,6 +239,10 @@ typedef struct nomos_attn_args {
  * while that preceding kernel is still finishing (the query, the S newest rows and every
  * output are still ordered after it). */
 #define NOMOS_ATTN_SETTLED_CACHE 1
+/* flags bit: fetch every tile with 16-byte cp.async copies instead of TMA tensor copies.
+ * Same results bit for bit; for comparing the two copy paths (the environment variable
+ * NOMOS_ATTN_NO_TMA=1 does the same for a whole process). */
+#define NOMOS_ATTN_NO_TMA 2
 
 /* Bytes of workspace the call needs (>= 0), or a negative status. */
 int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args);

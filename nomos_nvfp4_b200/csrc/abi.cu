@@ -40,6 +40,10 @@ static inline bool hd_ok(int hd) { return hd == 128 || hd == 256 || hd == 512; }
 
 NOMOS_EXPORT int32_t nomos_attn_version(void) { return 100; }
 NOMOS_EXPORT const char *nomos_attn_last_error(void) { return g_err; }
+NOMOS_EXPORT int32_t nomos_attn_device_faults(uint32_t *out_bits, int32_t clear) {
+    REQUIRE(out_bits, "nomos_attn_device_faults: null pointer");
+    return nomos::read_attn_faults(out_bits, clear != 0);
+}
 
 // ------------------------------------------------------------------- codecs
 
@@ -361,6 +365,7 @@ static int unpack_args(const nomos_attn_args_t *u, AttnArgs &a, const char *who)
     a.scale_batch_stride = u->scale_batch_stride ? u->scale_batch_stride : scale_bytes;
     a.force_splits = (int)u->force_splits;
     a.settled_cache = (u->flags & NOMOS_ATTN_SETTLED_CACHE) ? 1 : 0;
+    a.no_tma = (u->flags & NOMOS_ATTN_NO_TMA) ? 1 : 0;
     return NOMOS_OK;
 }
 

@@ -10,8 +10,10 @@
 // Work decomposition
 //   grid = (splits, nkv, batch * row_groups); one CTA streams one KV head's chunk of
 //   the window and serves every query row of the GQA group from the same bytes.
-//   Each warp owns a private cp.async ring of 32-token tiles (16-byte coalesced
-//   global->shared copies into an XOR-swizzled layout, no CTA barrier in the loop).
+//   Each warp owns a private ring of 32-token tiles in an XOR-swizzled layout, with no CTA
+//   barrier in the loop.  Whole tiles of 64- or 128-byte rows are fetched by TMA (one lane
+//   issues two cp.async.bulk.tensor boxes + two bulk copies of scales against the stage's
+//   mbarrier); ragged or ring-wrapping tiles and wider rows use 16-byte cp.async copies.
 // Arithmetic per warp tile (all contractions on the tensor cores, no integer->float
 // conversion of cache bytes anywhere)
 //   QK:  int8 MMA m16n8k32.  A = the query rows as two int8 limbs of a 15-bit fixed
@@ -30,6 +32,11 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include <cudaTypedefs.h>     // PFN_cuTensorMapEncodeTiled
 
 #include "attn_fused_kernel.cuh"
 
@@ -51,6 +58,78 @@ static DeviceInfo device_info() {
         int n = 0;
         cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
         cached[dev].sm_count = n > 0 ? n : 148;
+    }
+    return cached[dev];
+}
+
+// ------------------------------------------------------------------ tensor maps
+// cuTensorMapEncodeTiled is resolved through the runtime, so the library links against
+// cudart only.  A null result (old driver) just keeps every tile on the cp.async path.
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            sym = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+static bool tma_disabled_by_env() {
+    static const bool off = [] { const char *e = std::getenv("NOMOS_ATTN_NO_TMA"); return e && e[0] == '1'; }();
+    return off;
+}
+
+// {row bytes, rows, batch} view of one byte plane of the cache; box = one 32-row tile.
+struct MapKey {
+    const void *base; int row_bytes, row_stride, rows, batch; long batch_stride;
+    bool operator==(const MapKey &o) const {
+        return base == o.base && row_bytes == o.row_bytes && row_stride == o.row_stride && rows == o.rows && batch == o.batch &&
+               batch_stride == o.batch_stride;
+    }
+};
+static bool encode_plane(const MapKey &k, CUtensorMap *out) {
+    // small per-thread cache: a decode loop alternates between a few layer caches
+    struct Entry { MapKey key; CUtensorMap map; bool used = false; };
+    thread_local Entry cache[16];
+    thread_local int next = 0;
+    for (auto &e : cache)
+        if (e.used && e.key == k) { *out = e.map; return true; }
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (enc == nullptr) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)k.row_bytes, (cuuint64_t)k.rows, (cuuint64_t)k.batch};
+    const cuuint64_t strides[2] = {(cuuint64_t)k.row_stride,
+                                   (cuuint64_t)(k.batch > 1 ? k.batch_stride : (long)k.rows * k.row_stride)};
+    const cuuint32_t box[3] = {(cuuint32_t)k.row_bytes, (cuuint32_t)TILE, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapSwizzle swz = k.row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    CUtensorMap m;
+    if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(k.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    Entry &e = cache[next];
+    next = (next + 1) % 16;
+    e.key = k; e.map = m; e.used = true;
+    *out = m;
+    return true;
+}
+
+// Sticky per-device fault word the kernels OR into when a bounded wait runs out.
+__device__ unsigned int g_attn_fault;
+static unsigned int *fault_word() {
+    static unsigned int *cached[64];
+    static std::mutex mu;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_attn_fault) == cudaSuccess) cached[dev] = static_cast<unsigned int *>(ptr);
     }
     return cached[dev];
 }
@@ -174,6 +253,30 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     p.qk_scale_log2 = a.softmax_scale * LOG2E;
     p.q_batch_stride = a.q_batch_stride; p.kv_batch_stride = a.kv_batch_stride;
     p.scale_batch_stride = a.scale_batch_stride; p.out_batch_stride = a.out_batch_stride;
+    p.fault = fault_word();
+    if (p.fault == nullptr) { set_error("attn_fused: device fault word unavailable"); return NOMOS_ECUDA; }
+    // TMA for whole tiles when the row geometry matches a hardware swizzle pattern and the
+    // planes satisfy the tensor-map rules (16-byte aligned base and strides).
+    TmaMaps tm;
+    std::memset(&tm, 0, sizeof(tm));
+    p.use_tma = 0;
+    if (C::TMA_OK && !a.no_tma && !tma_disabled_by_env()) {
+        const int row_stride = (FMT == KV_I8) ? a.cache_hd : a.cache_hd / 2;
+        const auto al16 = [](const void *x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
+        const long rows = (long)a.nkv * a.cache_cap;
+        const bool ok = al16(a.k_cache) && al16(a.v_cache) && row_stride % 16 == 0 && (a.batch == 1 || a.kv_batch_stride % 16 == 0) &&
+                        rows < (1l << 31);
+        if (ok) {
+            const MapKey kk{a.k_cache, C::ROWB, row_stride, (int)rows, a.batch, a.kv_batch_stride};
+            const MapKey kv{a.v_cache, C::ROWB, row_stride, (int)rows, a.batch, a.kv_batch_stride};
+            if (encode_plane(kk, &tm.k) && encode_plane(kv, &tm.v)) {
+                p.use_tma = 1;
+                if (al16(a.k_scales) && al16(a.v_scales) && ((long)a.cache_cap * C::SCB) % 16 == 0 &&
+                    (a.batch == 1 || a.scale_batch_stride % 16 == 0))
+                    p.use_tma |= 2;
+            }
+        }
+    }
     dim3 grid(pl.splits, a.nkv, a.batch * pl.row_groups);
     // Launched with programmatic stream serialization allowed: after a grid that triggers early
     // (another attention call of this library) the grid is set up while the predecessor drains and
@@ -185,7 +288,7 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     cudaLaunchConfig_t mcfg = {};
     mcfg.gridDim = grid; mcfg.blockDim = dim3(C::NW * 32); mcfg.dynamicSmemBytes = C::SMEM_BYTES; mcfg.stream = st;
     mcfg.attrs = pdl; mcfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&mcfg, attn_fused_kernel<FMT, HD, MT>, p);
+    cudaError_t e = cudaLaunchKernelEx(&mcfg, attn_fused_kernel<FMT, HD, MT>, p, tm);
     if (e != cudaSuccess) { set_error("attn_fused launch: %s", cudaGetErrorString(e)); return NOMOS_ECUDA; }
     return NOMOS_OK;
 }
@@ -225,6 +328,15 @@ long attn_workspace_bytes(const AttnArgs &a) {
 }
 
 int launch_attn_fused(cudaStream_t st, const AttnArgs &a) { return dispatch(st, a, false, nullptr); }
+
+int read_attn_faults(unsigned int *out, bool clear) {
+    unsigned int *w = fault_word();
+    if (w == nullptr) { set_error("device fault word unavailable"); return NOMOS_ECUDA; }
+    cudaError_t e = cudaMemcpy(out, w, sizeof(unsigned int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && clear && *out != 0) e = cudaMemset(w, 0, sizeof(unsigned int));
+    if (e != cudaSuccess) { set_error("fault word read: %s", cudaGetErrorString(e)); return NOMOS_ECUDA; }
+    return NOMOS_OK;
+}
 
 #ifdef NOMOS_TIMELINE
 extern "C" __attribute__((visibility("default"))) int nomos_debug_timeline(unsigned long long *host_out, int n_ctas) {

@@ -2,6 +2,7 @@
 // (sm_100a).  See attn_fused.cu for the host side and the overall description.
 #pragma once
 
+#include <cuda.h>             // CUtensorMap (type only: the encoder is resolved at run time)
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -25,7 +26,7 @@ namespace fused {
 #endif
 
 constexpr int TILE = 32;                 // tokens per warp tile
-constexpr int NSTAGE = NOMOS_NSTAGE;     // cp.async stages per warp
+constexpr int NSTAGE = NOMOS_NSTAGE;     // tile stages per warp
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float M_INIT = -1.0e30f;       // finite "minus infinity" for the running max
@@ -52,9 +53,23 @@ struct Cfg {
     static constexpr int NW_MEM = (200 * 1024) / (NSTAGE * STAGE_BYTES);
     static constexpr int NW = NW_REG < NW_MEM ? NW_REG : (NW_MEM < 1 ? 1 : NW_MEM);
     static constexpr int APPEND_BYTES = NW * (ROWB + 64);                     // per warp: one quantised row + its scales
-    static constexpr int PIPE_BYTES = NW * NSTAGE * STAGE_BYTES;
+    // Shared-memory map: [K/V tiles of every warp and stage | scales | query limbs | slot
+    // constants | append scratch | mbarriers].  The tile region starts on a 1024-byte boundary
+    // (what the TMA swizzle patterns are defined against) and is reused for the merges.
+    static constexpr int TILES_BYTES = NW * NSTAGE * 2 * KV_BYTES;
+    static constexpr int SCALES_BYTES = NW * NSTAGE * 2 * SC_BYTES;
     static constexpr int MERGE_BYTES = NW * NSLOT * (HD + 2) * 4;
-    static constexpr int SMEM_BYTES = Q_BYTES + SLOT_BYTES + APPEND_BYTES + (PIPE_BYTES > MERGE_BYTES ? PIPE_BYTES : MERGE_BYTES);
+    static constexpr int REGION0_BYTES = ((TILES_BYTES > MERGE_BYTES ? TILES_BYTES : MERGE_BYTES) + 15) / 16 * 16;
+    static constexpr int BAR_BYTES = NW * NSTAGE * 8;
+    static constexpr int SMEM_BYTES = 1024 + REGION0_BYTES + SCALES_BYTES + Q_BYTES + SLOT_BYTES + APPEND_BYTES + BAR_BYTES;
+    // Rows of 64 / 128 bytes map one-to-one onto the TMA 64B / 128B swizzle patterns, which are
+    // the XOR layouts swz_chunk() defines; wider rows stay on the cp.async path.
+    static constexpr bool TMA_OK = (ROWB == 64 || ROWB == 128);
+};
+
+// Tensor maps of the K and V byte planes: {row bytes, nkv * cache_cap rows, batch}.
+struct TmaMaps {
+    CUtensorMap k, v;
 };
 
 struct KParams {
@@ -79,6 +94,8 @@ struct KParams {
     uint8_t *k_cache_w, *v_cache_w, *k_scales_w, *v_scales_w;   // writable aliases of the cache
     int n_new, new_stride, new_base_pos;
     long q_batch_stride, kv_batch_stride, scale_batch_stride, out_batch_stride;
+    int use_tma;             // bit 0: whole tiles come by TMA; bit 1: their scales by bulk copy
+    unsigned int *fault;     // sticky device word: bit 0 = a tile never arrived within the wait limit
 };
 
 __device__ __forceinline__ float load_q(const uint8_t *q, int q_type, long idx) {
@@ -122,6 +139,53 @@ __device__ __forceinline__ void mma_u8u8_zero(int (&d)[4], uint32_t a0, uint32_t
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
 }
 
+// ---- TMA and mbarrier wrappers (CTA-local; no cluster multicast anywhere)
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Waits for the phase with the given parity to complete; gives up after about two seconds.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > 2000000000ull) return false;
+    }
+}
+// One 32-row box of a {bytes, rows, batch} byte tensor into shared memory.
+__device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap *map, int row, int batch, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(dst),
+        "l"(reinterpret_cast<unsigned long long>(map)), "r"(0), "r"(row), "r"(batch), "r"(bar)
+        : "memory");
+}
+// Contiguous bytes (16-byte aligned both sides, size a multiple of 16) into shared memory.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
@@ -132,17 +196,21 @@ namespace nomos {
 namespace fused {
 
 template <int FMT, int HD, int MT>
-__global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(const KParams p) {
+__global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
+    attn_fused_kernel(const KParams p, const __grid_constant__ TmaMaps tm) {
     using C = Cfg<FMT, HD, MT>;
     constexpr int NWARP = C::NW;
-    extern __shared__ __align__(128) uint8_t smem[];
-    int8_t *q_limbs = reinterpret_cast<int8_t *>(smem);                        // [2][NSLOT][HD]
-    float *slot_qscale = reinterpret_cast<float *>(smem + C::Q_BYTES);         // [NSLOT]
-    int *slot_lo = reinterpret_cast<int *>(smem + C::Q_BYTES + C::NSLOT * 4);
-    int *slot_hi = reinterpret_cast<int *>(smem + C::Q_BYTES + C::NSLOT * 8);
-    int *slot_qsum = reinterpret_cast<int *>(smem + C::Q_BYTES + C::NSLOT * 16);   // [NSLOT][NBLK]
-    uint8_t *append_scratch = smem + C::Q_BYTES + C::SLOT_BYTES;                  // [NW][ROWB + 64]
-    uint8_t *pipe = append_scratch + C::APPEND_BYTES;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *pipe = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // K/V tiles [NW][NSTAGE][2]
+    uint8_t *sc_region = pipe + C::REGION0_BYTES;                                  // scales  [NW][NSTAGE][2]
+    uint8_t *qreg = sc_region + C::SCALES_BYTES;
+    int8_t *q_limbs = reinterpret_cast<int8_t *>(qreg);                        // [2][NSLOT][HD]
+    float *slot_qscale = reinterpret_cast<float *>(qreg + C::Q_BYTES);         // [NSLOT]
+    int *slot_lo = reinterpret_cast<int *>(qreg + C::Q_BYTES + C::NSLOT * 4);
+    int *slot_hi = reinterpret_cast<int *>(qreg + C::Q_BYTES + C::NSLOT * 8);
+    int *slot_qsum = reinterpret_cast<int *>(qreg + C::Q_BYTES + C::NSLOT * 16);   // [NSLOT][NBLK]
+    uint8_t *append_scratch = qreg + C::Q_BYTES + C::SLOT_BYTES;                  // [NW][ROWB + 64]
+    const uint32_t bars_u32 = smem_u32(append_scratch + C::APPEND_BYTES);         // [NW][NSTAGE] mbarriers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -161,9 +229,24 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
     const uint8_t *ksbase = p.k_scales + b * p.scale_batch_stride + (size_t)kvh * p.cache_cap * C::SCB;
     const uint8_t *vsbase = p.v_scales + b * p.scale_batch_stride + (size_t)kvh * p.cache_cap * C::SCB;
 
-    uint8_t *my_pipe = pipe + warp * NSTAGE * C::STAGE_BYTES;
-    const uint32_t my_pipe_u32 = smem_u32(my_pipe);
+    uint8_t *my_pipe = pipe + warp * NSTAGE * 2 * C::KV_BYTES;       // stage s: K tile, V tile
+    uint8_t *my_sc = sc_region + warp * NSTAGE * 2 * C::SC_BYTES;    // stage s: K scales, V scales
+    const uint32_t my_pipe_u32 = smem_u32(my_pipe), my_sc_u32 = smem_u32(my_sc);
+    const uint32_t my_bar_u32 = bars_u32 + warp * NSTAGE * 8;
     const int ring0 = p.win_start % p.cache_cap;
+
+    // TMA path: one lane requests a whole tile (two tensor copies + two bulk copies of scales)
+    // against the stage's mbarrier; the warp waits on the barrier's phase.  tma_mask marks the
+    // stages whose current tile came that way, phase_bits their barrier parity.
+    uint32_t tma_mask = 0, phase_bits = 0;
+    if constexpr (C::TMA_OK) {
+        if (p.use_tma && lane == 0) {
+#pragma unroll
+            for (int s = 0; s < NSTAGE; ++s) mbar_init(my_bar_u32 + 8 * s, 1);
+            fence_mbar_init();
+        }
+        __syncwarp();
+    }
 
     // Copy geometry: per cp.async instruction the warp covers 8 rows x 64 bytes; lane = (row r, chunk c0).
     constexpr int HPASS = C::CHUNKS / 4;                     // 64-byte column groups per row
@@ -185,11 +268,36 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
     auto issue = [&](int it) {
         if (it < my_count) {
             const int tok0 = (my_first + it * NWARP) * TILE;
-            const uint32_t st = my_pipe_u32 + (it % NSTAGE) * C::STAGE_BYTES;
+            const int stg = it % NSTAGE;
+            const uint32_t st = my_pipe_u32 + stg * 2 * C::KV_BYTES;
+            const uint32_t ss = my_sc_u32 + stg * 2 * C::SC_BYTES;
             int slot0 = ring0 + tok0;
             slot0 = slot0 >= p.cache_cap ? slot0 - p.cache_cap : slot0;          // klen <= cache_cap (host-checked)
-            if (slot0 + TILE <= p.cache_cap && tok0 + TILE <= p.klen) {
-                // fast path: the 32 rows are contiguous in the ring and all inside the window
+            const bool whole = slot0 + TILE <= p.cache_cap && tok0 + TILE <= p.klen;
+            tma_mask &= ~(1u << stg);
+            if (C::TMA_OK && p.use_tma && whole) {
+                // the 32 rows are contiguous in the ring and inside the window: one box per plane
+                const bool bulk_sc = (p.use_tma & 2) && ((slot0 * C::SCB) & 15) == 0;
+                fence_proxy_async();          // earlier generic-proxy accesses of the stage precede the copies
+                __syncwarp();
+                if (lane == 0) {
+                    const uint32_t bar = my_bar_u32 + 8 * stg;
+                    mbar_expect_tx(bar, 2 * C::KV_BYTES + (bulk_sc ? 2 * C::SC_BYTES : 0));
+                    tma_load_tile(st, &tm.k, kvh * p.cache_cap + slot0, b, bar);
+                    tma_load_tile(st + C::KV_BYTES, &tm.v, kvh * p.cache_cap + slot0, b, bar);
+                    if (bulk_sc) {
+                        bulk_load(ss, ksbase + (size_t)slot0 * C::SCB, C::SC_BYTES, bar);
+                        bulk_load(ss + C::SC_BYTES, vsbase + (size_t)slot0 * C::SCB, C::SC_BYTES, bar);
+                    }
+                }
+                if (!bulk_sc) {
+                    const size_t sg = (size_t)(slot0 + lane) * C::SCB;
+                    copy_scales(ss + lane * C::SCB, ksbase + sg, true);
+                    copy_scales(ss + C::SC_BYTES + lane * C::SCB, vsbase + sg, true);
+                }
+                tma_mask |= 1u << stg;
+            } else if (whole) {
+                // cp.async path: 16-byte coalesced copies into the same swizzled layout
                 const uint8_t *gk = kbase + (size_t)slot0 * row_stride + lane_goff;
                 const uint8_t *gv = vbase + (size_t)slot0 * row_stride + lane_goff;
 #pragma unroll
@@ -202,8 +310,8 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
                         cp_async16(so + C::KV_BYTES, gv + go, 16);
                     }
                 const size_t sg = (size_t)(slot0 + lane) * C::SCB;
-                copy_scales(st + 2 * C::KV_BYTES + lane * C::SCB, ksbase + sg, true);
-                copy_scales(st + 2 * C::KV_BYTES + C::SC_BYTES + lane * C::SCB, vsbase + sg, true);
+                copy_scales(ss + lane * C::SCB, ksbase + sg, true);
+                copy_scales(ss + C::SC_BYTES + lane * C::SCB, vsbase + sg, true);
             } else {
                 // ragged tile: wraps the ring or runs past the window; rows past the end are zero-filled
 #pragma unroll
@@ -225,8 +333,8 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
                 slot = slot >= p.cache_cap ? slot - p.cache_cap : slot;
                 const bool ok = tok < p.klen;
                 const size_t sg = (size_t)(ok ? slot : 0) * C::SCB;
-                copy_scales(st + 2 * C::KV_BYTES + lane * C::SCB, ksbase + sg, ok);
-                copy_scales(st + 2 * C::KV_BYTES + C::SC_BYTES + lane * C::SCB, vsbase + sg, ok);
+                copy_scales(ss + lane * C::SCB, ksbase + sg, ok);
+                copy_scales(ss + C::SC_BYTES + lane * C::SCB, vsbase + sg, ok);
             }
         }
         cp_async_commit();
@@ -374,14 +482,20 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
 
     for (int it = 0; it < my_count; ++it) {
         issue(it + NSTAGE - 1);
+        const int stg = it % NSTAGE;
         cp_async_wait<NSTAGE - 1>();
+        if constexpr (C::TMA_OK) {
+            if ((tma_mask >> stg) & 1u) {
+                if (!mbar_wait_bounded(my_bar_u32 + 8 * stg, (phase_bits >> stg) & 1u) && lane == 0) atomicOr(p.fault, 1u);
+                phase_bits ^= 1u << stg;
+            }
+        }
         __syncwarp();
 
         const int tok0 = (my_first + it * NWARP) * TILE;
-        const uint32_t st = my_pipe_u32 + (it % NSTAGE) * C::STAGE_BYTES;
-        const uint8_t *stp = my_pipe + (it % NSTAGE) * C::STAGE_BYTES;
+        const uint32_t st = my_pipe_u32 + stg * 2 * C::KV_BYTES;
         const bool need_mask = (tok0 + TILE > hi_min) || (tok0 < lo_max);
-        const uint8_t *ksm = stp + 2 * C::KV_BYTES;                 // K scales of the tile, token-major
+        const uint8_t *ksm = my_sc + stg * 2 * C::SC_BYTES;         // K scales of the tile, token-major
         const uint8_t *vsm = ksm + C::SC_BYTES;                     // V scales
 
         // ------------------------------------------- fused quantize-on-write of the new keys
@@ -400,8 +514,8 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32) attn_fused_kernel(c
 #pragma unroll
                 for (int kv = 0; kv < 2; ++kv) {
                     const float *src = (kv ? p.new_v : p.new_k) + ((size_t)b * p.n_new + i) * p.new_stride + kvh * HD;
-                    uint8_t *tile_rows = my_pipe + (it % NSTAGE) * C::STAGE_BYTES + kv * C::KV_BYTES;
-                    uint8_t *tile_sc = my_pipe + (it % NSTAGE) * C::STAGE_BYTES + 2 * C::KV_BYTES + kv * C::SC_BYTES + r * C::SCB;
+                    uint8_t *tile_rows = my_pipe + (stg * 2 + kv) * C::KV_BYTES;
+                    uint8_t *tile_sc = my_sc + (stg * 2 + kv) * C::SC_BYTES + r * C::SCB;
                     uint8_t *g_rows = (kv ? p.v_cache_w : p.k_cache_w) + b * p.kv_batch_stride + crow * row_stride;
                     uint8_t *g_sc = (kv ? p.v_scales_w : p.k_scales_w) + b * p.scale_batch_stride;
                     const bool writer = (rg == 0);

@@ -51,12 +51,15 @@ struct AttnArgs {
     float softmax_scale;
     long q_batch_stride, kv_batch_stride, scale_batch_stride, out_batch_stride;   // elements (q/out), bytes (kv, scales)
     int force_splits;       // 0 = choose; >0 = use exactly this many splits (tests)
+    int no_tma;             // 1: keep every tile on the cp.async path
     int settled_cache;      // 1: rows older than the S query rows may be read before the stream predecessor completes
     int fit_splits_to_ws;   // 1: use fewer splits rather than fail when the workspace is small (thin entry points)
 };
 
 long attn_workspace_bytes(const AttnArgs &a);
 int launch_attn_fused(cudaStream_t st, const AttnArgs &a);
+// Reads (and optionally clears) the device word the kernels OR into when a bounded wait runs out.
+int read_attn_faults(unsigned int *out, bool clear);
 // partials [G][rows][l_hd+2] = (o.., m, l) with m in natural-log units (the exported form)
 int launch_merge_partials(cudaStream_t st, const float *partials, int G, int rows, int l_hd, void *out, int out_type);
 // same, m in log2 units (in-library split partials), fp32 output

@@ -20,6 +20,7 @@ from ._lib import AttnArgs
 KV_I8, KV_I4, KV_I4B32 = 0, 1, 2
 F32, BF16 = 0, 1
 SETTLED_CACHE = 1            # nomos_attn_args_t.flags bit, see include/nomos_attn.h
+NO_TMA = 2                   # nomos_attn_args_t.flags bit: cp.async copies only
 
 
 class NomosError(RuntimeError):
@@ -52,6 +53,15 @@ def _check(status: int) -> None:
 
 def version() -> int:
     return _lib.lib().nomos_attn_version()
+
+
+def device_faults(clear: bool = False) -> int:
+    """Fault bits the kernels of the current device have raised (0 = none); synchronises."""
+    import ctypes
+
+    bits = ctypes.c_uint32(0)
+    _check(_lib.lib().nomos_attn_device_faults(ctypes.byref(bits), 1 if clear else 0))
+    return int(bits.value)
 
 
 # ---------------------------------------------------------------------- codecs

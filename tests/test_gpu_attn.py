@@ -332,6 +332,34 @@ def test_settled_cache_flag_gives_identical_output(oracle):
     assert within(outs[1], want, TOL)[0]
 
 
+@pytest.mark.parametrize("fmt,hd,win_start", [("i8", 128, 0), ("i8", 128, 1237), ("i4", 128, 0), ("i4b32", 128, 5), ("i4", 256, 0)])
+def test_tma_and_cp_async_copy_paths_agree(oracle, fmt, hd, win_start):
+    """Whole tiles come by TMA tensor copies, ragged / ring-wrapping ones by cp.async; forcing
+    everything onto cp.async must not change a bit.  Odd window starts make the scale rows
+    miss the 16-byte rule of the bulk copy (scales then ride cp.async beside a TMA tile)."""
+    rng = np.random.default_rng(600 + hd + win_start)
+    nkv, kvg, T = 4, 2, 3000
+    nh = nkv * kvg
+    cap = 4096 if win_start else T
+    c = build_cache(fmt, rng, T, nkv, hd, cap=cap, start=win_start)
+    q = bf16_normal(rng, (1, nh, hd))
+    keep = [dev(q), dev(c.k), dev(c.v), dev(c.ks), dev(c.vs)]
+    outs = []
+    for flags in (0, ops.NO_TMA):
+        out = torch.full((1, nh, hd), SENTINEL, dtype=torch.float32, device=DEV)
+        a = ops.make_args(q=keep[0], k_cache=keep[1], v_cache=keep[2], k_scales=keep[3], v_scales=keep[4], out=out,
+                          kv_fmt=c.kv_fmt, nh=nh, nkv=nkv, kvg=kvg, l_hd=hd, cache_hd=hd, cache_cap=cap, klen=T,
+                          win_start=win_start, softmax_scale=0.1, flags=flags)
+        ws = torch.empty(max(ops.attn_workspace_bytes(a), 16), dtype=torch.uint8, device=DEV)
+        a.workspace, a.ws_bytes = ws.data_ptr(), ws.numel()
+        ops.attn_fused(None, a)
+        torch.cuda.synchronize()
+        outs.append(host(out))
+    assert np.array_equal(outs[0], outs[1])
+    want = exact(oracle, c, q, klen=T, win_start=win_start, scale=0.1)
+    assert within(outs[0], want, TOL)[0]
+
+
 @pytest.mark.parametrize("S,kvg", [(17, 2), (9, 8), (4, 8)])
 def test_many_verify_rows(oracle, S, kvg):
     """More than 24 query rows per KV head (the 24-row CTA path) and wide GQA groups."""

@@ -68,3 +68,9 @@ def test_static_workspace_refuses_oversized_request():
         ops.attn_fused_static_ws(None, a)
     assert e.value.status == -3
     torch.cuda.synchronize()
+
+
+def test_no_device_fault_bits_after_the_suite():
+    """Every wait in the kernels is bounded and reports through a sticky device word; after
+    all the GPU tests above it must still read zero."""
+    assert ops.device_faults() == 0
