@@ -243,6 +243,10 @@ typedef struct nomos_attn_args {
  * Same results bit for bit; for comparing the two copy paths (the environment variable
  * NOMOS_ATTN_NO_TMA=1 does the same for a whole process). */
 #define NOMOS_ATTN_NO_TMA 2
+/* flags bit: keep int8 / head_dim 128 calls on the mma.sync kernel instead of the tcgen05 one
+ * (both pass the same accuracy gate; their roundings differ).  The environment variable
+ * NOMOS_ATTN_NO_TCGEN05=1 does the same for a whole process. */
+#define NOMOS_ATTN_NO_TCGEN05 4
 
 /* Bytes of workspace the call needs (>= 0), or a negative status. */
 int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args);

@@ -32,6 +32,7 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -39,6 +40,7 @@
 #include <cudaTypedefs.h>     // PFN_cuTensorMapEncodeTiled
 
 #include "attn_fused_kernel.cuh"
+#include "attn_tc5_kernel.cuh"
 
 namespace nomos {
 
@@ -84,35 +86,48 @@ static bool tma_disabled_by_env() {
     return off;
 }
 
-// {row bytes, rows, batch} view of one byte plane of the cache; box = one 32-row tile.
+// kind 0: {row bytes, rows, batch} view of one byte plane of the cache, box = box_rows rows,
+//         swizzled by the row length (64 or 128 bytes);
+// kind 1: {rows, batch} view of an fp32 row-scale plane, box = box_rows scales.
 struct MapKey {
-    const void *base; int row_bytes, row_stride, rows, batch; long batch_stride;
+    const void *base; int kind, row_bytes, row_stride, rows, batch, box_rows; long batch_stride;
     bool operator==(const MapKey &o) const {
-        return base == o.base && row_bytes == o.row_bytes && row_stride == o.row_stride && rows == o.rows && batch == o.batch &&
-               batch_stride == o.batch_stride;
+        return base == o.base && kind == o.kind && row_bytes == o.row_bytes && row_stride == o.row_stride && rows == o.rows &&
+               batch == o.batch && box_rows == o.box_rows && batch_stride == o.batch_stride;
     }
 };
 static bool encode_plane(const MapKey &k, CUtensorMap *out) {
     // small per-thread cache: a decode loop alternates between a few layer caches
+    constexpr int NCACHE = 64;
     struct Entry { MapKey key; CUtensorMap map; bool used = false; };
-    thread_local Entry cache[16];
+    thread_local Entry cache[NCACHE];
     thread_local int next = 0;
     for (auto &e : cache)
         if (e.used && e.key == k) { *out = e.map; return true; }
     EncodeTiledFn enc = encode_tiled_fn();
     if (enc == nullptr) return false;
-    const cuuint64_t dims[3] = {(cuuint64_t)k.row_bytes, (cuuint64_t)k.rows, (cuuint64_t)k.batch};
-    const cuuint64_t strides[2] = {(cuuint64_t)k.row_stride,
-                                   (cuuint64_t)(k.batch > 1 ? k.batch_stride : (long)k.rows * k.row_stride)};
-    const cuuint32_t box[3] = {(cuuint32_t)k.row_bytes, (cuuint32_t)TILE, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
-    const CUtensorMapSwizzle swz = k.row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     CUtensorMap m;
-    if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(k.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
+    CUresult rc;
+    if (k.kind == 0) {
+        const cuuint64_t dims[3] = {(cuuint64_t)k.row_bytes, (cuuint64_t)k.rows, (cuuint64_t)k.batch};
+        const cuuint64_t strides[2] = {(cuuint64_t)k.row_stride,
+                                       (cuuint64_t)(k.batch > 1 ? k.batch_stride : (long)k.rows * k.row_stride)};
+        const cuuint32_t box[3] = {(cuuint32_t)k.row_bytes, (cuuint32_t)k.box_rows, 1};
+        const CUtensorMapSwizzle swz = k.row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+        rc = enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(k.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        const cuuint64_t dims[2] = {(cuuint64_t)k.rows, (cuuint64_t)k.batch};
+        const cuuint64_t strides[1] = {(cuuint64_t)(k.batch > 1 ? k.batch_stride : (long)k.rows * 4)};
+        const cuuint32_t box[2] = {(cuuint32_t)k.box_rows, 1};
+        rc = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(k.base), dims, strides, box, estr,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (rc != CUDA_SUCCESS) return false;
     Entry &e = cache[next];
-    next = (next + 1) % 16;
+    next = (next + 1) % NCACHE;
     e.key = k; e.map = m; e.used = true;
     *out = m;
     return true;
@@ -253,6 +268,7 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     p.qk_scale_log2 = a.softmax_scale * LOG2E;
     p.q_batch_stride = a.q_batch_stride; p.kv_batch_stride = a.kv_batch_stride;
     p.scale_batch_stride = a.scale_batch_stride; p.out_batch_stride = a.out_batch_stride;
+    p.kvg_magic = a.kvg > 1 ? (unsigned int)(((1ull << 32) + a.kvg - 1) / a.kvg) : 0u;
     p.fault = fault_word();
     if (p.fault == nullptr) { set_error("attn_fused: device fault word unavailable"); return NOMOS_ECUDA; }
     // TMA for whole tiles when the row geometry matches a hardware swizzle pattern and the
@@ -267,8 +283,8 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
         const bool ok = al16(a.k_cache) && al16(a.v_cache) && row_stride % 16 == 0 && (a.batch == 1 || a.kv_batch_stride % 16 == 0) &&
                         rows < (1l << 31);
         if (ok) {
-            const MapKey kk{a.k_cache, C::ROWB, row_stride, (int)rows, a.batch, a.kv_batch_stride};
-            const MapKey kv{a.v_cache, C::ROWB, row_stride, (int)rows, a.batch, a.kv_batch_stride};
+            const MapKey kk{a.k_cache, 0, C::ROWB, row_stride, (int)rows, a.batch, TILE, a.kv_batch_stride};
+            const MapKey kv{a.v_cache, 0, C::ROWB, row_stride, (int)rows, a.batch, TILE, a.kv_batch_stride};
             if (encode_plane(kk, &tm.k) && encode_plane(kv, &tm.v)) {
                 p.use_tma = 1;
                 if (al16(a.k_scales) && al16(a.v_scales) && ((long)a.cache_cap * C::SCB) % 16 == 0 &&
@@ -293,6 +309,171 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     return NOMOS_OK;
 }
 
+// ------------------------------------------------------------------ tcgen05 path
+// int8 KV, head_dim 128, no fused append: the contraction runs on tcgen05 with accumulators in
+// tensor memory (attn_tc5_kernel.cuh).  Everything else stays on the kernel above.
+static bool tc5_disabled_by_env() {
+    static const bool off = [] { const char *e = std::getenv("NOMOS_ATTN_NO_TCGEN05"); return e && e[0] == '1'; }();
+    return off;
+}
+static bool tc5_eligible(const AttnArgs &a) {
+    if (a.kv_fmt != KV_I8 || a.l_hd != 128 || a.new_k != nullptr || a.no_tma || a.no_tcgen05) return false;
+    // more than eight query rows per KV head (verify) currently run faster on the mma.sync kernel
+    static const bool wide = [] { const char *e = std::getenv("NOMOS_ATTN_TCGEN05_VERIFY"); return e && e[0] == '1'; }();
+    if (a.S * a.kvg > 8 && !wide) return false;
+    if (tc5_disabled_by_env() || tma_disabled_by_env() || encode_tiled_fn() == nullptr) return false;
+    const auto al16 = [](const void *x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
+    if (!al16(a.k_cache) || !al16(a.v_cache) || a.cache_hd % 16 != 0) return false;
+    if (a.batch > 1 && a.kv_batch_stride % 16 != 0) return false;
+    if ((long)a.nkv * a.cache_cap >= (1l << 31)) return false;
+    return true;
+}
+
+struct Tc5Plan {
+    int ns, row_groups, tbase, ntiles, splits, tiles_per_split, grows;
+};
+
+template <int NS>
+static int tc5_occupancy() {
+    static int occ[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (occ[dev] == 0) {
+        cudaFuncSetAttribute(tc5::attn_tc5_kernel<NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc5::Cfg<NS>::SMEM_BYTES);
+        cudaFuncSetAttribute(tc5::attn_tc5_kernel<NS>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        int n = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, tc5::attn_tc5_kernel<NS>, tc5::NTHREADS, tc5::Cfg<NS>::SMEM_BYTES);
+        // two CTAs of 256 tensor-memory columns each is all an SM holds
+        // The occupancy query answers 1 for this kernel although two CTAs of 111 KB shared memory,
+        // 256 threads x <=128 registers and 256 tensor-memory columns each do run side by side on an
+        // SM (seen in per-CTA start times); plan with the residency the launch bounds were written for.
+        occ[dev] = std::max(n > 0 ? n : 1, tc5::Cfg<NS>::MIN_CTAS);
+    }
+    return occ[dev];
+}
+
+static Tc5Plan tc5_plan(const AttnArgs &a, int ns, int occupancy) {
+    Tc5Plan pl;
+    const int slots = a.S * a.kvg;
+    pl.ns = ns;
+    pl.row_groups = (slots + ns - 1) / ns;
+    pl.tbase = a.window > 0 ? std::max(0, (a.klen - (a.S - 1)) - a.window) : 0;
+    // the window's keys as up to two runs of ring slots, cut into 128-slot tiles (see WindowGeo)
+    const int ring0 = (int)(((long)a.win_start + pl.tbase) % a.cache_cap);
+    const int len = a.klen - pl.tbase;
+    const int len_a = std::min(len, a.cache_cap - ring0);
+    const int a0 = ring0 & ~3;
+    const int n_a = (ring0 + len_a - a0 + tc5::KT - 1) / tc5::KT;
+    const int n_b = (len - len_a + tc5::KT - 1) / tc5::KT;
+    pl.ntiles = n_a + n_b;
+    pl.grows = a.batch * a.S * a.nh;
+    const int units = a.nkv * a.batch * pl.row_groups;
+    const int slots_gpu = device_info().sm_count * occupancy;
+    int best = 1;
+    if (a.force_splits > 0) {
+        best = std::min(a.force_splits, pl.ntiles);
+    } else {
+        double best_cost = 1e30;
+        int max_splits = std::min(pl.ntiles, 512);
+        if (a.fit_splits_to_ws) {
+            const long per_split = (long)pl.grows * (a.l_hd + 2) * 4;
+            const long fixed = 16 + 8L * units;
+            max_splits = (int)std::max<long>(1, std::min<long>(max_splits, a.workspace ? (a.ws_bytes - fixed) / per_split : 0));
+        }
+        for (int n = 1; n <= max_splits; ++n) {
+            const int tps = (pl.ntiles + n - 1) / n;
+            if ((pl.ntiles + tps - 1) / tps != n) continue;
+            const long ctas = (long)units * n;
+            const long waves = (ctas + slots_gpu - 1) / slots_gpu;
+            // in units of one tile's streaming time per CTA: a wave costs its tiles plus ~3 of start-up
+            // and drain; more than one split adds the partial store, arrival and merge at the end
+            const double cost = (double)waves * (tps + 3.0) + (n > 1 ? 3.0 + 0.03 * n : 0.0);
+            if (cost < best_cost) { best_cost = cost; best = n; }
+        }
+    }
+    pl.tiles_per_split = (pl.ntiles + best - 1) / best;
+    pl.splits = (pl.ntiles + pl.tiles_per_split - 1) / pl.tiles_per_split;
+    return pl;
+}
+
+template <int NS>
+static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *ws_needed) {
+    using C = tc5::Cfg<NS>;
+    const Tc5Plan pl = tc5_plan(a, NS, tc5_occupancy<NS>());
+    const long units = (long)a.nkv * a.batch * pl.row_groups;
+    const long part_bytes = (((long)pl.splits * pl.grows * (a.l_hd + 2) * 4) + 15) / 16 * 16;
+    const long need = pl.splits > 1 ? part_bytes + units * 8 : 0;
+    if (query_ws) { *ws_needed = need; return NOMOS_OK; }
+    if (need > a.ws_bytes || (need > 0 && a.workspace == nullptr)) {
+        set_error("attention workspace too small: need %ld bytes, have %ld", need, a.ws_bytes);
+        return NOMOS_ECAPACITY;
+    }
+    if (pl.splits > MERGE_MAX_G) { set_error("too many splits (%d)", pl.splits); return NOMOS_EUNSUPPORTED; }
+    tc5::TmaMaps4 tm;
+    const int rows = a.nkv * a.cache_cap;
+    const MapKey mk{a.k_cache, 0, 128, a.cache_hd, rows, a.batch, tc5::KT, a.kv_batch_stride};
+    const MapKey mv{a.v_cache, 0, 128, a.cache_hd, rows, a.batch, tc5::KT, a.kv_batch_stride};
+    const MapKey mks{a.k_scales, 1, 4, 4, rows, a.batch, tc5::KT, a.scale_batch_stride};
+    const MapKey mvs{a.v_scales, 1, 4, 4, rows, a.batch, tc5::KT, a.scale_batch_stride};
+    if (!encode_plane(mk, &tm.k) || !encode_plane(mv, &tm.v)) return 1;
+    const auto al16 = [](const void *x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
+    const bool scales_by_tma = al16(a.k_scales) && al16(a.v_scales) && a.cache_cap % 4 == 0 &&
+                               (a.batch == 1 || a.scale_batch_stride % 16 == 0) && encode_plane(mks, &tm.ks) && encode_plane(mvs, &tm.vs);
+    if (!scales_by_tma) { tm.ks = tm.k; tm.vs = tm.k; }       // never dereferenced
+    KParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.use_tma = scales_by_tma ? 3 : 1;
+    p.k_scales = static_cast<const uint8_t *>(a.k_scales);
+    p.v_scales = static_cast<const uint8_t *>(a.v_scales);
+    p.q = static_cast<const uint8_t *>(a.q);
+    p.out = static_cast<uint8_t *>(a.out);
+    const bool direct_export = (pl.splits == 1 && a.partial_out != nullptr);
+    p.partial = direct_export ? a.partial_out : static_cast<float *>(a.workspace);
+    p.write_partial = (pl.splits > 1 || direct_export) ? 1 : 0;
+    p.export_nat = direct_export ? 1 : 0;
+    p.counters = pl.splits > 1 ? reinterpret_cast<unsigned long long *>(static_cast<char *>(a.workspace) + part_bytes) : nullptr;
+    p.epoch = next_epoch();
+    p.splits = pl.splits;
+    p.partial_export = a.partial_out;
+    p.early_rows = a.settled_cache ? std::max(0, a.klen - std::max(a.S, a.n_new)) : 0;
+    p.q_type = a.q_type; p.out_type = a.out_type;
+    p.S = a.S; p.nh = a.nh; p.nkv = a.nkv; p.kvg = a.kvg; p.cache_hd = a.cache_hd; p.cache_cap = a.cache_cap;
+    p.win_start = a.win_start; p.klen = a.klen; p.window = a.window;
+    p.tile0 = pl.tbase; p.ntiles = pl.ntiles; p.tiles_per_split = pl.tiles_per_split;
+    p.row_groups = pl.row_groups; p.grows = pl.grows;
+    p.qk_scale_log2 = a.softmax_scale * LOG2E;
+    p.q_batch_stride = a.q_batch_stride; p.kv_batch_stride = a.kv_batch_stride;
+    p.scale_batch_stride = a.scale_batch_stride; p.out_batch_stride = a.out_batch_stride;
+    p.kvg_magic = a.kvg > 1 ? (unsigned int)(((1ull << 32) + a.kvg - 1) / a.kvg) : 0u;
+    p.fault = fault_word();
+    if (p.fault == nullptr) { set_error("attn_fused: device fault word unavailable"); return NOMOS_ECUDA; }
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pl.splits, a.nkv, a.batch * pl.row_groups);
+    cfg.blockDim = dim3(tc5::NTHREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = st;
+    cfg.attrs = pdl; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, tc5::attn_tc5_kernel<NS>, p, tm);
+    if (e != cudaSuccess) { set_error("attn_tc5 launch: %s", cudaGetErrorString(e)); return NOMOS_ECUDA; }
+    return NOMOS_OK;
+}
+
+// Returns 1 when the tensor maps could not be encoded (the caller then uses the other kernel).
+static int launch_tc5(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
+    const int slots = a.S * a.kvg;
+    if (slots <= 2) return launch_tc5_inst<2>(st, a, q, ws);
+    if (slots <= 4) return launch_tc5_inst<4>(st, a, q, ws);
+    if (slots <= 8) return launch_tc5_inst<8>(st, a, q, ws);
+    if (slots <= 12) return launch_tc5_inst<12>(st, a, q, ws);
+    if (slots <= 16) return launch_tc5_inst<16>(st, a, q, ws);
+    if (slots <= 20) return launch_tc5_inst<20>(st, a, q, ws);
+    return launch_tc5_inst<24>(st, a, q, ws);
+}
+
 template <int FMT, int HD>
 static int dispatch_mt(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
     return pick_mt(a.S * a.kvg) == 1 ? launch_inst<FMT, HD, 1>(st, a, q, ws) : launch_inst<FMT, HD, 3>(st, a, q, ws);
@@ -310,13 +491,29 @@ static int dispatch_hd(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
     }
 }
 
-static int dispatch(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
+static int dispatch_mma(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
     switch (a.kv_fmt) {
         case KV_I8: return dispatch_hd<KV_I8>(st, a, q, ws);
         case KV_I4: return dispatch_hd<KV_I4>(st, a, q, ws);
         case KV_I4B32: return dispatch_hd<KV_I4B32>(st, a, q, ws);
         default: set_error("kv_fmt %d unknown", a.kv_fmt); return NOMOS_EBADARG;
     }
+}
+
+static int dispatch(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
+    if (!tc5_eligible(a)) return dispatch_mma(st, a, q, ws);
+    if (q) {
+        // a later call with the same geometry may carry new rows to append and take the other
+        // kernel: report what either needs
+        long w_tc = 0, w_mma = 0;
+        const int rc1 = launch_tc5(st, a, true, &w_tc);
+        const int rc2 = dispatch_mma(st, a, true, &w_mma);
+        if (rc2 != NOMOS_OK) return rc2;
+        *ws = rc1 == NOMOS_OK ? std::max(w_tc, w_mma) : w_mma;
+        return NOMOS_OK;
+    }
+    const int rc = launch_tc5(st, a, false, nullptr);
+    return rc == 1 ? dispatch_mma(st, a, false, nullptr) : rc;
 }
 
 }  // namespace
@@ -339,6 +536,15 @@ int read_attn_faults(unsigned int *out, bool clear) {
 }
 
 #ifdef NOMOS_TIMELINE
+extern "C" __attribute__((visibility("default"))) int nomos_debug_merge(unsigned long long *host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, fused::g_merge_tl, sizeof(unsigned long long) * 320 * 8);
+}
+extern "C" __attribute__((visibility("default"))) int nomos_debug_tc5_cta(unsigned long long *host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, tc5::g_tc5_cta, sizeof(unsigned long long) * 320 * 8);
+}
+extern "C" __attribute__((visibility("default"))) int nomos_debug_tc5_timeline(unsigned long long *host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, tc5::g_tc5_tl, sizeof(unsigned long long) * 320 * 40 * 6);
+}
 extern "C" __attribute__((visibility("default"))) int nomos_debug_timeline(unsigned long long *host_out, int n_ctas) {
     return (int)cudaMemcpyFromSymbol(host_out, fused::g_timeline, sizeof(unsigned long long) * 6 * n_ctas);
 }

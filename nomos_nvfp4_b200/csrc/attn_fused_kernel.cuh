@@ -94,9 +94,15 @@ struct KParams {
     uint8_t *k_cache_w, *v_cache_w, *k_scales_w, *v_scales_w;   // writable aliases of the cache
     int n_new, new_stride, new_base_pos;
     long q_batch_stride, kv_batch_stride, scale_batch_stride, out_batch_stride;
+    unsigned int kvg_magic;  // ceil(2^32 / kvg), 0 for kvg == 1: idx / kvg = umulhi(idx, kvg_magic)
     int use_tma;             // bit 0: whole tiles come by TMA; bit 1: their scales by bulk copy
     unsigned int *fault;     // sticky device word: bit 0 = a tile never arrived within the wait limit
 };
+
+// idx / kvg for the small non-negative indices used here, without the division routine.
+__device__ __forceinline__ int div_kvg(const KParams &p, int idx) {
+    return p.kvg_magic ? (int)__umulhi((unsigned)idx, p.kvg_magic) : idx;
+}
 
 __device__ __forceinline__ float load_q(const uint8_t *q, int q_type, long idx) {
     return q_type == ET_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(q)[idx])
@@ -127,8 +133,17 @@ __device__ __forceinline__ unsigned long long gtime() {
             if (cta < 4096) g_timeline[cta][slot] = gtime();                                                \
         }                                                                                                   \
     } while (0)
+__device__ unsigned long long g_merge_tl[320][8];
+#define MERGE_MARK(slot)                                                                                    \
+    do {                                                                                                    \
+        if (threadIdx.x == 0) {                                                                             \
+            const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                 \
+            if (cta < 320) g_merge_tl[cta][slot] = gtime();                                                 \
+        }                                                                                                   \
+    } while (0)
 #else
 #define NOMOS_MARK(slot) do {} while (0)
+#define MERGE_MARK(slot) do {} while (0)
 #endif
 
 __device__ __forceinline__ void mma_u8u8_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -194,6 +209,180 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\
 
 namespace nomos {
 namespace fused {
+
+// In-kernel merge across the splits of one (batch, KV head, row group) unit, called by every
+// thread of a CTA after its partial (o, m, l) rows are stored.  The last CTA of the unit to
+// arrive merges the unit's rows; the others return.  `scratch` is shared memory the CTA no
+// longer needs, at least 8 * NSLOT * splits bytes.
+template <int NSLOT, int HD, int NTHR, int GB = 8>
+__device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t *scratch, int b, int kvh, int rg) {
+    if (p.counters == nullptr) return;
+
+    // ------------------------------------------- in-kernel merge across the splits
+    // Arrival counting without a zeroed workspace (see the tag below).
+    __shared__ int s_last;
+    MERGE_MARK(0);
+    __syncthreads();                      // all partial stores of this CTA are issued
+    MERGE_MARK(1);
+    if (threadIdx.x == 0) {
+        __threadfence();                  // cumulative: orders the whole CTA's stores before the arrival
+        unsigned long long *ctr = p.counters + ((size_t)blockIdx.z * gridDim.y + blockIdx.y);
+        // The word is (tag << 16 | arrivals).  The merging CTA leaves it tagged with zero arrivals, so
+        // the common case is a single atomic add.  A word without the tag has never been used by this
+        // library (the workspace is caller-owned and arrives uninitialised): the add went to garbage,
+        // and the arrivals that find garbage install a tagged word with compare-and-swap, which only
+        // fails when another arrival made progress.
+        constexpr unsigned long long TAG = 0x6e6f6d6f7341ull;
+        unsigned long long old = atomicAdd(ctr, 1ull);
+        int arrived = -1;
+        if ((old >> 16) == TAG) {
+            arrived = (int)(old & 0xffffull) + 1;
+        } else {
+            for (int tries = 0; tries < (1 << 16); ++tries) {    // bounded: gives up rather than spin forever
+                const unsigned long long cur = *reinterpret_cast<volatile unsigned long long *>(ctr);
+                if ((cur >> 16) == TAG) {
+                    old = atomicAdd(ctr, 1ull);
+                    if ((old >> 16) == TAG) { arrived = (int)(old & 0xffffull) + 1; break; }
+                } else if (atomicCAS(ctr, cur, (TAG << 16) | 1ull) == cur) {
+                    arrived = 1;
+                    break;
+                }
+            }
+        }
+        if (arrived == p.splits) *ctr = TAG << 16;                // clean for the next launch on this workspace
+        s_last = (arrived == p.splits);
+    }
+    __syncthreads();
+    MERGE_MARK(2);
+    if (!s_last) return;
+    __threadfence();
+    NOMOS_MARK(5);
+    MERGE_MARK(3);
+
+    // The last CTA of the unit merges its rows.  Phase A stages every split's (m, l) in shared
+    // memory; phase B (a warp per row) turns them into weights 2^(m_i - m*) and the merged
+    // denominator; phase C gives each thread (row, dim) elements and streams the splits' partial
+    // outputs from L2 with many independent loads in flight.
+    const int G = p.splits;
+    float *ms = reinterpret_cast<float *>(scratch);      // [NSLOT][G]  m of each split, then its weight
+    float *ls = ms + NSLOT * G;                          // [NSLOT][G]  l of each split
+    __shared__ float s_mstar[NSLOT], s_lstar[NSLOT];
+    const int first = rg * NSLOT;
+    const int nrows = min(NSLOT, p.S * p.kvg - first);   // valid slots of this row group
+    const size_t rstride = (size_t)p.grows * (HD + 2);
+    auto grow_of = [&](int sl) {
+        const int idx = first + sl;
+        const int r = div_kvg(p, idx);
+        return ((long)b * p.S + r) * p.nh + kvh * p.kvg + (idx - r * p.kvg);
+    };
+    // Small merges (the common decode case): every thread owns one (row, dim) and requests its
+    // G partial outputs BEFORE the (m, l) staging barrier, so both sets of L2 loads are in flight
+    // together (one round trip instead of two).
+    constexpr int GFAST = 32;
+    const bool fast = (G <= GFAST) && (nrows * HD <= NTHR);
+    float pre[GFAST];
+    if (fast && (int)threadIdx.x < nrows * HD) {
+        const int sl = threadIdx.x / HD, d = threadIdx.x - sl * HD;
+        const float *base = p.partial + (size_t)grow_of(sl) * (HD + 2) + d;
+#pragma unroll
+        for (int i = 0; i < GFAST; ++i) pre[i] = __ldcg(base + (size_t)min(i, G - 1) * rstride);   // unconditional: batches freely
+    }
+    for (int e = threadIdx.x; e < nrows * G; e += NTHR) {
+        const int sl = e / G, i = e - sl * G;
+        const float *pr = p.partial + (size_t)i * rstride + (size_t)grow_of(sl) * (HD + 2);
+        const float li = __ldcg(pr + HD + 1);
+        ls[sl * G + i] = li;
+        ms[sl * G + i] = li > 0.0f ? __ldcg(pr + HD) : -CUDART_INF_F;
+    }
+    __syncthreads();
+    MERGE_MARK(4);
+    {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int sl = warp; sl < nrows; sl += NTHR / 32) {
+            float m = -CUDART_INF_F;
+            for (int i = lane; i < G; i += 32) m = fmaxf(m, ms[sl * G + i]);
+            m = warp_max(m);
+            if (m == -CUDART_INF_F) m = 0.0f;            // no split saw a key for this row: weights are all 0
+            float lp = 0.0f;
+            for (int i = lane; i < G; i += 32) {
+                const float w = ex2f(ms[sl * G + i] - m);
+                lp = fmaf(w, ls[sl * G + i], lp);
+                ms[sl * G + i] = w;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) lp += __shfl_xor_sync(0xffffffffu, lp, o);
+            if (lane == 0) { s_mstar[sl] = m; s_lstar[sl] = lp; }
+        }
+    }
+    __syncthreads();
+    MERGE_MARK(5);
+    auto emit = [&](int sl, int d, float o) {
+        const long grow = grow_of(sl);
+        const float lstar = s_lstar[sl];
+        if (p.partial_export) {
+            p.partial_export[(size_t)grow * (HD + 2) + d] = o;
+            if (d == 0) {
+                p.partial_export[(size_t)grow * (HD + 2) + HD] = lstar > 0.0f ? s_mstar[sl] * LN2 : 0.0f;
+                p.partial_export[(size_t)grow * (HD + 2) + HD + 1] = lstar;
+            }
+        } else {
+            const float v = lstar > 0.0f ? o / lstar : 0.0f;
+            const int idx = first + sl;
+            const int r = div_kvg(p, idx);
+            const long oi = b * p.out_batch_stride + ((long)r * p.nh + kvh * p.kvg + (idx - r * p.kvg)) * HD + d;
+            if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
+            else reinterpret_cast<float *>(p.out)[oi] = v;
+        }
+    };
+    if (fast) {
+        if ((int)threadIdx.x < nrows * HD) {
+            const int sl = threadIdx.x / HD, d = threadIdx.x - sl * HD;
+            float o0 = 0.0f, o1 = 0.0f;
+#pragma unroll
+            for (int k = 0; k < GFAST; k += 2) {
+                if (k < G) o0 = fmaf(ms[sl * G + k], pre[k], o0);
+                if (k + 1 < G) o1 = fmaf(ms[sl * G + k + 1], pre[k + 1], o1);
+            }
+            emit(sl, d, o0 + o1);
+        }
+        return;
+    }
+    // General case: four elements per thread at a time, GB splits each, all loads issued before use.
+    constexpr int EL = 4;
+    const int total = nrows * HD;
+    for (int e0 = threadIdx.x; e0 < total; e0 += EL * NTHR) {
+        const float *base[EL];
+        int sl[EL];
+        float o[EL];
+#pragma unroll
+        for (int j = 0; j < EL; ++j) {
+            const int e = min(e0 + j * NTHR, total - 1);
+            sl[j] = e / HD;
+            base[j] = p.partial + (size_t)grow_of(sl[j]) * (HD + 2) + (e - sl[j] * HD);
+            o[j] = 0.0f;
+        }
+        for (int i0 = 0; i0 < G; i0 += GB) {
+            float v[EL][GB];
+#pragma unroll
+            for (int j = 0; j < EL; ++j)
+#pragma unroll
+                for (int k = 0; k < GB; ++k) v[j][k] = __ldcg(base[j] + (size_t)min(i0 + k, G - 1) * rstride);   // unconditional: batches freely
+#pragma unroll
+            for (int j = 0; j < EL; ++j)
+#pragma unroll
+                for (int k = 0; k < GB; ++k) {
+                    const float w = i0 + k < G ? ms[sl[j] * G + i0 + k] : 0.0f;
+                    o[j] = fmaf(w, v[j][k], o[j]);
+                }
+        }
+#pragma unroll
+        for (int j = 0; j < EL; ++j) {
+            const int e = e0 + j * NTHR;
+            if (e < total) emit(sl[j], e - sl[j] * HD, o[j]);
+        }
+    }
+    MERGE_MARK(6);
+}
 
 template <int FMT, int HD, int MT>
 __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
@@ -363,7 +552,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
     for (int qi = 0; qi < QITER; ++qi) {
         const int sl = warp + qi * NWARP;
         const int idx = rg * C::NSLOT + sl;
-        const int r = idx / p.kvg, j = idx % p.kvg;
+        const int r = div_kvg(p, idx), j = idx - r * p.kvg;
         const bool valid = sl < C::NSLOT && r < p.S;
 #pragma unroll
         for (int i = 0; i < HD / 32; ++i)
@@ -377,7 +566,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
         const int sl = warp + qi * NWARP;
         if (sl >= C::NSLOT) break;
         const int idx = rg * C::NSLOT + sl;
-        const int r = idx / p.kvg;
+        const int r = div_kvg(p, idx);
         const bool valid = r < p.S;
         float amax = 0.0f;
 #pragma unroll
@@ -828,7 +1017,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
 
     for (int sl = 0; sl < C::NSLOT; ++sl) {
         const int idx = rg * C::NSLOT + sl;
-        const int r = idx / p.kvg, j = idx % p.kvg;
+        const int r = div_kvg(p, idx), j = idx - r * p.kvg;
         if (r >= p.S) break;
         float mstar = M_INIT;
 #pragma unroll
@@ -861,112 +1050,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
         }
     }
     NOMOS_MARK(4);
-    if (p.counters == nullptr) return;
-
-    // ------------------------------------------- in-kernel merge across the splits
-    // Arrival counting without a zeroed workspace: the counter word carries the launch's
-    // epoch, so whatever an earlier launch (or nobody) left there counts as zero arrivals.
-    __shared__ int s_last;
-    __syncthreads();                      // all partial stores of this CTA are issued
-    if (threadIdx.x == 0) {
-        __threadfence();                  // cumulative: orders the whole CTA's stores before the arrival
-        unsigned long long *ctr = p.counters + ((size_t)blockIdx.z * gridDim.y + blockIdx.y);
-        unsigned long long old = *reinterpret_cast<volatile unsigned long long *>(ctr);
-        int arrived = -1;
-        for (int tries = 0; tries < (1 << 20); ++tries) {        // bounded: gives up rather than spin forever
-            const unsigned long long cnt = (old >> 16) == p.epoch ? (old & 0xffffull) : 0ull;
-            const unsigned long long prev = atomicCAS(ctr, old, (p.epoch << 16) | (cnt + 1));
-            if (prev == old) { arrived = (int)cnt + 1; break; }
-            old = prev;
-        }
-        s_last = (arrived == p.splits);
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    NOMOS_MARK(5);
-
-    // The last CTA of the unit merges its rows.  Phase A stages every split's (m, l) in shared
-    // memory; phase B gives each thread one (row, dim) and streams the splits' partial outputs
-    // from L2 with independent loads in flight.
-    constexpr int NTHR = NWARP * 32;
-    const int G = p.splits;
-    float *ms = reinterpret_cast<float *>(pipe);            // [NSLOT][G]  m of each split (-inf if empty)
-    float *ls = ms + C::NSLOT * G;                          // [NSLOT][G]  l of each split
-    const int first = rg * C::NSLOT;
-    const int nrows = min(C::NSLOT, p.S * p.kvg - first);   // valid slots of this row group
-    const size_t rstride = (size_t)p.grows * (HD + 2);
-    auto grow_of = [&](int sl) {
-        const int idx = first + sl;
-        return ((long)b * p.S + idx / p.kvg) * p.nh + kvh * p.kvg + idx % p.kvg;
-    };
-    // Small merges (the common decode case): every thread owns one (row, dim) and requests its
-    // G partial outputs BEFORE the (m, l) staging barrier, so both sets of L2 loads are in flight
-    // together (one round trip instead of two).
-    constexpr int GFAST = 16;
-    const bool fast = (G <= GFAST) && (nrows * HD <= NTHR);
-    float pre[GFAST];
-    if (fast && (int)threadIdx.x < nrows * HD) {
-        const int sl = threadIdx.x / HD, d = threadIdx.x - sl * HD;
-        const float *base = p.partial + (size_t)grow_of(sl) * (HD + 2) + d;
-#pragma unroll
-        for (int i = 0; i < GFAST; ++i) pre[i] = i < G ? __ldcg(base + (size_t)i * rstride) : 0.0f;
-    }
-    for (int e = threadIdx.x; e < nrows * G; e += NTHR) {
-        const int sl = e / G, i = e - sl * G;
-        const float *pr = p.partial + (size_t)i * rstride + (size_t)grow_of(sl) * (HD + 2);
-        const float li = __ldcg(pr + HD + 1);
-        ls[sl * G + i] = li;
-        ms[sl * G + i] = li > 0.0f ? __ldcg(pr + HD) : -CUDART_INF_F;
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < nrows * HD; e += NTHR) {
-        const int sl = e / HD, d = e - sl * HD;
-        const long grow = grow_of(sl);
-        const float *base = p.partial + (size_t)grow * (HD + 2) + d;
-        float mstar = -CUDART_INF_F;
-        for (int i = 0; i < G; ++i) mstar = fmaxf(mstar, ms[sl * G + i]);
-        if (mstar == -CUDART_INF_F) mstar = 0.0f;           // no split saw a key for this row: weights are all 0
-        float lstar = 0.0f, o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
-        int i = 0;
-        if (fast) {
-#pragma unroll
-            for (int k = 0; k < GFAST; ++k)
-                if (k < G) {
-                    const float w = ex2f(ms[sl * G + k] - mstar);
-                    lstar = fmaf(w, ls[sl * G + k], lstar);
-                    o0 = fmaf(w, pre[k], o0);
-                }
-            i = G;
-        }
-        for (; i + 4 <= G; i += 4) {
-            const float v0 = __ldcg(base + (size_t)i * rstride), v1 = __ldcg(base + (size_t)(i + 1) * rstride);
-            const float v2 = __ldcg(base + (size_t)(i + 2) * rstride), v3 = __ldcg(base + (size_t)(i + 3) * rstride);
-            const float w0 = ex2f(ms[sl * G + i] - mstar), w1 = ex2f(ms[sl * G + i + 1] - mstar);
-            const float w2 = ex2f(ms[sl * G + i + 2] - mstar), w3 = ex2f(ms[sl * G + i + 3] - mstar);
-            lstar += w0 * ls[sl * G + i] + w1 * ls[sl * G + i + 1] + w2 * ls[sl * G + i + 2] + w3 * ls[sl * G + i + 3];
-            o0 = fmaf(w0, v0, o0); o1 = fmaf(w1, v1, o1); o2 = fmaf(w2, v2, o2); o3 = fmaf(w3, v3, o3);
-        }
-        for (; i < G; ++i) {
-            const float w = ex2f(ms[sl * G + i] - mstar);
-            lstar += w * ls[sl * G + i];
-            o0 = fmaf(w, __ldcg(base + (size_t)i * rstride), o0);
-        }
-        const float o = (o0 + o1) + (o2 + o3);
-        if (p.partial_export) {
-            p.partial_export[(size_t)grow * (HD + 2) + d] = o;
-            if (d == 0) {
-                p.partial_export[(size_t)grow * (HD + 2) + HD] = lstar > 0.0f ? mstar * LN2 : 0.0f;
-                p.partial_export[(size_t)grow * (HD + 2) + HD + 1] = lstar;
-            }
-        } else {
-            const float v = lstar > 0.0f ? o / lstar : 0.0f;
-            const int idx = first + sl;
-            const long oi = b * p.out_batch_stride + ((long)(idx / p.kvg) * p.nh + kvh * p.kvg + idx % p.kvg) * HD + d;
-            if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
-            else reinterpret_cast<float *>(p.out)[oi] = v;
-        }
-    }
+    merge_splits_in_kernel<C::NSLOT, HD, NWARP * 32>(p, pipe, b, kvh, rg);
 }
 
 // Merge G partial triples per row.  partials [G][rows][hd+2] = (o.., m, l); m in log2

@@ -1,0 +1,627 @@
+// Decode / verify attention over the int8 KV ring on the fifth-generation tensor cores
+// (tcgen05 + tensor memory), head_dim 128, sm_100a.  See attn_tc5.cu for the host side.
+//
+// The contraction is laid out so that the 128-row M dimension of tcgen05.mma is always full,
+// however few query rows there are:
+//   QK:  S^T[128 keys x N] = K_tile[128 keys x 128 B] (A, K-major, exactly the bytes TMA wrote)
+//                            x Qlimbs[N x 128 B]      (B, K-major)
+//   PV:  O^T[128 dims x N] = V_tile^T[128 dims x 128 keys] (A, MN-major: the same [key][dim]
+//                            bytes TMA wrote, read transposed by the tensor core)
+//                            x Plimbs[N x 128 keys]   (B, K-major)
+// N = 2 x (padded slots): column s holds the high limb of slot s (a query row x group head),
+// column NSP+s the low limb, for the 15-bit fixed-point query and the 16-bit fixed-point softmax
+// weights alike, so every product is an exact int32.
+// Accumulators live in tensor memory: warp w of the four softmax warps reads TMEM lanes
+// 32w..32w+31, i.e. thread = one key of the tile for S^T, thread = one output dim for O^T.
+//
+// Roles (256 threads): warps 0-3 softmax + output, warp 4 lane 0 TMA producer, warp 5 lane 0
+// MMA issuer, warps 6-7 only help in the split merge.  Every wait is an mbarrier wait with a
+// time limit; a wait that runs out raises the CTA's abort flag and a bit in the device fault
+// word, every role leaves its loop, tensor memory is freed and the CTA exits.
+#pragma once
+
+#include "attn_fused_kernel.cuh"
+
+namespace nomos {
+namespace tc5 {
+
+using fused::KParams;
+using fused::LOG2E;
+using fused::LN2;
+using fused::M_INIT;
+using fused::Q_FIX_MAX;
+using fused::P_FIX;
+using fused::LAZY_MAX;
+using fused::RND_MAGIC;
+
+constexpr int KT = 128;                      // keys per tile = M of the QK MMA
+constexpr int HD = 128;                      // head dim = M of the PV MMA
+constexpr int TILE_BYTES = KT * HD;          // one K or V tile (int8)
+constexpr int SCALE_BYTES = KT * 4;          // one tile's fp32 row scales
+constexpr int NTHREADS = 256;
+constexpr int TMEM_COLS = 256;               // S0 | S1 | O0 | O1, 64 columns each
+constexpr float LG2_VS_MIN = -64.0f;
+
+#ifdef NOMOS_TIMELINE
+// Debug builds only: per-CTA, per-tile wall-clock marks (ns) of the softmax role.
+__device__ unsigned long long g_tc5_tl[320][40][6];
+#define TC5_MARK(tile, slot)                                                                     \
+    do {                                                                                         \
+        const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);         \
+        if (threadIdx.x == 0 && cta_ < 320 && (tile) < 40) g_tc5_tl[cta_][tile][slot] = fused::gtime(); \
+    } while (0)
+__device__ unsigned long long g_tc5_cta[320][8];
+#define TC5_CTA_MARK(slot)                                                                       \
+    do {                                                                                         \
+        const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);         \
+        if (threadIdx.x == 0 && cta_ < 320) g_tc5_cta[cta_][slot] = fused::gtime();              \
+    } while (0)
+#else
+#define TC5_MARK(tile, slot) do {} while (0)
+#define TC5_CTA_MARK(slot) do {} while (0)
+#endif
+
+template <int NS>
+struct Cfg {
+    static constexpr int NSP = (NS + 7) / 8 * 8;                     // slots padded to the MMA's N granularity
+    static constexpr int N = 2 * NSP;
+    static constexpr int NSTG = NS <= 8 ? 3 : 6;                     // 3 stages: two CTAs per SM
+    static constexpr int MIN_CTAS = NS <= 8 ? 2 : 1;
+    static constexpr int QP_BYTES = N * 128;                         // Q limbs, or one buffer of P limbs
+    static constexpr int OFF_SCALES = NSTG * 2 * TILE_BYTES;
+    static constexpr int OFF_Q = OFF_SCALES + NSTG * 2 * SCALE_BYTES;
+    static constexpr int OFF_P = OFF_Q + QP_BYTES;
+    static constexpr int OFF_XCH = OFF_P + 2 * QP_BYTES;             // [2][NSP][4] warp maxima
+    static constexpr int OFF_SLOT = OFF_XCH + 2 * NSP * 16;          // qscale[NSP], lo[NSP], hi[NSP]
+    static constexpr int OFF_BAR = OFF_SLOT + NSP * 12;
+    static constexpr int NBAR = 2 * NSTG + 11;                       // full, empty, s_ready, p_ready, o_ready, o_free, xch, q_ready
+    static constexpr int OFF_MISC = OFF_BAR + NBAR * 8;              // tmem base, abort flag
+    static constexpr int SMEM_BYTES = 1024 + OFF_MISC + 16;
+    static_assert(OFF_BAR % 8 == 0, "mbarriers need 8-byte alignment");
+    static_assert(OFF_Q % 1024 == 0 && QP_BYTES % 1024 == 0, "operand tiles sit on swizzle-pattern boundaries");
+};
+
+struct TmaMaps4 {
+    CUtensorMap k, v;        // {row bytes, nkv * cache_cap rows, batch}, box {128 B, 128 rows, 1}, 128B swizzle
+    CUtensorMap ks, vs;      // {nkv * cache_cap fp32, batch}, box {128, 1}
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+                 "l"(reinterpret_cast<unsigned long long>(map)), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(base), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+// D[tmem] (+)= A[smem] * B[smem], int8 operands, int32 accumulate; issued by one thread.
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The mbarrier gets one arrival when every MMA this thread issued so far has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+// This warp's 32 TMEM lanes x COUNT consecutive 32-bit columns: thread t gets lane t's row.
+template <int COUNT>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, int (&r)[COUNT]) {
+    static_assert(COUNT == 2 || COUNT == 4 || COUNT == 8, "column count");
+    if constexpr (COUNT == 2)
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(taddr));
+    else if constexpr (COUNT == 4)
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];\n"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                     : "r"(taddr));
+    else
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                     : "r"(taddr));
+}
+// int -> float for |x| < 2^22 on the integer and FMA pipes (the conversion instruction shares the
+// quarter-rate unit with ex2, the busiest one here): x + 1.5 * 2^23 read as a float, minus 1.5 * 2^23.
+__device__ __forceinline__ float i2f_small(int x) { return __int_as_float(x + 0x4B400000) - 12582912.0f; }
+__device__ __forceinline__ int redux_max(int v) {
+    int r;
+    asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;\n" : "=r"(r) : "r"(v));
+    return r;
+}
+// float <-> int with the same ordering (an involution)
+__device__ __forceinline__ int f2ord(float f) {
+    const int k = __float_as_int(f);
+    return k ^ ((k >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float ord2f(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
+
+// Shared-memory matrix descriptors (sm_100 format: version 1, 128-byte swizzle, 8-row groups of
+// 128-byte rows 1024 bytes apart).  K-major: rows = M/N index, the 128 bytes of a row = K.
+// MN-major: the 128 bytes of a row = 128 consecutive M indices, rows = K index.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: int32 accumulate, M = 128, given N, operand signedness and A major-ness.
+__device__ __forceinline__ uint32_t make_idesc(int n, bool a_signed, bool b_signed, bool a_mn_major) {
+    return (2u << 4) | ((a_signed ? 1u : 0u) << 7) | ((b_signed ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+           ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+// Bounded mbarrier wait shared by all roles of a CTA: false = gave up (own time limit of about a
+// second, or another role already raised the abort flag).
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned int *fault) {
+    if (fused::mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        if (fused::mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > 1000000000ull) {
+            *abort_flag = 1;
+            atomicOr(fault, 2u);
+            return false;
+        }
+    }
+}
+
+// Window geometry in slot space.  The keys of the window [tbase, klen) live in up to two runs of
+// consecutive ring slots; tiles are 128 slots, the first of a run starting at a multiple of four
+// slots (16-byte rule of the scale copies), so a tile's first rows may precede the run.
+struct TileGeo {
+    int slot0;      // ring slot of the tile's row 0
+    int t0;         // window index of row 0 (may be negative or below tbase)
+    int t_lo, t_hi; // rows with window index in [t_lo, t_hi) belong to the tile
+};
+struct WindowGeo {
+    int ring0, len_a, a0, n_a, tbase, klen;
+    __device__ __forceinline__ TileGeo tile(int j) const {
+        TileGeo g;
+        if (j < n_a) {
+            g.slot0 = a0 + j * KT;
+            g.t0 = tbase + g.slot0 - ring0;
+            g.t_lo = tbase;
+            g.t_hi = tbase + len_a;
+        } else {
+            g.slot0 = (j - n_a) * KT;
+            g.t0 = tbase + len_a + g.slot0;
+            g.t_lo = tbase + len_a;
+            g.t_hi = klen;
+        }
+        return g;
+    }
+};
+
+template <int NS>
+__global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
+    attn_tc5_kernel(const KParams p, const __grid_constant__ TmaMaps4 tm) {
+    using C = Cfg<NS>;
+    constexpr int NSP = C::NSP, NSTG = C::NSTG;
+    constexpr int CH = NS < 4 ? NS : 4;              // slots per TMEM load
+    constexpr int NCH = NS / CH;
+    static_assert(NS == 2 || NS % 4 == 0, "slot count");
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const uint32_t sm_u32 = smem_u32(sm);
+    float *slot_qscale = reinterpret_cast<float *>(sm + C::OFF_SLOT);
+    int *slot_lo = reinterpret_cast<int *>(sm + C::OFF_SLOT + NSP * 4);
+    int *slot_hi = reinterpret_cast<int *>(sm + C::OFF_SLOT + NSP * 8);
+    int *xch = reinterpret_cast<int *>(sm + C::OFF_XCH);                    // [2][NSP][4]
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(sm + C::OFF_MISC);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(sm + C::OFF_MISC + 4);
+    const uint32_t bar0 = sm_u32 + C::OFF_BAR;
+    auto bar_full = [&](int s) { return bar0 + 8 * s; };
+    auto bar_empty = [&](int s) { return bar0 + 8 * (NSTG + s); };
+    auto bar_s_ready = [&](int i) { return bar0 + 8 * (2 * NSTG + i); };
+    auto bar_p_ready = [&](int i) { return bar0 + 8 * (2 * NSTG + 2 + i); };
+    auto bar_o_ready = [&](int i) { return bar0 + 8 * (2 * NSTG + 4 + i); };
+    auto bar_o_free = [&](int i) { return bar0 + 8 * (2 * NSTG + 6 + i); };
+    auto bar_xch = [&](int i) { return bar0 + 8 * (2 * NSTG + 8 + i); };
+    const uint32_t bar_q_ready = bar0 + 8 * (2 * NSTG + 10);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int split = blockIdx.x, kvh = blockIdx.y;
+    const int b = blockIdx.z / p.row_groups, rg = blockIdx.z % p.row_groups;
+    TC5_CTA_MARK(0);
+
+    // ------------------------------------------------------------ window and tile schedule
+    WindowGeo wg;
+    wg.tbase = p.tile0;                               // first window index any query row needs
+    wg.klen = p.klen;
+    wg.ring0 = (p.win_start + wg.tbase) % p.cache_cap;
+    wg.len_a = min(p.klen - wg.tbase, p.cache_cap - wg.ring0);
+    wg.a0 = wg.ring0 & ~3;
+    wg.n_a = (wg.ring0 + wg.len_a - wg.a0 + KT - 1) / KT;
+    const int tile_begin = split * p.tiles_per_split;
+    const int tile_end = min(p.ntiles, tile_begin + p.tiles_per_split);
+    const int my_n = max(0, tile_end - tile_begin);
+    const int row_base = kvh * p.cache_cap;          // this head's first row in the {rows} dimension of the maps
+    // fp32 row scales ride TMA when every tile's first scale sits on a 16-byte boundary; otherwise
+    // each softmax thread fetches its key's two scales one tile ahead with plain loads
+    const bool scales_by_tma = (p.use_tma & 2) != 0;
+
+    // ------------------------------------------------------------ set-up
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+#pragma unroll
+        for (int s = 0; s < NSTG; ++s) { fused::mbar_init(bar_full(s), 1); fused::mbar_init(bar_empty(s), 1); }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            fused::mbar_init(bar_s_ready(i), 1);
+            fused::mbar_init(bar_p_ready(i), 128);
+            fused::mbar_init(bar_o_ready(i), 1);
+            fused::mbar_init(bar_o_free(i), 128);
+            fused::mbar_init(bar_xch(i), 128);
+        }
+        fused::mbar_init(bar_q_ready, 128);
+        fused::fence_mbar_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(sm_u32 + C::OFF_MISC, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    TC5_CTA_MARK(1);
+    // Programmatic dependent launch: every thread waits for the stream predecessor before it lets
+    // this grid's own dependents be scheduled (the producer thread first requests the tiles the
+    // caller declared settled).
+    if (!(warp == 4 && lane == 0)) {
+        fused::pdl_wait();
+        fused::pdl_launch_dependents();
+    }
+
+    if (warp == 4) {
+        // =========================================================== TMA producer
+        if (lane == 0) {
+            bool waited = false;
+            for (int i = 0; i < my_n; ++i) {
+                const int st = i % NSTG;
+                const TileGeo g = wg.tile(tile_begin + i);
+                // rows the caller declared settled may be requested before the stream predecessor is done
+                if (!waited && g.t0 + KT > p.early_rows) { fused::pdl_wait(); fused::pdl_launch_dependents(); waited = true; }
+                if (i >= NSTG && !wait_or_abort(bar_empty(st), ((i / NSTG) - 1) & 1, abort_flag, p.fault)) break;
+                const uint32_t kdst = sm_u32 + st * 2 * TILE_BYTES;
+                const uint32_t sdst = sm_u32 + C::OFF_SCALES + st * 2 * SCALE_BYTES;
+                fused::mbar_expect_tx(bar_full(st), 2 * TILE_BYTES + (scales_by_tma ? 2 * SCALE_BYTES : 0));
+                fused::tma_load_tile(kdst, &tm.k, row_base + g.slot0, b, bar_full(st));
+                fused::tma_load_tile(kdst + TILE_BYTES, &tm.v, row_base + g.slot0, b, bar_full(st));
+                if (scales_by_tma) {
+                    tma_load_2d(sdst, &tm.ks, row_base + g.slot0, b, bar_full(st));
+                    tma_load_2d(sdst + SCALE_BYTES, &tm.vs, row_base + g.slot0, b, bar_full(st));
+                }
+            }
+            if (!waited) { fused::pdl_wait(); fused::pdl_launch_dependents(); }
+        }
+        __syncwarp();
+    } else if (warp == 5) {
+        // =========================================================== MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_qk = make_idesc(C::N, true, true, false);
+            const uint32_t idesc_pv = make_idesc(C::N, true, false, true);
+            const uint64_t qdesc = smem_desc_sw128(sm_u32 + C::OFF_Q);
+            bool go = wait_or_abort(bar_q_ready, 0, abort_flag, p.fault);
+            for (int i = 0; go && i <= my_n; ++i) {
+                if (i < my_n) {
+                    // S^T[i&1] = K_i x Q^T.  The buffer's previous reader (tile i-2) was done before
+                    // p_ready(i-2), which this thread observed when it issued PV(i-2).
+                    const int st = i % NSTG;
+                    if (!wait_or_abort(bar_full(st), (i / NSTG) & 1, abort_flag, p.fault)) break;
+                    tc_fence_after();
+                    const uint64_t kdesc = smem_desc_sw128(sm_u32 + st * 2 * TILE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < HD / 32; ++k)      // 32 bytes of K per instruction: +32 B on both operands
+                        umma_i8(tmem_base + 64 * (i & 1), kdesc + 2 * k, qdesc + 2 * k, idesc_qk, k > 0);
+                    umma_commit(bar_s_ready(i & 1));
+                }
+                if (i >= 1) {
+                    // O^T[j&1] = V_j^T x P_j^T
+                    const int j = i - 1, st = j % NSTG;
+                    if (!wait_or_abort(bar_p_ready(j & 1), (j >> 1) & 1, abort_flag, p.fault)) break;
+                    if (j >= 2 && !wait_or_abort(bar_o_free(j & 1), ((j - 2) >> 1) & 1, abort_flag, p.fault)) break;
+                    tc_fence_after();
+                    const uint64_t vdesc = smem_desc_sw128(sm_u32 + st * 2 * TILE_BYTES + TILE_BYTES);
+                    const uint64_t pdesc = smem_desc_sw128(sm_u32 + C::OFF_P + (j & 1) * C::QP_BYTES);
+#pragma unroll
+                    for (int k = 0; k < KT / 32; ++k)      // 32 keys per instruction: 4 row groups of V (+4096 B), +32 B of P
+                        umma_i8(tmem_base + 128 + 64 * (j & 1), vdesc + 256 * k, pdesc + 2 * k, idesc_pv, k > 0);
+                    umma_commit(bar_o_ready(j & 1));
+                    umma_commit(bar_empty(st));
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp < 4) {
+        // =========================================================== softmax warps
+        TC5_CTA_MARK(2);
+        const int kr = threadIdx.x;                      // key row of S^T, output dim of O^T
+        const uint32_t tmem_lane = tmem_base + ((uint32_t)(32 * warp) << 16);
+        auto wait_warp = [&](uint32_t bar, uint32_t parity) {
+            return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag, p.fault)) != 0;
+        };
+        // byte (row, col) of a K-major operand tile with 128-byte rows, 128B-swizzled
+        auto at = [](int row, int col) { return (row >> 3) * 1024 + (row & 7) * 128 + ((((col >> 4) ^ (row & 7)) << 4) | (col & 15)); };
+
+        // ---- query rows -> two int8 limbs each (15-bit fixed point: q ~= sq * (128 hi + lo)).
+        // A warp prepares slots warp, warp+4, ...; all their loads are issued before the first use.
+        constexpr int QPW = NSP / 4;
+        uint32_t qraw[QPW][HD / 32];
+        {
+            long qoff[QPW];
+#pragma unroll
+            for (int k = 0; k < QPW; ++k) {
+                const int idx = rg * NS + warp + 4 * k;
+                const int r = fused::div_kvg(p, idx), j = idx - r * p.kvg;
+                const bool valid = warp + 4 * k < NS && r < p.S;
+                qoff[k] = b * p.q_batch_stride + (valid ? ((long)r * p.nh + kvh * p.kvg + j) * HD : (long)(kvh * p.kvg) * HD) + lane;
+            }
+            // raw bits first, conversions afterwards: every load is in flight before the first use
+            if (p.q_type == ET_BF16) {
+#pragma unroll
+                for (int k = 0; k < QPW; ++k)
+#pragma unroll
+                    for (int i = 0; i < HD / 32; ++i) qraw[k][i] = (uint32_t)__ldg(reinterpret_cast<const uint16_t *>(p.q) + qoff[k] + 32 * i) << 16;
+            } else {
+#pragma unroll
+                for (int k = 0; k < QPW; ++k)
+#pragma unroll
+                    for (int i = 0; i < HD / 32; ++i) qraw[k][i] = __ldg(reinterpret_cast<const uint32_t *>(p.q) + qoff[k] + 32 * i);
+            }
+        }
+        float qx[QPW][HD / 32];
+#pragma unroll
+        for (int k = 0; k < QPW; ++k) {
+            const int idx = rg * NS + warp + 4 * k;
+            const bool valid = warp + 4 * k < NS && fused::div_kvg(p, idx) < p.S;
+#pragma unroll
+            for (int i = 0; i < HD / 32; ++i) qx[k][i] = valid ? __uint_as_float(qraw[k][i]) : 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < QPW; ++k) {
+            const int sl = warp + 4 * k;
+            const int idx = rg * NS + sl;
+            const int r = fused::div_kvg(p, idx);
+            const bool valid = sl < NS && r < p.S;
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < HD / 32; ++i) amax = fmaxf(amax, fabsf(qx[k][i]));
+            amax = warp_max(amax);
+            const float sq = amax > 0.0f ? amax * (1.0f / (float)Q_FIX_MAX) : 1.0f;
+            const float inv = rcpf(sq);
+#pragma unroll
+            for (int i = 0; i < HD / 32; ++i) {
+                int qf = __float2int_rn(qx[k][i] * inv);
+                qf = max(-Q_FIX_MAX, min(Q_FIX_MAX, qf));
+                const int hi = (qf + 64) >> 7, lo = qf - (hi << 7);
+                sm[C::OFF_Q + at(sl, lane + 32 * i)] = (uint8_t)(int8_t)hi;
+                sm[C::OFF_Q + at(NSP + sl, lane + 32 * i)] = (uint8_t)(int8_t)lo;
+            }
+            if (lane == 0) {
+                const int hi_b = valid ? p.klen - (p.S - 1 - r) : 0;
+                slot_qscale[sl] = valid ? sq * p.qk_scale_log2 : 0.0f;
+                slot_hi[sl] = hi_b;
+                slot_lo[sl] = (valid && p.window > 0) ? max(0, hi_b - p.window) : 0;
+            }
+        }
+        fused::fence_proxy_async();                      // the limbs are read by the tensor core (async proxy)
+        mbar_arrive(bar_q_ready);
+        bool alive = wait_warp(bar_q_ready, 0);          // slot constants of the other warps are visible
+        TC5_CTA_MARK(3);
+
+        // The loops below are written phase by phase over all slots (loads, then arithmetic, then
+        // stores) so that the slots' independent instruction chains overlap: each scheduler of the
+        // SM runs a single softmax warp and has nothing else to hide latencies with.
+        float R[NS], lsum[NS], acc[NS], f_prev[NS];
+        int lo_max = 0, hi_min = 0x7fffffff;
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            R[s] = M_INIT; lsum[s] = 0.0f; acc[s] = 0.0f; f_prev[s] = 0.0f;
+            if (alive && slot_hi[s] > 0) { lo_max = max(lo_max, slot_lo[s]); hi_min = min(hi_min, slot_hi[s]); }
+        }
+        // O^T of tile j: add the exact int32 sums with the tile's weight
+        auto epilogue = [&](int j) -> bool {
+            if (!wait_warp(bar_o_ready(j & 1), (j >> 1) & 1)) return false;
+            tc_fence_after();
+            int oh[NCH][CH], ol[NCH][CH];
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                tmem_ld<CH>(tmem_lane + 128 + 64 * (j & 1) + CH * c, oh[c]);
+                tmem_ld<CH>(tmem_lane + 128 + 64 * (j & 1) + NSP + CH * c, ol[c]);
+            }
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < NCH; ++c)
+#pragma unroll
+                for (int e = 0; e < CH; ++e)      // each limb sum is below 128 * 255 * 127 < 2^22
+                    acc[c * CH + e] = fmaf(fmaf(i2f_small(oh[c][e]), 256.0f, i2f_small(ol[c][e])), f_prev[c * CH + e], acc[c * CH + e]);
+            tc_fence_before();
+            mbar_arrive(bar_o_free(j & 1));
+            return true;
+        };
+
+        const float *gks = reinterpret_cast<const float *>(p.k_scales + b * p.scale_batch_stride);
+        const float *gvs = reinterpret_cast<const float *>(p.v_scales + b * p.scale_batch_stride);
+        const int last_row = p.nkv * p.cache_cap - 1;
+        float ks_next = 0.0f, vs_next = 1.0f;
+        auto fetch_scales = [&](int i) {
+            if (!scales_by_tma && i < my_n) {
+                const int row = min(row_base + wg.tile(tile_begin + i).slot0 + kr, last_row);   // rows past the cache are masked anyway
+                ks_next = __ldg(gks + row);
+                vs_next = __ldg(gvs + row);
+            }
+        };
+        fetch_scales(0);
+        int done = 0;                                    // tiles whose P was handed to the tensor core
+        for (int i = 0; alive && i < my_n; ++i) {
+            const int st = i % NSTG, b2 = i & 1;
+            const TileGeo g = wg.tile(tile_begin + i);
+            const float ks_ld = ks_next, vs_ld = vs_next;
+            fetch_scales(i + 1);
+            TC5_MARK(i, 0);
+            if (!wait_warp(bar_full(st), (i / NSTG) & 1)) { alive = false; break; }
+            TC5_MARK(i, 1);
+            const float *sc = reinterpret_cast<const float *>(sm + C::OFF_SCALES + st * 2 * SCALE_BYTES);
+            const int t = g.t0 + kr;
+            const bool row_ok = t >= g.t_lo && t < g.t_hi;
+            const bool need_mask = g.t0 < max(g.t_lo, lo_max) || g.t0 + KT > min(g.t_hi, hi_min);
+            const float ks = scales_by_tma ? sc[kr] : ks_ld;
+            const float vs = row_ok ? fmaxf(scales_by_tma ? sc[KT + kr] : vs_ld, 5.421011e-20f) : 1.0f;   // floor 2^-64: keeps 1/vs finite
+            const float lvs = lg2f(vs), rvs = row_ok ? rcpf(vs) : 0.0f;
+            float qk[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) qk[s] = slot_qscale[s] * ks;
+            if (!wait_warp(bar_s_ready(b2), (i >> 1) & 1)) { alive = false; break; }
+            tc_fence_after();
+            TC5_MARK(i, 2);
+            int sh[NCH][CH], sl_[NCH][CH];
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                tmem_ld<CH>(tmem_lane + 64 * b2 + CH * c, sh[c]);
+                tmem_ld<CH>(tmem_lane + 64 * b2 + NSP + CH * c, sl_[c]);
+            }
+            tmem_wait_ld();
+            // u = base-2 logit + log2(v_scale): 2^(u - max u) is the key's weight on the V bytes relative
+            // to the tile's largest, the quantity that goes to the tensor core as 16-bit fixed point
+            float u[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s)          // limb sums are below 128 * 127 * 127 < 2^22
+                u[s] = fmaf(fmaf(i2f_small(sh[s / CH][s % CH]), 128.0f, i2f_small(sl_[s / CH][s % CH])), qk[s], lvs);
+            if (need_mask) {
+#pragma unroll
+                for (int s = 0; s < NS; ++s) {
+                    const bool ok = row_ok && t >= slot_lo[s] && t < slot_hi[s];
+                    u[s] = ok ? u[s] : -CUDART_INF_F;
+                }
+            }
+            // tile maximum per slot: one warp-wide integer max each, exchanged through shared memory;
+            // lane s carries slot s's value to a single store
+            int mine = 0;
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                const int wm = redux_max(f2ord(u[s]));
+                mine = lane == s ? wm : mine;
+            }
+            if (lane < NS) xch[(b2 * NSP + lane) * 4 + warp] = mine;
+            mbar_arrive(bar_xch(b2));
+            if (!wait_warp(bar_xch(b2), (i >> 1) & 1)) { alive = false; break; }
+            TC5_MARK(i, 3);
+            float umax[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                const int4 m4 = *reinterpret_cast<const int4 *>(xch + (b2 * NSP + s) * 4);
+                umax[s] = ord2f(max(max(m4.x, m4.y), max(m4.z, m4.w)));
+            }
+            float f_cur[NS];
+            uint32_t fx[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                const bool empty = umax[s] == -CUDART_INF_F;         // every key of the tile is masked for this slot
+                // The running reference only moves when the tile maximum exceeds it by more than 2^8
+                // (weights are normalised per tile, so a stale reference costs no precision).  Either the
+                // reference stays (alpha = 1, tile weight 2^d) or it moves to the tile maximum (tile weight
+                // 1, alpha = 2^-d): one exponential, and unconditional arithmetic keeps the slots' chains
+                // free of branches.
+                const float d = umax[s] - R[s];
+                const bool moved = d > LAZY_MAX;
+                const float e = ex2f(moved ? -d : d);
+                const float alpha = moved ? e : 1.0f;
+                const float tw = moved ? 1.0f : e;                       // 0 for an empty tile (d = -inf)
+                R[s] = moved ? umax[s] : R[s];
+                const float w = ex2f(u[s] - (empty ? 0.0f : umax[s]));   // in [0, 1]
+                f_cur[s] = tw * (1.0f / P_FIX);
+                f_prev[s] *= alpha;
+                acc[s] *= alpha;
+                lsum[s] = fmaf(w * tw, rvs, lsum[s] * alpha);            // 2^(logit - R): the softmax denominator
+                fx[s] = __float_as_uint(fmaf(w, P_FIX, RND_MAGIC));
+            }
+            uint8_t *pt = sm + C::OFF_P + b2 * C::QP_BYTES;
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                pt[at(s, kr)] = (uint8_t)(fx[s] >> 8);
+                pt[at(NSP + s, kr)] = (uint8_t)fx[s];
+            }
+            fused::fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(bar_p_ready(b2));
+            TC5_MARK(i, 4);
+            done = i + 1;
+            if (i >= 1 && !epilogue(i - 1)) { alive = false; break; }
+            TC5_MARK(i, 5);
+#pragma unroll
+            for (int s = 0; s < NS; ++s) f_prev[s] = f_cur[s];
+        }
+        if (alive && done == my_n && my_n >= 1) alive = epilogue(my_n - 1);
+
+        TC5_CTA_MARK(4);
+        // ---- denominators: sum the per-key partial sums over the 128 threads
+        float *lred = reinterpret_cast<float *>(xch);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int s = 0; s < NS; ++s) lsum[s] += __shfl_xor_sync(0xffffffffu, lsum[s], o);
+        {
+            float mine_l = 0.0f;
+#pragma unroll
+            for (int s = 0; s < NS; ++s) mine_l = lane == s ? lsum[s] : mine_l;
+            if (lane < NS) lred[lane * 4 + warp] = mine_l;
+        }
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        // ---- outputs: this thread owns dim kr of every slot
+        float lfin[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            const float4 l4 = *reinterpret_cast<const float4 *>(lred + s * 4);
+            lfin[s] = (l4.x + l4.y) + (l4.z + l4.w);
+        }
+        const int nvalid = min(NS, p.S * p.kvg - rg * NS);
+        float *pbase = p.partial + ((size_t)split * p.grows) * (HD + 2) + kr;
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            if (s < nvalid) {
+                const int idx = rg * NS + s;
+                const int r = fused::div_kvg(p, idx);
+                const int hrow = r * p.nh + kvh * p.kvg + (idx - r * p.kvg);          // row within the batch element
+                if (p.write_partial) {
+                    float *pr = pbase + (size_t)(b * p.S * p.nh + hrow) * (HD + 2);
+                    pr[0] = acc[s];
+                    if (kr == 0) { pr[HD] = p.export_nat ? R[s] * LN2 : R[s]; pr[HD + 1] = lfin[s]; }
+                } else {
+                    const float v = lfin[s] > 0.0f ? acc[s] / lfin[s] : 0.0f;
+                    const long oi = b * p.out_batch_stride + (long)hrow * HD + kr;
+                    if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
+                    else reinterpret_cast<float *>(p.out)[oi] = v;
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------ tear-down
+    TC5_CTA_MARK(5);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem_base, TMEM_COLS);
+    TC5_CTA_MARK(6);
+    fused::merge_splits_in_kernel<NS, HD, NTHREADS, (NS > 8 ? 16 : 8)>(p, sm, b, kvh, rg);
+    TC5_CTA_MARK(7);
+}
+
+}  // namespace tc5
+}  // namespace nomos

@@ -52,6 +52,7 @@ struct AttnArgs {
     long q_batch_stride, kv_batch_stride, scale_batch_stride, out_batch_stride;   // elements (q/out), bytes (kv, scales)
     int force_splits;       // 0 = choose; >0 = use exactly this many splits (tests)
     int no_tma;             // 1: keep every tile on the cp.async path
+    int no_tcgen05;         // 1: never take the tcgen05 kernel
     int settled_cache;      // 1: rows older than the S query rows may be read before the stream predecessor completes
     int fit_splits_to_ws;   // 1: use fewer splits rather than fail when the workspace is small (thin entry points)
 };

@@ -21,6 +21,7 @@ KV_I8, KV_I4, KV_I4B32 = 0, 1, 2
 F32, BF16 = 0, 1
 SETTLED_CACHE = 1            # nomos_attn_args_t.flags bit, see include/nomos_attn.h
 NO_TMA = 2                   # nomos_attn_args_t.flags bit: cp.async copies only
+NO_TCGEN05 = 4               # nomos_attn_args_t.flags bit: stay on the mma.sync kernel
 
 
 class NomosError(RuntimeError):

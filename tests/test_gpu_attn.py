@@ -19,6 +19,19 @@ TOL = 2e-3
 SENTINEL = -1.0e30
 
 
+# Every test that goes through fused() runs twice: on the kernel the library picks (tcgen05 for
+# int8 / head_dim 128 without a fused append) and pinned to the mma.sync kernel.
+EXTRA_FLAGS = 0
+
+
+@pytest.fixture(autouse=True, params=["auto", "mma_sync"])
+def kernel_path(request):
+    global EXTRA_FLAGS
+    EXTRA_FLAGS = ops.NO_TCGEN05 if request.param == "mma_sync" else 0
+    yield request.param
+    EXTRA_FLAGS = 0
+
+
 def build_cache(fmt, rng, T, nkv, hd, cap=None, outliers=False, cache_hd=None, start=0):
     cap = cap or T
     k = k_with_outliers(rng, T, nkv, hd) if outliers else bf16_normal(rng, (T, nkv, hd))
@@ -41,7 +54,7 @@ def fused(c: KVCache, q, *, S=1, klen, win_start=0, window=0, scale=1.0, q_type=
     a = ops.make_args(q=dq, k_cache=dk, v_cache=dv, k_scales=dks, v_scales=dvs, out=out, partial_out=part,
                       kv_fmt=c.kv_fmt, q_type=q_type, out_type=out_type, S=S, nh=nh, nkv=nkv, kvg=nh // nkv,
                       l_hd=hd, cache_hd=c.cache_hd, cache_cap=c.cache_cap, win_start=win_start, klen=klen,
-                      window=window, softmax_scale=scale, force_splits=force_splits)
+                      window=window, softmax_scale=scale, force_splits=force_splits, flags=EXTRA_FLAGS)
     if new_k is not None:
         keep = (dev(np.ascontiguousarray(new_k, np.float32)), dev(np.ascontiguousarray(new_v, np.float32)))
         a.new_k, a.new_v, a.n_new, a.new_base_pos = keep[0].data_ptr(), keep[1].data_ptr(), new_k.shape[0], new_base_pos
@@ -81,7 +94,7 @@ def test_config1_decode_i8(oracle):
     assert np.all(np.abs(got_bf - want_bf) <= ulp + TOL * np.sqrt(np.mean(want ** 2)))
 
 
-@pytest.mark.parametrize("T", [1, 2, 31, 32, 33, 63, 64, 65, 127, 1023, 1024, 1025, 4097])
+@pytest.mark.parametrize("T", [1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 256, 257, 1023, 1024, 1025, 4097])
 def test_decode_i8_lengths(oracle, T):
     rng = np.random.default_rng(T)
     nh, nkv, hd = 8, 4, 128
@@ -92,6 +105,29 @@ def test_decode_i8_lengths(oracle, T):
     ok, rel = within(got, want, TOL)
     assert ok, f"T={T}: {rel:.2e} x RMS"
     assert not np.any(got == SENTINEL), "output not fully written"
+
+
+def test_decode_i8_many_tiles_per_cta_back_to_back(oracle):
+    """One CTA walks 100 tiles of 128 keys (every pipeline stage and barrier phase is reused many
+    times), launched several times in a row without a host synchronisation in between."""
+    rng = np.random.default_rng(77)
+    nh, nkv, hd, T = 4, 2, 128, 12800
+    c = build_cache("i8", rng, T, nkv, hd)
+    q = bf16_normal(rng, (1, nh, hd)) * np.float32(0.5)
+    want = exact(oracle, c, q, klen=T)
+    keep = [dev(np.ascontiguousarray(q, np.float32)), dev(c.k), dev(c.v), dev(c.ks), dev(c.vs)]
+    for splits in (1, 5):
+        out = torch.full((1, nh, hd), SENTINEL, dtype=torch.float32, device=DEV)
+        a = ops.make_args(q=keep[0], k_cache=keep[1], v_cache=keep[2], k_scales=keep[3], v_scales=keep[4], out=out,
+                          kv_fmt=ops.KV_I8, nh=nh, nkv=nkv, kvg=2, l_hd=hd, cache_hd=hd, cache_cap=T, klen=T,
+                          force_splits=splits, flags=EXTRA_FLAGS)
+        ws = torch.empty(max(ops.attn_workspace_bytes(a), 16), dtype=torch.uint8, device=DEV)
+        a.workspace, a.ws_bytes = ws.data_ptr(), ws.numel()
+        for _ in range(6):
+            ops.attn_fused(None, a)
+        torch.cuda.synchronize()
+        ok, rel = within(host(out), want, TOL)
+        assert ok, f"splits={splits}: {rel:.2e} x RMS"
 
 
 @pytest.mark.parametrize("splits", [1, 2, 3, 7, 16])
@@ -345,7 +381,7 @@ def test_tma_and_cp_async_copy_paths_agree(oracle, fmt, hd, win_start):
     q = bf16_normal(rng, (1, nh, hd))
     keep = [dev(q), dev(c.k), dev(c.v), dev(c.ks), dev(c.vs)]
     outs = []
-    for flags in (0, ops.NO_TMA):
+    for flags in (ops.NO_TCGEN05, ops.NO_TCGEN05 | ops.NO_TMA):      # both on the mma.sync kernel
         out = torch.full((1, nh, hd), SENTINEL, dtype=torch.float32, device=DEV)
         a = ops.make_args(q=keep[0], k_cache=keep[1], v_cache=keep[2], k_scales=keep[3], v_scales=keep[4], out=out,
                           kv_fmt=c.kv_fmt, nh=nh, nkv=nkv, kvg=kvg, l_hd=hd, cache_hd=hd, cache_cap=cap, klen=T,
