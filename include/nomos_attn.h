@@ -247,6 +247,9 @@ typedef struct nomos_attn_args {
  * (both pass the same accuracy gate; their roundings differ).  The environment variable
  * NOMOS_ATTN_NO_TCGEN05=1 does the same for a whole process. */
 #define NOMOS_ATTN_NO_TCGEN05 4
+/* flags bit: take the tcgen05 kernel for every call it supports, also where the library's
+ * own choice would be the mma.sync kernel (for comparing the two). */
+#define NOMOS_ATTN_TCGEN05_ALWAYS 8
 
 /* Bytes of workspace the call needs (>= 0), or a negative status. */
 int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args);

@@ -367,6 +367,7 @@ static int unpack_args(const nomos_attn_args_t *u, AttnArgs &a, const char *who)
     a.settled_cache = (u->flags & NOMOS_ATTN_SETTLED_CACHE) ? 1 : 0;
     a.no_tma = (u->flags & NOMOS_ATTN_NO_TMA) ? 1 : 0;
     a.no_tcgen05 = (u->flags & NOMOS_ATTN_NO_TCGEN05) ? 1 : 0;
+    a.tcgen05_always = (u->flags & NOMOS_ATTN_TCGEN05_ALWAYS) ? 1 : 0;
     return NOMOS_OK;
 }
 

@@ -320,7 +320,7 @@ static bool tc5_eligible(const AttnArgs &a) {
     if (a.kv_fmt != KV_I8 || a.l_hd != 128 || a.new_k != nullptr || a.no_tma || a.no_tcgen05) return false;
     // more than eight query rows per KV head (verify) currently run faster on the mma.sync kernel
     static const bool wide = [] { const char *e = std::getenv("NOMOS_ATTN_TCGEN05_VERIFY"); return e && e[0] == '1'; }();
-    if (a.S * a.kvg > 8 && !wide) return false;
+    if (a.S * a.kvg > 8 && !wide && !a.tcgen05_always) return false;
     if (tc5_disabled_by_env() || tma_disabled_by_env() || encode_tiled_fn() == nullptr) return false;
     const auto al16 = [](const void *x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
     if (!al16(a.k_cache) || !al16(a.v_cache) || a.cache_hd % 16 != 0) return false;
@@ -343,7 +343,7 @@ static int tc5_occupancy() {
         cudaFuncSetAttribute(tc5::attn_tc5_kernel<NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc5::Cfg<NS>::SMEM_BYTES);
         cudaFuncSetAttribute(tc5::attn_tc5_kernel<NS>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         int n = 0;
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, tc5::attn_tc5_kernel<NS>, tc5::NTHREADS, tc5::Cfg<NS>::SMEM_BYTES);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, tc5::attn_tc5_kernel<NS>, tc5::Cfg<NS>::NTHREADS, tc5::Cfg<NS>::SMEM_BYTES);
         // two CTAs of 256 tensor-memory columns each is all an SM holds
         // The occupancy query answers 1 for this kernel although two CTAs of 111 KB shared memory,
         // 256 threads x <=128 registers and 256 tensor-memory columns each do run side by side on an
@@ -453,7 +453,7 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     pdl[0].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(pl.splits, a.nkv, a.batch * pl.row_groups);
-    cfg.blockDim = dim3(tc5::NTHREADS);
+    cfg.blockDim = dim3(C::NTHREADS);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = st;
     cfg.attrs = pdl; cfg.numAttrs = 1;

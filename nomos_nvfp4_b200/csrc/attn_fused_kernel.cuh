@@ -163,16 +163,18 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One attempt; the hardware may keep the thread suspended (no issue slots used) for up to the
+// hinted time before it answers.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(200000u)
         : "memory");
     return ok != 0;
 }
@@ -210,6 +212,12 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\
 namespace nomos {
 namespace fused {
 
+__device__ __forceinline__ unsigned long long arrive_add(unsigned long long *ctr) {
+    unsigned long long old;
+    asm volatile("atom.acq_rel.gpu.global.add.u64 %0, [%1], 1;\n" : "=l"(old) : "l"(ctr) : "memory");
+    return old;
+}
+
 // In-kernel merge across the splits of one (batch, KV head, row group) unit, called by every
 // thread of a CTA after its partial (o, m, l) rows are stored.  The last CTA of the unit to
 // arrive merges the unit's rows; the others return.  `scratch` is shared memory the CTA no
@@ -225,7 +233,9 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
     __syncthreads();                      // all partial stores of this CTA are issued
     MERGE_MARK(1);
     if (threadIdx.x == 0) {
-        __threadfence();                  // cumulative: orders the whole CTA's stores before the arrival
+        // The arrival is one acquire-release atomic at GPU scope: release makes the whole CTA's partial
+        // stores (ordered before it by the barrier above) visible before the count, acquire orders the
+        // merging CTA's loads (all its threads, through the barrier below) after every other arrival.
         unsigned long long *ctr = p.counters + ((size_t)blockIdx.z * gridDim.y + blockIdx.y);
         // The word is (tag << 16 | arrivals).  The merging CTA leaves it tagged with zero arrivals, so
         // the common case is a single atomic add.  A word without the tag has never been used by this
@@ -233,7 +243,7 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
         // and the arrivals that find garbage install a tagged word with compare-and-swap, which only
         // fails when another arrival made progress.
         constexpr unsigned long long TAG = 0x6e6f6d6f7341ull;
-        unsigned long long old = atomicAdd(ctr, 1ull);
+        unsigned long long old = arrive_add(ctr);
         int arrived = -1;
         if ((old >> 16) == TAG) {
             arrived = (int)(old & 0xffffull) + 1;
@@ -241,11 +251,13 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
             for (int tries = 0; tries < (1 << 16); ++tries) {    // bounded: gives up rather than spin forever
                 const unsigned long long cur = *reinterpret_cast<volatile unsigned long long *>(ctr);
                 if ((cur >> 16) == TAG) {
-                    old = atomicAdd(ctr, 1ull);
+                    old = arrive_add(ctr);
                     if ((old >> 16) == TAG) { arrived = (int)(old & 0xffffull) + 1; break; }
-                } else if (atomicCAS(ctr, cur, (TAG << 16) | 1ull) == cur) {
-                    arrived = 1;
-                    break;
+                } else {
+                    __threadfence();          // rare path: plain fences around the compare-and-swap
+                    const bool won = atomicCAS(ctr, cur, (TAG << 16) | 1ull) == cur;
+                    __threadfence();
+                    if (won) { arrived = 1; break; }
                 }
             }
         }
@@ -255,7 +267,6 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
     __syncthreads();
     MERGE_MARK(2);
     if (!s_last) return;
-    __threadfence();
     NOMOS_MARK(5);
     MERGE_MARK(3);
 
@@ -290,9 +301,9 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
     for (int e = threadIdx.x; e < nrows * G; e += NTHR) {
         const int sl = e / G, i = e - sl * G;
         const float *pr = p.partial + (size_t)i * rstride + (size_t)grow_of(sl) * (HD + 2);
-        const float li = __ldcg(pr + HD + 1);
-        ls[sl * G + i] = li;
-        ms[sl * G + i] = li > 0.0f ? __ldcg(pr + HD) : -CUDART_INF_F;
+        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(pr + HD));     // (m, l): 8-byte aligned, one round trip
+        ls[sl * G + i] = ml.y;
+        ms[sl * G + i] = ml.y > 0.0f ? ml.x : -CUDART_INF_F;
     }
     __syncthreads();
     MERGE_MARK(4);
@@ -350,6 +361,10 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
     // General case: four elements per thread at a time, GB splits each, all loads issued before use.
     constexpr int EL = 4;
     const int total = nrows * HD;
+#ifdef NOMOS_TIMELINE
+    for (int pass_ = 0; pass_ < 2; ++pass_) {            // debug builds: second pass times the same code warm
+    if (pass_ == 1) { __syncthreads(); MERGE_MARK(6); }
+#endif
     for (int e0 = threadIdx.x; e0 < total; e0 += EL * NTHR) {
         const float *base[EL];
         int sl[EL];
@@ -361,19 +376,30 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
             base[j] = p.partial + (size_t)grow_of(sl[j]) * (HD + 2) + (e - sl[j] * HD);
             o[j] = 0.0f;
         }
-        for (int i0 = 0; i0 < G; i0 += GB) {
+        int i0 = 0;
+        for (; i0 + GB <= G; i0 += GB) {
             float v[EL][GB];
 #pragma unroll
             for (int j = 0; j < EL; ++j)
 #pragma unroll
-                for (int k = 0; k < GB; ++k) v[j][k] = __ldcg(base[j] + (size_t)min(i0 + k, G - 1) * rstride);   // unconditional: batches freely
+                for (int k = 0; k < GB; ++k) v[j][k] = __ldcg(base[j] + (size_t)(i0 + k) * rstride);
 #pragma unroll
             for (int j = 0; j < EL; ++j)
 #pragma unroll
-                for (int k = 0; k < GB; ++k) {
-                    const float w = i0 + k < G ? ms[sl[j] * G + i0 + k] : 0.0f;
-                    o[j] = fmaf(w, v[j][k], o[j]);
-                }
+                for (int k = 0; k < GB; ++k) o[j] = fmaf(ms[sl[j] * G + i0 + k], v[j][k], o[j]);
+        }
+        for (; i0 < G; i0 += 2) {             // remainder, two splits at a time (the second clamped, weight 0)
+            float v[EL][2];
+#pragma unroll
+            for (int j = 0; j < EL; ++j) {
+                v[j][0] = __ldcg(base[j] + (size_t)i0 * rstride);
+                v[j][1] = __ldcg(base[j] + (size_t)min(i0 + 1, G - 1) * rstride);
+            }
+#pragma unroll
+            for (int j = 0; j < EL; ++j) {
+                o[j] = fmaf(ms[sl[j] * G + i0], v[j][0], o[j]);
+                o[j] = fmaf(i0 + 1 < G ? ms[sl[j] * G + i0 + 1] : 0.0f, v[j][1], o[j]);
+            }
         }
 #pragma unroll
         for (int j = 0; j < EL; ++j) {
@@ -381,7 +407,11 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
             if (e < total) emit(sl[j], e - sl[j] * HD, o[j]);
         }
     }
-    MERGE_MARK(6);
+#ifdef NOMOS_TIMELINE
+    }
+    __syncthreads();
+    MERGE_MARK(7);
+#endif
 }
 
 template <int FMT, int HD, int MT>

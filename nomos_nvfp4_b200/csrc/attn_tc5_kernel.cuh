@@ -14,8 +14,10 @@
 // Accumulators live in tensor memory: warp w of the four softmax warps reads TMEM lanes
 // 32w..32w+31, i.e. thread = one key of the tile for S^T, thread = one output dim for O^T.
 //
-// Roles (256 threads): warps 0-3 softmax + output, warp 4 lane 0 TMA producer, warp 5 lane 0
-// MMA issuer, warps 6-7 only help in the split merge.  Every wait is an mbarrier wait with a
+// Roles: four softmax warps per group (one group up to eight slots, two groups sharing the slots
+// of a tile beyond that: thread = key / dim as above, each group owns half the columns), then one
+// warp whose lane 0 is the TMA producer and one whose lane 0 issues the MMAs; the rest only help
+// in the split merge.  Every wait is an mbarrier wait with a
 // time limit; a wait that runs out raises the CTA's abort flag and a bit in the device fault
 // word, every role leaves its loop, tensor memory is freed and the CTA exits.
 #pragma once
@@ -38,9 +40,11 @@ constexpr int KT = 128;                      // keys per tile = M of the QK MMA
 constexpr int HD = 128;                      // head dim = M of the PV MMA
 constexpr int TILE_BYTES = KT * HD;          // one K or V tile (int8)
 constexpr int SCALE_BYTES = KT * 4;          // one tile's fp32 row scales
-constexpr int NTHREADS = 256;
 constexpr int TMEM_COLS = 256;               // S0 | S1 | O0 | O1, 64 columns each
 constexpr float LG2_VS_MIN = -64.0f;
+#ifndef NOMOS_TC5_NSG
+#define NOMOS_TC5_NSG 4                      // slots per softmax warp group when a CTA serves more than eight
+#endif
 
 #ifdef NOMOS_TIMELINE
 // Debug builds only: per-CTA, per-tile wall-clock marks (ns) of the softmax role.
@@ -67,14 +71,20 @@ struct Cfg {
     static constexpr int N = 2 * NSP;
     static constexpr int NSTG = NS <= 8 ? 3 : 6;                     // 3 stages: two CTAs per SM
     static constexpr int MIN_CTAS = NS <= 8 ? 2 : 1;
+    static constexpr int NSG = NS <= 8 ? NS : NOMOS_TC5_NSG;         // slots per softmax warp group
+    static constexpr int NG = NS / NSG;                              // softmax warp groups
+    static constexpr int NSW = 4 * NG;                               // softmax warps; then the TMA warp, then the MMA warp
+    static constexpr int NTHREADS = NG == 1 ? 256 : 32 * (NSW + 2);
+    static_assert(NS % NSG == 0 && NSG % 2 == 0 && NG <= 6, "slots split evenly over the groups");
     static constexpr int QP_BYTES = N * 128;                         // Q limbs, or one buffer of P limbs
     static constexpr int OFF_SCALES = NSTG * 2 * TILE_BYTES;
     static constexpr int OFF_Q = OFF_SCALES + NSTG * 2 * SCALE_BYTES;
     static constexpr int OFF_P = OFF_Q + QP_BYTES;
     static constexpr int OFF_XCH = OFF_P + 2 * QP_BYTES;             // [2][NSP][4] warp maxima
     static constexpr int OFF_SLOT = OFF_XCH + 2 * NSP * 16;          // qscale[NSP], lo[NSP], hi[NSP]
-    static constexpr int OFF_BAR = OFF_SLOT + NSP * 12;
-    static constexpr int NBAR = 2 * NSTG + 11;                       // full, empty, s_ready, p_ready, o_ready, o_free, xch, q_ready
+    static constexpr int OFF_SLOTC = (OFF_SLOT + NSP * 12 + 15) / 16 * 16;   // per softmax warp: 16 x (max, weight, alpha, -)
+    static constexpr int OFF_BAR = OFF_SLOTC + NSW * 16 * 16;
+    static constexpr int NBAR = 2 * NSTG + 9 + 2 * NG;               // full, empty, s_ready, p_ready, o_ready, o_free (x2 each), xch (x2 per group), q_ready
     static constexpr int OFF_MISC = OFF_BAR + NBAR * 8;              // tmem base, abort flag
     static constexpr int SMEM_BYTES = 1024 + OFF_MISC + 16;
     static_assert(OFF_BAR % 8 == 0, "mbarriers need 8-byte alignment");
@@ -169,7 +179,9 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     unsigned long long t0, t1;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     for (;;) {
-        if (fused::mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+        for (int k = 0; k < 32; ++k)                     // try_wait itself suspends the thread for a while
+            if (fused::mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
         if (t1 - t0 > 1000000000ull) {
@@ -208,13 +220,13 @@ struct WindowGeo {
 };
 
 template <int NS>
-__global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
+__global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     attn_tc5_kernel(const KParams p, const __grid_constant__ TmaMaps4 tm) {
     using C = Cfg<NS>;
     constexpr int NSP = C::NSP, NSTG = C::NSTG;
-    constexpr int CH = NS < 4 ? NS : 4;              // slots per TMEM load
-    constexpr int NCH = NS / CH;
-    static_assert(NS == 2 || NS % 4 == 0, "slot count");
+    constexpr int NG = C::NG, NSG = C::NSG, NSW = C::NSW, NTHREADS = C::NTHREADS;
+    constexpr int CH = NSG % 4 == 0 ? 4 : 2;         // slots per TMEM load
+    constexpr int NCH = NSG / CH;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -232,8 +244,8 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
     auto bar_p_ready = [&](int i) { return bar0 + 8 * (2 * NSTG + 2 + i); };
     auto bar_o_ready = [&](int i) { return bar0 + 8 * (2 * NSTG + 4 + i); };
     auto bar_o_free = [&](int i) { return bar0 + 8 * (2 * NSTG + 6 + i); };
-    auto bar_xch = [&](int i) { return bar0 + 8 * (2 * NSTG + 8 + i); };
-    const uint32_t bar_q_ready = bar0 + 8 * (2 * NSTG + 10);
+    auto bar_xch = [&](int g, int i) { return bar0 + 8 * (2 * NSTG + 9 + 2 * g + i); };
+    const uint32_t bar_q_ready = bar0 + 8 * (2 * NSTG + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, kvh = blockIdx.y;
@@ -264,15 +276,16 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             fused::mbar_init(bar_s_ready(i), 1);
-            fused::mbar_init(bar_p_ready(i), 128);
+            fused::mbar_init(bar_p_ready(i), 128 * NG);
             fused::mbar_init(bar_o_ready(i), 1);
-            fused::mbar_init(bar_o_free(i), 128);
-            fused::mbar_init(bar_xch(i), 128);
+            fused::mbar_init(bar_o_free(i), 128 * NG);
+#pragma unroll
+            for (int g = 0; g < NG; ++g) fused::mbar_init(bar_xch(g, i), 128);
         }
-        fused::mbar_init(bar_q_ready, 128);
+        fused::mbar_init(bar_q_ready, 128 * NG);
         fused::fence_mbar_init();
     }
-    if (warp == 4) {
+    if (warp == NSW) {
         tmem_alloc(sm_u32 + C::OFF_MISC, TMEM_COLS);
         tmem_relinquish();
     }
@@ -284,12 +297,12 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
     // Programmatic dependent launch: every thread waits for the stream predecessor before it lets
     // this grid's own dependents be scheduled (the producer thread first requests the tiles the
     // caller declared settled).
-    if (!(warp == 4 && lane == 0)) {
+    if (!(warp == NSW && lane == 0)) {
         fused::pdl_wait();
         fused::pdl_launch_dependents();
     }
 
-    if (warp == 4) {
+    if (warp == NSW) {
         // =========================================================== TMA producer
         if (lane == 0) {
             bool waited = false;
@@ -312,7 +325,7 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
             if (!waited) { fused::pdl_wait(); fused::pdl_launch_dependents(); }
         }
         __syncwarp();
-    } else if (warp == 5) {
+    } else if (warp == NSW + 1) {
         // =========================================================== MMA issuer
         if (lane == 0) {
             const uint32_t idesc_qk = make_idesc(C::N, true, true, false);
@@ -349,11 +362,13 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
             }
         }
         __syncwarp();
-    } else if (warp < 4) {
+    } else if (warp < NSW) {
         // =========================================================== softmax warps
         TC5_CTA_MARK(2);
-        const int kr = threadIdx.x;                      // key row of S^T, output dim of O^T
-        const uint32_t tmem_lane = tmem_base + ((uint32_t)(32 * warp) << 16);
+        const int grp = warp >> 2, wq = warp & 3;        // group, and the TMEM lane quarter this warp may read
+        const int kr = threadIdx.x & 127;                // key row of S^T, output dim of O^T
+        const int s0 = grp * NSG;                        // first slot of this group
+        const uint32_t tmem_lane = tmem_base + ((uint32_t)(32 * wq) << 16);
         auto wait_warp = [&](uint32_t bar, uint32_t parity) {
             return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag, p.fault)) != 0;
         };
@@ -362,15 +377,15 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
 
         // ---- query rows -> two int8 limbs each (15-bit fixed point: q ~= sq * (128 hi + lo)).
         // A warp prepares slots warp, warp+4, ...; all their loads are issued before the first use.
-        constexpr int QPW = NSP / 4;
+        constexpr int QPW = (NSP + NSW - 1) / NSW;
         uint32_t qraw[QPW][HD / 32];
         {
             long qoff[QPW];
 #pragma unroll
             for (int k = 0; k < QPW; ++k) {
-                const int idx = rg * NS + warp + 4 * k;
+                const int idx = rg * NS + warp + NSW * k;
                 const int r = fused::div_kvg(p, idx), j = idx - r * p.kvg;
-                const bool valid = warp + 4 * k < NS && r < p.S;
+                const bool valid = warp + NSW * k < NS && r < p.S;
                 qoff[k] = b * p.q_batch_stride + (valid ? ((long)r * p.nh + kvh * p.kvg + j) * HD : (long)(kvh * p.kvg) * HD) + lane;
             }
             // raw bits first, conversions afterwards: every load is in flight before the first use
@@ -389,14 +404,15 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
         float qx[QPW][HD / 32];
 #pragma unroll
         for (int k = 0; k < QPW; ++k) {
-            const int idx = rg * NS + warp + 4 * k;
-            const bool valid = warp + 4 * k < NS && fused::div_kvg(p, idx) < p.S;
+            const int idx = rg * NS + warp + NSW * k;
+            const bool valid = warp + NSW * k < NS && fused::div_kvg(p, idx) < p.S;
 #pragma unroll
             for (int i = 0; i < HD / 32; ++i) qx[k][i] = valid ? __uint_as_float(qraw[k][i]) : 0.0f;
         }
 #pragma unroll
         for (int k = 0; k < QPW; ++k) {
-            const int sl = warp + 4 * k;
+            const int sl = warp + NSW * k;
+            if (sl >= NSP) break;
             const int idx = rg * NS + sl;
             const int r = fused::div_kvg(p, idx);
             const bool valid = sl < NS && r < p.S;
@@ -429,12 +445,16 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
         // The loops below are written phase by phase over all slots (loads, then arithmetic, then
         // stores) so that the slots' independent instruction chains overlap: each scheduler of the
         // SM runs a single softmax warp and has nothing else to hide latencies with.
-        float R[NS], lsum[NS], acc[NS], f_prev[NS];
+        float lsum[NSG], acc[NSG], f_prev[NSG];               // this group's slots s0 .. s0+NSG-1
+        float r_lane = M_INIT;                                // running reference of slot s0+lane (lanes < NSG)
+        float4 *my_consts = reinterpret_cast<float4 *>(sm + C::OFF_SLOTC) + warp * 16;
+        int p_off[NSG];                                       // byte of (high-limb row of slot, this key) in a P tile
         int lo_max = 0, hi_min = 0x7fffffff;
 #pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            R[s] = M_INIT; lsum[s] = 0.0f; acc[s] = 0.0f; f_prev[s] = 0.0f;
-            if (alive && slot_hi[s] > 0) { lo_max = max(lo_max, slot_lo[s]); hi_min = min(hi_min, slot_hi[s]); }
+        for (int s = 0; s < NSG; ++s) {
+            lsum[s] = 0.0f; acc[s] = 0.0f; f_prev[s] = 0.0f;
+            p_off[s] = at(s0 + s, kr);
+            if (alive && slot_hi[s0 + s] > 0) { lo_max = max(lo_max, slot_lo[s0 + s]); hi_min = min(hi_min, slot_hi[s0 + s]); }
         }
         // O^T of tile j: add the exact int32 sums with the tile's weight
         auto epilogue = [&](int j) -> bool {
@@ -443,8 +463,8 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
             int oh[NCH][CH], ol[NCH][CH];
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
-                tmem_ld<CH>(tmem_lane + 128 + 64 * (j & 1) + CH * c, oh[c]);
-                tmem_ld<CH>(tmem_lane + 128 + 64 * (j & 1) + NSP + CH * c, ol[c]);
+                tmem_ld<CH>(tmem_lane + 128 + 64 * (j & 1) + s0 + CH * c, oh[c]);
+                tmem_ld<CH>(tmem_lane + 128 + 64 * (j & 1) + NSP + s0 + CH * c, ol[c]);
             }
             tmem_wait_ld();
 #pragma unroll
@@ -485,29 +505,29 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
             const float ks = scales_by_tma ? sc[kr] : ks_ld;
             const float vs = row_ok ? fmaxf(scales_by_tma ? sc[KT + kr] : vs_ld, 5.421011e-20f) : 1.0f;   // floor 2^-64: keeps 1/vs finite
             const float lvs = lg2f(vs), rvs = row_ok ? rcpf(vs) : 0.0f;
-            float qk[NS];
+            float qk[NSG];
 #pragma unroll
-            for (int s = 0; s < NS; ++s) qk[s] = slot_qscale[s] * ks;
+            for (int s = 0; s < NSG; ++s) qk[s] = slot_qscale[s0 + s] * ks;
             if (!wait_warp(bar_s_ready(b2), (i >> 1) & 1)) { alive = false; break; }
             tc_fence_after();
             TC5_MARK(i, 2);
             int sh[NCH][CH], sl_[NCH][CH];
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
-                tmem_ld<CH>(tmem_lane + 64 * b2 + CH * c, sh[c]);
-                tmem_ld<CH>(tmem_lane + 64 * b2 + NSP + CH * c, sl_[c]);
+                tmem_ld<CH>(tmem_lane + 64 * b2 + s0 + CH * c, sh[c]);
+                tmem_ld<CH>(tmem_lane + 64 * b2 + NSP + s0 + CH * c, sl_[c]);
             }
             tmem_wait_ld();
             // u = base-2 logit + log2(v_scale): 2^(u - max u) is the key's weight on the V bytes relative
             // to the tile's largest, the quantity that goes to the tensor core as 16-bit fixed point
-            float u[NS];
+            float u[NSG];
 #pragma unroll
-            for (int s = 0; s < NS; ++s)          // limb sums are below 128 * 127 * 127 < 2^22
+            for (int s = 0; s < NSG; ++s)         // limb sums are below 128 * 127 * 127 < 2^22
                 u[s] = fmaf(fmaf(i2f_small(sh[s / CH][s % CH]), 128.0f, i2f_small(sl_[s / CH][s % CH])), qk[s], lvs);
             if (need_mask) {
 #pragma unroll
-                for (int s = 0; s < NS; ++s) {
-                    const bool ok = row_ok && t >= slot_lo[s] && t < slot_hi[s];
+                for (int s = 0; s < NSG; ++s) {
+                    const bool ok = row_ok && t >= slot_lo[s0 + s] && t < slot_hi[s0 + s];
                     u[s] = ok ? u[s] : -CUDART_INF_F;
                 }
             }
@@ -515,48 +535,55 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
             // lane s carries slot s's value to a single store
             int mine = 0;
 #pragma unroll
-            for (int s = 0; s < NS; ++s) {
+            for (int s = 0; s < NSG; ++s) {
                 const int wm = redux_max(f2ord(u[s]));
                 mine = lane == s ? wm : mine;
             }
-            if (lane < NS) xch[(b2 * NSP + lane) * 4 + warp] = mine;
-            mbar_arrive(bar_xch(b2));
-            if (!wait_warp(bar_xch(b2), (i >> 1) & 1)) { alive = false; break; }
+            if (lane < NSG) xch[(b2 * NSP + s0 + lane) * 4 + wq] = mine;
+            mbar_arrive(bar_xch(grp, b2));
+            if (!wait_warp(bar_xch(grp, b2), (i >> 1) & 1)) { alive = false; break; }
             TC5_MARK(i, 3);
-            float umax[NS];
-#pragma unroll
-            for (int s = 0; s < NS; ++s) {
-                const int4 m4 = *reinterpret_cast<const int4 *>(xch + (b2 * NSP + s) * 4);
-                umax[s] = ord2f(max(max(m4.x, m4.y), max(m4.z, m4.w)));
-            }
-            float f_cur[NS];
-            uint32_t fx[NS];
-#pragma unroll
-            for (int s = 0; s < NS; ++s) {
-                const bool empty = umax[s] == -CUDART_INF_F;         // every key of the tile is masked for this slot
-                // The running reference only moves when the tile maximum exceeds it by more than 2^8
-                // (weights are normalised per tile, so a stale reference costs no precision).  Either the
-                // reference stays (alpha = 1, tile weight 2^d) or it moves to the tile maximum (tile weight
-                // 1, alpha = 2^-d): one exponential, and unconditional arithmetic keeps the slots' chains
-                // free of branches.
-                const float d = umax[s] - R[s];
-                const bool moved = d > LAZY_MAX;
+            // Per-slot constants of the tile are the same for every key: lane s of each warp works them
+            // out for slot s0+s (the running reference R of that slot lives in that lane) and the warp
+            // shares them through shared memory, instead of every thread repeating them for every slot.
+            // The reference only moves when the tile maximum exceeds it by more than 2^8 (weights are
+            // normalised per tile, so a stale reference costs no precision): either it stays (alpha = 1,
+            // tile weight 2^d) or it moves to the tile maximum (tile weight 1, alpha = 2^-d).
+            bool moved = false;
+            if (lane < NSG) {
+                const int4 m4 = *reinterpret_cast<const int4 *>(xch + (b2 * NSP + s0 + lane) * 4);
+                const float umax = ord2f(max(max(m4.x, m4.y), max(m4.z, m4.w)));
+                const float d = umax - r_lane;                           // -inf when every key of the tile is masked
+                moved = d > LAZY_MAX;
                 const float e = ex2f(moved ? -d : d);
-                const float alpha = moved ? e : 1.0f;
-                const float tw = moved ? 1.0f : e;                       // 0 for an empty tile (d = -inf)
-                R[s] = moved ? umax[s] : R[s];
-                const float w = ex2f(u[s] - (empty ? 0.0f : umax[s]));   // in [0, 1]
-                f_cur[s] = tw * (1.0f / P_FIX);
-                f_prev[s] *= alpha;
-                acc[s] *= alpha;
-                lsum[s] = fmaf(w * tw, rvs, lsum[s] * alpha);            // 2^(logit - R): the softmax denominator
+                r_lane = moved ? umax : r_lane;
+                my_consts[lane] = make_float4(umax == -CUDART_INF_F ? 0.0f : umax, moved ? 1.0f : e, moved ? e : 1.0f, 0.0f);
+            }
+            const bool any_moved = __any_sync(0xffffffffu, moved);
+            __syncwarp();
+            if (any_moved) {
+#pragma unroll
+                for (int s = 0; s < NSG; ++s) {
+                    const float alpha = my_consts[s].z;
+                    lsum[s] *= alpha; acc[s] *= alpha; f_prev[s] *= alpha;
+                }
+            }
+            float f_cur[NSG];
+            uint32_t fx[NSG];
+#pragma unroll
+            for (int s = 0; s < NSG; ++s) {
+                const float4 c = my_consts[s];                           // (tile max or 0, tile weight, alpha, -)
+                const float w = ex2f(u[s] - c.x);                        // in [0, 1]
+                f_cur[s] = c.y * (1.0f / P_FIX);
+                lsum[s] = fmaf(w * c.y, rvs, lsum[s]);                   // 2^(logit - R): the softmax denominator
                 fx[s] = __float_as_uint(fmaf(w, P_FIX, RND_MAGIC));
             }
+            __syncwarp();                                                // my_consts is rewritten next tile
             uint8_t *pt = sm + C::OFF_P + b2 * C::QP_BYTES;
 #pragma unroll
-            for (int s = 0; s < NS; ++s) {
-                pt[at(s, kr)] = (uint8_t)(fx[s] >> 8);
-                pt[at(NSP + s, kr)] = (uint8_t)fx[s];
+            for (int s = 0; s < NSG; ++s) {
+                pt[p_off[s]] = (uint8_t)(fx[s] >> 8);
+                pt[p_off[s] + NSP * 128] = (uint8_t)fx[s];               // low limbs: NSP rows (a multiple of 8) further down
             }
             fused::fence_proxy_async();
             tc_fence_before();
@@ -566,7 +593,7 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
             if (i >= 1 && !epilogue(i - 1)) { alive = false; break; }
             TC5_MARK(i, 5);
 #pragma unroll
-            for (int s = 0; s < NS; ++s) f_prev[s] = f_cur[s];
+            for (int s = 0; s < NSG; ++s) f_prev[s] = f_cur[s];
         }
         if (alive && done == my_n && my_n >= 1) alive = epilogue(my_n - 1);
 
@@ -576,33 +603,38 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-            for (int s = 0; s < NS; ++s) lsum[s] += __shfl_xor_sync(0xffffffffu, lsum[s], o);
+            for (int s = 0; s < NSG; ++s) lsum[s] += __shfl_xor_sync(0xffffffffu, lsum[s], o);
         {
             float mine_l = 0.0f;
 #pragma unroll
-            for (int s = 0; s < NS; ++s) mine_l = lane == s ? lsum[s] : mine_l;
-            if (lane < NS) lred[lane * 4 + warp] = mine_l;
+            for (int s = 0; s < NSG; ++s) mine_l = lane == s ? lsum[s] : mine_l;
+            if (lane < NSG) lred[(s0 + lane) * 4 + wq] = mine_l;
+            if (lane < NSG && wq == 0) lred[(NSP + s0 + lane) * 4] = r_lane;
         }
-        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        asm volatile("bar.sync %0, 128;\n" ::"r"(1 + grp) : "memory");     // the four warps of this group
         // ---- outputs: this thread owns dim kr of every slot
-        float lfin[NS];
+        float lfin[NSG];
 #pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            const float4 l4 = *reinterpret_cast<const float4 *>(lred + s * 4);
+        for (int s = 0; s < NSG; ++s) {
+            const float4 l4 = *reinterpret_cast<const float4 *>(lred + (s0 + s) * 4);
             lfin[s] = (l4.x + l4.y) + (l4.z + l4.w);
         }
         const int nvalid = min(NS, p.S * p.kvg - rg * NS);
         float *pbase = p.partial + ((size_t)split * p.grows) * (HD + 2) + kr;
 #pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            if (s < nvalid) {
-                const int idx = rg * NS + s;
+        for (int s = 0; s < NSG; ++s) {
+            if (s0 + s < nvalid) {
+                const int idx = rg * NS + s0 + s;
                 const int r = fused::div_kvg(p, idx);
                 const int hrow = r * p.nh + kvh * p.kvg + (idx - r * p.kvg);          // row within the batch element
                 if (p.write_partial) {
                     float *pr = pbase + (size_t)(b * p.S * p.nh + hrow) * (HD + 2);
                     pr[0] = acc[s];
-                    if (kr == 0) { pr[HD] = p.export_nat ? R[s] * LN2 : R[s]; pr[HD + 1] = lfin[s]; }
+                    if (kr == 0) {
+                        const float rs = lred[(NSP + s0 + s) * 4];
+                        pr[HD] = p.export_nat ? rs * LN2 : rs;
+                        pr[HD + 1] = lfin[s];
+                    }
                 } else {
                     const float v = lfin[s] > 0.0f ? acc[s] / lfin[s] : 0.0f;
                     const long oi = b * p.out_batch_stride + (long)hrow * HD + kr;
@@ -617,9 +649,9 @@ __global__ void __launch_bounds__(NTHREADS, Cfg<NS>::MIN_CTAS)
     TC5_CTA_MARK(5);
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem_base, TMEM_COLS);
+    if (warp == NSW) tmem_dealloc(tmem_base, TMEM_COLS);
     TC5_CTA_MARK(6);
-    fused::merge_splits_in_kernel<NS, HD, NTHREADS, (NS > 8 ? 16 : 8)>(p, sm, b, kvh, rg);
+    fused::merge_splits_in_kernel<NS, HD, NTHREADS, 8>(p, sm, b, kvh, rg);
     TC5_CTA_MARK(7);
 }
 

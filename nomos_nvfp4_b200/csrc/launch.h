@@ -53,6 +53,7 @@ struct AttnArgs {
     int force_splits;       // 0 = choose; >0 = use exactly this many splits (tests)
     int no_tma;             // 1: keep every tile on the cp.async path
     int no_tcgen05;         // 1: never take the tcgen05 kernel
+    int tcgen05_always;     // 1: take the tcgen05 kernel whenever it supports the call
     int settled_cache;      // 1: rows older than the S query rows may be read before the stream predecessor completes
     int fit_splits_to_ws;   // 1: use fewer splits rather than fail when the workspace is small (thin entry points)
 };

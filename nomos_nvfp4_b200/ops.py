@@ -22,6 +22,7 @@ F32, BF16 = 0, 1
 SETTLED_CACHE = 1            # nomos_attn_args_t.flags bit, see include/nomos_attn.h
 NO_TMA = 2                   # nomos_attn_args_t.flags bit: cp.async copies only
 NO_TCGEN05 = 4               # nomos_attn_args_t.flags bit: stay on the mma.sync kernel
+TCGEN05_ALWAYS = 8           # nomos_attn_args_t.flags bit: tcgen05 kernel wherever it supports the call
 
 
 class NomosError(RuntimeError):

@@ -19,15 +19,16 @@ TOL = 2e-3
 SENTINEL = -1.0e30
 
 
-# Every test that goes through fused() runs twice: on the kernel the library picks (tcgen05 for
-# int8 / head_dim 128 without a fused append) and pinned to the mma.sync kernel.
+# Every test that goes through fused() runs three times: on the kernel the library picks, pinned
+# to the mma.sync kernel, and on the tcgen05 kernel wherever it supports the call (int8 KV,
+# head_dim 128, no fused append).
 EXTRA_FLAGS = 0
 
 
-@pytest.fixture(autouse=True, params=["auto", "mma_sync"])
+@pytest.fixture(autouse=True, params=["auto", "mma_sync", "tcgen05"])
 def kernel_path(request):
     global EXTRA_FLAGS
-    EXTRA_FLAGS = ops.NO_TCGEN05 if request.param == "mma_sync" else 0
+    EXTRA_FLAGS = {"auto": 0, "mma_sync": ops.NO_TCGEN05, "tcgen05": ops.TCGEN05_ALWAYS}[request.param]
     yield request.param
     EXTRA_FLAGS = 0
 
