@@ -287,13 +287,15 @@ def run_ours(args) -> dict:
         zc_s = float(tt.item())
 
     peak, peak_src = measured_peak_gbs()
+    tc5 = os.environ.get("NOMOS_ATTN_NO_TCGEN05", "0") != "1" and os.environ.get("NOMOS_ATTN_NO_TMA", "0") != "1"
+    kernel_name = "attn_tc5_kernel<2> (tcgen05 + TMEM + TMA)" if tc5 else "attn_fused_kernel<int8,128,1> (mma.sync)"
     # roofline: algorithmic bytes / average launch duration over the timed region (launches run
     # back to back there, as they do in a decode loop); the event-bracketed single launch is kept too
     achieved = step_bytes_rank / (ms_per_step * 1e-3) / 1e9
     result = {
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": N, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": round(ms_per_step, 6), "us_per_layer": round(ms_per_step * 1000, 3), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "int8 (KV bytes x fixed-point Q / softmax weights on int8 tensor cores, fp32 accumulate)",
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 (KV bytes x fixed-point Q / softmax weights on tcgen05 int8 tensor cores, int32 in tensor memory, fp32 running sums)",
         "data": "synthetic",
         "config": {"workload": f"C2 decode layer: {N} seq x 32768 cached keys, 32q/16kv heads x 128, int8 row-scale KV, "
                                f"bf16 Q/out, sharded by KV-head groups ({nkv_l} heads x {seqs} seq per GPU)",
@@ -302,7 +304,7 @@ def run_ours(args) -> dict:
                    "seed": 1002},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": None, "peak_source": f"of {peak_src}",
-                     "kernel": "attn_fused_kernel<int8,128,1>", "launch_us": round(ms_per_step * 1000, 3),
+                     "kernel": kernel_name, "launch_us": round(ms_per_step * 1000, 3),
                      "launch_us_isolated": round(kern_ms * 1000, 3)},
         "e2e": {"value": round(e2e_val, 1), "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "us_per_layer": round(e2e_s * 1e6, 2),
@@ -311,9 +313,10 @@ def run_ours(args) -> dict:
         "clocks": clocks,
     }
     if N == 1:
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
-        # ncu capture summarised in profiles/attn_fused_int8_hd128_decode_c2.md (138.49 MB + 3.45 MB)
-        result["roofline"]["traffic"] = 141.94e6
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the ncu
+        # captures summarised in profiles/attn_tc5_int8_hd128_decode_c2.md (138.50 MB + 3.97 MB) and, for the
+        # mma.sync kernel, profiles/attn_fused_int8_hd128_decode_c2.md (138.49 MB + 3.45 MB)
+        result["roofline"]["traffic"] = 142.47e6 if tc5 else 141.94e6
 
     if rank == 0 and N == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_reference_leg(sample_heads=16, repeats=4, threads=None)

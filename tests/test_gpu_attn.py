@@ -4,7 +4,7 @@ Gate (the parity bar for a re-ordered floating-point reduction): on the fp32
 output, max|out - exact| <= 2e-3 * RMS(exact), where `exact` is the oracle's
 fp64 attention over the bit-identical quantised cache.  Deviations from the
 reference's two lossy realisations (int8 re-quantised Q/P; bf16-materialised) are
-reported by test_gpu_report.py, not gated.
+measured in test_oracle_pins.py on the CPU, not gated here.
 """
 import numpy as np
 import pytest
