@@ -441,6 +441,34 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
             del cs, ws
         except Exception as e:
             out[name] = {"error": str(e)}
+    # producer epilogue: V-norm + QK-norm + RoPE + quantize-on-write of one decode token in one launch
+    # (the reference: five kernels and the append), at the configurations' and the model's layer geometries
+    for name, nh_p, nkv_p, hd_p, fmt_p, cap_p, theta_p, rdim_p in (
+            ("producer_c2_hd128_i8", NH, NKV, HD, ops.KV_I8, 32768, 10000.0, HD),
+            ("producer_g4_sliding_hd256_i4b32", NH, 16, 256, ops.KV_I4B32, 1024, 10000.0, 256),
+            ("producer_g4_full_hd512_i4b32", NH, 4, 512, ops.KV_I4B32, 32768, 1000000.0, 128)):
+        try:
+            row_b = hd_p if fmt_p == ops.KV_I8 else hd_p // 2
+            nb = hd_p // 32
+            sc_b = nkv_p * cap_p * (4 if fmt_p == ops.KV_I8 else nb * 2 + 4)
+            ck = torch.zeros((nkv_p, cap_p, row_b), dtype=torch.uint8, device=dev); cv = torch.zeros_like(ck)
+            cks = torch.zeros(sc_b, dtype=torch.uint8, device=dev); cvs = torch.zeros_like(cks)
+            qp = torch.randn((1, nh_p, hd_p), device=dev); kp = torch.randn((1, nkv_p, hd_p), device=dev)
+            vp = torch.randn((1, nkv_p, hd_p), device=dev)
+            qw = torch.ones(hd_p, device=dev); kw = torch.ones(hd_p, device=dev)
+            pos = [0]
+
+            def fnp():
+                ops.kv_norm_rope_append(stream, qp, qw, kp, vp, kw, ck, cv, cks, cvs, n_s=1, nh=nh_p, nkv=nkv_p, l_hd=hd_p,
+                                        l_kvd=nkv_p * hd_p, cache_cap=cap_p, cache_hd=hd_p, base_pos=pos[0] % cap_p,
+                                        theta=theta_p, rope_dim=rdim_p, kv_fmt=fmt_p)
+                pos[0] += 1
+
+            out[name] = {"us_per_call": round(time_call(torch, fnp, iters), 2), "launches": 1, "reference_launches": 6,
+                         "note": "a few KB per call: bounded by the host's launch rate through ctypes, not by the GPU"}
+            del ck, cv, cks, cvs
+        except Exception as e:
+            out[name] = {"error": str(e)}
     # configuration 5b: batch 1 x 524288 keys, sharded by sequence chunks, (o, m, l) all-gathered and merged
     try:
         T5 = 524288 // world

@@ -251,6 +251,31 @@ typedef struct nomos_attn_args {
  * own choice would be the mma.sync kernel (for comparing the two). */
 #define NOMOS_ATTN_TCGEN05_ALWAYS 8
 
+/* K / V / Q producer epilogue fused with the quantising append: from the raw projection rows of
+ * n_s new tokens to cache bytes in one launch.  Replaces the sequence of lib/gemma4_layer.mojo:326-340
+ *   gpu_rmsnorm_no_weight_mojo(v)           lib/ops_gpu_mojo_reductions.mojo:353-417
+ *   gpu_qk_norm_mojo(q), gpu_qk_norm_mojo(k)  lib/ops_gpu_mojo_reductions.mojo:422-485
+ *   gpu_rope_mojo(q), gpu_rope_mojo(k)      lib/ops_gpu_mojo.mojo:310-368 (token s at base_pos + s as in
+ *                                           the batched kernel, :371 ff.)
+ * followed by gpu_append_quant_kv_i8 / _i4 (lib/kv_cache_quant.mojo:252, :803).
+ *   q        [n_s, nh, l_hd] fp32, normalised and rotated IN PLACE (0 = no query rows)
+ *   src_k/v  [n_s, nkv, l_hd] fp32 with token stride l_kvd, not modified
+ *   *_norm_w [l_hd] fp32 weights of the Q / K norms (V has none)
+ *   k_out/v_out optional [n_s, nkv, l_hd] fp32: the rows exactly as they were quantised (0 = none)
+ *   theta, rope_dim: pairs (i, i + l_hd/2) for i < rope_dim/2 rotate by (base_pos + s) *
+ *     exp(-(2 i / l_hd) * ln theta); like the reference, ln theta is ln(1e6) when theta == 1e6 and
+ *     ln(1e4) for every other value.  rope_dim = l_hd on sliding layers, l_hd / 4 on full layers.
+ *   kv_fmt: NOMOS_KV_I8 / _I4 / _I4B32 select the cache layout (block-32: one scale block per 32
+ *     values and the cached q8 row scale, as nomos_kv_append_quant_i4 with scale_blocks > 1);
+ *     negative = no cache write (norm + rope only).
+ * The cache bytes and scales are those the append entry points produce from k_out / v_out, bit for
+ * bit; the normalised values themselves agree with the reference's float32 kernels to rounding. */
+int32_t nomos_kv_norm_rope_append(void *stream, uint64_t q, uint64_t q_norm_w, uint64_t src_k, uint64_t src_v,
+                                   uint64_t k_norm_w, uint64_t dst_k, uint64_t dst_v, uint64_t k_scales,
+                                   uint64_t v_scales, uint64_t k_out, uint64_t v_out, int32_t n_s, int32_t nh,
+                                   int32_t nkv, int32_t l_hd, int32_t l_kvd, int32_t cache_cap, int32_t cache_hd,
+                                   int32_t base_pos, float theta, int32_t rope_dim, int32_t kv_fmt);
+
 /* Bytes of workspace the call needs (>= 0), or a negative status. */
 int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args);
 /* Run it. */

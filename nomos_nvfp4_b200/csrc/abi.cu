@@ -86,6 +86,40 @@ NOMOS_EXPORT int32_t nomos_kv_append_quant_i8(void *stream, uint64_t src_k, uint
                             ptr(v_scales), n_s, nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos);
 }
 
+NOMOS_EXPORT int32_t nomos_kv_norm_rope_append(void *stream, uint64_t q, uint64_t q_norm_w, uint64_t src_k, uint64_t src_v,
+                                                uint64_t k_norm_w, uint64_t dst_k, uint64_t dst_v, uint64_t k_scales,
+                                                uint64_t v_scales, uint64_t k_out, uint64_t v_out, int32_t n_s, int32_t nh,
+                                                int32_t nkv, int32_t l_hd, int32_t l_kvd, int32_t cache_cap,
+                                                int32_t cache_hd, int32_t base_pos, float theta, int32_t rope_dim,
+                                                int32_t kv_fmt) {
+    const char *who = "nomos_kv_norm_rope_append";
+    if (n_s <= 0) return NOMOS_OK;
+    REQUIRE(src_k && src_v && k_norm_w, "%s: null pointer", who);
+    REQUIRE(!q || (q_norm_w && nh > 0), "%s: query rows need q_norm_w and nh", who);
+    REQUIRE(nkv > 0 && l_hd > 0 && l_hd % 2 == 0, "%s: bad geometry nkv=%d l_hd=%d", who, nkv, l_hd);
+    REQUIRE(l_kvd >= nkv * l_hd || n_s == 1, "%s: token stride l_kvd=%d < nkv*l_hd", who, l_kvd);
+    REQUIRE(base_pos >= 0, "%s: base_pos %d", who, base_pos);
+    REQUIRE(rope_dim >= 0 && rope_dim <= l_hd && rope_dim % 2 == 0, "%s: rope_dim %d for head_dim %d", who, rope_dim, l_hd);
+    if (l_hd > 512) { set_error("%s: head_dim %d unsupported (at most 512)", who, l_hd); return NOMOS_EUNSUPPORTED; }
+    if (kv_fmt >= 0) {
+        if (kv_fmt != KV_I8 && kv_fmt != KV_I4 && kv_fmt != KV_I4B32) { set_error("%s: kv_fmt %d unknown", who, kv_fmt); return NOMOS_EBADARG; }
+        REQUIRE(dst_k && dst_v && k_scales && v_scales, "%s: null cache pointer", who);
+        REQUIRE(cache_cap > 0 && cache_hd >= l_hd, "%s: bad cache geometry cache_cap=%d cache_hd=%d", who, cache_cap, cache_hd);
+        REQUIRE(kv_fmt == KV_I8 || cache_hd % 2 == 0, "%s: odd cache_hd %d", who, cache_hd);
+        REQUIRE(n_s <= cache_cap, "%s: n_s=%d rows would overwrite each other in a ring of %d", who, n_s, cache_cap);
+    }
+    ProducerArgs a;
+    a.q = static_cast<float *>(ptr(q)); a.q_norm_w = static_cast<const float *>(ptr(q_norm_w));
+    a.src_k = static_cast<const float *>(ptr(src_k)); a.src_v = static_cast<const float *>(ptr(src_v));
+    a.k_norm_w = static_cast<const float *>(ptr(k_norm_w));
+    a.dst_k = static_cast<uint8_t *>(ptr(dst_k)); a.dst_v = static_cast<uint8_t *>(ptr(dst_v));
+    a.k_scales = static_cast<uint8_t *>(ptr(k_scales)); a.v_scales = static_cast<uint8_t *>(ptr(v_scales));
+    a.k_out = static_cast<float *>(ptr(k_out)); a.v_out = static_cast<float *>(ptr(v_out));
+    a.n_s = n_s; a.nh = nh; a.nkv = nkv; a.l_hd = l_hd; a.l_kvd = l_kvd; a.cache_cap = cache_cap; a.cache_hd = cache_hd;
+    a.base_pos = base_pos; a.rope_dim = rope_dim; a.kv_fmt = kv_fmt; a.theta = theta;
+    return launch_kv_producer(as_stream(stream), a);
+}
+
 static int check_scale_blocks(const char *who, int l_hd, int scale_blocks) {
     REQUIRE(scale_blocks >= 1, "%s: scale_blocks %d", who, scale_blocks);
     if (scale_blocks > 1 && scale_blocks != (l_hd + 31) / 32) {

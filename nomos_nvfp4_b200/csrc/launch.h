@@ -68,6 +68,20 @@ int launch_merge_partials(cudaStream_t st, const float *partials, int G, int row
 int launch_merge_partials_log2(cudaStream_t st, const float *partials, int G, int rows, int l_hd, float *out);
 
 // ---- attn_dense.cu : fp32 / bf16 KV decode + prefix-batched attention
+// K / V / Q producer epilogue (kv_producer.cu): RMSNorm (+ weight), RoPE, quantize-on-write.
+struct ProducerArgs {
+    float *q;                     // [n_s][nh][l_hd] fp32, normalised + rotated in place; nullptr = no query rows
+    const float *q_norm_w;        // [l_hd]
+    const float *src_k, *src_v;   // [n_s][nkv][l_hd] fp32 raw projection rows, token stride l_kvd (not modified)
+    const float *k_norm_w;        // [l_hd]
+    uint8_t *dst_k, *dst_v;       // cache planes (layout of kv_fmt)
+    uint8_t *k_scales, *v_scales;
+    float *k_out, *v_out;         // optional [n_s][nkv][l_hd] fp32: the rows exactly as they were quantised
+    int n_s, nh, nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos, rope_dim, kv_fmt;   // kv_fmt < 0: no cache write
+    float theta;
+};
+int launch_kv_producer(cudaStream_t st, const ProducerArgs &a);
+
 struct DenseAttnArgs {
     const float *q;          // [S][nh][l_hd] fp32
     const void *k_cache;     // [nkv][max_seq][cache_hd] fp32 or bf16

@@ -86,6 +86,18 @@ def gpu_append_quant_kv_i8(stream, src_k, src_v, dst_k_i8, dst_v_i8, k_scales, v
         n_s, nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos))
 
 
+def kv_norm_rope_append(stream, q, q_norm_w, src_k, src_v, k_norm_w, dst_k, dst_v, k_scales, v_scales, *,
+                         n_s, nh, nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos, theta, rope_dim, kv_fmt,
+                         k_out=None, v_out=None):
+    """V-norm, QK-norm, RoPE (lib/gemma4_layer.mojo:326-340) and the quantising append in one launch.
+    `q` (or None) is rewritten in place; `kv_fmt` < 0 skips the cache write."""
+    def a(x):
+        return 0 if x is None else _addr(x)
+    _check(_lib.lib().nomos_kv_norm_rope_append(
+        _stream(stream), a(q), a(q_norm_w), a(src_k), a(src_v), a(k_norm_w), a(dst_k), a(dst_v), a(k_scales), a(v_scales),
+        a(k_out), a(v_out), n_s, nh, nkv, l_hd, l_kvd, cache_cap, cache_hd, base_pos, float(theta), rope_dim, kv_fmt))
+
+
 def gpu_dequant_kv_i8_layer(stream, src_i8, scales, dst_bf16, nkv, klen, cache_hd, max_seq, cache_cap, win_start):
     """lib/kv_cache_quant.mojo:274"""
     _check(_lib.lib().nomos_kv_dequant_i8_layer(

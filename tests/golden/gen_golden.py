@@ -47,8 +47,28 @@ def attn_case(fmt: str, seed: int, nh, nkv, hd, T, cap, S=1, window=0, scale=1.0
                 meta=np.array([nh, nkv, hd, T, cap, S, window], np.int64), scale=np.array([scale], np.float64))
 
 
+def producer_case(seed: int):
+    """Producer epilogue (V-norm, QK-norm, RoPE): 3 tokens from position 1022, 8 q / 4 kv heads x 128,
+    full rotary with theta 1e4, and the partial-rotary / theta 1e6 variant on the same inputs."""
+    from oracle import np_producer as npp
+    rng = np.random.default_rng(seed)
+    n_s, nh, nkv, hd, base = 3, 8, 4, 128, 1022
+    q = (rng.standard_normal((n_s, nh, hd)) * 3.0).astype(np.float32)
+    k = (rng.standard_normal((n_s, nkv, hd)) * 2.0).astype(np.float32)
+    v = (rng.standard_normal((n_s, nkv, hd)) * 0.7).astype(np.float32)
+    qw = (1.0 + 0.1 * rng.standard_normal(hd)).astype(np.float32)
+    kw = (1.0 + 0.1 * rng.standard_normal(hd)).astype(np.float32)
+    out = dict(q=q, k=k, v=v, qw=qw, kw=kw, meta=np.array([n_s, nh, nkv, hd, base], np.int64),
+               v_out=npp.rmsnorm_no_weight(v))
+    for tag, theta, rdim in (("sliding", 10000.0, hd), ("full", 1000000.0, hd // 4)):
+        out[f"k_out_{tag}"] = npp.rope(npp.qk_norm(k, kw), base, theta, rdim)
+        out[f"q_out_{tag}"] = npp.rope(npp.qk_norm(q, qw), base, theta, rdim)
+    return out
+
+
 def main():
     orc.build()
+    np.savez_compressed(HERE / "producer.npz", **producer_case(1010))
     for fmt in ("i8", "i4", "i4b32"):
         np.savez_compressed(HERE / f"codec_{fmt}.npz", **codec_case(fmt, 7))
     # configuration 1 (8/4 heads, hd 128, 512 keys, scale 1/sqrt(128)), int8

@@ -35,3 +35,13 @@ def test_attention_golden(oracle, name, fmt):
     out = oracle.attn_exact(g["q"], g["cache_k"], g["cache_v"], g["scales_k"], g["scales_v"], FMT_ID[fmt], nh, nkv, hd, hd,
                             cap, S=S, window=window, query_base_pos=T - S, win_lo=T - klen, softmax_scale=float(g["scale"][0]))
     assert np.allclose(out, g["out"], rtol=0, atol=1e-6)
+
+
+def test_producer_golden():
+    from oracle import np_producer as npp
+    g = load("producer.npz")
+    n_s, nh, nkv, hd, base = (int(x) for x in g["meta"])
+    assert np.allclose(npp.rmsnorm_no_weight(g["v"]), g["v_out"], rtol=0, atol=1e-12)
+    for tag, theta, rdim in (("sliding", 10000.0, hd), ("full", 1000000.0, hd // 4)):
+        assert np.allclose(npp.rope(npp.qk_norm(g["k"], g["kw"]), base, theta, rdim), g[f"k_out_{tag}"], rtol=0, atol=1e-12)
+        assert np.allclose(npp.rope(npp.qk_norm(g["q"], g["qw"]), base, theta, rdim), g[f"q_out_{tag}"], rtol=0, atol=1e-12)

@@ -54,3 +54,21 @@ def test_attention_golden(name, fmt):
     for r in range(S):
         ok, rel = within(got[r], g["out"][r], 2e-3)
         assert ok, f"{name} row {r}: {rel:.2e} x RMS"
+
+
+@pytest.mark.parametrize("tag,theta,rdim_div", [("sliding", 10000.0, 1), ("full", 1000000.0, 4)])
+def test_producer_golden(tag, theta, rdim_div):
+    """Producer epilogue against the stored float64 rows, within the float32 bound of oracle/np_producer.py."""
+    from oracle import np_producer as npp
+    g = load("producer.npz")
+    n_s, nh, nkv, hd, base = (int(x) for x in g["meta"])
+    rdim = hd // rdim_div
+    dq = dev(g["q"])
+    ko = torch.zeros((n_s, nkv, hd), dtype=torch.float32, device=DEV); vo = torch.zeros_like(ko)
+    ops.kv_norm_rope_append(None, dq, dev(g["qw"]), dev(g["k"]), dev(g["v"]), dev(g["kw"]), None, None, None, None,
+                            n_s=n_s, nh=nh, nkv=nkv, l_hd=hd, l_kvd=nkv * hd, cache_cap=0, cache_hd=hd, base_pos=base,
+                            theta=theta, rope_dim=rdim, kv_fmt=-1, k_out=ko, v_out=vo)
+    torch.cuda.synchronize()
+    assert np.all(np.abs(host(vo) - g["v_out"]) <= 2e-6 * np.max(np.abs(g["v_out"]), axis=-1, keepdims=True) + 1e-7)
+    assert np.all(np.abs(host(ko) - g[f"k_out_{tag}"]) <= npp.rope_tolerance(npp.qk_norm(g["k"], g["kw"]), base, theta, rdim))
+    assert np.all(np.abs(host(dq) - g[f"q_out_{tag}"]) <= npp.rope_tolerance(npp.qk_norm(g["q"], g["qw"]), base, theta, rdim))
