@@ -154,7 +154,7 @@ __device__ __forceinline__ void mma_u8u8_zero(int (&d)[4], uint32_t a0, uint32_t
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
 }
 
-// ---- TMA and mbarrier wrappers (CTA-local; no cluster multicast anywhere)
+// ---- TMA and mbarrier wrappers (every copy targets this CTA only)
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
 }
