@@ -218,9 +218,9 @@ def run_ours(args) -> dict:
         return {"metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": N, "steps": args.steps,
                 "ms_per_step": round(ms_per_step, 6), "quick": True} if rank == 0 else {}
 
-    # end to end through the C ABI with HOST buffers: per step one H2D copy (pinned) of the bf16 query and
-    # the new token's fp32 K/V rows, ONE library call (quantize-on-write fused into the attention kernel),
-    # one D2H copy of the bf16 output, host synchronisation.
+    # end to end through the C ABI with HOST buffers (nomos_attn_fused_host): per step one H2D copy (pinned) of
+    # the bf16 query and the new token's fp32 K/V rows, the fused kernel (quantize-on-write inside the attention
+    # kernel), one D2H copy of the bf16 output, host synchronisation -- all inside ONE library call.
     q_bytes, kv_bytes = seqs * nh_l * HD * 2, seqs * nkv_l * HD * 4
     stage_h = torch.empty(q_bytes + 2 * kv_bytes, dtype=torch.uint8).pin_memory()
     stage_h[:q_bytes].view(torch.bfloat16).copy_(torch.randn(seqs * nh_l * HD).to(torch.bfloat16))
@@ -237,12 +237,13 @@ def run_ours(args) -> dict:
             new_k=stage_d.data_ptr() + q_bytes, new_v=stage_d.data_ptr() + q_bytes + kv_bytes, n_new=1, new_base_pos=T - 1))
     h2d, d2h = stage_h.numel(), host_out.numel() * 2
 
+    hin, din, hout = stage_h.data_ptr(), stage_d.data_ptr(), host_out.data_ptr()
+    douts = [o.data_ptr() for o in outs]
+
     def e2e_step(i):
+        # nomos_attn_fused_host: cudaMemcpyAsync H2D, the fused kernel, cudaMemcpyAsync D2H, cudaStreamSynchronize
         j = i % NLAYERS
-        stage_d.copy_(stage_h, non_blocking=True)
-        ops.attn_fused(stream, e2e_args[j])
-        host_out.copy_(outs[j], non_blocking=True)
-        torch.cuda.synchronize()
+        ops.attn_fused_host(stream, e2e_args[j], hin, din, h2d, hout, douts[j], d2h)
 
     for i in range(3):
         e2e_step(i)

@@ -281,6 +281,16 @@ int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args);
 /* Run it. */
 int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *args);
 
+/* One decode / verify step for a caller whose step inputs and result live in HOST memory: copies
+ * in_bytes from host_in (pinned) to dev_in on the stream, runs nomos_attn_fused(stream, args) -- args
+ * point into dev_in for the query and the new K/V rows, and at dev_out for the output --, copies
+ * out_bytes from dev_out back to host_out (pinned) and synchronises the stream.  The KV cache stays
+ * resident on the device.  Either byte count may be 0.  No counterpart in the reference (its decode
+ * loop keeps activations on the device; only tokens cross the bus): it exists so that a host-side
+ * caller pays one library call per step instead of three runtime calls and a synchronise. */
+int32_t nomos_attn_fused_host(void *stream, const nomos_attn_args_t *args, uint64_t host_in, uint64_t dev_in,
+                              int64_t in_bytes, uint64_t host_out, uint64_t dev_out, int64_t out_bytes);
+
 /* nomos_attn_fused for callers that cannot pass a workspace.  No counterpart in the
  * reference (its engine allocates every scratch buffer itself at start-up).  The Nomos
  * engine commits its whole device-memory budget when it starts and treats a failed

@@ -430,6 +430,24 @@ NOMOS_EXPORT int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *arg
     return run_fused(as_stream(stream), a, "nomos_attn_fused");
 }
 
+NOMOS_EXPORT int32_t nomos_attn_fused_host(void *stream, const nomos_attn_args_t *args, uint64_t host_in, uint64_t dev_in,
+                                           int64_t in_bytes, uint64_t host_out, uint64_t dev_out, int64_t out_bytes) {
+    const char *who = "nomos_attn_fused_host";
+    REQUIRE(in_bytes >= 0 && out_bytes >= 0, "%s: negative byte count", who);
+    REQUIRE(in_bytes == 0 || (host_in && dev_in), "%s: null input staging pointer", who);
+    REQUIRE(out_bytes == 0 || (host_out && dev_out), "%s: null output staging pointer", who);
+    cudaStream_t st = as_stream(stream);
+    cudaError_t e = cudaSuccess;
+    if (in_bytes) e = cudaMemcpyAsync(ptr(dev_in), ptr(host_in), (size_t)in_bytes, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) { set_error("%s: host-to-device copy: %s", who, cudaGetErrorString(e)); return NOMOS_ECUDA; }
+    const int rc = nomos_attn_fused(stream, args);
+    if (rc) return rc;
+    if (out_bytes) e = cudaMemcpyAsync(ptr(host_out), ptr(dev_out), (size_t)out_bytes, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) { set_error("%s: device-to-host copy / synchronise: %s", who, cudaGetErrorString(e)); return NOMOS_ECUDA; }
+    return NOMOS_OK;
+}
+
 NOMOS_EXPORT int32_t nomos_attn_merge_partials(void *stream, uint64_t partials, int32_t G, int32_t rows, int32_t l_hd,
                                                uint64_t out, int32_t out_type) {
     if (rows <= 0) return NOMOS_OK;

@@ -252,6 +252,14 @@ def attn_fused(stream, args: AttnArgs) -> None:
     _check(_lib.lib().nomos_attn_fused(_stream(stream), C.byref(args)))
 
 
+def attn_fused_host(stream, args: AttnArgs, host_in, dev_in, in_bytes: int, host_out, dev_out, out_bytes: int) -> None:
+    """One step with host-resident inputs and result: pinned ``host_in`` -> ``dev_in``, ``attn_fused``,
+    ``dev_out`` -> pinned ``host_out``, stream synchronised -- one library call instead of three runtime
+    calls and a synchronise."""
+    _check(_lib.lib().nomos_attn_fused_host(_stream(stream), C.byref(args), _addr(host_in), _addr(dev_in), int(in_bytes),
+                                            _addr(host_out), _addr(dev_out), int(out_bytes)))
+
+
 def attn_fused_static_ws(stream, args: AttnArgs) -> None:
     """``attn_fused`` for callers that cannot provide a workspace (an engine whose memory budget
     is fully committed at start-up, a decode loop that must never call the allocator): the split

@@ -296,6 +296,38 @@ def test_fused_append_then_attend_i8(oracle):
     assert np.array_equal(caches[1].view(np.uint8), c.v.view(np.uint8)) and np.array_equal(caches[3], c.vs)
 
 
+def test_host_buffer_step_matches_device_call(oracle):
+    """nomos_attn_fused_host: query and new rows arrive in pinned host memory, the output lands there;
+    the result and the appended cache rows equal those of the device-buffer call."""
+    rng = np.random.default_rng(43)
+    nh, nkv, hd, cap, T = 8, 4, 128, 512, 400
+    c = build_cache("i8", rng, T - 1, nkv, hd, cap=cap)
+    new_k, new_v = bf16_normal(rng, (1, nkv, hd)), bf16_normal(rng, (1, nkv, hd))
+    q = bf16_normal(rng, (1, nh, hd))
+    qb, kb = nh * hd * 4, nkv * hd * 4
+    host_in = torch.empty(qb + 2 * kb, dtype=torch.uint8).pin_memory()
+    host_in[:qb].view(torch.float32).copy_(torch.from_numpy(np.ascontiguousarray(q, np.float32)).reshape(-1))
+    host_in[qb:qb + kb].view(torch.float32).copy_(torch.from_numpy(np.ascontiguousarray(new_k, np.float32)).reshape(-1))
+    host_in[qb + kb:].view(torch.float32).copy_(torch.from_numpy(np.ascontiguousarray(new_v, np.float32)).reshape(-1))
+    dev_in = torch.zeros_like(host_in, device=DEV)
+    host_out = torch.full((1, nh, hd), SENTINEL, dtype=torch.float32).pin_memory()
+    dev_out = torch.zeros((1, nh, hd), dtype=torch.float32, device=DEV)
+    dk, dv, dks, dvs = dev(c.k), dev(c.v), dev(c.ks), dev(c.vs)
+    a = ops.make_args(q=dev_in.data_ptr(), k_cache=dk, v_cache=dv, k_scales=dks, v_scales=dvs, out=dev_out, kv_fmt=ops.KV_I8,
+                      nh=nh, nkv=nkv, kvg=2, l_hd=hd, cache_hd=hd, cache_cap=cap, klen=T, softmax_scale=0.1,
+                      new_k=dev_in.data_ptr() + qb, new_v=dev_in.data_ptr() + qb + kb, n_new=1, new_base_pos=T - 1,
+                      flags=EXTRA_FLAGS)
+    ws = torch.empty(max(ops.attn_workspace_bytes(a), 16), dtype=torch.uint8, device=DEV)
+    a.workspace, a.ws_bytes = ws.data_ptr(), ws.numel()
+    ops.attn_fused_host(None, a, host_in, dev_in, host_in.numel(), host_out, dev_out, host_out.numel() * 4)
+    got = host_out.numpy().copy()                       # no synchronise here: the call returns with the data in place
+    c.append(new_k, new_v, T - 1)
+    want = exact(oracle, c, q, klen=T, scale=0.1)
+    ok, rel = within(got, want, TOL)
+    assert ok, f"{rel:.2e} x RMS"
+    assert np.array_equal(host(dk).view(np.uint8), c.k.view(np.uint8)) and np.array_equal(host(dks), c.ks)
+
+
 # ------------------------------------------------------- partial export and merge
 
 def test_partials_merge_equals_full(oracle):
