@@ -276,6 +276,47 @@ int32_t nomos_kv_norm_rope_append(void *stream, uint64_t q, uint64_t q_norm_w, u
                                    int32_t nkv, int32_t l_hd, int32_t l_kvd, int32_t cache_cap, int32_t cache_hd,
                                    int32_t base_pos, float theta, int32_t rope_dim, int32_t kv_fmt);
 
+/* ------------------------------------------------------------------------- *
+ *  Ring bookkeeping (host only, no device work)                              *
+ * ------------------------------------------------------------------------- *
+ * One layer's lengths and window arithmetic, which the reference keeps in its engine loops
+ * (lib/engine_decode.mojo:420-444: win_start / klen / lo; lib/gemma4_engine.mojo:897-901:
+ * set_cache_len for KV reuse and for the roll-back after a verify pass).  The reference refuses
+ * verify, offset prefill and chunked appends on its sliding-window ring (lib/engine_prefill.mojo:87-88,
+ * lib/engine_decode.mojo:158-176) because a ring of exactly W slots lets a batch overwrite keys its
+ * own earlier rows still need.  A ring with max_rows - 1 slots of slack does not have that problem:
+ * nomos_kv_ring_init insists on cache_cap >= window + max_rows - 1. */
+typedef struct nomos_kv_ring {
+    int64_t struct_bytes;       /* sizeof(nomos_kv_ring_t), set by nomos_kv_ring_init            */
+    int64_t cache_cap;          /* slots per KV head                                             */
+    int64_t window;             /* sliding window W; 0 = linear cache (full attention)           */
+    int64_t max_rows;           /* most rows one call appends (1 = decode only, VB = verify)     */
+    int64_t len;                /* committed positions [0, len)                                  */
+    int64_t staged;             /* rows the last plan placed at len .. len+staged-1, uncommitted */
+    int64_t high;               /* one past the highest position ever written                    */
+} nomos_kv_ring_t;
+
+typedef struct nomos_kv_step {
+    int64_t base_pos;           /* position of the first new row = append base = query_base_pos  */
+    int64_t n_new;              /* rows of this call (S of the attention call)                   */
+    int64_t win_start;          /* absolute position of window index 0                           */
+    int64_t klen;               /* keys in the window, the new rows included                     */
+    int64_t window;             /* per-row sliding window to pass on (0 = none)                  */
+} nomos_kv_step_t;
+
+int32_t nomos_kv_ring_init(nomos_kv_ring_t *ring, int64_t cache_cap, int64_t window, int64_t max_rows);
+/* Places n_new rows at positions len .. len+n_new-1 and works out the attention window of the call
+ * that appends and reads them (decode: n_new = 1; verify: n_new = VB).  -3 when a linear cache would
+ * overflow (the reference's capacity guard, lib/engine_decode.mojo:166-188) or n_new > max_rows. */
+int32_t nomos_kv_ring_plan(nomos_kv_ring_t *ring, int64_t n_new, nomos_kv_step_t *step);
+/* Keeps the first `accepted` of the staged rows (len += accepted); the rest is overwritten later. */
+int32_t nomos_kv_ring_commit(nomos_kv_ring_t *ring, int64_t accepted);
+/* set_cache_len: truncate to n <= len committed positions (KV reuse).  On a ring, -3 if the rows the
+ * next step needs have already been overwritten. */
+int32_t nomos_kv_ring_set_len(nomos_kv_ring_t *ring, int64_t n);
+/* Copies cache_cap, S, win_start, klen, window, n_new, new_base_pos of the step into args. */
+int32_t nomos_kv_ring_fill_args(const nomos_kv_ring_t *ring, const nomos_kv_step_t *step, nomos_attn_args_t *args);
+
 /* Bytes of workspace the call needs (>= 0), or a negative status. */
 int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args);
 /* Run it. */

@@ -36,8 +36,24 @@ class AttnArgs(C.Structure):
     ]
 
 
+class KvRing(C.Structure):
+    """Mirror of ``nomos_kv_ring_t``."""
+    _fields_ = [("struct_bytes", i64), ("cache_cap", i64), ("window", i64), ("max_rows", i64), ("len", i64),
+                ("staged", i64), ("high", i64)]
+
+
+class KvStep(C.Structure):
+    """Mirror of ``nomos_kv_step_t``."""
+    _fields_ = [("base_pos", i64), ("n_new", i64), ("win_start", i64), ("klen", i64), ("window", i64)]
+
+
 # name -> (restype, argtypes); must list every symbol include/nomos_attn.h declares.
 PROTOTYPES = {
+    "nomos_kv_ring_init": (i32, [C.POINTER(KvRing), i64, i64, i64]),
+    "nomos_kv_ring_plan": (i32, [C.POINTER(KvRing), i64, C.POINTER(KvStep)]),
+    "nomos_kv_ring_commit": (i32, [C.POINTER(KvRing), i64]),
+    "nomos_kv_ring_set_len": (i32, [C.POINTER(KvRing), i64]),
+    "nomos_kv_ring_fill_args": (i32, [C.POINTER(KvRing), C.POINTER(KvStep), C.POINTER(AttnArgs)]),
     "nomos_attn_version": (i32, []),
     "nomos_attn_last_error": (C.c_char_p, []),
     "nomos_attn_device_faults": (i32, [C.POINTER(C.c_uint32), i32]),

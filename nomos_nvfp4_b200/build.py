@@ -25,7 +25,7 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler",
 # Per-file extra flags.  The codecs must not contract a*b+c into an FMA: their
 # bytes are compared bit-for-bit with a CPU restatement of the reference.
 EXTRA = {"kv_quant.cu": ["-fmad=false"], "kv_producer.cu": ["-fmad=false"]}
-SOURCES = ["abi.cu", "kv_quant.cu", "kv_producer.cu", "attn_fused.cu", "attn_dense.cu"]
+SOURCES = ["abi.cu", "kv_quant.cu", "kv_producer.cu", "kv_ring.cu", "attn_fused.cu", "attn_dense.cu"]
 
 
 def nvcc() -> str:

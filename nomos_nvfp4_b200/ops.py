@@ -252,6 +252,34 @@ def attn_fused(stream, args: AttnArgs) -> None:
     _check(_lib.lib().nomos_attn_fused(_stream(stream), C.byref(args)))
 
 
+class KvRing:
+    """One layer's ring bookkeeping (``nomos_kv_ring_*``): lengths, window arithmetic, staged rows,
+    roll-back.  ``window`` = 0 is a linear cache.  A ring that serves batches of ``max_rows`` rows needs
+    ``cache_cap >= window + max_rows - 1``."""
+
+    def __init__(self, cache_cap: int, window: int, max_rows: int = 1):
+        self.c = _lib.KvRing()
+        _check(_lib.lib().nomos_kv_ring_init(C.byref(self.c), cache_cap, window, max_rows))
+
+    @property
+    def len(self) -> int:
+        return int(self.c.len)
+
+    def plan(self, n_new: int) -> "_lib.KvStep":
+        step = _lib.KvStep()
+        _check(_lib.lib().nomos_kv_ring_plan(C.byref(self.c), n_new, C.byref(step)))
+        return step
+
+    def commit(self, accepted: int) -> None:
+        _check(_lib.lib().nomos_kv_ring_commit(C.byref(self.c), accepted))
+
+    def set_len(self, n: int) -> None:
+        _check(_lib.lib().nomos_kv_ring_set_len(C.byref(self.c), n))
+
+    def fill_args(self, step, args: AttnArgs) -> None:
+        _check(_lib.lib().nomos_kv_ring_fill_args(C.byref(self.c), C.byref(step), C.byref(args)))
+
+
 def attn_fused_host(stream, args: AttnArgs, host_in, dev_in, in_bytes: int, host_out, dev_out, out_bytes: int) -> None:
     """One step with host-resident inputs and result: pinned ``host_in`` -> ``dev_in``, ``attn_fused``,
     ``dev_out`` -> pinned ``host_out``, stream synchronised -- one library call instead of three runtime
