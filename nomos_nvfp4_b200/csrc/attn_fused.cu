@@ -317,7 +317,8 @@ static bool tc5_disabled_by_env() {
     return off;
 }
 static bool tc5_eligible(const AttnArgs &a) {
-    if (a.kv_fmt != KV_I8 || a.l_hd != 128 || a.new_k != nullptr || a.no_tma || a.no_tcgen05) return false;
+    if (a.kv_fmt != KV_I8 || a.l_hd != 128 || a.no_tma || a.no_tcgen05) return false;
+    if (a.new_k != nullptr && (a.n_new > tc5::NEW_MAX || a.cache_hd != a.l_hd)) return false;
     // more than eight query rows per KV head (verify) currently run faster on the mma.sync kernel
     static const bool wide = [] { const char *e = std::getenv("NOMOS_ATTN_TCGEN05_VERIFY"); return e && e[0] == '1'; }();
     if (a.S * a.kvg > 8 && !wide && !a.tcgen05_always) return false;
@@ -446,6 +447,10 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     p.q_batch_stride = a.q_batch_stride; p.kv_batch_stride = a.kv_batch_stride;
     p.scale_batch_stride = a.scale_batch_stride; p.out_batch_stride = a.out_batch_stride;
     p.kvg_magic = a.kvg > 1 ? (unsigned int)(((1ull << 32) + a.kvg - 1) / a.kvg) : 0u;
+    p.new_k = a.new_k; p.new_v = a.new_v;
+    p.n_new = a.new_k ? a.n_new : 0; p.new_stride = a.new_stride; p.new_base_pos = a.new_base_pos;
+    p.k_cache_w = static_cast<uint8_t *>(const_cast<void *>(a.k_cache)); p.v_cache_w = static_cast<uint8_t *>(const_cast<void *>(a.v_cache));
+    p.k_scales_w = static_cast<uint8_t *>(const_cast<void *>(a.k_scales)); p.v_scales_w = static_cast<uint8_t *>(const_cast<void *>(a.v_scales));
     p.fault = fault_word();
     if (p.fault == nullptr) { set_error("attn_fused: device fault word unavailable"); return NOMOS_ECUDA; }
     cudaLaunchAttribute pdl[1];

@@ -23,6 +23,7 @@
 #pragma once
 
 #include "attn_fused_kernel.cuh"
+#include "kv_rows.cuh"
 
 namespace nomos {
 namespace tc5 {
@@ -42,6 +43,7 @@ constexpr int TILE_BYTES = KT * HD;          // one K or V tile (int8)
 constexpr int SCALE_BYTES = KT * 4;          // one tile's fp32 row scales
 constexpr int TMEM_COLS = 256;               // S0 | S1 | O0 | O1, 64 columns each
 constexpr float LG2_VS_MIN = -64.0f;
+constexpr int NEW_MAX = 8;                   // most rows one call may quantise on the way in
 #ifndef NOMOS_TC5_NSG
 #define NOMOS_TC5_NSG 4                      // slots per softmax warp group when a CTA serves more than eight
 #endif
@@ -84,9 +86,12 @@ struct Cfg {
     static constexpr int OFF_SLOT = OFF_XCH + 2 * NSP * 16;          // qscale[NSP], lo[NSP], hi[NSP]
     static constexpr int OFF_SLOTC = (OFF_SLOT + NSP * 12 + 15) / 16 * 16;   // per softmax warp: 16 x (max, weight, alpha, -)
     static constexpr int OFF_BAR = OFF_SLOTC + NSW * 16 * 16;
-    static constexpr int NBAR = 2 * NSTG + 9 + 2 * NG;               // full, empty, s_ready, p_ready, o_ready, o_free (x2 each), xch (x2 per group), q_ready
+    static constexpr int NBAR = 2 * NSTG + 10 + 2 * NG;              // full, empty, s_ready, p_ready, o_ready, o_free (x2 each), q_ready, xch (x2 per group), patched
     static constexpr int OFF_MISC = OFF_BAR + NBAR * 8;              // tmem base, abort flag
-    static constexpr int SMEM_BYTES = 1024 + OFF_MISC + 16;
+    static constexpr int OFF_NEW = OFF_MISC + 16;                    // quantize-on-write: one row of codes + its scale for K and V
+    static constexpr int OFF_NEWSC = OFF_NEW + 2 * (128 + 16);       // scales of the new rows [2][NEW_MAX]
+    static constexpr int SMEM_BYTES = 1024 + OFF_NEWSC + 2 * NEW_MAX * 4;
+    static_assert(OFF_NEW % 16 == 0, "row scratch is copied in 16-byte chunks");
     static_assert(OFF_BAR % 8 == 0, "mbarriers need 8-byte alignment");
     static_assert(OFF_Q % 1024 == 0 && QP_BYTES % 1024 == 0, "operand tiles sit on swizzle-pattern boundaries");
 };
@@ -246,6 +251,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     auto bar_o_free = [&](int i) { return bar0 + 8 * (2 * NSTG + 6 + i); };
     auto bar_xch = [&](int g, int i) { return bar0 + 8 * (2 * NSTG + 9 + 2 * g + i); };
     const uint32_t bar_q_ready = bar0 + 8 * (2 * NSTG + 8);
+    const uint32_t bar_patched = bar0 + 8 * (2 * NSTG + 9 + 2 * NG);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, kvh = blockIdx.y;
@@ -264,6 +270,9 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     const int tile_end = min(p.ntiles, tile_begin + p.tiles_per_split);
     const int my_n = max(0, tile_end - tile_begin);
     const int row_base = kvh * p.cache_cap;          // this head's first row in the {rows} dimension of the maps
+    // fused quantize-on-write: the last n_new keys of the window arrive as fp32 rows with this call
+    const int new_lo = p.new_k ? p.klen - p.n_new : 0x7fffffff;      // window index of the first new key
+    auto tile_has_new = [&](const TileGeo &g) { return min(g.t0 + KT, g.t_hi) > new_lo; };
     // fp32 row scales ride TMA when every tile's first scale sits on a 16-byte boundary; otherwise
     // each softmax thread fetches its key's two scales one tile ahead with plain loads
     const bool scales_by_tma = (p.use_tma & 2) != 0;
@@ -283,6 +292,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             for (int g = 0; g < NG; ++g) fused::mbar_init(bar_xch(g, i), 128);
         }
         fused::mbar_init(bar_q_ready, 128 * NG);
+        fused::mbar_init(bar_patched, 32);
         fused::fence_mbar_init();
     }
     if (warp == NSW) {
@@ -332,12 +342,17 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             const uint32_t idesc_pv = make_idesc(C::N, true, false, true);
             const uint64_t qdesc = smem_desc_sw128(sm_u32 + C::OFF_Q);
             bool go = wait_or_abort(bar_q_ready, 0, abort_flag, p.fault);
+            int n_patched = 0;
             for (int i = 0; go && i <= my_n; ++i) {
                 if (i < my_n) {
                     // S^T[i&1] = K_i x Q^T.  The buffer's previous reader (tile i-2) was done before
                     // p_ready(i-2), which this thread observed when it issued PV(i-2).
                     const int st = i % NSTG;
                     if (!wait_or_abort(bar_full(st), (i / NSTG) & 1, abort_flag, p.fault)) break;
+                    if (tile_has_new(wg.tile(tile_begin + i))) {      // softmax warp 0 overwrites the new keys' rows first
+                        if (!wait_or_abort(bar_patched, n_patched & 1, abort_flag, p.fault)) break;
+                        ++n_patched;
+                    }
                     tc_fence_after();
                     const uint64_t kdesc = smem_desc_sw128(sm_u32 + st * 2 * TILE_BYTES);
 #pragma unroll
@@ -489,6 +504,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             }
         };
         fetch_scales(0);
+        int n_patched = 0;                               // tiles whose new rows were quantised in
         int done = 0;                                    // tiles whose P was handed to the tensor core
         for (int i = 0; alive && i < my_n; ++i) {
             const int st = i % NSTG, b2 = i & 1;
@@ -502,8 +518,51 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             const int t = g.t0 + kr;
             const bool row_ok = t >= g.t_lo && t < g.t_hi;
             const bool need_mask = g.t0 < max(g.t_lo, lo_max) || g.t0 + KT > min(g.t_hi, hi_min);
-            const float ks = scales_by_tma ? sc[kr] : ks_ld;
-            const float vs = row_ok ? fmaxf(scales_by_tma ? sc[KT + kr] : vs_ld, 5.421011e-20f) : 1.0f;   // floor 2^-64: keeps 1/vs finite
+            float ks = scales_by_tma ? sc[kr] : ks_ld;
+            float vs_raw = scales_by_tma ? sc[KT + kr] : vs_ld;
+            if (tile_has_new(g)) {
+                // ---- fused quantize-on-write.  Warp 0 quantises the fp32 rows with the row codec of the
+                // append kernels (bit for bit), overwrites the rows TMA fetched for those slots, keeps
+                // their scales in shared memory and -- row group 0 only, so once per KV head -- stores
+                // bytes and scales into the ring for later calls.  The MMA issuer waits for this.
+                if (warp == 0) {
+                    uint8_t *scr = sm + C::OFF_NEW;
+                    float *new_sc = reinterpret_cast<float *>(sm + C::OFF_NEWSC);
+                    for (int n = 0; n < p.n_new; ++n) {
+                        const int wi = new_lo + n;                        // window index of new key n
+                        if (wi < max(g.t0, g.t_lo) || wi >= min(g.t0 + KT, g.t_hi)) continue;
+                        const int r = wi - g.t0;
+                        const size_t crow = (size_t)row_base + (size_t)((p.new_base_pos + n) % p.cache_cap);
+#pragma unroll
+                        for (int kv = 0; kv < 2; ++kv) {
+                            const float *src = (kv ? p.new_v : p.new_k) + ((size_t)b * p.n_new + n) * p.new_stride + kvh * HD;
+                            quant_row_i8(src, HD, HD, reinterpret_cast<int8_t *>(scr + kv * 144), reinterpret_cast<float *>(scr + kv * 144 + 128), lane);
+                            if (rg == 0) {
+                                int8_t *g_rows = reinterpret_cast<int8_t *>(kv ? p.v_cache_w : p.k_cache_w) + b * p.kv_batch_stride + crow * p.cache_hd;
+                                float *g_sc = reinterpret_cast<float *>((kv ? p.v_scales_w : p.k_scales_w) + b * p.scale_batch_stride) + crow;
+                                quant_row_i8(src, HD, p.cache_hd, g_rows, g_sc, lane);
+                            }
+                            __syncwarp();
+                            uint8_t *tile_rows = sm + st * 2 * TILE_BYTES + kv * TILE_BYTES;
+                            if (lane < 8)
+                                *reinterpret_cast<uint4 *>(tile_rows + (r >> 3) * 1024 + (r & 7) * 128 + ((lane ^ (r & 7)) << 4)) =
+                                    *reinterpret_cast<const uint4 *>(scr + kv * 144 + lane * 16);
+                            if (lane == 0) new_sc[kv * NEW_MAX + n] = *reinterpret_cast<const float *>(scr + kv * 144 + 128);
+                            __syncwarp();
+                        }
+                    }
+                    fused::fence_proxy_async();                          // the tensor core reads the patched rows
+                    mbar_arrive(bar_patched);
+                }
+                if (!wait_warp(bar_patched, n_patched & 1)) { alive = false; break; }
+                ++n_patched;
+                if (t >= new_lo && row_ok) {
+                    const float *new_sc = reinterpret_cast<const float *>(sm + C::OFF_NEWSC);
+                    ks = new_sc[t - new_lo];
+                    vs_raw = new_sc[NEW_MAX + t - new_lo];
+                }
+            }
+            const float vs = row_ok ? fmaxf(vs_raw, 5.421011e-20f) : 1.0f;   // floor 2^-64: keeps 1/vs finite
             const float lvs = lg2f(vs), rvs = row_ok ? rcpf(vs) : 0.0f;
             float qk[NSG];
 #pragma unroll

@@ -22,7 +22,7 @@ def test_verify_over_ring_with_rollback(oracle, fmt):
     c = KVCache(fmt, nkv, cap, hd)
     dk, dv, dks, dvs = dev(c.k), dev(c.v), dev(c.ks), dev(c.vs)
     hist_k = np.zeros((0, nkv, hd), np.float32); hist_v = np.zeros((0, nkv, hd), np.float32)
-    for step_no in range(40):
+    for step_no in range(110):
         n = 1 if step_no % 3 == 0 else int(rng.integers(2, VB + 1))
         st = ring.plan(n)
         L = int(st.base_pos)
@@ -52,4 +52,4 @@ def test_verify_over_ring_with_rollback(oracle, fmt):
         accepted = n if n == 1 else int(rng.integers(0, n + 1))
         ring.commit(accepted)
         hist_k = np.concatenate([hist_k, new_k[:accepted]]); hist_v = np.concatenate([hist_v, new_v[:accepted]])
-    assert ring.len == hist_k.shape[0] and ring.len > W          # the ring wrapped several times
+    assert ring.len == hist_k.shape[0] and ring.len > cap        # the ring wrapped
