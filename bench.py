@@ -470,6 +470,26 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
             del ck, cv, cks, cvs
         except Exception as e:
             out[name] = {"error": str(e)}
+    # configuration 5a: batch 8 x 131072 keys, sharded by KV-head groups (16 / world heads per GPU, no collective)
+    try:
+        B5, T5a = 8, 131072
+        nkv5 = NKV // world
+        nh5 = nkv5 * (NH // NKV)
+        cache = make_layer_cache(torch, ops, dev, B5, nkv5, T5a, HD, 1105 + rank)
+        q = torch.randn((B5, 1, nh5, HD), device=dev).to(torch.bfloat16)
+        o = torch.zeros((B5, 1, nh5, HD), dtype=torch.bfloat16, device=dev)
+        a5 = decode_args(ops, q, cache, o, nh5, nkv5, HD, T5a, B5)
+        wsb = ops.attn_workspace_bytes(a5)
+        ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+        a5.workspace, a5.ws_bytes = ws.data_ptr(), wsb
+        us = time_call(torch, lambda: ops.attn_fused(stream, a5), max(10, iters // 8))
+        if world > 1:
+            tt = torch.tensor([us], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX); us = float(tt.item())
+        by = algorithmic_bytes(NKV, NH // NKV, T5a, HD, B5)
+        out["c5a_batch8_131k_head_sharded"] = {"us_per_layer": round(us, 2), "GBps_aggregate": round(by / us / 1e3, 1), "gpus": world}
+        del cache, ws
+    except Exception as e:
+        out["c5a_batch8_131k_head_sharded"] = {"error": str(e)}
     # configuration 5b: batch 1 x 524288 keys, sharded by sequence chunks, (o, m, l) all-gathered and merged
     try:
         T5 = 524288 // world
