@@ -161,17 +161,17 @@ struct Plan {
     int mt, row_groups, tile0, ntiles, splits, tiles_per_split, grows;
 };
 
-template <int FMT, int HD, int MT>
+template <int FMT, int HD, int MT, int DS>
 static int kernel_occupancy() {
     static int occ[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (occ[dev] == 0) {
-        using C = Cfg<FMT, HD, MT>;
-        cudaFuncSetAttribute(attn_fused_kernel<FMT, HD, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        using C = Cfg<FMT, HD, MT, DS>;
+        cudaFuncSetAttribute(attn_fused_kernel<FMT, HD, MT, DS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         int n = 0;
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_fused_kernel<FMT, HD, MT>, C::NW * 32, C::SMEM_BYTES);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_fused_kernel<FMT, HD, MT, DS>, C::NW * 32, C::SMEM_BYTES);
         occ[dev] = n > 0 ? n : 1;
     }
     return occ[dev];
@@ -183,7 +183,7 @@ static int kernel_occupancy() {
 // and 255 registers.  Beyond that the 24-row kernel keeps the number of L2 re-reads down.
 static int pick_mt(int slots, int hd = 128) { return (slots <= 24 || hd > 128) ? 1 : 3; }
 
-static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp) {
+static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp, int dsplit = 1) {
     Plan pl;
     const int slots = a.S * a.kvg;
     pl.mt = pick_mt(slots, hd);
@@ -194,7 +194,7 @@ static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp) {
     pl.tile0 = j_begin / TILE;
     pl.ntiles = (a.klen + TILE - 1) / TILE - pl.tile0;
     pl.grows = a.batch * a.S * a.nh;
-    const int units = a.nkv * a.batch * pl.row_groups;
+    const int units = a.nkv * a.batch * pl.row_groups * dsplit;      // CTAs per sequence split
     const int slots_gpu = device_info().sm_count * occupancy;
     int best = 1;
     if (a.force_splits > 0) {
@@ -226,11 +226,11 @@ static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp) {
     return pl;
 }
 
-template <int FMT, int HD, int MT>
+template <int FMT, int HD, int MT, int DS = 1>
 static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *ws_needed) {
-    using C = Cfg<FMT, HD, MT>;
-    const int occ = kernel_occupancy<FMT, HD, MT>();
-    const Plan pl = make_plan(a, occ, HD, C::NW);
+    using C = Cfg<FMT, HD, MT, DS>;
+    const int occ = kernel_occupancy<FMT, HD, MT, DS>();
+    const Plan pl = make_plan(a, occ, HD, C::NW, DS);
     const long units = (long)a.nkv * a.batch * pl.row_groups;
     const long part_bytes = (((long)pl.splits * pl.grows * (HD + 2) * 4) + 15) / 16 * 16;
     const long need = pl.splits > 1 ? part_bytes + units * 8 : 0;
@@ -253,6 +253,7 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     p.counters = pl.splits > 1 ? reinterpret_cast<unsigned long long *>(static_cast<char *>(a.workspace) + part_bytes) : nullptr;
     p.epoch = next_epoch();
     p.splits = pl.splits;
+    p.arrivals = pl.splits * DS;
     p.partial_export = a.partial_out;
     p.early_rows = a.settled_cache ? std::max(0, a.klen - std::max(a.S, a.n_new)) : 0;
     p.new_k = a.new_k; p.new_v = a.new_v;
@@ -293,7 +294,7 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
             }
         }
     }
-    dim3 grid(pl.splits, a.nkv, a.batch * pl.row_groups);
+    dim3 grid(pl.splits * DS, a.nkv, a.batch * pl.row_groups);
     // Launched with programmatic stream serialization allowed: after a grid that triggers early
     // (another attention call of this library) the grid is set up while the predecessor drains and
     // blocks in griddepcontrol.wait before its first global access; after any other kernel it
@@ -304,7 +305,7 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     cudaLaunchConfig_t mcfg = {};
     mcfg.gridDim = grid; mcfg.blockDim = dim3(C::NW * 32); mcfg.dynamicSmemBytes = C::SMEM_BYTES; mcfg.stream = st;
     mcfg.attrs = pdl; mcfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&mcfg, attn_fused_kernel<FMT, HD, MT>, p, tm);
+    cudaError_t e = cudaLaunchKernelEx(&mcfg, attn_fused_kernel<FMT, HD, MT, DS>, p, tm);
     if (e != cudaSuccess) { set_error("attn_fused launch: %s", cudaGetErrorString(e)); return NOMOS_ECUDA; }
     return NOMOS_OK;
 }
@@ -436,6 +437,7 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     p.counters = pl.splits > 1 ? reinterpret_cast<unsigned long long *>(static_cast<char *>(a.workspace) + part_bytes) : nullptr;
     p.epoch = next_epoch();
     p.splits = pl.splits;
+    p.arrivals = pl.splits;
     p.partial_export = a.partial_out;
     p.early_rows = a.settled_cache ? std::max(0, a.klen - std::max(a.S, a.n_new)) : 0;
     p.q_type = a.q_type; p.out_type = a.out_type;
@@ -488,10 +490,16 @@ template <int FMT>
 static int dispatch_hd(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
     switch (a.l_hd) {
         case 128: return dispatch_mt<FMT, 128>(st, a, q, ws);
-        // wider heads keep 64 / 128 fp32 sums per thread for one 8-row tile: more query rows are
-        // covered by row groups (extra CTAs over the same cache bytes, served from L2)
-        case 256: return launch_inst<FMT, 256, 1>(st, a, q, ws);
-        case 512: return launch_inst<FMT, 512, 1>(st, a, q, ws);
+        // Wider heads: one 8-row tile per CTA (more query rows are covered by row groups), and the PV
+        // product split over CTAs that each hold a 128-dim slice of the output (they all compute the
+        // full QK; K is read from HBM once and served to the other slices from L2).  Calls that append
+        // rows in the same launch keep the unsplit kernel.
+        case 256:
+            if (a.new_k == nullptr && FMT == KV_I8) return launch_inst<FMT, 256, 1, 2>(st, a, q, ws);
+            return launch_inst<FMT, 256, 1>(st, a, q, ws);
+        case 512:
+            if (a.new_k == nullptr) return launch_inst<FMT, 512, 1, 4>(st, a, q, ws);
+            return launch_inst<FMT, 512, 1>(st, a, q, ws);
         default: set_error("head_dim %d unsupported (128, 256, 512)", a.l_hd); return NOMOS_EUNSUPPORTED;
     }
 }

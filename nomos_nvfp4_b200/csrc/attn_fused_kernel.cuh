@@ -35,36 +35,46 @@ constexpr float P_FIX = 65535.0f;        // probabilities reach the tensor core 
 constexpr float LAZY_MAX = 8.0f;         // base-2 slack before the running softmax reference is moved
 constexpr float RND_MAGIC = 8388608.0f;  // 2^23: adding it leaves round-to-nearest(x) in the low mantissa bits
 
-template <int FMT, int HD, int MT>
+// DS > 1 splits the head dimension of the PV product over DS CTAs: each of them computes the full
+// QK (it reads all of K, the others' copies come from L2) but holds only HD / DS output dims and
+// streams only that slice of every V row.  Wide heads then keep as many warps per SM as head_dim 128.
+template <int FMT, int HD, int MT, int DS = 1>
 struct Cfg {
+    static constexpr int HDV = HD / DS;                                       // output dims of this CTA
     static constexpr int ROWB = (FMT == KV_I8) ? HD : HD / 2;                 // cache bytes per token row
+    static constexpr int ROWBV = ROWB / DS;                                   // bytes of a V row this CTA reads
     static constexpr int CHUNKS = ROWB / 16;                                  // 16-byte chunks per row
+    static constexpr int CHUNKSV = ROWBV / 16;
     static constexpr int NBLK = HD / 32;
+    static constexpr int NBLKV = HDV / 32;
     static constexpr int SCB = (FMT == KV_I4B32) ? NBLK * 2 : 4;              // scale bytes per token
-    static constexpr int KV_BYTES = TILE * ROWB;
+    static constexpr int KV_BYTES = TILE * ROWB;                              // K tile
+    static constexpr int V_BYTES = TILE * ROWBV;                              // V tile (slice)
+    static constexpr int ST_BYTES = KV_BYTES + V_BYTES;                       // tiles of one stage
     static constexpr int SC_BYTES = TILE * SCB;
-    static constexpr int STAGE_BYTES = 2 * KV_BYTES + 2 * SC_BYTES;
+    static constexpr int STAGE_BYTES = ST_BYTES + 2 * SC_BYTES;
     static constexpr int NSLOT = 8 * MT;                                      // query rows (row x group head) per CTA
-    static constexpr int NT = HD / 8;                                         // PV N tiles (8 output dims each)
+    static constexpr int NT = HDV / 8;                                        // PV N tiles (8 output dims each)
+    static_assert(ROWBV >= 64 && ROWBV % 64 == 0, "a V slice is copied in 64-byte column groups");
     static constexpr int Q_BYTES = 2 * NSLOT * HD;                            // two limbs
     static constexpr int SLOT_BYTES = NSLOT * 16 + NSLOT * NBLK * 4;          // qscale, lo, hi, pad; 8*sum(q) per block
     // warps per CTA: as many as the register file and ~200 KB of pipeline memory allow
-    static constexpr int NW_REG = (MT == 1 && HD <= 256) ? NOMOS_NWARP : NOMOS_NWARP_MULTI;
+    static constexpr int NW_REG = (MT == 1 && HDV <= 256) ? NOMOS_NWARP : NOMOS_NWARP_MULTI;
     static constexpr int NW_MEM = (200 * 1024) / (NSTAGE * STAGE_BYTES);
     static constexpr int NW = NW_REG < NW_MEM ? NW_REG : (NW_MEM < 1 ? 1 : NW_MEM);
     static constexpr int APPEND_BYTES = NW * (ROWB + 64);                     // per warp: one quantised row + its scales
     // Shared-memory map: [K/V tiles of every warp and stage | scales | query limbs | slot
     // constants | append scratch | mbarriers].  The tile region starts on a 1024-byte boundary
     // (what the TMA swizzle patterns are defined against) and is reused for the merges.
-    static constexpr int TILES_BYTES = NW * NSTAGE * 2 * KV_BYTES;
+    static constexpr int TILES_BYTES = NW * NSTAGE * ST_BYTES;
     static constexpr int SCALES_BYTES = NW * NSTAGE * 2 * SC_BYTES;
-    static constexpr int MERGE_BYTES = NW * NSLOT * (HD + 2) * 4;
+    static constexpr int MERGE_BYTES = NW * NSLOT * (HDV + 2) * 4;
     static constexpr int REGION0_BYTES = ((TILES_BYTES > MERGE_BYTES ? TILES_BYTES : MERGE_BYTES) + 15) / 16 * 16;
     static constexpr int BAR_BYTES = NW * NSTAGE * 8;
     static constexpr int SMEM_BYTES = 1024 + REGION0_BYTES + SCALES_BYTES + Q_BYTES + SLOT_BYTES + APPEND_BYTES + BAR_BYTES;
     // Rows of 64 / 128 bytes map one-to-one onto the TMA 64B / 128B swizzle patterns, which are
     // the XOR layouts swz_chunk() defines; wider rows stay on the cp.async path.
-    static constexpr bool TMA_OK = (ROWB == 64 || ROWB == 128);
+    static constexpr bool TMA_OK = (ROWB == 64 || ROWB == 128) && DS == 1;
 };
 
 // Tensor maps of the K and V byte planes: {row bytes, nkv * cache_cap rows, batch}.
@@ -87,6 +97,7 @@ struct KParams {
     unsigned long long *counters;   // one word per unit: (epoch << 16) | arrivals; nullptr = no in-kernel merge
     unsigned long long epoch;       // unique per launch, so stale or uninitialised words read as "0 arrivals"
     int splits;
+    int arrivals;                   // CTAs per unit that arrive before the merge: splits x head-dim slices
     float *partial_export;          // optional exported (o, m, l) per row, m in natural-log units
     int early_rows;                 // window rows [0, early_rows) may be read before griddepcontrol.wait
     // fused quantize-on-write: the last n_new keys of the window are given as fp32 rows
@@ -261,8 +272,8 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
                 }
             }
         }
-        if (arrived == p.splits) *ctr = TAG << 16;                // clean for the next launch on this workspace
-        s_last = (arrived == p.splits);
+        if (arrived == p.arrivals) *ctr = TAG << 16;                // clean for the next launch on this workspace
+        s_last = (arrived == p.arrivals);
     }
     __syncthreads();
     MERGE_MARK(2);
@@ -414,10 +425,11 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
 #endif
 }
 
-template <int FMT, int HD, int MT>
-__global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
+template <int FMT, int HD, int MT, int DS = 1>
+__global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
     attn_fused_kernel(const KParams p, const __grid_constant__ TmaMaps tm) {
-    using C = Cfg<FMT, HD, MT>;
+    using C = Cfg<FMT, HD, MT, DS>;
+    constexpr int HDV = C::HDV;
     constexpr int NWARP = C::NW;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *pipe = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // K/V tiles [NW][NSTAGE][2]
@@ -433,7 +445,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int split = blockIdx.x, kvh = blockIdx.y;
+    const int split = blockIdx.x / DS, dsl = blockIdx.x % DS, kvh = blockIdx.y;     // dsl: head-dim slice of this CTA
     const int b = blockIdx.z / p.row_groups, rg = blockIdx.z % p.row_groups;
 
     // ------------------------------------------------------------ tile schedule
@@ -444,11 +456,11 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
 
     const int row_stride = (FMT == KV_I8) ? p.cache_hd : p.cache_hd / 2;   // bytes between consecutive token rows
     const uint8_t *kbase = p.k_cache + b * p.kv_batch_stride + (size_t)kvh * p.cache_cap * (size_t)row_stride;
-    const uint8_t *vbase = p.v_cache + b * p.kv_batch_stride + (size_t)kvh * p.cache_cap * (size_t)row_stride;
+    const uint8_t *vbase = p.v_cache + b * p.kv_batch_stride + (size_t)kvh * p.cache_cap * (size_t)row_stride + dsl * C::ROWBV;
     const uint8_t *ksbase = p.k_scales + b * p.scale_batch_stride + (size_t)kvh * p.cache_cap * C::SCB;
     const uint8_t *vsbase = p.v_scales + b * p.scale_batch_stride + (size_t)kvh * p.cache_cap * C::SCB;
 
-    uint8_t *my_pipe = pipe + warp * NSTAGE * 2 * C::KV_BYTES;       // stage s: K tile, V tile
+    uint8_t *my_pipe = pipe + warp * NSTAGE * C::ST_BYTES;           // stage s: K tile, V tile (slice)
     uint8_t *my_sc = sc_region + warp * NSTAGE * 2 * C::SC_BYTES;    // stage s: K scales, V scales
     const uint32_t my_pipe_u32 = smem_u32(my_pipe), my_sc_u32 = smem_u32(my_sc);
     const uint32_t my_bar_u32 = bars_u32 + warp * NSTAGE * 8;
@@ -474,6 +486,10 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
     uint32_t lane_soff[HPASS];
 #pragma unroll
     for (int h = 0; h < HPASS; ++h) lane_soff[h] = cr * C::ROWB + swz_chunk<C::ROWB>(cr, cc0 + 4 * h) * 16;
+    constexpr int HPASSV = C::CHUNKSV / 4;
+    uint32_t lane_soffv[HPASSV];
+#pragma unroll
+    for (int h = 0; h < HPASSV; ++h) lane_soffv[h] = cr * C::ROWBV + swz_chunk<C::ROWBV>(cr, cc0 + 4 * h) * 16;
 
     // one token's scale bytes (4: fp32 row scale; 2 per block of 32 for the block-32 layout)
     auto copy_scales = [&](uint32_t dst, const uint8_t *src, bool ok) {
@@ -488,7 +504,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
         if (it < my_count) {
             const int tok0 = (my_first + it * NWARP) * TILE;
             const int stg = it % NSTAGE;
-            const uint32_t st = my_pipe_u32 + stg * 2 * C::KV_BYTES;
+            const uint32_t st = my_pipe_u32 + stg * C::ST_BYTES;
             const uint32_t ss = my_sc_u32 + stg * 2 * C::SC_BYTES;
             int slot0 = ring0 + tok0;
             slot0 = slot0 >= p.cache_cap ? slot0 - p.cache_cap : slot0;          // klen <= cache_cap (host-checked)
@@ -520,14 +536,14 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
                 const uint8_t *gk = kbase + (size_t)slot0 * row_stride + lane_goff;
                 const uint8_t *gv = vbase + (size_t)slot0 * row_stride + lane_goff;
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
+                for (int i = 0; i < 4; ++i) {
 #pragma unroll
-                    for (int h = 0; h < HPASS; ++h) {
-                        const size_t go = (size_t)(8 * i) * row_stride + 64 * h;
-                        const uint32_t so = st + lane_soff[h] + 8 * i * C::ROWB;
-                        cp_async16(so, gk + go, 16);
-                        cp_async16(so + C::KV_BYTES, gv + go, 16);
-                    }
+                    for (int h = 0; h < HPASS; ++h)
+                        cp_async16(st + lane_soff[h] + 8 * i * C::ROWB, gk + (size_t)(8 * i) * row_stride + 64 * h, 16);
+#pragma unroll
+                    for (int h = 0; h < HPASSV; ++h)
+                        cp_async16(st + C::KV_BYTES + lane_soffv[h] + 8 * i * C::ROWBV, gv + (size_t)(8 * i) * row_stride + 64 * h, 16);
+                }
                 const size_t sg = (size_t)(slot0 + lane) * C::SCB;
                 copy_scales(ss + lane * C::SCB, ksbase + sg, true);
                 copy_scales(ss + C::SC_BYTES + lane * C::SCB, vsbase + sg, true);
@@ -541,11 +557,10 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
                     const bool ok = tok < p.klen;
                     const size_t go = (size_t)(ok ? slot : 0) * row_stride + cc0 * 16;
 #pragma unroll
-                    for (int h = 0; h < HPASS; ++h) {
-                        const uint32_t so = st + lane_soff[h] + 8 * i * C::ROWB;
-                        cp_async16(so, kbase + go + 64 * h, ok ? 16 : 0);
-                        cp_async16(so + C::KV_BYTES, vbase + go + 64 * h, ok ? 16 : 0);
-                    }
+                    for (int h = 0; h < HPASS; ++h) cp_async16(st + lane_soff[h] + 8 * i * C::ROWB, kbase + go + 64 * h, ok ? 16 : 0);
+#pragma unroll
+                    for (int h = 0; h < HPASSV; ++h)
+                        cp_async16(st + C::KV_BYTES + lane_soffv[h] + 8 * i * C::ROWBV, vbase + go + 64 * h, ok ? 16 : 0);
                 }
                 const int tok = tok0 + lane;
                 int slot = ring0 + tok;
@@ -712,7 +727,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
         __syncwarp();
 
         const int tok0 = (my_first + it * NWARP) * TILE;
-        const uint32_t st = my_pipe_u32 + stg * 2 * C::KV_BYTES;
+        const uint32_t st = my_pipe_u32 + stg * C::ST_BYTES;
         const bool need_mask = (tok0 + TILE > hi_min) || (tok0 < lo_max);
         const uint8_t *ksm = my_sc + stg * 2 * C::SC_BYTES;         // K scales of the tile, token-major
         const uint8_t *vsm = ksm + C::SC_BYTES;                     // V scales
@@ -733,7 +748,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
 #pragma unroll
                 for (int kv = 0; kv < 2; ++kv) {
                     const float *src = (kv ? p.new_v : p.new_k) + ((size_t)b * p.n_new + i) * p.new_stride + kvh * HD;
-                    uint8_t *tile_rows = my_pipe + (stg * 2 + kv) * C::KV_BYTES;
+                    uint8_t *tile_rows = my_pipe + stg * C::ST_BYTES + kv * C::KV_BYTES;      // fused append runs with DS == 1 only
                     uint8_t *tile_sc = my_sc + (stg * 2 + kv) * C::SC_BYTES + r * C::SCB;
                     uint8_t *g_rows = (kv ? p.v_cache_w : p.k_cache_w) + b * p.kv_batch_stride + crow * row_stride;
                     uint8_t *g_sc = (kv ? p.v_scales_w : p.k_scales_w) + b * p.scale_batch_stride;
@@ -884,7 +899,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
         // w = 2^(s - tile max) * v_scale, divided by the tile's largest w, is rounded to u16 and
         // split into two u8 limbs for the tensor core; F carries the tile's weight into the fp32
         // running sums.  Block-32 caches have one v_scale per (token, block of 32 dims).
-        constexpr int NVB = (FMT == KV_I4B32) ? C::NBLK : 1;
+        constexpr int NVB = (FMT == KV_I4B32) ? C::NBLKV : 1;             // V scale blocks of this CTA's slice
         float vsc[4][2][NVB];
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
@@ -893,7 +908,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
                 for (int e = 0; e < 2; ++e)
 #pragma unroll
                     for (int vb = 0; vb < NVB; ++vb)
-                        vsc[n][e][vb] = __half2float(*reinterpret_cast<const __half *>(vsm + ((8 * n + 2 * t + e) * C::NBLK + vb) * 2));
+                        vsc[n][e][vb] = __half2float(*reinterpret_cast<const __half *>(vsm + ((8 * n + 2 * t + e) * C::NBLK + dsl * C::NBLKV + vb) * 2));
             } else {
                 const float2 vv = *reinterpret_cast<const float2 *>(vsm + (8 * n + 2 * t) * 4);
                 vsc[n][0][0] = vv.x; vsc[n][1][0] = vv.y;
@@ -970,9 +985,9 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
         const uint32_t vst = st + C::KV_BYTES;
         if constexpr (FMT == KV_I8) {
 #pragma unroll
-            for (int ch = 0; ch < HD / 16; ++ch) {
+            for (int ch = 0; ch < HDV / 16; ++ch) {
                 uint32_t vr[4];           // vr[o]: tokens 8o+2t, 8o+2t+1 x dims 16ch+2g, 16ch+2g+1
-                ldmatrix_x4_trans(vr, vst + lane * C::ROWB + swz_chunk<C::ROWB>(lane, ch) * 16);
+                ldmatrix_x4_trans(vr, vst + lane * C::ROWBV + swz_chunk<C::ROWBV>(lane, ch) * 16);
                 const uint32_t be0 = prmt(vr[0], vr[1], 0x6420u), bo0 = prmt(vr[0], vr[1], 0x7531u);
                 const uint32_t be1 = prmt(vr[2], vr[3], 0x6420u), bo1 = prmt(vr[2], vr[3], 0x7531u);
 #pragma unroll
@@ -988,9 +1003,9 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
             }
         } else {
 #pragma unroll
-            for (int ch = 0; ch < HD / 32; ++ch) {          // packed chunk ch = block ch = dims 32ch..32ch+31
+            for (int ch = 0; ch < HDV / 32; ++ch) {         // packed chunk ch = block ch = dims 32ch..32ch+31 of the slice
                 uint32_t vr[4];           // vr[o]: tokens 8o+2t, 8o+2t+1 x packed bytes 16ch+2g, 16ch+2g+1
-                ldmatrix_x4_trans(vr, vst + lane * C::ROWB + swz_chunk<C::ROWB>(lane, ch) * 16);
+                ldmatrix_x4_trans(vr, vst + lane * C::ROWBV + swz_chunk<C::ROWBV>(lane, ch) * 16);
                 uint32_t pb[2][2];        // [byte 2g | 2g+1][tokens 0-15 | 16-31]: one packed byte of four tokens
                 pb[0][0] = prmt(vr[0], vr[1], 0x6420u); pb[1][0] = prmt(vr[0], vr[1], 0x7531u);
                 pb[0][1] = prmt(vr[2], vr[3], 0x6420u); pb[1][1] = prmt(vr[2], vr[3], 0x7531u);
@@ -1023,10 +1038,10 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
         l[mt] += __shfl_xor_sync(0xffffffffu, l[mt], 2);
     }
     __syncthreads();                      // every warp is done with its pipeline memory
-    float *mbuf = reinterpret_cast<float *>(pipe);          // [NWARP][NSLOT][HD+2]
+    float *mbuf = reinterpret_cast<float *>(pipe);          // [NWARP][NSLOT][HDV+2]
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
-        float *r0 = mbuf + ((size_t)warp * C::NSLOT + mt * 8 + g) * (HD + 2);
+        float *r0 = mbuf + ((size_t)warp * C::NSLOT + mt * 8 + g) * (HDV + 2);
 #pragma unroll
         for (int nt = 0; nt < C::NT; ++nt) {
             // this thread has MMA columns 2t, 2t+1 of n tile nt.  int8: column c of tile nt is
@@ -1041,7 +1056,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
                 r0[d0 + 4] = acc[mt][nt][1];
             }
         }
-        if (t == 0) { r0[HD] = M[mt]; r0[HD + 1] = l[mt]; }
+        if (t == 0) { r0[HDV] = M[mt]; r0[HDV + 1] = l[mt]; }
     }
     __syncthreads();
 
@@ -1051,29 +1066,29 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT>::NW * 32)
         if (r >= p.S) break;
         float mstar = M_INIT;
 #pragma unroll
-        for (int w = 0; w < NWARP; ++w) mstar = fmaxf(mstar, mbuf[((size_t)w * C::NSLOT + sl) * (HD + 2) + HD]);
+        for (int w = 0; w < NWARP; ++w) mstar = fmaxf(mstar, mbuf[((size_t)w * C::NSLOT + sl) * (HDV + 2) + HDV]);
         float wgt[NWARP], lstar = 0.0f;
 #pragma unroll
         for (int w = 0; w < NWARP; ++w) {
-            const float *rw = mbuf + ((size_t)w * C::NSLOT + sl) * (HD + 2);
-            wgt[w] = ex2f(rw[HD] - mstar);
-            lstar += wgt[w] * rw[HD + 1];
+            const float *rw = mbuf + ((size_t)w * C::NSLOT + sl) * (HDV + 2);
+            wgt[w] = ex2f(rw[HDV] - mstar);
+            lstar += wgt[w] * rw[HDV + 1];
         }
         const long grow = ((long)b * p.S + r) * p.nh + kvh * p.kvg + j;
-        for (int d = threadIdx.x; d < HD; d += NWARP * 32) {
+        for (int d = threadIdx.x; d < HDV; d += NWARP * 32) {
             float o = 0.0f;
 #pragma unroll
-            for (int w = 0; w < NWARP; ++w) o += wgt[w] * mbuf[((size_t)w * C::NSLOT + sl) * (HD + 2) + d];
+            for (int w = 0; w < NWARP; ++w) o += wgt[w] * mbuf[((size_t)w * C::NSLOT + sl) * (HDV + 2) + d];
             if (p.write_partial) {
-                p.partial[((size_t)split * p.grows + grow) * (HD + 2) + d] = o;
+                p.partial[((size_t)split * p.grows + grow) * (HD + 2) + dsl * HDV + d] = o;
             } else {
                 const float v = lstar > 0.0f ? o / lstar : 0.0f;
-                const long oi = b * p.out_batch_stride + ((long)r * p.nh + kvh * p.kvg + j) * HD + d;
+                const long oi = b * p.out_batch_stride + ((long)r * p.nh + kvh * p.kvg + j) * HD + dsl * HDV + d;
                 if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
                 else reinterpret_cast<float *>(p.out)[oi] = v;
             }
         }
-        if (p.write_partial && threadIdx.x == 0) {
+        if (p.write_partial && threadIdx.x == 0 && dsl == 0) {     // every slice computes the same (m, l)
             float *pr = p.partial + ((size_t)split * p.grows + grow) * (HD + 2);
             pr[HD] = p.export_nat ? mstar * LN2 : mstar;
             pr[HD + 1] = lstar;
