@@ -490,6 +490,39 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
         del cache, ws
     except Exception as e:
         out["c5a_batch8_131k_head_sharded"] = {"error": str(e)}
+    # configuration 5a on PAGED caches: same bytes, pages of 128 keys behind a shuffled block table (serving layout)
+    try:
+        B5, T5a = 8, 131072
+        nkv5 = NKV // world
+        nh5 = nkv5 * (NH // NKV)
+        ppseq = T5a // 128
+        n_pages = B5 * ppseq
+        g = torch.Generator(device=dev); g.manual_seed(1205 + rank)
+        kp = torch.randint(-127, 128, (n_pages, nkv5, 128, HD), dtype=torch.int8, device=dev, generator=g)
+        vp = torch.randint(-127, 128, (n_pages, nkv5, 128, HD), dtype=torch.int8, device=dev, generator=g)
+        ksp = torch.rand((n_pages, nkv5, 128), device=dev, generator=g) * 0.02 + 0.01
+        vsp = torch.rand((n_pages, nkv5, 128), device=dev, generator=g) * 0.02 + 0.01
+        table = torch.randperm(n_pages, device=dev, generator=g).to(torch.int32).reshape(B5, ppseq).contiguous()
+        lens = torch.full((B5,), T5a, dtype=torch.int32, device=dev)
+        q = torch.randn((B5, nh5, HD), device=dev).to(torch.bfloat16)
+        o = torch.zeros((B5, nh5, HD), dtype=torch.bfloat16, device=dev)
+        wsb = ops.attn_paged_workspace_bytes(B5, nh5, nkv5, NH // NKV, HD, T5a)
+        ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+
+        def fnpg():
+            ops.attn_paged_decode_i8(stream, q, kp, vp, ksp, vsp, table, lens, o, ws, wsb, batch=B5, nh=nh5, nkv=nkv5, kvg=NH // NKV,
+                                     l_hd=HD, n_pages=n_pages, max_pages=ppseq, max_len=T5a, softmax_scale=SOFTMAX_SCALE,
+                                     q_type=ops.BF16, out_type=ops.BF16)
+
+        us = time_call(torch, fnpg, max(10, iters // 8))
+        if world > 1:
+            tt = torch.tensor([us], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX); us = float(tt.item())
+        by = algorithmic_bytes(NKV, NH // NKV, T5a, HD, B5)
+        out["c5a_paged_batch8_131k"] = {"us_per_layer": round(us, 2), "GBps_aggregate": round(by / us / 1e3, 1), "gpus": world,
+                                        "page_keys": 128}
+        del kp, vp, ksp, vsp, ws
+    except Exception as e:
+        out["c5a_paged_batch8_131k"] = {"error": str(e)}
     # configuration 5b: batch 1 x 524288 keys, sharded by sequence chunks, (o, m, l) all-gathered and merged
     try:
         T5 = 524288 // world

@@ -346,6 +346,27 @@ int32_t nomos_attn_fused_host(void *stream, const nomos_attn_args_t *args, uint6
  * capture begins. */
 int32_t nomos_attn_fused_static_ws(void *stream, const nomos_attn_args_t *args);
 
+/* ------------------------------------------------------------------------- *
+ *  Paged caches (batch > 1 serving; no counterpart in the reference, whose cache is one          *
+ *  contiguous [nkv, cache_cap, hd] block per layer for a single sequence)                        *
+ * ------------------------------------------------------------------------- *
+ * int8 row-scale KV, head_dim 128, decode (one query row per sequence).  The pools hold n_pages pages;
+ * a page is [nkv][128 rows][128] int8 (k_pool, v_pool) and [nkv][128] fp32 (ks_pool, vs_pool).  Key t of
+ * sequence b lives in row t % 128 of page block_table[b * max_pages + t / 128] (int32); seq_lens[b]
+ * (int32) keys of sequence b are attended, the query being the last of them.  q and out are
+ * [batch, nh, 128].  max_len >= every seq_lens[b] sizes the launch.  Pools must be 16-byte aligned. */
+int64_t nomos_attn_paged_workspace_bytes(int32_t batch, int32_t nh, int32_t nkv, int32_t kvg, int32_t l_hd, int32_t max_len);
+int32_t nomos_attn_paged_decode_i8(void *stream, uint64_t q, uint64_t k_pool, uint64_t v_pool, uint64_t ks_pool,
+                                   uint64_t vs_pool, uint64_t block_table, uint64_t seq_lens, uint64_t out,
+                                   uint64_t workspace, int64_t ws_bytes, int32_t batch, int32_t nh, int32_t nkv,
+                                   int32_t kvg, int32_t l_hd, int32_t n_pages, int32_t max_pages, int32_t max_len,
+                                   double softmax_scale, int32_t q_type, int32_t out_type);
+/* Quantising append of one new row per sequence (src [batch, nkv, l_hd] fp32, sequence stride l_kvd) at
+ * position positions[b] (int32) of sequence b, with the row codec of nomos_kv_append_quant_i8. */
+int32_t nomos_kv_paged_append_quant_i8(void *stream, uint64_t src_k, uint64_t src_v, uint64_t k_pool, uint64_t v_pool,
+                                       uint64_t ks_pool, uint64_t vs_pool, uint64_t block_table, uint64_t positions,
+                                       int32_t batch, int32_t nkv, int32_t l_hd, int32_t l_kvd, int32_t max_pages);
+
 /* Merge G partial triples (as written through partial_out, gathered from G
  * sequence shards) into a normalised output.  partials: fp32 [G][rows][l_hd+2];
  * out: [rows][l_hd] of out_type.  No counterpart in the reference (which is

@@ -57,6 +57,9 @@ PROTOTYPES = {
     "nomos_attn_version": (i32, []),
     "nomos_attn_last_error": (C.c_char_p, []),
     "nomos_attn_device_faults": (i32, [C.POINTER(C.c_uint32), i32]),
+    "nomos_attn_paged_workspace_bytes": (i64, [i32] * 6),
+    "nomos_attn_paged_decode_i8": (i32, [vp] + [u64] * 9 + [i64] + [i32] * 8 + [C.c_double, i32, i32]),
+    "nomos_kv_paged_append_quant_i8": (i32, [vp] + [u64] * 8 + [i32] * 5),
     "nomos_attn_fused_host": (i32, [vp, C.POINTER(AttnArgs), u64, u64, C.c_int64, u64, u64, C.c_int64]),
     "nomos_kv_norm_rope_append": (i32, [vp] + [u64] * 11 + [i32] * 8 + [C.c_float, i32, i32]),
     "nomos_kv_quant_i8": (i32, [vp, u64, u64, u64, i32, i32]),

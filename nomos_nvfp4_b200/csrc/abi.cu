@@ -448,6 +448,72 @@ NOMOS_EXPORT int32_t nomos_attn_fused_host(void *stream, const nomos_attn_args_t
     return NOMOS_OK;
 }
 
+// ------------------------------------------------------------------- paged caches
+
+static int fill_paged(AttnArgs &a, const char *who, uint64_t q, uint64_t k_pool, uint64_t v_pool, uint64_t ks_pool, uint64_t vs_pool,
+                      uint64_t block_table, uint64_t seq_lens, uint64_t out, uint64_t workspace, int64_t ws_bytes, int batch, int nh,
+                      int nkv, int kvg, int l_hd, int n_pages, int max_pages, int max_len, double softmax_scale, int q_type,
+                      int out_type) {
+    int rc = check_attn_geometry(who, nh, nkv, l_hd, l_hd, kvg);
+    if (rc) return rc;
+    if (l_hd != 128 || kvg > 8) { set_error("%s: paged caches support head_dim 128 and at most 8 query heads per KV head", who); return NOMOS_EUNSUPPORTED; }
+    REQUIRE(batch > 0 && n_pages > 0 && max_pages > 0 && max_len > 0, "%s: bad batch/n_pages/max_pages/max_len", who);
+    REQUIRE((long)max_pages * 128 >= max_len, "%s: max_len %d exceeds max_pages %d x 128", who, max_len, max_pages);
+    REQUIRE((long)n_pages * nkv * 128 < (1l << 31), "%s: pool of %d pages too large", who, n_pages);
+    REQUIRE((q_type == ET_F32 || q_type == ET_BF16) && (out_type == ET_F32 || out_type == ET_BF16), "%s: element type", who);
+    memset(&a, 0, sizeof(a));
+    a.q = ptr(q); a.k_cache = ptr(k_pool); a.v_cache = ptr(v_pool); a.k_scales = ptr(ks_pool); a.v_scales = ptr(vs_pool);
+    a.out = ptr(out); a.workspace = ptr(workspace); a.ws_bytes = ws_bytes;
+    a.block_table = static_cast<const int *>(ptr(block_table)); a.seq_lens = static_cast<const int *>(ptr(seq_lens));
+    a.max_pages = max_pages; a.n_pages = n_pages;
+    a.kv_fmt = KV_I8; a.q_type = q_type; a.out_type = out_type;
+    a.batch = batch; a.S = 1; a.nh = nh; a.nkv = nkv; a.kvg = kvg; a.l_hd = l_hd; a.cache_hd = l_hd;
+    a.cache_cap = 128;                       // rows of one KV head inside a page
+    a.klen = max_len; a.softmax_scale = (float)softmax_scale;
+    a.q_batch_stride = (long)nh * l_hd; a.out_batch_stride = (long)nh * l_hd;
+    a.kv_batch_stride = (long)n_pages * nkv * 128 * l_hd; a.scale_batch_stride = (long)n_pages * nkv * 128 * 4;
+    a.tcgen05_always = 1;
+    return NOMOS_OK;
+}
+
+NOMOS_EXPORT int64_t nomos_attn_paged_workspace_bytes(int32_t batch, int32_t nh, int32_t nkv, int32_t kvg, int32_t l_hd,
+                                                      int32_t max_len) {
+    AttnArgs a;
+    static const int dummy = 0;
+    int rc = fill_paged(a, "nomos_attn_paged_workspace_bytes", 0, 0, 0, 0, 0, (uint64_t)(uintptr_t)&dummy, (uint64_t)(uintptr_t)&dummy, 0, 0,
+                        0, batch, nh, nkv, kvg, l_hd, 1, (max_len + 127) / 128, max_len, 1.0, ET_F32, ET_F32);
+    if (rc) return rc;
+    return attn_paged_workspace_bytes(a);
+}
+
+NOMOS_EXPORT int32_t nomos_attn_paged_decode_i8(void *stream, uint64_t q, uint64_t k_pool, uint64_t v_pool, uint64_t ks_pool,
+                                                uint64_t vs_pool, uint64_t block_table, uint64_t seq_lens, uint64_t out,
+                                                uint64_t workspace, int64_t ws_bytes, int32_t batch, int32_t nh, int32_t nkv,
+                                                int32_t kvg, int32_t l_hd, int32_t n_pages, int32_t max_pages, int32_t max_len,
+                                                double softmax_scale, int32_t q_type, int32_t out_type) {
+    const char *who = "nomos_attn_paged_decode_i8";
+    if (batch <= 0 || nh <= 0 || max_len <= 0) return NOMOS_OK;
+    REQUIRE(q && k_pool && v_pool && ks_pool && vs_pool && block_table && seq_lens && out, "%s: null pointer", who);
+    REQUIRE(aligned(k_pool, 16) && aligned(v_pool, 16) && aligned(ks_pool, 16) && aligned(vs_pool, 16) && aligned(q, 4), "%s: misaligned buffer", who);
+    AttnArgs a;
+    int rc = fill_paged(a, who, q, k_pool, v_pool, ks_pool, vs_pool, block_table, seq_lens, out, workspace, ws_bytes, batch, nh, nkv, kvg,
+                        l_hd, n_pages, max_pages, max_len, softmax_scale, q_type, out_type);
+    if (rc) return rc;
+    return launch_attn_paged(as_stream(stream), a);
+}
+
+NOMOS_EXPORT int32_t nomos_kv_paged_append_quant_i8(void *stream, uint64_t src_k, uint64_t src_v, uint64_t k_pool, uint64_t v_pool,
+                                                    uint64_t ks_pool, uint64_t vs_pool, uint64_t block_table, uint64_t positions,
+                                                    int32_t batch, int32_t nkv, int32_t l_hd, int32_t l_kvd, int32_t max_pages) {
+    const char *who = "nomos_kv_paged_append_quant_i8";
+    if (batch <= 0) return NOMOS_OK;
+    REQUIRE(src_k && src_v && k_pool && v_pool && ks_pool && vs_pool && block_table && positions, "%s: null pointer", who);
+    REQUIRE(nkv > 0 && l_hd > 0 && max_pages > 0 && l_kvd >= nkv * l_hd, "%s: bad geometry", who);
+    return launch_append_paged_i8(as_stream(stream), ptr(src_k), ptr(src_v), ptr(k_pool), ptr(v_pool), ptr(ks_pool), ptr(vs_pool),
+                                  static_cast<const int *>(ptr(block_table)), static_cast<const int *>(ptr(positions)), batch, nkv,
+                                  l_hd, l_kvd, max_pages);
+}
+
 NOMOS_EXPORT int32_t nomos_attn_merge_partials(void *stream, uint64_t partials, int32_t G, int32_t rows, int32_t l_hd,
                                                uint64_t out, int32_t out_type) {
     if (rows <= 0) return NOMOS_OK;

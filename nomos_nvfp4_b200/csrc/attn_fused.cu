@@ -317,6 +317,9 @@ static bool tc5_disabled_by_env() {
     static const bool off = [] { const char *e = std::getenv("NOMOS_ATTN_NO_TCGEN05"); return e && e[0] == '1'; }();
     return off;
 }
+static bool tc5_eligible(const AttnArgs &a);
+static int launch_tc5(cudaStream_t st, const AttnArgs &a, bool q, long *ws);
+
 static bool tc5_eligible(const AttnArgs &a) {
     if (a.kv_fmt != KV_I8 || a.l_hd != 128 || a.no_tma || a.no_tcgen05) return false;
     if (a.new_k != nullptr && (a.n_new > tc5::NEW_MAX || a.cache_hd != a.l_hd)) return false;
@@ -361,6 +364,7 @@ static Tc5Plan tc5_plan(const AttnArgs &a, int ns, int occupancy) {
     pl.ns = ns;
     pl.row_groups = (slots + ns - 1) / ns;
     pl.tbase = a.window > 0 ? std::max(0, (a.klen - (a.S - 1)) - a.window) : 0;
+    const bool paged = a.block_table != nullptr;
     // the window's keys as up to two runs of ring slots, cut into 128-slot tiles (see WindowGeo)
     const int ring0 = (int)(((long)a.win_start + pl.tbase) % a.cache_cap);
     const int len = a.klen - pl.tbase;
@@ -368,7 +372,7 @@ static Tc5Plan tc5_plan(const AttnArgs &a, int ns, int occupancy) {
     const int a0 = ring0 & ~3;
     const int n_a = (ring0 + len_a - a0 + tc5::KT - 1) / tc5::KT;
     const int n_b = (len - len_a + tc5::KT - 1) / tc5::KT;
-    pl.ntiles = n_a + n_b;
+    pl.ntiles = paged ? (a.klen + tc5::KT - 1) / tc5::KT : n_a + n_b;
     pl.grows = a.batch * a.S * a.nh;
     const int units = a.nkv * a.batch * pl.row_groups;
     const int slots_gpu = device_info().sm_count * occupancy;
@@ -394,6 +398,7 @@ static Tc5Plan tc5_plan(const AttnArgs &a, int ns, int occupancy) {
             if (cost < best_cost) { best_cost = cost; best = n; }
         }
     }
+    if (paged && (pl.ntiles + best - 1) / best > tc5::MAX_PAGED_TILES) best = (pl.ntiles + tc5::MAX_PAGED_TILES - 1) / tc5::MAX_PAGED_TILES;
     pl.tiles_per_split = (pl.ntiles + best - 1) / best;
     pl.splits = (pl.ntiles + pl.tiles_per_split - 1) / pl.tiles_per_split;
     return pl;
@@ -413,16 +418,19 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     }
     if (pl.splits > MERGE_MAX_G) { set_error("too many splits (%d)", pl.splits); return NOMOS_EUNSUPPORTED; }
     tc5::TmaMaps4 tm;
-    const int rows = a.nkv * a.cache_cap;
-    const MapKey mk{a.k_cache, 0, 128, a.cache_hd, rows, a.batch, tc5::KT, a.kv_batch_stride};
-    const MapKey mv{a.v_cache, 0, 128, a.cache_hd, rows, a.batch, tc5::KT, a.kv_batch_stride};
-    const MapKey mks{a.k_scales, 1, 4, 4, rows, a.batch, tc5::KT, a.scale_batch_stride};
-    const MapKey mvs{a.v_scales, 1, 4, 4, rows, a.batch, tc5::KT, a.scale_batch_stride};
+    const bool paged = a.block_table != nullptr;
+    const int rows = paged ? a.n_pages * a.nkv * tc5::KT : a.nkv * a.cache_cap;      // paged: the pools are one plane
+    const int mb = paged ? 1 : a.batch;
+    const MapKey mk{a.k_cache, 0, 128, a.cache_hd, rows, mb, tc5::KT, a.kv_batch_stride};
+    const MapKey mv{a.v_cache, 0, 128, a.cache_hd, rows, mb, tc5::KT, a.kv_batch_stride};
+    const MapKey mks{a.k_scales, 1, 4, 4, rows, mb, tc5::KT, a.scale_batch_stride};
+    const MapKey mvs{a.v_scales, 1, 4, 4, rows, mb, tc5::KT, a.scale_batch_stride};
     if (!encode_plane(mk, &tm.k) || !encode_plane(mv, &tm.v)) return 1;
     const auto al16 = [](const void *x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
-    const bool scales_by_tma = al16(a.k_scales) && al16(a.v_scales) && a.cache_cap % 4 == 0 &&
-                               (a.batch == 1 || a.scale_batch_stride % 16 == 0) && encode_plane(mks, &tm.ks) && encode_plane(mvs, &tm.vs);
+    const bool scales_by_tma = al16(a.k_scales) && al16(a.v_scales) && (paged || a.cache_cap % 4 == 0) &&
+                               (mb == 1 || a.scale_batch_stride % 16 == 0) && encode_plane(mks, &tm.ks) && encode_plane(mvs, &tm.vs);
     if (!scales_by_tma) { tm.ks = tm.k; tm.vs = tm.k; }       // never dereferenced
+    if (paged && !scales_by_tma) { set_error("paged attention: scale pools must be 16-byte aligned"); return NOMOS_EBADARG; }
     KParams p;
     std::memset(&p, 0, sizeof(p));
     p.use_tma = scales_by_tma ? 3 : 1;
@@ -439,7 +447,8 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     p.splits = pl.splits;
     p.arrivals = pl.splits;
     p.partial_export = a.partial_out;
-    p.early_rows = a.settled_cache ? std::max(0, a.klen - std::max(a.S, a.n_new)) : 0;
+    p.early_rows = (a.settled_cache && !paged) ? std::max(0, a.klen - std::max(a.S, a.n_new)) : 0;
+    p.block_table = a.block_table; p.seq_lens = a.seq_lens; p.max_pages = a.max_pages;
     p.q_type = a.q_type; p.out_type = a.out_type;
     p.S = a.S; p.nh = a.nh; p.nkv = a.nkv; p.kvg = a.kvg; p.cache_hd = a.cache_hd; p.cache_cap = a.cache_cap;
     p.win_start = a.win_start; p.klen = a.klen; p.window = a.window;
@@ -538,6 +547,19 @@ long attn_workspace_bytes(const AttnArgs &a) {
 }
 
 int launch_attn_fused(cudaStream_t st, const AttnArgs &a) { return dispatch(st, a, false, nullptr); }
+
+// Paged caches exist in the tcgen05 kernel only.
+long attn_paged_workspace_bytes(const AttnArgs &a) {
+    long ws = 0;
+    const int rc = launch_tc5(nullptr, a, true, &ws);
+    return rc == NOMOS_OK ? ws : (long)(rc == 1 ? NOMOS_EUNSUPPORTED : rc);
+}
+int launch_attn_paged(cudaStream_t st, const AttnArgs &a) {
+    if (encode_tiled_fn() == nullptr) { set_error("paged attention needs the driver's tensor-map encoder"); return NOMOS_EUNSUPPORTED; }
+    const int rc = launch_tc5(st, a, false, nullptr);
+    if (rc == 1) { set_error("paged attention: the pools do not satisfy the tensor-map rules (16-byte aligned)"); return NOMOS_EBADARG; }
+    return rc;
+}
 
 int read_attn_faults(unsigned int *out, bool clear) {
     unsigned int *w = fault_word();

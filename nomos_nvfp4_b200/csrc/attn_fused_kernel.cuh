@@ -105,6 +105,9 @@ struct KParams {
     uint8_t *k_cache_w, *v_cache_w, *k_scales_w, *v_scales_w;   // writable aliases of the cache
     int n_new, new_stride, new_base_pos;
     long q_batch_stride, kv_batch_stride, scale_batch_stride, out_batch_stride;
+    const int *block_table;  // paged caches (tcgen05 kernel): [batch][max_pages] page of each 128-key tile; nullptr = contiguous
+    const int *seq_lens;     // paged caches: keys of each sequence
+    int max_pages;
     unsigned int kvg_magic;  // ceil(2^32 / kvg), 0 for kvg == 1: idx / kvg = umulhi(idx, kvg_magic)
     int use_tma;             // bit 0: whole tiles come by TMA; bit 1: their scales by bulk copy
     unsigned int *fault;     // sticky device word: bit 0 = a tile never arrived within the wait limit

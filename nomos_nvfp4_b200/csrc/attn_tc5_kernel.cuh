@@ -44,6 +44,7 @@ constexpr int SCALE_BYTES = KT * 4;          // one tile's fp32 row scales
 constexpr int TMEM_COLS = 256;               // S0 | S1 | O0 | O1, 64 columns each
 constexpr float LG2_VS_MIN = -64.0f;
 constexpr int NEW_MAX = 8;                   // most rows one call may quantise on the way in
+constexpr int MAX_PAGED_TILES = 256;         // paged caches: most tiles (pages) one CTA walks
 #ifndef NOMOS_TC5_NSG
 #define NOMOS_TC5_NSG 4                      // slots per softmax warp group when a CTA serves more than eight
 #endif
@@ -90,7 +91,8 @@ struct Cfg {
     static constexpr int OFF_MISC = OFF_BAR + NBAR * 8;              // tmem base, abort flag
     static constexpr int OFF_NEW = OFF_MISC + 16;                    // quantize-on-write: one row of codes + its scale for K and V
     static constexpr int OFF_NEWSC = OFF_NEW + 2 * (128 + 16);       // scales of the new rows [2][NEW_MAX]
-    static constexpr int SMEM_BYTES = 1024 + OFF_NEWSC + 2 * NEW_MAX * 4;
+    static constexpr int OFF_PAGES = OFF_NEWSC + 2 * NEW_MAX * 4;    // paged caches: page of each of this CTA's tiles
+    static constexpr int SMEM_BYTES = 1024 + OFF_PAGES + MAX_PAGED_TILES * 4;
     static_assert(OFF_NEW % 16 == 0, "row scratch is copied in 16-byte chunks");
     static_assert(OFF_BAR % 8 == 0, "mbarriers need 8-byte alignment");
     static_assert(OFF_Q % 1024 == 0 && QP_BYTES % 1024 == 0, "operand tiles sit on swizzle-pattern boundaries");
@@ -267,9 +269,14 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     wg.a0 = wg.ring0 & ~3;
     wg.n_a = (wg.ring0 + wg.len_a - wg.a0 + KT - 1) / KT;
     const int tile_begin = split * p.tiles_per_split;
-    const int tile_end = min(p.ntiles, tile_begin + p.tiles_per_split);
-    const int my_n = max(0, tile_end - tile_begin);
+    int tile_end = min(p.ntiles, tile_begin + p.tiles_per_split);
+    int my_n = max(0, tile_end - tile_begin);
     const int row_base = kvh * p.cache_cap;          // this head's first row in the {rows} dimension of the maps
+    // Paged caches (block_table != nullptr): the sequence's tile j lives in page block_table[b][j] of the
+    // pools, a page holding 128 rows of every KV head; its length comes from seq_lens[b].  Set below, after
+    // the stream-order wait (both arrays may have been written by the preceding kernel).
+    const bool paged = p.block_table != nullptr;
+    int *page_ids = reinterpret_cast<int *>(sm + C::OFF_PAGES);
     // fused quantize-on-write: the last n_new keys of the window arrive as fp32 rows with this call
     const int new_lo = p.new_k ? p.klen - p.n_new : 0x7fffffff;      // window index of the first new key
     auto tile_has_new = [&](const TileGeo &g) { return min(g.t0 + KT, g.t_hi) > new_lo; };
@@ -307,29 +314,40 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     // Programmatic dependent launch: every thread waits for the stream predecessor before it lets
     // this grid's own dependents be scheduled (the producer thread first requests the tiles the
     // caller declared settled).
-    if (!(warp == NSW && lane == 0)) {
+    if (!(warp == NSW && lane == 0) || paged) {
         fused::pdl_wait();
         fused::pdl_launch_dependents();
+    }
+    if (paged) {
+        const int len = p.seq_lens[b];
+        wg.klen = len; wg.ring0 = 0; wg.a0 = 0; wg.len_a = len;
+        wg.n_a = (len + KT - 1) / KT;
+        tile_end = min(wg.n_a, tile_begin + p.tiles_per_split);
+        my_n = max(0, tile_end - tile_begin);
+        for (int i = threadIdx.x; i < my_n; i += NTHREADS) page_ids[i] = p.block_table[(size_t)b * p.max_pages + tile_begin + i];
+        __syncthreads();
     }
 
     if (warp == NSW) {
         // =========================================================== TMA producer
         if (lane == 0) {
-            bool waited = false;
+            bool waited = paged;
             for (int i = 0; i < my_n; ++i) {
                 const int st = i % NSTG;
                 const TileGeo g = wg.tile(tile_begin + i);
+                const int row0 = paged ? (page_ids[i] * p.nkv + kvh) * KT : row_base + g.slot0;   // first row of the tile in the maps
                 // rows the caller declared settled may be requested before the stream predecessor is done
                 if (!waited && g.t0 + KT > p.early_rows) { fused::pdl_wait(); fused::pdl_launch_dependents(); waited = true; }
                 if (i >= NSTG && !wait_or_abort(bar_empty(st), ((i / NSTG) - 1) & 1, abort_flag, p.fault)) break;
                 const uint32_t kdst = sm_u32 + st * 2 * TILE_BYTES;
                 const uint32_t sdst = sm_u32 + C::OFF_SCALES + st * 2 * SCALE_BYTES;
                 fused::mbar_expect_tx(bar_full(st), 2 * TILE_BYTES + (scales_by_tma ? 2 * SCALE_BYTES : 0));
-                fused::tma_load_tile(kdst, &tm.k, row_base + g.slot0, b, bar_full(st));
-                fused::tma_load_tile(kdst + TILE_BYTES, &tm.v, row_base + g.slot0, b, bar_full(st));
+                const int bc = paged ? 0 : b;                    // the pools are one plane for all sequences
+                fused::tma_load_tile(kdst, &tm.k, row0, bc, bar_full(st));
+                fused::tma_load_tile(kdst + TILE_BYTES, &tm.v, row0, bc, bar_full(st));
                 if (scales_by_tma) {
-                    tma_load_2d(sdst, &tm.ks, row_base + g.slot0, b, bar_full(st));
-                    tma_load_2d(sdst + SCALE_BYTES, &tm.vs, row_base + g.slot0, b, bar_full(st));
+                    tma_load_2d(sdst, &tm.ks, row0, bc, bar_full(st));
+                    tma_load_2d(sdst + SCALE_BYTES, &tm.vs, row0, bc, bar_full(st));
                 }
             }
             if (!waited) { fused::pdl_wait(); fused::pdl_launch_dependents(); }
@@ -446,7 +464,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 sm[C::OFF_Q + at(NSP + sl, lane + 32 * i)] = (uint8_t)(int8_t)lo;
             }
             if (lane == 0) {
-                const int hi_b = valid ? p.klen - (p.S - 1 - r) : 0;
+                const int hi_b = valid ? wg.klen - (p.S - 1 - r) : 0;
                 slot_qscale[sl] = valid ? sq * p.qk_scale_log2 : 0.0f;
                 slot_hi[sl] = hi_b;
                 slot_lo[sl] = (valid && p.window > 0) ? max(0, hi_b - p.window) : 0;

@@ -47,6 +47,23 @@ append_i8_kernel(const float *src_k, const float *src_v, int8_t *dst_k, int8_t *
     quant_row_i8(src_v + src, l_hd, cache_hd, dst_v + row * cache_hd, v_scales + row, lane);
 }
 
+// Paged int8 caches: one new row per sequence, at position positions[b] of sequence b, i.e. row
+// positions[b] % 128 of page block_table[b][positions[b] / 128]; a page holds 128 rows of every KV head.
+__global__ void __launch_bounds__(ROWS_PER_BLOCK * 32)
+append_paged_i8_kernel(const float *src_k, const float *src_v, int8_t *k_pool, int8_t *v_pool, float *ks_pool, float *vs_pool,
+                       const int *block_table, const int *positions, int batch, int nkv, int l_hd, int l_kvd, int max_pages) {
+    const int w = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+    if (w >= batch * nkv) return;
+    const int lane = threadIdx.x & 31;
+    const int h = w % nkv, b = w / nkv;
+    const int pos = positions[b];
+    const int page = block_table[(size_t)b * max_pages + pos / 128];
+    const size_t row = ((size_t)page * nkv + h) * 128 + (size_t)(pos % 128);
+    const size_t src = (size_t)b * l_kvd + (size_t)h * l_hd;
+    quant_row_i8(src_k + src, l_hd, l_hd, k_pool + row * l_hd, ks_pool + row, lane);
+    quant_row_i8(src_v + src, l_hd, l_hd, v_pool + row * l_hd, vs_pool + row, lane);
+}
+
 // ------------------------------------------------------------- int4 row codecs
 
 struct AppendI4Args {
@@ -207,6 +224,16 @@ int launch_append_i8(cudaStream_t st, const void *src_k, const void *src_v, void
         static_cast<int8_t *>(dst_v), static_cast<float *>(k_scales), static_cast<float *>(v_scales), n_s, nkv, l_hd, l_kvd,
         cache_cap, cache_hd, base_pos);
     return check_launch("nomos_kv_append_quant_i8");
+}
+
+int launch_append_paged_i8(cudaStream_t st, const void *src_k, const void *src_v, void *k_pool, void *v_pool, void *ks_pool,
+                           void *vs_pool, const int *block_table, const int *positions, int batch, int nkv, int l_hd, int l_kvd,
+                           int max_pages) {
+    append_paged_i8_kernel<<<blocks_for((long)batch * nkv, ROWS_PER_BLOCK), ROWS_PER_BLOCK * 32, 0, st>>>(
+        static_cast<const float *>(src_k), static_cast<const float *>(src_v), static_cast<int8_t *>(k_pool),
+        static_cast<int8_t *>(v_pool), static_cast<float *>(ks_pool), static_cast<float *>(vs_pool), block_table, positions, batch,
+        nkv, l_hd, l_kvd, max_pages);
+    return check_launch("nomos_kv_paged_append_quant_i8");
 }
 
 int launch_append_i4(cudaStream_t st, const void *src_k, const void *src_v, void *dst_k, void *dst_v, void *k_scales,

@@ -13,6 +13,9 @@ int launch_quant_i8(cudaStream_t st, const void *in_bf16, void *out_i8, void *ou
 int launch_dequant_i8(cudaStream_t st, const void *in_i8, const void *in_scales, void *out_bf16, int n_rows, int dim);
 int launch_append_i8(cudaStream_t st, const void *src_k, const void *src_v, void *dst_k, void *dst_v, void *k_scales,
                      void *v_scales, int n_s, int nkv, int l_hd, int l_kvd, int cache_cap, int cache_hd, int base_pos);
+int launch_append_paged_i8(cudaStream_t st, const void *src_k, const void *src_v, void *k_pool, void *v_pool, void *ks_pool,
+                           void *vs_pool, const int *block_table, const int *positions, int batch, int nkv, int l_hd, int l_kvd,
+                           int max_pages);
 int launch_append_i4(cudaStream_t st, const void *src_k, const void *src_v, void *dst_k, void *dst_v, void *k_scales,
                      void *v_scales, void *k_q8, void *v_q8, void *k_q8_scales, void *v_q8_scales, int n_s, int nkv,
                      int l_hd, int l_kvd, int cache_cap, int cache_hd, int base_pos, int q8_pitch, int scale_blocks);
@@ -50,6 +53,12 @@ struct AttnArgs {
     int window;             // sliding window per row (0 = none): lo_r = max(0, hi_r - window)
     float softmax_scale;
     long q_batch_stride, kv_batch_stride, scale_batch_stride, out_batch_stride;   // elements (q/out), bytes (kv, scales)
+    // paged caches (int8, head_dim 128, tcgen05 kernel only): k_cache/v_cache/k_scales/v_scales are pools of
+    // n_pages pages of [nkv][128 rows]; tile j of sequence b is page block_table[b * max_pages + j]; klen is
+    // the longest sequence (for the plan), seq_lens[b] the keys of sequence b.  nullptr = contiguous caches.
+    const int *block_table;
+    const int *seq_lens;
+    int max_pages, n_pages;
     int force_splits;       // 0 = choose; >0 = use exactly this many splits (tests)
     int no_tma;             // 1: keep every tile on the cp.async path
     int no_tcgen05;         // 1: never take the tcgen05 kernel
@@ -60,6 +69,8 @@ struct AttnArgs {
 
 long attn_workspace_bytes(const AttnArgs &a);
 int launch_attn_fused(cudaStream_t st, const AttnArgs &a);
+long attn_paged_workspace_bytes(const AttnArgs &a);
+int launch_attn_paged(cudaStream_t st, const AttnArgs &a);
 // Reads (and optionally clears) the device word the kernels OR into when a bounded wait runs out.
 int read_attn_faults(unsigned int *out, bool clear);
 // partials [G][rows][l_hd+2] = (o.., m, l) with m in natural-log units (the exported form)

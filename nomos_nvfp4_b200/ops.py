@@ -252,6 +252,29 @@ def attn_fused(stream, args: AttnArgs) -> None:
     _check(_lib.lib().nomos_attn_fused(_stream(stream), C.byref(args)))
 
 
+def attn_paged_workspace_bytes(batch, nh, nkv, kvg, l_hd, max_len) -> int:
+    n = _lib.lib().nomos_attn_paged_workspace_bytes(batch, nh, nkv, kvg, l_hd, max_len)
+    if n < 0:
+        _check(int(n))
+    return int(n)
+
+
+def attn_paged_decode_i8(stream, q, k_pool, v_pool, ks_pool, vs_pool, block_table, seq_lens, out, workspace, ws_bytes, *,
+                         batch, nh, nkv, kvg, l_hd, n_pages, max_pages, max_len, softmax_scale=1.0, q_type=F32, out_type=F32):
+    """Decode attention over paged int8 caches (pages of 128 keys); see include/nomos_attn.h."""
+    _check(_lib.lib().nomos_attn_paged_decode_i8(
+        _stream(stream), _addr(q), _addr(k_pool), _addr(v_pool), _addr(ks_pool), _addr(vs_pool), _addr(block_table),
+        _addr(seq_lens), _addr(out), _addr(workspace), int(ws_bytes), batch, nh, nkv, kvg, l_hd, n_pages, max_pages, max_len,
+        float(softmax_scale), q_type, out_type))
+
+
+def kv_paged_append_quant_i8(stream, src_k, src_v, k_pool, v_pool, ks_pool, vs_pool, block_table, positions, *,
+                             batch, nkv, l_hd, l_kvd, max_pages):
+    _check(_lib.lib().nomos_kv_paged_append_quant_i8(
+        _stream(stream), _addr(src_k), _addr(src_v), _addr(k_pool), _addr(v_pool), _addr(ks_pool), _addr(vs_pool),
+        _addr(block_table), _addr(positions), batch, nkv, l_hd, l_kvd, max_pages))
+
+
 class KvRing:
     """One layer's ring bookkeeping (``nomos_kv_ring_*``): lengths, window arithmetic, staged rows,
     roll-back.  ``window`` = 0 is a linear cache.  A ring that serves batches of ``max_rows`` rows needs

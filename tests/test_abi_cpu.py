@@ -92,6 +92,28 @@ def test_bad_arguments_are_refused_before_launch(lib):
     ops.gpu_append_quant_kv_i8(0, 0, 0, 0, 0, 0, 0, 0, 4, 128, 512, 64, 128, 0)
 
 
+def test_paged_arguments_are_refused_before_launch(lib):
+    from nomos_nvfp4_b200 import ops
+    P = 0x1000   # never dereferenced: validation fails first
+    kw = dict(batch=2, nh=8, nkv=4, kvg=2, l_hd=128, n_pages=8, max_pages=4, max_len=300)
+    with pytest.raises(ops.NomosError) as e:                     # null block table
+        ops.attn_paged_decode_i8(0, P, P, P, P, P, None, P, P, P, 64, **kw)
+    assert e.value.status == -1
+    with pytest.raises(ops.NomosError) as e:                     # head_dim 256 is not paged
+        ops.attn_paged_decode_i8(0, P, P, P, P, P, P, P, P, P, 64, **{**kw, "l_hd": 256})
+    assert e.value.status == -2
+    with pytest.raises(ops.NomosError) as e:                     # max_len beyond the block table
+        ops.attn_paged_decode_i8(0, P, P, P, P, P, P, P, P, P, 64, **{**kw, "max_len": 4 * 128 + 1})
+    assert e.value.status == -1
+    with pytest.raises(ops.NomosError) as e:                     # misaligned pool
+        ops.attn_paged_decode_i8(0, P, P + 8, P, P, P, P, P, P, P, 64, **kw)
+    assert e.value.status == -1
+    with pytest.raises(ops.NomosError) as e:
+        ops.kv_paged_append_quant_i8(0, P, P, P, P, P, P, P, None, batch=2, nkv=4, l_hd=128, l_kvd=512, max_pages=4)
+    assert e.value.status == -1
+    assert ops.attn_paged_workspace_bytes(2, 8, 4, 2, 128, 100) >= 0
+
+
 def test_fused_args_validation(lib):
     from nomos_nvfp4_b200 import ops
     a = ops.make_args(q=0x1000, k_cache=0x1000, v_cache=0x1000, k_scales=0x1000, v_scales=0x1000, out=0x1000,
