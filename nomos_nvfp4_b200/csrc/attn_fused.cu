@@ -217,7 +217,7 @@ static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp, int d
             const long waves = (ctas + slots_gpu - 1) / slots_gpu;
             // in units of one warp-tile (~1.7 us on B200): streaming rounds plus ~1.5 of CTA start-up per wave, and what a split costs at the
             // end (partial store, fence, arrival, merge by the last CTA) when there is more than one
-            const double cost = (double)waves * (per_warp + 1.5) + (n > 1 ? 2.0 + 0.02 * n : 0.0);
+            const double cost = (double)waves * (per_warp + 1.5) + (n > 1 ? 1.4 + 0.02 * n : 0.0);
             if (cost < best_cost) { best_cost = cost; best = n; }
         }
     }
