@@ -430,6 +430,25 @@ NOMOS_EXPORT int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *arg
     return run_fused(as_stream(stream), a, "nomos_attn_fused");
 }
 
+// Device-visible address of a pinned host buffer (0 if the GPU cannot address it).  The last answers
+// are remembered per thread: a decode loop passes the same two buffers every step.
+static uint64_t device_view_of_host(uint64_t host) {
+    struct Entry { uint64_t host = 0, dev = 0; };
+    thread_local Entry cache[4];
+    thread_local int next = 0;
+    for (const Entry &c : cache)
+        if (c.host == host) return c.dev;
+    cudaPointerAttributes at;
+    uint64_t dev = 0;
+    if (cudaPointerGetAttributes(&at, ptr(host)) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer != nullptr)
+        dev = (uint64_t)(uintptr_t)at.devicePointer;
+    else
+        cudaGetLastError();                       // not an error of the call: just not mapped
+    cache[next].host = host; cache[next].dev = dev;
+    next = (next + 1) % 4;
+    return dev;
+}
+
 NOMOS_EXPORT int32_t nomos_attn_fused_host(void *stream, const nomos_attn_args_t *args, uint64_t host_in, uint64_t dev_in,
                                            int64_t in_bytes, uint64_t host_out, uint64_t dev_out, int64_t out_bytes) {
     const char *who = "nomos_attn_fused_host";
@@ -438,6 +457,27 @@ NOMOS_EXPORT int32_t nomos_attn_fused_host(void *stream, const nomos_attn_args_t
     REQUIRE(out_bytes == 0 || (host_out && dev_out), "%s: null output staging pointer", who);
     cudaStream_t st = as_stream(stream);
     cudaError_t e = cudaSuccess;
+    // Small steps with pinned, GPU-addressable host buffers skip the two copies: the kernel reads the query and
+    // the new rows from host memory and writes its output there (the same bytes cross the bus, inside the one
+    // launch); the staging buffers are then left untouched.
+    if (args != nullptr && args->struct_bytes == sizeof(nomos_attn_args_t) && in_bytes <= (64 << 10) && out_bytes <= (64 << 10)) {
+        const uint64_t hin = in_bytes ? device_view_of_host(host_in) : 1, hout = out_bytes ? device_view_of_host(host_out) : 1;
+        if (hin && hout) {
+            nomos_attn_args_t z = *args;
+            const auto rebase = [](uint64_t p, uint64_t from, int64_t n, uint64_t to) {
+                return (n > 0 && p >= from && p < from + (uint64_t)n) ? to + (p - from) : p;
+            };
+            z.q = rebase(z.q, dev_in, in_bytes, hin);
+            z.new_k = rebase(z.new_k, dev_in, in_bytes, hin);
+            z.new_v = rebase(z.new_v, dev_in, in_bytes, hin);
+            z.out = rebase(z.out, dev_out, out_bytes, hout);
+            const int rc = nomos_attn_fused(stream, &z);
+            if (rc) return rc;
+            e = cudaStreamSynchronize(st);
+            if (e != cudaSuccess) { set_error("%s: synchronise: %s", who, cudaGetErrorString(e)); return NOMOS_ECUDA; }
+            return NOMOS_OK;
+        }
+    }
     if (in_bytes) e = cudaMemcpyAsync(ptr(dev_in), ptr(host_in), (size_t)in_bytes, cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) { set_error("%s: host-to-device copy: %s", who, cudaGetErrorString(e)); return NOMOS_ECUDA; }
     const int rc = nomos_attn_fused(stream, args);

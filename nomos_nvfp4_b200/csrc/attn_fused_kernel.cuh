@@ -203,6 +203,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
         if (t1 - t0 > 2000000000ull) return false;
     }
 }
+// Starts the fetch of a tensor map into the descriptor cache ahead of its first use.
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<unsigned long long>(map)) : "memory");
+}
 // One 32-row box of a {bytes, rows, batch} byte tensor into shared memory.
 __device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap *map, int row, int batch, uint32_t bar) {
     asm volatile(

@@ -302,6 +302,10 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         fused::mbar_init(bar_patched, 32);
         fused::fence_mbar_init();
     }
+    if (warp == NSW + 1 && lane == 0) {
+        fused::prefetch_tensormap(&tm.k); fused::prefetch_tensormap(&tm.v);
+        if (scales_by_tma) { fused::prefetch_tensormap(&tm.ks); fused::prefetch_tensormap(&tm.vs); }
+    }
     if (warp == NSW) {
         tmem_alloc(sm_u32 + C::OFF_MISC, TMEM_COLS);
         tmem_relinquish();

@@ -296,21 +296,25 @@ def test_fused_append_then_attend_i8(oracle):
     assert np.array_equal(caches[1].view(np.uint8), c.v.view(np.uint8)) and np.array_equal(caches[3], c.vs)
 
 
-def test_host_buffer_step_matches_device_call(oracle):
-    """nomos_attn_fused_host: query and new rows arrive in pinned host memory, the output lands there;
-    the result and the appended cache rows equal those of the device-buffer call."""
+@pytest.mark.parametrize("pinned", [True, False])
+def test_host_buffer_step_matches_device_call(oracle, pinned):
+    """nomos_attn_fused_host: query and new rows arrive in host memory, the output lands there; the
+    result and the appended cache rows equal those of the device-buffer call.  Pinned buffers are
+    read and written by the kernel directly, pageable ones go through the staging copies."""
     rng = np.random.default_rng(43)
     nh, nkv, hd, cap, T = 8, 4, 128, 512, 400
     c = build_cache("i8", rng, T - 1, nkv, hd, cap=cap)
     new_k, new_v = bf16_normal(rng, (1, nkv, hd)), bf16_normal(rng, (1, nkv, hd))
     q = bf16_normal(rng, (1, nh, hd))
     qb, kb = nh * hd * 4, nkv * hd * 4
-    host_in = torch.empty(qb + 2 * kb, dtype=torch.uint8).pin_memory()
+    host_in = torch.empty(qb + 2 * kb, dtype=torch.uint8)
+    host_in = host_in.pin_memory() if pinned else host_in
     host_in[:qb].view(torch.float32).copy_(torch.from_numpy(np.ascontiguousarray(q, np.float32)).reshape(-1))
     host_in[qb:qb + kb].view(torch.float32).copy_(torch.from_numpy(np.ascontiguousarray(new_k, np.float32)).reshape(-1))
     host_in[qb + kb:].view(torch.float32).copy_(torch.from_numpy(np.ascontiguousarray(new_v, np.float32)).reshape(-1))
     dev_in = torch.zeros_like(host_in, device=DEV)
-    host_out = torch.full((1, nh, hd), SENTINEL, dtype=torch.float32).pin_memory()
+    host_out = torch.full((1, nh, hd), SENTINEL, dtype=torch.float32)
+    host_out = host_out.pin_memory() if pinned else host_out
     dev_out = torch.zeros((1, nh, hd), dtype=torch.float32, device=DEV)
     dk, dv, dks, dvs = dev(c.k), dev(c.v), dev(c.ks), dev(c.vs)
     a = ops.make_args(q=dev_in.data_ptr(), k_cache=dk, v_cache=dv, k_scales=dks, v_scales=dvs, out=dev_out, kv_fmt=ops.KV_I8,
