@@ -42,6 +42,9 @@
 #include "attn_fused_kernel.cuh"
 #include "attn_tc5_kernel.cuh"
 
+#ifndef NOMOS_DS512
+#define NOMOS_DS512 4
+#endif
 namespace nomos {
 
 using namespace fused;
@@ -507,7 +510,7 @@ static int dispatch_hd(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
             if (a.new_k == nullptr && FMT == KV_I8) return launch_inst<FMT, 256, 1, 2>(st, a, q, ws);
             return launch_inst<FMT, 256, 1>(st, a, q, ws);
         case 512:
-            if (a.new_k == nullptr) return launch_inst<FMT, 512, 1, 4>(st, a, q, ws);
+            if (a.new_k == nullptr) return launch_inst<FMT, 512, 1, NOMOS_DS512>(st, a, q, ws);
             return launch_inst<FMT, 512, 1>(st, a, q, ws);
         default: set_error("head_dim %d unsupported (128, 256, 512)", a.l_hd); return NOMOS_EUNSUPPORTED;
     }
