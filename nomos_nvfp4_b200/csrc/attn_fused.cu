@@ -1,4 +1,6 @@
-// Split-K flash-decoding attention over the PACKED quantised KV ring (sm_100a): host side.
+// Split-K flash-decoding attention over the PACKED quantised KV ring (sm_100a): host side of both
+// kernels -- the mma.sync kernel described here (attn_fused_kernel.cuh) and the tcgen05 kernel for
+// int8 / head_dim 128 (attn_tc5_kernel.cuh, described there; plan and launch further down).
 //
 // Replaces, in one launch (+ a tiny dependent merge when the sequence is split), what
 // the reference does per layer with 5-7 launches: window reader -> int8/bf16 scratch

@@ -1,5 +1,6 @@
-// Decode / verify attention over the int8 KV ring on the fifth-generation tensor cores
-// (tcgen05 + tensor memory), head_dim 128, sm_100a.  See attn_tc5.cu for the host side.
+// Decode / verify attention over the int8 KV cache on the fifth-generation tensor cores
+// (tcgen05 + tensor memory), head_dim 128, sm_100a.  The host side (plan, tensor maps, launch)
+// is in attn_fused.cu.
 //
 // The contraction is laid out so that the 128-row M dimension of tcgen05.mma is always full,
 // however few query rows there are:
@@ -11,15 +12,17 @@
 // N = 2 x (padded slots): column s holds the high limb of slot s (a query row x group head),
 // column NSP+s the low limb, for the 15-bit fixed-point query and the 16-bit fixed-point softmax
 // weights alike, so every product is an exact int32.
-// Accumulators live in tensor memory: warp w of the four softmax warps reads TMEM lanes
-// 32w..32w+31, i.e. thread = one key of the tile for S^T, thread = one output dim for O^T.
+// Accumulators live in tensor memory: a softmax warp reads the TMEM lanes 32(w%4)..32(w%4)+31,
+// i.e. thread = one key of the tile for S^T, thread = one output dim for O^T.
 //
-// Roles: four softmax warps per group (one group up to eight slots, two groups sharing the slots
-// of a tile beyond that: thread = key / dim as above, each group owns half the columns), then one
-// warp whose lane 0 is the TMA producer and one whose lane 0 issues the MMAs; the rest only help
-// in the split merge.  Every wait is an mbarrier wait with a
-// time limit; a wait that runs out raises the CTA's abort flag and a bit in the device fault
-// word, every role leaves its loop, tensor memory is freed and the CTA exits.
+// Roles: groups of four softmax warps (one group for up to eight slots; beyond that one group per
+// NOMOS_TC5_NSG slots, each owning its slots' columns of S^T, P and O^T), then one warp whose lane
+// 0 is the TMA producer and one whose lane 0 issues the MMAs; with a single group two more warps
+// only help in the split merge.  Optional in the same launch: quantize-on-write of up to NEW_MAX
+// new rows (softmax warp 0 overwrites the rows TMA fetched), and paged caches (a tile is a page of
+// 128 keys looked up in a block table).  Every wait is an mbarrier wait with a time limit; a wait
+// that runs out raises the CTA's abort flag and a bit in the device fault word, every role leaves
+// its loop, tensor memory is freed and the CTA exits.
 #pragma once
 
 #include "attn_fused_kernel.cuh"
