@@ -2,16 +2,15 @@
 // kernels -- the mma.sync kernel described here (attn_fused_kernel.cuh) and the tcgen05 kernel for
 // int8 / head_dim 128 (attn_tc5_kernel.cuh, described there; plan and launch further down).
 //
-// Replaces, in one launch (+ a tiny dependent merge when the sequence is split), what
-// the reference does per layer with 5-7 launches: window reader -> int8/bf16 scratch
+// Replaces, in one launch, what the reference does per layer with 5-7 launches: window reader -> int8/bf16 scratch
 // (lib/kv_cache_quant.mojo:221-249,708-800,925-953), QK (lib/attention_gpu_int8.mojo:48-91
 // or cuBLAS, lib/attention_gpu.mojo:231-238), row softmax (lib/softmax_gpu_mojo.mojo:37-134)
 // and PV (lib/attention_gpu_int8.mojo:94-137 / lib/attention_gpu.mojo:241-248), and for
 // S>1 the multirow verify kernels (lib/attention_gpu_int8.mojo:322-584).
 //
 // Work decomposition
-//   grid = (splits, nkv, batch * row_groups); one CTA streams one KV head's chunk of
-//   the window and serves every query row of the GQA group from the same bytes.
+//   grid = (splits x head-dim slices, nkv, batch * row_groups); one CTA streams one KV head's
+//   chunk of the window and serves every query row of the GQA group from the same bytes.
 //   Each warp owns a private ring of 32-token tiles in an XOR-swizzled layout, with no CTA
 //   barrier in the loop.  Whole tiles of 64- or 128-byte rows are fetched by TMA (one lane
 //   issues two cp.async.bulk.tensor boxes + two bulk copies of scales against the stage's
@@ -28,13 +27,12 @@
 //        (the QK C fragment is already in A-fragment order), B = the V bytes as
 //        stored, transposed by ldmatrix.trans + one byte permute.  Exact int32 sums
 //        are folded into fp32 accumulators with the tile's weight.
-// The un-normalised (m, l, o) of the warps are merged in shared memory, then across
-// splits by merge_kernel, launched as a programmatic dependent so its launch latency
-// overlaps the main kernel (or exported for the multi-GPU all-gather).
+// The un-normalised (m, l, o) of the warps are merged in shared memory, then across splits
+// inside the same launch by the last CTA of the (batch, head, row group) to arrive
+// (merge_splits_in_kernel), or exported for the multi-GPU all-gather (merge_kernel runs after it).
 #include <algorithm>
 #include <atomic>
 #include <chrono>
-#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
