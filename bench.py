@@ -466,6 +466,36 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
             del ck, cv, cks, cvs
         except Exception as e:
             out[name] = {"error": str(e)}
+    # one decode step of a layer's attention path at configuration 2: producer epilogue (norms, RoPE, quantize-on-write
+    # of the new token) then attention over the 32768 keys -- two launches chained by programmatic dependent launch
+    try:
+        caches = [make_layer_cache(torch, ops, dev, 1, NKV, T, HD, 1302 + i) for i in range(NLAYERS)]
+        qf = torch.randn((1, NH, HD), device=dev); kf = torch.randn((1, NKV, HD), device=dev); vf = torch.randn((1, NKV, HD), device=dev)
+        qw = torch.ones(HD, device=dev); kw = torch.ones(HD, device=dev)
+        o = torch.zeros((1, 1, NH, HD), dtype=torch.bfloat16, device=dev)
+        al = []
+        for k, v, ks, vs in caches:
+            al.append((ops.make_args(q=qf, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=o, kv_fmt=ops.KV_I8, q_type=ops.F32,
+                                     out_type=ops.BF16, nh=NH, nkv=NKV, kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=T, klen=T,
+                                     softmax_scale=SOFTMAX_SCALE, flags=ops.SETTLED_CACHE), (k, v, ks, vs)))
+        wsb = ops.attn_workspace_bytes(al[0][0])
+        ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+        for a_, _ in al:
+            a_.workspace, a_.ws_bytes = ws.data_ptr(), wsb
+        ctr2 = [0]
+
+        def fstep():
+            a_, (k, v, ks, vs) = al[ctr2[0] % NLAYERS]; ctr2[0] += 1
+            ops.kv_norm_rope_append(stream, qf, qw, kf, vf, kw, k, v, ks, vs, n_s=1, nh=NH, nkv=NKV, l_hd=HD, l_kvd=NKV * HD,
+                                    cache_cap=T, cache_hd=HD, base_pos=T - 1, theta=10000.0, rope_dim=HD, kv_fmt=ops.KV_I8)
+            ops.attn_fused(stream, a_)
+
+        us = time_call(torch, fstep, iters)
+        out["decode_step_c2_producer_plus_attention"] = {"us_per_layer": round(us, 2), "launches": 2,
+                                                         "reference_launches": "6 + append + 2 dequant + 5 attention"}
+        del caches, ws
+    except Exception as e:
+        out["decode_step_c2_producer_plus_attention"] = {"error": str(e)}
     # configuration 5a: batch 8 x 131072 keys, sharded by KV-head groups (16 / world heads per GPU, no collective)
     try:
         B5, T5a = 8, 131072

@@ -29,6 +29,11 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 __global__ void __launch_bounds__(ROWS_PER_BLOCK * 32) kv_producer_kernel(ProducerArgs a) {
     __shared__ __align__(16) float rows[ROWS_PER_BLOCK][MAX_HD];
+    // Programmatic dependent launch on both sides: wait for the stream predecessor (the projections that
+    // wrote the source rows), then let the attention grid that follows be set up right away -- it blocks in
+    // its own wait until this grid is done, but may already stream the cache rows declared settled.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int w = blockIdx.x * ROWS_PER_BLOCK + wib;
     const int n_kv = a.n_s * a.nkv, n_q = a.q ? a.n_s * a.nh : 0;
@@ -107,8 +112,14 @@ __global__ void __launch_bounds__(ROWS_PER_BLOCK * 32) kv_producer_kernel(Produc
 int launch_kv_producer(cudaStream_t st, const ProducerArgs &a) {
     const long rows = 2L * a.n_s * a.nkv + (a.q ? (long)a.n_s * a.nh : 0);
     const unsigned blocks = (unsigned)((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
-    kv_producer_kernel<<<blocks, ROWS_PER_BLOCK * 32, 0, st>>>(a);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks); cfg.blockDim = dim3(ROWS_PER_BLOCK * 32); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cfg.attrs = pdl; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kv_producer_kernel, a);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) { set_error("nomos_kv_norm_rope_append launch: %s", cudaGetErrorString(e)); return NOMOS_ECUDA; }
     return NOMOS_OK;
 }
