@@ -612,6 +612,49 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
     }
     for (int s = early_n; s < NSTAGE - 1; ++s) issue(s);
 
+    // ------------------------------------------- fused quantize-on-write of the new keys
+    // The newest n_new keys arrive as fp32 rows.  A warp quantises one (row, plane) with the row codec
+    // of the append kernels (bit for bit) into its scratch row [codes | scales]; for row group 0 and
+    // head-dim slice 0 -- so exactly once per KV head -- it also copies bytes and scales into the
+    // ring for later calls.  Returns the block-32 row's cached q8 scale (unused otherwise).
+    auto quantize_new = [&](int i, int kv, uint8_t *scr) {
+        const float *src = (kv ? p.new_v : p.new_k) + ((size_t)b * p.n_new + i) * p.new_stride + kvh * HD;
+        const size_t crow = (size_t)kvh * p.cache_cap + (size_t)((p.new_base_pos + i) % p.cache_cap);
+        float q8s = 0.0f;
+        if constexpr (FMT == KV_I8) {
+            quant_row_i8(src, HD, HD, reinterpret_cast<int8_t *>(scr), reinterpret_cast<float *>(scr + C::ROWB), lane);
+        } else if constexpr (FMT == KV_I4) {
+            const float sc = quant_row_i4(src, HD, HD, scr, nullptr, lane);
+            if (lane == 0) *reinterpret_cast<float *>(scr + C::ROWB) = sc;
+        } else {
+            q8s = quant_row_i4_block32(src, HD, scr, reinterpret_cast<__half *>(scr + C::ROWB), lane);
+        }
+        __syncwarp();
+        if (rg == 0 && dsl == 0) {
+            uint8_t *g_rows = (kv ? p.v_cache_w : p.k_cache_w) + b * p.kv_batch_stride + crow * row_stride;
+            uint8_t *g_sc = (kv ? p.v_scales_w : p.k_scales_w) + b * p.scale_batch_stride;
+            // the row, zero-padded to the cache row width like the append kernels do (block-32 rows are never wider)
+            const int row_chunks = (FMT == KV_I4B32) ? C::CHUNKS : row_stride / 16;
+            for (int c = lane; c < row_chunks; c += 32)
+                reinterpret_cast<uint4 *>(g_rows)[c] = c < C::CHUNKS ? reinterpret_cast<const uint4 *>(scr)[c] : make_uint4(0, 0, 0, 0);
+            if constexpr (FMT == KV_I4B32) {
+                if (lane < C::NBLK) reinterpret_cast<uint16_t *>(g_sc)[crow * C::NBLK + lane] = reinterpret_cast<const uint16_t *>(scr + C::ROWB)[lane];
+                if (lane == 0) reinterpret_cast<float *>(g_sc + (size_t)p.nkv * p.cache_cap * C::NBLK * 2)[crow] = q8s;
+            } else {
+                if (lane == 0) reinterpret_cast<float *>(g_sc)[crow] = *reinterpret_cast<const float *>(scr + C::ROWB);
+            }
+        }
+    };
+    // A single new row (decode) is quantised NOW, while the first tiles and the query are in flight, by two
+    // warps (K and V) of the CTA that owns its tile, so that the codec's global round trips are off the path
+    // of the warp that will use the row; the CTA barrier after the query prologue publishes the scratch rows.
+    const int new_tile = (p.klen - 1) / TILE;                             // tile of the newest key
+    const bool early_new = p.new_k != nullptr && p.n_new == 1 && NWARP >= 2 && new_tile >= tile_begin && new_tile < tile_end;
+    const int new_owner = early_new ? (new_tile - tile_begin) % NWARP : -1;
+    const int new_helper = early_new ? (new_owner + 1) % NWARP : -1;
+    if (warp == new_owner) quantize_new(0, 0, append_scratch + warp * (C::ROWB + 64));
+    if (warp == new_helper) quantize_new(0, 1, append_scratch + warp * (C::ROWB + 64));
+
     // Each row becomes 15-bit fixed point: q ~= sq * (128*hi + lo), hi/lo int8.
 #pragma unroll
     for (int qi = 0; qi < QITER; ++qi) {
@@ -739,52 +782,34 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
         const uint8_t *ksm = my_sc + stg * 2 * C::SC_BYTES;         // K scales of the tile, token-major
         const uint8_t *vsm = ksm + C::SC_BYTES;                     // V scales
 
-        // ------------------------------------------- fused quantize-on-write of the new keys
-        // The newest n_new keys arrive as fp32 rows.  The warp that owns their tile quantises them
-        // (same row codec as the append kernels, bit for bit), overwrites the rows the copy engine
-        // fetched for those slots in shared memory, and -- for row group 0, so exactly once per KV
-        // head -- stores bytes and scales into the ring for later calls.
+        // ------------------------------------------- new keys of this tile
+        // Overwrite the rows the copy engine fetched for the new keys' slots with their quantised form
+        // (from the scratch rows filled in the prologue, or quantised here when there are several).
         if (p.new_k != nullptr && tok0 + TILE > p.klen - p.n_new) {
-            uint8_t *scr = append_scratch + warp * (C::ROWB + 64);
-            for (int i = 0; i < p.n_new; ++i) {
-                const int wi = p.klen - p.n_new + i;                 // window index of new key i
-                if (wi < tok0 || wi >= tok0 + TILE) continue;
-                const int r = wi - tok0;
-                const int slot = (p.new_base_pos + i) % p.cache_cap;
-                const size_t crow = (size_t)kvh * p.cache_cap + slot;
+            auto patch = [&](int r, int kv, const uint8_t *scr) {
+                uint8_t *tile_rows = my_pipe + stg * C::ST_BYTES + kv * C::KV_BYTES;          // fused append runs with DS == 1 only
+                uint8_t *tile_sc = my_sc + (stg * 2 + kv) * C::SC_BYTES + r * C::SCB;
+                if (lane < C::CHUNKS)
+                    *reinterpret_cast<uint4 *>(tile_rows + r * C::ROWB + swz_chunk<C::ROWB>(r, lane) * 16) =
+                        *reinterpret_cast<const uint4 *>(scr + lane * 16);
+                if (lane < C::SCB / 2)
+                    reinterpret_cast<uint16_t *>(tile_sc)[lane] = reinterpret_cast<const uint16_t *>(scr + C::ROWB)[lane];
+                __syncwarp();
+            };
+            if (early_new) {
+                const int r = p.klen - 1 - tok0;
+                patch(r, 0, append_scratch + new_owner * (C::ROWB + 64));
+                patch(r, 1, append_scratch + new_helper * (C::ROWB + 64));
+            } else {
+                uint8_t *scr = append_scratch + warp * (C::ROWB + 64);
+                for (int i = 0; i < p.n_new; ++i) {
+                    const int wi = p.klen - p.n_new + i;                 // window index of new key i
+                    if (wi < tok0 || wi >= tok0 + TILE) continue;
 #pragma unroll
-                for (int kv = 0; kv < 2; ++kv) {
-                    const float *src = (kv ? p.new_v : p.new_k) + ((size_t)b * p.n_new + i) * p.new_stride + kvh * HD;
-                    uint8_t *tile_rows = my_pipe + stg * C::ST_BYTES + kv * C::KV_BYTES;      // fused append runs with DS == 1 only
-                    uint8_t *tile_sc = my_sc + (stg * 2 + kv) * C::SC_BYTES + r * C::SCB;
-                    uint8_t *g_rows = (kv ? p.v_cache_w : p.k_cache_w) + b * p.kv_batch_stride + crow * row_stride;
-                    uint8_t *g_sc = (kv ? p.v_scales_w : p.k_scales_w) + b * p.scale_batch_stride;
-                    const bool writer = (rg == 0);
-                    if constexpr (FMT == KV_I8) {
-                        quant_row_i8(src, HD, HD, reinterpret_cast<int8_t *>(scr), reinterpret_cast<float *>(scr + C::ROWB), lane);
-                        if (writer) quant_row_i8(src, HD, p.cache_hd, reinterpret_cast<int8_t *>(g_rows), reinterpret_cast<float *>(g_sc) + crow, lane);
-                    } else if constexpr (FMT == KV_I4) {
-                        const float sc = quant_row_i4(src, HD, HD, scr, nullptr, lane);
-                        if (lane == 0) *reinterpret_cast<float *>(scr + C::ROWB) = sc;
-                        if (writer) {
-                            const float sg = quant_row_i4(src, HD, p.cache_hd, g_rows, nullptr, lane);
-                            if (lane == 0) reinterpret_cast<float *>(g_sc)[crow] = sg;
-                        }
-                    } else {
-                        quant_row_i4_block32(src, HD, scr, reinterpret_cast<__half *>(scr + C::ROWB), lane);
-                        if (writer) {
-                            const float q8s = quant_row_i4_block32(src, HD, g_rows, reinterpret_cast<__half *>(g_sc) + crow * C::NBLK, lane);
-                            if (lane == 0)
-                                reinterpret_cast<float *>(g_sc + (size_t)p.nkv * p.cache_cap * C::NBLK * 2)[crow] = q8s;
-                        }
+                    for (int kv = 0; kv < 2; ++kv) {
+                        quantize_new(i, kv, scr);
+                        patch(wi - tok0, kv, scr);
                     }
-                    __syncwarp();
-                    if (lane < C::CHUNKS)
-                        *reinterpret_cast<uint4 *>(tile_rows + r * C::ROWB + swz_chunk<C::ROWB>(r, lane) * 16) =
-                            *reinterpret_cast<const uint4 *>(scr + lane * 16);
-                    if (lane < C::SCB / 2)
-                        reinterpret_cast<uint16_t *>(tile_sc)[lane] = reinterpret_cast<const uint16_t *>(scr + C::ROWB)[lane];
-                    __syncwarp();
                 }
             }
         }
