@@ -75,7 +75,7 @@ template <int NS>
 struct Cfg {
     static constexpr int NSP = (NS + 7) / 8 * 8;                     // slots padded to the MMA's N granularity
     static constexpr int N = 2 * NSP;
-    static constexpr int NSTG = NS <= 8 ? 3 : 6;                     // 3 stages: two CTAs per SM
+    static constexpr int NSTG = NS <= 8 ? 3 : 5;                     // 3 stages: two CTAs per SM
     static constexpr int MIN_CTAS = NS <= 8 ? 2 : 1;
     static constexpr int NSG = NS <= 8 ? NS : NOMOS_TC5_NSG;         // slots per softmax warp group
     static constexpr int NG = NS / NSG;                              // softmax warp groups
@@ -92,11 +92,12 @@ struct Cfg {
     static constexpr int OFF_BAR = OFF_SLOTC + NSW * 16 * 16;
     static constexpr int NBAR = 2 * NSTG + 10 + 2 * NG;              // full, empty, s_ready, p_ready, o_ready, o_free (x2 each), q_ready, xch (x2 per group), patched
     static constexpr int OFF_MISC = OFF_BAR + NBAR * 8;              // tmem base, abort flag
-    static constexpr int OFF_NEW = OFF_MISC + 16;                    // quantize-on-write: one row of codes + its scale for K and V
-    static constexpr int OFF_NEWSC = OFF_NEW + 2 * (128 + 16);       // scales of the new rows [2][NEW_MAX]
+    static constexpr int OFF_NEW = OFF_MISC + 16;                    // quantize-on-write: [NEW_MAX][K, V] rows of codes + scale
+    static constexpr int OFF_NEWSC = OFF_NEW + 2 * NEW_MAX * (128 + 16);   // scales of the new rows [2][NEW_MAX]
     static constexpr int OFF_PAGES = OFF_NEWSC + 2 * NEW_MAX * 4;    // paged caches: page of each of this CTA's tiles
     static constexpr int SMEM_BYTES = 1024 + OFF_PAGES + MAX_PAGED_TILES * 4;
     static_assert(OFF_NEW % 16 == 0, "row scratch is copied in 16-byte chunks");
+    static_assert(SMEM_BYTES + 1024 <= 232448 / MIN_CTAS - (MIN_CTAS > 1 ? 1024 : 0), "shared memory budget of an SM (227 KB per CTA, 228 KB in all)");
     static_assert(OFF_BAR % 8 == 0, "mbarriers need 8-byte alignment");
     static_assert(OFF_Q % 1024 == 0 && QP_BYTES % 1024 == 0, "operand tiles sit on swizzle-pattern boundaries");
 };
@@ -441,6 +442,30 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                     for (int i = 0; i < HD / 32; ++i) qraw[k][i] = __ldg(reinterpret_cast<const uint32_t *>(p.q) + qoff[k] + 32 * i);
             }
         }
+        // ---- fused quantize-on-write, early: while the query and the first tiles are in flight, the softmax
+        // warps of the CTA that owns the tile(s) of the new keys quantise the fp32 rows with the row codec of
+        // the append kernels (bit for bit) into scratch rows, one (row, plane) per warp at a time, and -- row
+        // group 0 only, so once per KV head -- copy bytes and scale into the ring for later calls.
+        const bool cta_has_new = p.new_k != nullptr && my_n > 0 && tile_has_new(wg.tile(tile_end - 1));
+        if (cta_has_new) {
+            float *new_sc = reinterpret_cast<float *>(sm + C::OFF_NEWSC);
+            for (int pidx = warp; pidx < 2 * p.n_new; pidx += NSW) {
+                const int n = pidx >> 1, kv = pidx & 1;
+                uint8_t *scr = sm + C::OFF_NEW + pidx * 144;
+                const float *src = (kv ? p.new_v : p.new_k) + ((size_t)b * p.n_new + n) * p.new_stride + kvh * HD;
+                quant_row_i8(src, HD, HD, reinterpret_cast<int8_t *>(scr), reinterpret_cast<float *>(scr + 128), lane);
+                __syncwarp();
+                const float sc_row = *reinterpret_cast<const float *>(scr + 128);
+                if (lane == 0) new_sc[kv * NEW_MAX + n] = sc_row;
+                if (rg == 0) {
+                    const size_t crow = (size_t)row_base + (size_t)((p.new_base_pos + n) % p.cache_cap);
+                    uint8_t *g_rows = (kv ? p.v_cache_w : p.k_cache_w) + b * p.kv_batch_stride + crow * p.cache_hd;
+                    float *g_sc = reinterpret_cast<float *>((kv ? p.v_scales_w : p.k_scales_w) + b * p.scale_batch_stride) + crow;
+                    if (lane < 8) reinterpret_cast<uint4 *>(g_rows)[lane] = reinterpret_cast<const uint4 *>(scr)[lane];
+                    if (lane == 0) *g_sc = sc_row;
+                }
+            }
+        }
         float qx[QPW][HD / 32];
 #pragma unroll
         for (int k = 0; k < QPW; ++k) {
@@ -546,34 +571,20 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             float ks = scales_by_tma ? sc[kr] : ks_ld;
             float vs_raw = scales_by_tma ? sc[KT + kr] : vs_ld;
             if (tile_has_new(g)) {
-                // ---- fused quantize-on-write.  Warp 0 quantises the fp32 rows with the row codec of the
-                // append kernels (bit for bit), overwrites the rows TMA fetched for those slots, keeps
-                // their scales in shared memory and -- row group 0 only, so once per KV head -- stores
-                // bytes and scales into the ring for later calls.  The MMA issuer waits for this.
+                // ---- new keys of this tile: warp 0 overwrites the rows TMA fetched for their slots with the
+                // codes quantised in the prologue; the MMA issuer waits for this.
                 if (warp == 0) {
-                    uint8_t *scr = sm + C::OFF_NEW;
-                    float *new_sc = reinterpret_cast<float *>(sm + C::OFF_NEWSC);
                     for (int n = 0; n < p.n_new; ++n) {
                         const int wi = new_lo + n;                        // window index of new key n
                         if (wi < max(g.t0, g.t_lo) || wi >= min(g.t0 + KT, g.t_hi)) continue;
                         const int r = wi - g.t0;
-                        const size_t crow = (size_t)row_base + (size_t)((p.new_base_pos + n) % p.cache_cap);
 #pragma unroll
                         for (int kv = 0; kv < 2; ++kv) {
-                            const float *src = (kv ? p.new_v : p.new_k) + ((size_t)b * p.n_new + n) * p.new_stride + kvh * HD;
-                            quant_row_i8(src, HD, HD, reinterpret_cast<int8_t *>(scr + kv * 144), reinterpret_cast<float *>(scr + kv * 144 + 128), lane);
-                            if (rg == 0) {
-                                int8_t *g_rows = reinterpret_cast<int8_t *>(kv ? p.v_cache_w : p.k_cache_w) + b * p.kv_batch_stride + crow * p.cache_hd;
-                                float *g_sc = reinterpret_cast<float *>((kv ? p.v_scales_w : p.k_scales_w) + b * p.scale_batch_stride) + crow;
-                                quant_row_i8(src, HD, p.cache_hd, g_rows, g_sc, lane);
-                            }
-                            __syncwarp();
+                            const uint8_t *scr = sm + C::OFF_NEW + (2 * n + kv) * 144;
                             uint8_t *tile_rows = sm + st * 2 * TILE_BYTES + kv * TILE_BYTES;
                             if (lane < 8)
                                 *reinterpret_cast<uint4 *>(tile_rows + (r >> 3) * 1024 + (r & 7) * 128 + ((lane ^ (r & 7)) << 4)) =
-                                    *reinterpret_cast<const uint4 *>(scr + kv * 144 + lane * 16);
-                            if (lane == 0) new_sc[kv * NEW_MAX + n] = *reinterpret_cast<const float *>(scr + kv * 144 + 128);
-                            __syncwarp();
+                                    *reinterpret_cast<const uint4 *>(scr + lane * 16);
                         }
                     }
                     fused::fence_proxy_async();                          // the tensor core reads the patched rows
