@@ -2,6 +2,8 @@
 // (sm_100a).  See attn_fused.cu for the host side and the overall description.
 #pragma once
 
+#include <type_traits>
+
 #include <cuda.h>             // CUtensorMap (type only: the encoder is resolved at run time)
 #include <math_constants.h>
 
@@ -304,28 +306,17 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
         const int r = div_kvg(p, idx);
         return ((long)b * p.S + r) * p.nh + kvh * p.kvg + (idx - r * p.kvg);
     };
-    // Small merges (the common decode case): every thread owns one (row, dim) and requests its
-    // G partial outputs BEFORE the (m, l) staging barrier, so both sets of L2 loads are in flight
-    // together (one round trip instead of two).
-    constexpr int GFAST = 32;
-    const bool fast = (G <= GFAST) && (nrows * HD <= NTHR);
-    float pre[GFAST];
-    if (fast && (int)threadIdx.x < nrows * HD) {
-        const int sl = threadIdx.x / HD, d = threadIdx.x - sl * HD;
-        const float *base = p.partial + (size_t)grow_of(sl) * (HD + 2) + d;
-#pragma unroll
-        for (int i = 0; i < GFAST; ++i) pre[i] = __ldcg(base + (size_t)min(i, G - 1) * rstride);   // unconditional: batches freely
-    }
-    for (int e = threadIdx.x; e < nrows * G; e += NTHR) {
-        const int sl = e / G, i = e - sl * G;
-        const float *pr = p.partial + (size_t)i * rstride + (size_t)grow_of(sl) * (HD + 2);
-        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(pr + HD));     // (m, l): 8-byte aligned, one round trip
-        ls[sl * G + i] = ml.y;
-        ms[sl * G + i] = ml.y > 0.0f ? ml.x : -CUDART_INF_F;
-    }
-    __syncthreads();
-    MERGE_MARK(4);
-    {
+    // (m, l) of every split -> shared memory; then a warp per row: weights 2^(m_i - m*) and the merged denominator
+    auto stage_weights = [&]() {
+        for (int e = threadIdx.x; e < nrows * G; e += NTHR) {
+            const int sl = e / G, i = e - sl * G;
+            const float *pr = p.partial + (size_t)i * rstride + (size_t)grow_of(sl) * (HD + 2);
+            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(pr + HD));     // (m, l): 8-byte aligned, one round trip
+            ls[sl * G + i] = ml.y;
+            ms[sl * G + i] = ml.y > 0.0f ? ml.x : -CUDART_INF_F;
+        }
+        __syncthreads();
+        MERGE_MARK(4);
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         for (int sl = warp; sl < nrows; sl += NTHR / 32) {
             float m = -CUDART_INF_F;
@@ -342,9 +333,9 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
             for (int o = 16; o > 0; o >>= 1) lp += __shfl_xor_sync(0xffffffffu, lp, o);
             if (lane == 0) { s_mstar[sl] = m; s_lstar[sl] = lp; }
         }
-    }
-    __syncthreads();
-    MERGE_MARK(5);
+        __syncthreads();
+        MERGE_MARK(5);
+    };
     auto emit = [&](int sl, int d, float o) {
         const long grow = grow_of(sl);
         const float lstar = s_lstar[sl];
@@ -363,9 +354,21 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
             else reinterpret_cast<float *>(p.out)[oi] = v;
         }
     };
-    if (fast) {
-        if ((int)threadIdx.x < nrows * HD) {
-            const int sl = threadIdx.x / HD, d = threadIdx.x - sl * HD;
+    // Small merges (the common decode case): every thread owns one (row, dim) and requests its
+    // G partial outputs BEFORE the (m, l) staging barrier, so both sets of L2 loads are in flight
+    // together (one round trip instead of two).
+    constexpr int GFAST = 32;
+    if ((G <= GFAST) && (nrows * HD <= NTHR)) {
+        float pre[GFAST];
+        const bool mine = (int)threadIdx.x < nrows * HD;
+        const int sl = mine ? threadIdx.x / HD : 0, d = mine ? threadIdx.x - sl * HD : 0;
+        if (mine) {
+            const float *base = p.partial + (size_t)grow_of(sl) * (HD + 2) + d;
+#pragma unroll
+            for (int i = 0; i < GFAST; ++i) pre[i] = __ldcg(base + (size_t)min(i, G - 1) * rstride);   // unconditional: batches freely
+        }
+        stage_weights();
+        if (mine) {
             float o0 = 0.0f, o1 = 0.0f;
 #pragma unroll
             for (int k = 0; k < GFAST; k += 2) {
@@ -376,60 +379,70 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
         }
         return;
     }
-    // General case: four elements per thread at a time, GB splits each, all loads issued before use.
-    constexpr int EL = 4;
-    const int total = nrows * HD;
-#ifdef NOMOS_TIMELINE
-    for (int pass_ = 0; pass_ < 2; ++pass_) {            // debug builds: second pass times the same code warm
-    if (pass_ == 1) { __syncthreads(); MERGE_MARK(6); }
-#endif
-    for (int e0 = threadIdx.x; e0 < total; e0 += EL * NTHR) {
+    // General case: a thread takes EL pairs of dims at a time (partial rows are 8-byte aligned) and
+    // up to GBW splits of each, every load of such a batch issued before the first use (clamped
+    // instead of predicated, so they batch freely); the first batch is requested before the (m, l)
+    // staging barrier, like above.  GBW follows the number of splits so that up to twelve take a
+    // single round trip to L2.
+    constexpr int EL = 4, HP = HD / 2;
+    const int total = nrows * HP;
+    auto general = [&](auto gbw_tag) {
+        constexpr int GBW = decltype(gbw_tag)::value;
         const float *base[EL];
         int sl[EL];
-        float o[EL];
+        float2 v[EL][GBW];
+        auto setup = [&](int e0) {
 #pragma unroll
-        for (int j = 0; j < EL; ++j) {
-            const int e = min(e0 + j * NTHR, total - 1);
-            sl[j] = e / HD;
-            base[j] = p.partial + (size_t)grow_of(sl[j]) * (HD + 2) + (e - sl[j] * HD);
-            o[j] = 0.0f;
-        }
-        int i0 = 0;
-        for (; i0 + GB <= G; i0 += GB) {
-            float v[EL][GB];
+            for (int j = 0; j < EL; ++j) {
+                const int e = min(e0 + j * NTHR, total - 1);
+                sl[j] = e / HP;
+                base[j] = p.partial + (size_t)grow_of(sl[j]) * (HD + 2) + 2 * (e - sl[j] * HP);
+            }
+        };
+        auto issue = [&](int i0) {
 #pragma unroll
             for (int j = 0; j < EL; ++j)
 #pragma unroll
-                for (int k = 0; k < GB; ++k) v[j][k] = __ldcg(base[j] + (size_t)(i0 + k) * rstride);
+                for (int k = 0; k < GBW; ++k)
+                    v[j][k] = __ldcg(reinterpret_cast<const float2 *>(base[j] + (size_t)min(i0 + k, G - 1) * rstride));
+        };
+        int e0 = threadIdx.x;
+        setup(e0);
+        issue(0);
+        stage_weights();
+        for (bool first_round = true; e0 < total; e0 += EL * NTHR, first_round = false) {
+            if (!first_round) { setup(e0); issue(0); }
+            float2 o[EL];
 #pragma unroll
-            for (int j = 0; j < EL; ++j)
+            for (int j = 0; j < EL; ++j) o[j] = make_float2(0.0f, 0.0f);
+            for (int i0 = 0;;) {
 #pragma unroll
-                for (int k = 0; k < GB; ++k) o[j] = fmaf(ms[sl[j] * G + i0 + k], v[j][k], o[j]);
-        }
-        for (; i0 < G; i0 += 2) {             // remainder, two splits at a time (the second clamped, weight 0)
-            float v[EL][2];
+                for (int j = 0; j < EL; ++j)
 #pragma unroll
-            for (int j = 0; j < EL; ++j) {
-                v[j][0] = __ldcg(base[j] + (size_t)i0 * rstride);
-                v[j][1] = __ldcg(base[j] + (size_t)min(i0 + 1, G - 1) * rstride);
+                    for (int k = 0; k < GBW; ++k) {
+                        const float w = i0 + k < G ? ms[sl[j] * G + i0 + k] : 0.0f;
+                        o[j].x = fmaf(w, v[j][k].x, o[j].x);
+                        o[j].y = fmaf(w, v[j][k].y, o[j].y);
+                    }
+                i0 += GBW;
+                if (i0 >= G) break;
+                issue(i0);
             }
 #pragma unroll
             for (int j = 0; j < EL; ++j) {
-                o[j] = fmaf(ms[sl[j] * G + i0], v[j][0], o[j]);
-                o[j] = fmaf(i0 + 1 < G ? ms[sl[j] * G + i0 + 1] : 0.0f, v[j][1], o[j]);
+                const int e = e0 + j * NTHR;
+                if (e < total) {
+                    const int d = 2 * (e - sl[j] * HP);
+                    emit(sl[j], d, o[j].x);
+                    emit(sl[j], d + 1, o[j].y);
+                }
             }
         }
-#pragma unroll
-        for (int j = 0; j < EL; ++j) {
-            const int e = e0 + j * NTHR;
-            if (e < total) emit(sl[j], e - sl[j] * HD, o[j]);
-        }
-    }
-#ifdef NOMOS_TIMELINE
-    }
-    __syncthreads();
-    MERGE_MARK(7);
-#endif
+    };
+    if (G <= 4) general(std::integral_constant<int, 4>{});
+    else if (G <= 8) general(std::integral_constant<int, 8>{});
+    else general(std::integral_constant<int, 12>{});
+    MERGE_MARK(6);
 }
 
 template <int FMT, int HD, int MT, int DS = 1>

@@ -15,12 +15,16 @@
 // Accumulators live in tensor memory: a softmax warp reads the TMEM lanes 32(w%4)..32(w%4)+31,
 // i.e. thread = one key of the tile for S^T, thread = one output dim for O^T.
 //
-// Roles: groups of four softmax warps (one group for up to eight slots; beyond that one group per
-// NOMOS_TC5_NSG slots, each owning its slots' columns of S^T, P and O^T), then one warp whose lane
-// 0 is the TMA producer and one whose lane 0 issues the MMAs; with a single group two more warps
-// only help in the split merge.  Optional in the same launch: quantize-on-write of up to NEW_MAX
-// new rows (softmax warp 0 overwrites the rows TMA fetched), and paged caches (a tile is a page of
-// 128 keys looked up in a block table).  Every wait is an mbarrier wait with a time limit; a wait
+// Roles: groups of four softmax warps (128 threads = the 128 TMEM lanes), then one warp whose lane
+// 0 is the TMA producer and one whose lane 0 issues the MMAs.  Up to eight slots: one group, two
+// S/P/O buffers, two CTAs per SM (two more warps only help in the split merge).  More slots
+// (speculative verify): NOMOS_TC5_NG groups take the CTA's tiles in turn -- group g owns tiles g,
+// g+NG, ... with all their slots, keeps its own running reference, denominators and output sums,
+// and the groups are merged in shared memory at the end -- over four S/P/O buffers, so that one
+// group's dependent chain (TMEM load, maxima, weights, P store, O read-back) overlaps the others'.
+// Optional in the same launch: quantize-on-write of up to NEW_MAX new rows (a softmax warp
+// overwrites the rows TMA fetched), and paged caches (a tile is a page of 128 keys looked up in a
+// block table).  Every wait is an mbarrier wait with a time limit; a wait
 // that runs out raises the CTA's abort flag and a bit in the device fault word, every role leaves
 // its loop, tensor memory is freed and the CTA exits.
 #pragma once
@@ -44,12 +48,11 @@ constexpr int KT = 128;                      // keys per tile = M of the QK MMA
 constexpr int HD = 128;                      // head dim = M of the PV MMA
 constexpr int TILE_BYTES = KT * HD;          // one K or V tile (int8)
 constexpr int SCALE_BYTES = KT * 4;          // one tile's fp32 row scales
-constexpr int TMEM_COLS = 256;               // S0 | S1 | O0 | O1, 64 columns each
 constexpr float LG2_VS_MIN = -64.0f;
 constexpr int NEW_MAX = 8;                   // most rows one call may quantise on the way in
 constexpr int MAX_PAGED_TILES = 256;         // paged caches: most tiles (pages) one CTA walks
-#ifndef NOMOS_TC5_NSG
-#define NOMOS_TC5_NSG 4                      // slots per softmax warp group when a CTA serves more than eight
+#ifndef NOMOS_TC5_NG
+#define NOMOS_TC5_NG 2                       // softmax warp groups (tiles in flight) when a CTA serves more than eight slots
 #endif
 
 #ifdef NOMOS_TIMELINE
@@ -58,7 +61,7 @@ __device__ unsigned long long g_tc5_tl[320][40][6];
 #define TC5_MARK(tile, slot)                                                                     \
     do {                                                                                         \
         const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);         \
-        if (threadIdx.x == 0 && cta_ < 320 && (tile) < 40) g_tc5_tl[cta_][tile][slot] = fused::gtime(); \
+        if ((threadIdx.x & 127) == 0 && threadIdx.x < 32 * Cfg<NS>::NSW && cta_ < 320 && (tile) < 40) g_tc5_tl[cta_][tile][slot] = fused::gtime(); \
     } while (0)
 __device__ unsigned long long g_tc5_cta[320][8];
 #define TC5_CTA_MARK(slot)                                                                       \
@@ -77,21 +80,26 @@ struct Cfg {
     static constexpr int N = 2 * NSP;
     static constexpr int NSTG = NS <= 8 ? 3 : 5;                     // 3 stages: two CTAs per SM
     static constexpr int MIN_CTAS = NS <= 8 ? 2 : 1;
-    static constexpr int NSG = NS <= 8 ? NS : NOMOS_TC5_NSG;         // slots per softmax warp group
-    static constexpr int NG = NS / NSG;                              // softmax warp groups
+    static constexpr int NG = NS <= 8 ? 1 : NOMOS_TC5_NG;            // softmax warp groups; group g owns tiles g, g+NG, ...
+    static constexpr int NB = NS <= 8 ? 2 : 4;                       // buffers of S^T, P and O^T (tile i uses buffer i % NB)
+    static constexpr int LAG = NG;                                   // the issuer sends PV(i - LAG) after QK(i)
+    static constexpr int TMEM_COLS = 128 * NB;                       // S buffers, then O buffers, 64 columns each
     static constexpr int NSW = 4 * NG;                               // softmax warps; then the TMA warp, then the MMA warp
     static constexpr int NTHREADS = NG == 1 ? 256 : 32 * (NSW + 2);
-    static_assert(NS % NSG == 0 && NSG % 2 == 0 && NG <= 6, "slots split evenly over the groups");
+    static_assert(NS % 2 == 0 && NS <= 32 && N <= 64, "a buffer is 64 TMEM columns; lane s of a warp keeps slot s's reference");
+    static_assert(LAG < NB && TMEM_COLS <= 512 && NG <= 3, "S buffer i % NB is rewritten NB tiles later, after p_ready(i) was seen");
     static constexpr int QP_BYTES = N * 128;                         // Q limbs, or one buffer of P limbs
     static constexpr int OFF_SCALES = NSTG * 2 * TILE_BYTES;
     static constexpr int OFF_Q = OFF_SCALES + NSTG * 2 * SCALE_BYTES;
     static constexpr int OFF_P = OFF_Q + QP_BYTES;
-    static constexpr int OFF_XCH = OFF_P + 2 * QP_BYTES;             // [2][NSP][4] warp maxima
-    static constexpr int OFF_SLOT = OFF_XCH + 2 * NSP * 16;          // qscale[NSP], lo[NSP], hi[NSP]
-    static constexpr int OFF_SLOTC = (OFF_SLOT + NSP * 12 + 15) / 16 * 16;   // per softmax warp: 16 x (max, weight, alpha, -)
-    static constexpr int OFF_BAR = OFF_SLOTC + NSW * 16 * 16;
-    static constexpr int NBAR = 2 * NSTG + 10 + 2 * NG;              // full, empty, s_ready, p_ready, o_ready, o_free (x2 each), q_ready, xch (x2 per group), patched
-    static constexpr int OFF_MISC = OFF_BAR + NBAR * 8;              // tmem base, abort flag
+    static constexpr int OFF_XCH = OFF_P + NB * QP_BYTES;            // [NG][2][NSP][4] warp maxima
+    static constexpr int OFF_SLOT = OFF_XCH + NG * 2 * NSP * 16;     // qscale[NSP], lo[NSP], hi[NSP]
+    static constexpr int OFF_SLOTC = (OFF_SLOT + NSP * 12 + 15) / 16 * 16;   // per softmax warp: NSP x (max, weight, alpha, -)
+    static constexpr int OFF_BAR = OFF_SLOTC + NSW * NSP * 16;
+    static constexpr int NBAR = 2 * NSTG + 4 * NB + 1 + 2 * NG + 2;  // full, empty; s_ready, p_ready, o_ready, o_free (per buffer); q_ready; xch (x2 per group); patched (x2)
+    static constexpr int MRG_BYTES = (NG - 1) * NS * HD * 4;         // output sums of groups 1.. for the merge, over the tile stages
+    static_assert(MRG_BYTES <= NSTG * 2 * TILE_BYTES, "group merge scratch reuses the tile stages");
+    static constexpr int OFF_MISC = (OFF_BAR + NBAR * 8 + 15) / 16 * 16;   // tmem base, abort flag
     static constexpr int OFF_NEW = OFF_MISC + 16;                    // quantize-on-write: [NEW_MAX][K, V] rows of codes + scale
     static constexpr int OFF_NEWSC = OFF_NEW + 2 * NEW_MAX * (128 + 16);   // scales of the new rows [2][NEW_MAX]
     static constexpr int OFF_PAGES = OFF_NEWSC + 2 * NEW_MAX * 4;    // paged caches: page of each of this CTA's tiles
@@ -235,9 +243,11 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     attn_tc5_kernel(const KParams p, const __grid_constant__ TmaMaps4 tm) {
     using C = Cfg<NS>;
     constexpr int NSP = C::NSP, NSTG = C::NSTG;
-    constexpr int NG = C::NG, NSG = C::NSG, NSW = C::NSW, NTHREADS = C::NTHREADS;
-    constexpr int CH = NSG % 4 == 0 ? 4 : 2;         // slots per TMEM load
+    constexpr int NG = C::NG, NB = C::NB, LAG = C::LAG, NSW = C::NSW, NTHREADS = C::NTHREADS;
+    constexpr int NSG = NS;                          // slots per softmax thread: all of the CTA's
+    constexpr int CH = NSG % 8 == 0 ? 8 : NSG % 4 == 0 ? 4 : 2;      // slots per TMEM load
     constexpr int NCH = NSG / CH;
+    constexpr uint32_t TMEM_O = 64 * NB;             // first column of the O^T buffers
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -245,19 +255,21 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     float *slot_qscale = reinterpret_cast<float *>(sm + C::OFF_SLOT);
     int *slot_lo = reinterpret_cast<int *>(sm + C::OFF_SLOT + NSP * 4);
     int *slot_hi = reinterpret_cast<int *>(sm + C::OFF_SLOT + NSP * 8);
-    int *xch = reinterpret_cast<int *>(sm + C::OFF_XCH);                    // [2][NSP][4]
+    int *xch_all = reinterpret_cast<int *>(sm + C::OFF_XCH);                // [NG][2][NSP][4]
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(sm + C::OFF_MISC);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(sm + C::OFF_MISC + 4);
     const uint32_t bar0 = sm_u32 + C::OFF_BAR;
     auto bar_full = [&](int s) { return bar0 + 8 * s; };
     auto bar_empty = [&](int s) { return bar0 + 8 * (NSTG + s); };
     auto bar_s_ready = [&](int i) { return bar0 + 8 * (2 * NSTG + i); };
-    auto bar_p_ready = [&](int i) { return bar0 + 8 * (2 * NSTG + 2 + i); };
-    auto bar_o_ready = [&](int i) { return bar0 + 8 * (2 * NSTG + 4 + i); };
-    auto bar_o_free = [&](int i) { return bar0 + 8 * (2 * NSTG + 6 + i); };
-    auto bar_xch = [&](int g, int i) { return bar0 + 8 * (2 * NSTG + 9 + 2 * g + i); };
-    const uint32_t bar_q_ready = bar0 + 8 * (2 * NSTG + 8);
-    const uint32_t bar_patched = bar0 + 8 * (2 * NSTG + 9 + 2 * NG);
+    auto bar_p_ready = [&](int i) { return bar0 + 8 * (2 * NSTG + NB + i); };
+    auto bar_o_ready = [&](int i) { return bar0 + 8 * (2 * NSTG + 2 * NB + i); };
+    auto bar_o_free = [&](int i) { return bar0 + 8 * (2 * NSTG + 3 * NB + i); };
+    const uint32_t bar_q_ready = bar0 + 8 * (2 * NSTG + 4 * NB);
+    auto bar_xch = [&](int g, int i) { return bar0 + 8 * (2 * NSTG + 4 * NB + 1 + 2 * g + i); };
+    // the new keys are the window's last ones, so at most the CTA's last two tiles hold any: each of
+    // those has a barrier of its own, used once
+    auto bar_patched = [&](int k) { return bar0 + 8 * (2 * NSTG + 4 * NB + 1 + 2 * NG + k); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, kvh = blockIdx.y;
@@ -284,6 +296,8 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     // fused quantize-on-write: the last n_new keys of the window arrive as fp32 rows with this call
     const int new_lo = p.new_k ? p.klen - p.n_new : 0x7fffffff;      // window index of the first new key
     auto tile_has_new = [&](const TileGeo &g) { return min(g.t0 + KT, g.t_hi) > new_lo; };
+    // which of the two "patched" barriers CTA tile i uses (only asked for tiles with new keys)
+    auto patch_index = [&](int i) { return (i >= 1 && tile_has_new(wg.tile(tile_begin + i - 1))) ? 1 : 0; };
     // fp32 row scales ride TMA when every tile's first scale sits on a 16-byte boundary; otherwise
     // each softmax thread fetches its key's two scales one tile ahead with plain loads
     const bool scales_by_tma = (p.use_tma & 2) != 0;
@@ -294,16 +308,17 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
 #pragma unroll
         for (int s = 0; s < NSTG; ++s) { fused::mbar_init(bar_full(s), 1); fused::mbar_init(bar_empty(s), 1); }
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < NB; ++i) {
             fused::mbar_init(bar_s_ready(i), 1);
-            fused::mbar_init(bar_p_ready(i), 128 * NG);
+            fused::mbar_init(bar_p_ready(i), 128);
             fused::mbar_init(bar_o_ready(i), 1);
-            fused::mbar_init(bar_o_free(i), 128 * NG);
-#pragma unroll
-            for (int g = 0; g < NG; ++g) fused::mbar_init(bar_xch(g, i), 128);
+            fused::mbar_init(bar_o_free(i), 128);
         }
+#pragma unroll
+        for (int g = 0; g < NG; ++g) { fused::mbar_init(bar_xch(g, 0), 128); fused::mbar_init(bar_xch(g, 1), 128); }
         fused::mbar_init(bar_q_ready, 128 * NG);
-        fused::mbar_init(bar_patched, 32);
+        fused::mbar_init(bar_patched(0), 32);
+        fused::mbar_init(bar_patched(1), 32);
         fused::fence_mbar_init();
     }
     if (warp == NSW + 1 && lane == 0) {
@@ -311,7 +326,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         if (scales_by_tma) { fused::prefetch_tensormap(&tm.ks); fused::prefetch_tensormap(&tm.vs); }
     }
     if (warp == NSW) {
-        tmem_alloc(sm_u32 + C::OFF_MISC, TMEM_COLS);
+        tmem_alloc(sm_u32 + C::OFF_MISC, C::TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -368,36 +383,34 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             const uint32_t idesc_pv = make_idesc(C::N, true, false, true);
             const uint64_t qdesc = smem_desc_sw128(sm_u32 + C::OFF_Q);
             bool go = wait_or_abort(bar_q_ready, 0, abort_flag, p.fault);
-            int n_patched = 0;
-            for (int i = 0; go && i <= my_n; ++i) {
+            for (int i = 0; go && i < my_n + LAG; ++i) {
                 if (i < my_n) {
-                    // S^T[i&1] = K_i x Q^T.  The buffer's previous reader (tile i-2) was done before
-                    // p_ready(i-2), which this thread observed when it issued PV(i-2).
-                    const int st = i % NSTG;
+                    // S^T[i % NB] = K_i x Q^T.  The buffer's previous reader (tile i-NB) was done before
+                    // p_ready(i-NB), which this thread observed when it issued PV(i-NB), LAG < NB rounds later.
+                    const int st = i % NSTG, bf = i % NB;
                     if (!wait_or_abort(bar_full(st), (i / NSTG) & 1, abort_flag, p.fault)) break;
-                    if (tile_has_new(wg.tile(tile_begin + i))) {      // softmax warp 0 overwrites the new keys' rows first
-                        if (!wait_or_abort(bar_patched, n_patched & 1, abort_flag, p.fault)) break;
-                        ++n_patched;
+                    if (tile_has_new(wg.tile(tile_begin + i))) {      // a softmax warp overwrites the new keys' rows first
+                        if (!wait_or_abort(bar_patched(patch_index(i)), 0, abort_flag, p.fault)) break;
                     }
                     tc_fence_after();
                     const uint64_t kdesc = smem_desc_sw128(sm_u32 + st * 2 * TILE_BYTES);
 #pragma unroll
                     for (int k = 0; k < HD / 32; ++k)      // 32 bytes of K per instruction: +32 B on both operands
-                        umma_i8(tmem_base + 64 * (i & 1), kdesc + 2 * k, qdesc + 2 * k, idesc_qk, k > 0);
-                    umma_commit(bar_s_ready(i & 1));
+                        umma_i8(tmem_base + 64 * bf, kdesc + 2 * k, qdesc + 2 * k, idesc_qk, k > 0);
+                    umma_commit(bar_s_ready(bf));
                 }
-                if (i >= 1) {
-                    // O^T[j&1] = V_j^T x P_j^T
-                    const int j = i - 1, st = j % NSTG;
-                    if (!wait_or_abort(bar_p_ready(j & 1), (j >> 1) & 1, abort_flag, p.fault)) break;
-                    if (j >= 2 && !wait_or_abort(bar_o_free(j & 1), ((j - 2) >> 1) & 1, abort_flag, p.fault)) break;
+                if (i >= LAG) {
+                    // O^T[j % NB] = V_j^T x P_j^T
+                    const int j = i - LAG, st = j % NSTG, bf = j % NB;
+                    if (!wait_or_abort(bar_p_ready(bf), (j / NB) & 1, abort_flag, p.fault)) break;
+                    if (j >= NB && !wait_or_abort(bar_o_free(bf), ((j - NB) / NB) & 1, abort_flag, p.fault)) break;
                     tc_fence_after();
                     const uint64_t vdesc = smem_desc_sw128(sm_u32 + st * 2 * TILE_BYTES + TILE_BYTES);
-                    const uint64_t pdesc = smem_desc_sw128(sm_u32 + C::OFF_P + (j & 1) * C::QP_BYTES);
+                    const uint64_t pdesc = smem_desc_sw128(sm_u32 + C::OFF_P + bf * C::QP_BYTES);
 #pragma unroll
                     for (int k = 0; k < KT / 32; ++k)      // 32 keys per instruction: 4 row groups of V (+4096 B), +32 B of P
-                        umma_i8(tmem_base + 128 + 64 * (j & 1), vdesc + 256 * k, pdesc + 2 * k, idesc_pv, k > 0);
-                    umma_commit(bar_o_ready(j & 1));
+                        umma_i8(tmem_base + TMEM_O + 64 * bf, vdesc + 256 * k, pdesc + 2 * k, idesc_pv, k > 0);
+                    umma_commit(bar_o_ready(bf));
                     umma_commit(bar_empty(st));
                 }
             }
@@ -408,7 +421,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         TC5_CTA_MARK(2);
         const int grp = warp >> 2, wq = warp & 3;        // group, and the TMEM lane quarter this warp may read
         const int kr = threadIdx.x & 127;                // key row of S^T, output dim of O^T
-        const int s0 = grp * NSG;                        // first slot of this group
+        int *xch = xch_all + grp * 2 * NSP * 4;          // this group's [2][NSP][4] exchange area
         const uint32_t tmem_lane = tmem_base + ((uint32_t)(32 * wq) << 16);
         auto wait_warp = [&](uint32_t bar, uint32_t parity) {
             return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag, p.fault)) != 0;
@@ -416,6 +429,18 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         // byte (row, col) of a K-major operand tile with 128-byte rows, 128B-swizzled
         auto at = [](int row, int col) { return (row >> 3) * 1024 + (row & 7) * 128 + ((((col >> 4) ^ (row & 7)) << 4) | (col & 15)); };
 
+        const float *gks = reinterpret_cast<const float *>(p.k_scales + b * p.scale_batch_stride);
+        const float *gvs = reinterpret_cast<const float *>(p.v_scales + b * p.scale_batch_stride);
+        const int last_row = p.nkv * p.cache_cap - 1;
+        float ks_next = 0.0f, vs_next = 1.0f;
+        auto fetch_scales = [&](int i) {
+            if (!scales_by_tma && i < my_n) {
+                const int row = min(row_base + wg.tile(tile_begin + i).slot0 + kr, last_row);   // rows past the cache are masked anyway
+                ks_next = __ldg(gks + row);
+                vs_next = __ldg(gvs + row);
+            }
+        };
+        fetch_scales(grp);                               // in flight while the query rows are prepared
         // ---- query rows -> two int8 limbs each (15-bit fixed point: q ~= sq * (128 hi + lo)).
         // A warp prepares slots warp, warp+4, ...; all their loads are issued before the first use.
         constexpr int QPW = (NSP + NSW - 1) / NSW;
@@ -510,26 +535,25 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         // The loops below are written phase by phase over all slots (loads, then arithmetic, then
         // stores) so that the slots' independent instruction chains overlap: each scheduler of the
         // SM runs a single softmax warp and has nothing else to hide latencies with.
-        float lsum[NSG], acc[NSG], f_prev[NSG];               // this group's slots s0 .. s0+NSG-1
-        float r_lane = M_INIT;                                // running reference of slot s0+lane (lanes < NSG)
-        float4 *my_consts = reinterpret_cast<float4 *>(sm + C::OFF_SLOTC) + warp * 16;
-        int p_off[NSG];                                       // byte of (high-limb row of slot, this key) in a P tile
+        float lsum[NSG], acc[NSG], f_prev[NSG];               // over this group's tiles, every slot
+        float r_lane = M_INIT;                                // running reference of slot `lane` (lanes < NSG)
+        float4 *my_consts = reinterpret_cast<float4 *>(sm + C::OFF_SLOTC) + warp * NSP;
         int lo_max = 0, hi_min = 0x7fffffff;
 #pragma unroll
         for (int s = 0; s < NSG; ++s) {
             lsum[s] = 0.0f; acc[s] = 0.0f; f_prev[s] = 0.0f;
-            p_off[s] = at(s0 + s, kr);
-            if (alive && slot_hi[s0 + s] > 0) { lo_max = max(lo_max, slot_lo[s0 + s]); hi_min = min(hi_min, slot_hi[s0 + s]); }
+            if (alive && slot_hi[s] > 0) { lo_max = max(lo_max, slot_lo[s]); hi_min = min(hi_min, slot_hi[s]); }
         }
         // O^T of tile j: add the exact int32 sums with the tile's weight
         auto epilogue = [&](int j) -> bool {
-            if (!wait_warp(bar_o_ready(j & 1), (j >> 1) & 1)) return false;
+            const int bf = j % NB;
+            if (!wait_warp(bar_o_ready(bf), (j / NB) & 1)) return false;
             tc_fence_after();
             int oh[NCH][CH], ol[NCH][CH];
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
-                tmem_ld<CH>(tmem_lane + 128 + 64 * (j & 1) + s0 + CH * c, oh[c]);
-                tmem_ld<CH>(tmem_lane + 128 + 64 * (j & 1) + NSP + s0 + CH * c, ol[c]);
+                tmem_ld<CH>(tmem_lane + TMEM_O + 64 * bf + CH * c, oh[c]);
+                tmem_ld<CH>(tmem_lane + TMEM_O + 64 * bf + NSP + CH * c, ol[c]);
             }
             tmem_wait_ld();
 #pragma unroll
@@ -538,29 +562,17 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 for (int e = 0; e < CH; ++e)      // each limb sum is below 128 * 255 * 127 < 2^22
                     acc[c * CH + e] = fmaf(fmaf(i2f_small(oh[c][e]), 256.0f, i2f_small(ol[c][e])), f_prev[c * CH + e], acc[c * CH + e]);
             tc_fence_before();
-            mbar_arrive(bar_o_free(j & 1));
+            mbar_arrive(bar_o_free(bf));
             return true;
         };
 
-        const float *gks = reinterpret_cast<const float *>(p.k_scales + b * p.scale_batch_stride);
-        const float *gvs = reinterpret_cast<const float *>(p.v_scales + b * p.scale_batch_stride);
-        const int last_row = p.nkv * p.cache_cap - 1;
-        float ks_next = 0.0f, vs_next = 1.0f;
-        auto fetch_scales = [&](int i) {
-            if (!scales_by_tma && i < my_n) {
-                const int row = min(row_base + wg.tile(tile_begin + i).slot0 + kr, last_row);   // rows past the cache are masked anyway
-                ks_next = __ldg(gks + row);
-                vs_next = __ldg(gvs + row);
-            }
-        };
-        fetch_scales(0);
-        int n_patched = 0;                               // tiles whose new rows were quantised in
-        int done = 0;                                    // tiles whose P was handed to the tensor core
-        for (int i = 0; alive && i < my_n; ++i) {
-            const int st = i % NSTG, b2 = i & 1;
+        int last_done = -1;                              // this group's last tile whose P was handed to the tensor core
+        for (int i = grp; alive && i < my_n; i += NG) {
+            const int st = i % NSTG, bf = i % NB;
+            const int b2 = (i / NG) & 1, xph = ((i / NG) >> 1) & 1;      // exchange buffer and its barrier's phase: per own tile
             const TileGeo g = wg.tile(tile_begin + i);
             const float ks_ld = ks_next, vs_ld = vs_next;
-            fetch_scales(i + 1);
+            fetch_scales(i + NG);
             TC5_MARK(i, 0);
             if (!wait_warp(bar_full(st), (i / NSTG) & 1)) { alive = false; break; }
             TC5_MARK(i, 1);
@@ -573,7 +585,8 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             if (tile_has_new(g)) {
                 // ---- new keys of this tile: warp 0 overwrites the rows TMA fetched for their slots with the
                 // codes quantised in the prologue; the MMA issuer waits for this.
-                if (warp == 0) {
+                const uint32_t bar_pt = bar_patched(patch_index(i));
+                if (wq == 0) {
                     for (int n = 0; n < p.n_new; ++n) {
                         const int wi = new_lo + n;                        // window index of new key n
                         if (wi < max(g.t0, g.t_lo) || wi >= min(g.t0 + KT, g.t_hi)) continue;
@@ -588,10 +601,9 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                         }
                     }
                     fused::fence_proxy_async();                          // the tensor core reads the patched rows
-                    mbar_arrive(bar_patched);
+                    mbar_arrive(bar_pt);
                 }
-                if (!wait_warp(bar_patched, n_patched & 1)) { alive = false; break; }
-                ++n_patched;
+                if (!wait_warp(bar_pt, 0)) { alive = false; break; }
                 if (t >= new_lo && row_ok) {
                     const float *new_sc = reinterpret_cast<const float *>(sm + C::OFF_NEWSC);
                     ks = new_sc[t - new_lo];
@@ -602,15 +614,15 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             const float lvs = lg2f(vs), rvs = row_ok ? rcpf(vs) : 0.0f;
             float qk[NSG];
 #pragma unroll
-            for (int s = 0; s < NSG; ++s) qk[s] = slot_qscale[s0 + s] * ks;
-            if (!wait_warp(bar_s_ready(b2), (i >> 1) & 1)) { alive = false; break; }
+            for (int s = 0; s < NSG; ++s) qk[s] = slot_qscale[s] * ks;
+            if (!wait_warp(bar_s_ready(bf), (i / NB) & 1)) { alive = false; break; }
             tc_fence_after();
             TC5_MARK(i, 2);
             int sh[NCH][CH], sl_[NCH][CH];
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
-                tmem_ld<CH>(tmem_lane + 64 * b2 + s0 + CH * c, sh[c]);
-                tmem_ld<CH>(tmem_lane + 64 * b2 + NSP + s0 + CH * c, sl_[c]);
+                tmem_ld<CH>(tmem_lane + 64 * bf + CH * c, sh[c]);
+                tmem_ld<CH>(tmem_lane + 64 * bf + NSP + CH * c, sl_[c]);
             }
             tmem_wait_ld();
             // u = base-2 logit + log2(v_scale): 2^(u - max u) is the key's weight on the V bytes relative
@@ -622,7 +634,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             if (need_mask) {
 #pragma unroll
                 for (int s = 0; s < NSG; ++s) {
-                    const bool ok = row_ok && t >= slot_lo[s0 + s] && t < slot_hi[s0 + s];
+                    const bool ok = row_ok && t >= slot_lo[s] && t < slot_hi[s];
                     u[s] = ok ? u[s] : -CUDART_INF_F;
                 }
             }
@@ -634,19 +646,19 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 const int wm = redux_max(f2ord(u[s]));
                 mine = lane == s ? wm : mine;
             }
-            if (lane < NSG) xch[(b2 * NSP + s0 + lane) * 4 + wq] = mine;
+            if (lane < NSG) xch[(b2 * NSP + lane) * 4 + wq] = mine;
             mbar_arrive(bar_xch(grp, b2));
-            if (!wait_warp(bar_xch(grp, b2), (i >> 1) & 1)) { alive = false; break; }
+            if (!wait_warp(bar_xch(grp, b2), xph)) { alive = false; break; }
             TC5_MARK(i, 3);
             // Per-slot constants of the tile are the same for every key: lane s of each warp works them
-            // out for slot s0+s (the running reference R of that slot lives in that lane) and the warp
+            // out for slot s (the running reference R of that slot lives in that lane) and the warp
             // shares them through shared memory, instead of every thread repeating them for every slot.
             // The reference only moves when the tile maximum exceeds it by more than 2^8 (weights are
             // normalised per tile, so a stale reference costs no precision): either it stays (alpha = 1,
             // tile weight 2^d) or it moves to the tile maximum (tile weight 1, alpha = 2^-d).
             bool moved = false;
             if (lane < NSG) {
-                const int4 m4 = *reinterpret_cast<const int4 *>(xch + (b2 * NSP + s0 + lane) * 4);
+                const int4 m4 = *reinterpret_cast<const int4 *>(xch + (b2 * NSP + lane) * 4);
                 const float umax = ord2f(max(max(m4.x, m4.y), max(m4.z, m4.w)));
                 const float d = umax - r_lane;                           // -inf when every key of the tile is masked
                 moved = d > LAZY_MAX;
@@ -674,27 +686,30 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 fx[s] = __float_as_uint(fmaf(w, P_FIX, RND_MAGIC));
             }
             __syncwarp();                                                // my_consts is rewritten next tile
-            uint8_t *pt = sm + C::OFF_P + b2 * C::QP_BYTES;
+            // byte (row s, key kr) of the 128B-swizzled P tile: the row picks the 1024-byte group and the
+            // line in it, and flips bits 4..6 of the key
+            uint8_t *pt = sm + C::OFF_P + bf * C::QP_BYTES;
 #pragma unroll
             for (int s = 0; s < NSG; ++s) {
-                pt[p_off[s]] = (uint8_t)(fx[s] >> 8);
-                pt[p_off[s] + NSP * 128] = (uint8_t)fx[s];               // low limbs: NSP rows (a multiple of 8) further down
+                const int off = (s >> 3) * 1024 + (s & 7) * 128 + (kr ^ ((s & 7) << 4));
+                pt[off] = (uint8_t)(fx[s] >> 8);
+                pt[off + NSP * 128] = (uint8_t)fx[s];                    // low limbs: NSP rows (a multiple of 8) further down
             }
             fused::fence_proxy_async();
             tc_fence_before();
-            mbar_arrive(bar_p_ready(b2));
+            mbar_arrive(bar_p_ready(bf));
             TC5_MARK(i, 4);
-            done = i + 1;
-            if (i >= 1 && !epilogue(i - 1)) { alive = false; break; }
+            if (last_done >= 0 && !epilogue(last_done)) { alive = false; break; }
+            last_done = i;
             TC5_MARK(i, 5);
 #pragma unroll
             for (int s = 0; s < NSG; ++s) f_prev[s] = f_cur[s];
         }
-        if (alive && done == my_n && my_n >= 1) alive = epilogue(my_n - 1);
+        if (alive && last_done >= 0) alive = epilogue(last_done);
 
         TC5_CTA_MARK(4);
-        // ---- denominators: sum the per-key partial sums over the 128 threads
-        float *lred = reinterpret_cast<float *>(xch);
+        // ---- denominators: sum the per-key partial sums over the group's 128 threads
+        float *lred = reinterpret_cast<float *>(xch);        // [NSP][4] sums, then [NSP][4] references (element 0)
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
@@ -703,38 +718,78 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             float mine_l = 0.0f;
 #pragma unroll
             for (int s = 0; s < NSG; ++s) mine_l = lane == s ? lsum[s] : mine_l;
-            if (lane < NSG) lred[(s0 + lane) * 4 + wq] = mine_l;
-            if (lane < NSG && wq == 0) lred[(NSP + s0 + lane) * 4] = r_lane;
+            if (lane < NSG) lred[lane * 4 + wq] = mine_l;
+            if (lane < NSG && wq == 0) lred[(NSP + lane) * 4] = r_lane;
         }
-        asm volatile("bar.sync %0, 128;\n" ::"r"(1 + grp) : "memory");     // the four warps of this group
-        // ---- outputs: this thread owns dim kr of every slot
-        float lfin[NSG];
+        if constexpr (NG == 1) {
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");                 // the four softmax warps
+        } else {
+            // Every group has seen its last O^T, so every MMA of the CTA has completed and every tile has
+            // landed: the tile stages are free to carry the other groups' output sums to group 0.
+            asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
+            float *mrg = reinterpret_cast<float *>(sm);                       // [NG-1][NS][128 dims]
+            if (grp > 0) {
 #pragma unroll
-        for (int s = 0; s < NSG; ++s) {
-            const float4 l4 = *reinterpret_cast<const float4 *>(lred + (s0 + s) * 4);
-            lfin[s] = (l4.x + l4.y) + (l4.z + l4.w);
+                for (int s = 0; s < NSG; ++s) mrg[((grp - 1) * NS + s) * HD + kr] = acc[s];
+            }
+            asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
         }
-        const int nvalid = min(NS, p.S * p.kvg - rg * NS);
-        float *pbase = p.partial + ((size_t)split * p.grows) * (HD + 2) + kr;
+        if (grp == 0) {
+            // ---- outputs: this thread owns dim kr of every slot
+            float lfin[NSG], rfin[NSG];
 #pragma unroll
-        for (int s = 0; s < NSG; ++s) {
-            if (s0 + s < nvalid) {
-                const int idx = rg * NS + s0 + s;
-                const int r = fused::div_kvg(p, idx);
-                const int hrow = r * p.nh + kvh * p.kvg + (idx - r * p.kvg);          // row within the batch element
-                if (p.write_partial) {
-                    float *pr = pbase + (size_t)(b * p.S * p.nh + hrow) * (HD + 2);
-                    pr[0] = acc[s];
-                    if (kr == 0) {
-                        const float rs = lred[(NSP + s0 + s) * 4];
-                        pr[HD] = p.export_nat ? rs * LN2 : rs;
-                        pr[HD + 1] = lfin[s];
+            for (int s = 0; s < NSG; ++s) {
+                const float4 l4 = *reinterpret_cast<const float4 *>(lred + s * 4);
+                lfin[s] = (l4.x + l4.y) + (l4.z + l4.w);
+                rfin[s] = lred[(NSP + s) * 4];
+            }
+            if constexpr (NG > 1) {
+                // merge the groups: common reference = the largest, sums rescaled by 2^(own - common)
+#pragma unroll
+                for (int s = 0; s < NSG; ++s) {
+                    float rg_[NG], lg_[NG];
+                    rg_[0] = rfin[s]; lg_[0] = lfin[s];
+                    float rmax = rfin[s];
+#pragma unroll
+                    for (int gg = 1; gg < NG; ++gg) {
+                        const float *lo = reinterpret_cast<const float *>(xch_all + gg * 2 * NSP * 4);
+                        const float4 l4 = *reinterpret_cast<const float4 *>(lo + s * 4);
+                        lg_[gg] = (l4.x + l4.y) + (l4.z + l4.w);
+                        rg_[gg] = lo[(NSP + s) * 4];
+                        rmax = fmaxf(rmax, rg_[gg]);
                     }
-                } else {
-                    const float v = lfin[s] > 0.0f ? acc[s] / lfin[s] : 0.0f;
-                    const long oi = b * p.out_batch_stride + (long)hrow * HD + kr;
-                    if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
-                    else reinterpret_cast<float *>(p.out)[oi] = v;
+                    const float *mrg = reinterpret_cast<const float *>(sm);
+                    float a = acc[s] * ex2f(rg_[0] - rmax), l = lg_[0] * ex2f(rg_[0] - rmax);
+#pragma unroll
+                    for (int gg = 1; gg < NG; ++gg) {
+                        const float w = ex2f(rg_[gg] - rmax);            // a group without tiles has sums 0 and the initial reference
+                        a = fmaf(mrg[((gg - 1) * NS + s) * HD + kr], w, a);
+                        l = fmaf(lg_[gg], w, l);
+                    }
+                    acc[s] = a; lfin[s] = l; rfin[s] = rmax;
+                }
+            }
+            const int nvalid = min(NS, p.S * p.kvg - rg * NS);
+            float *pbase = p.partial + ((size_t)split * p.grows) * (HD + 2) + kr;
+#pragma unroll
+            for (int s = 0; s < NSG; ++s) {
+                if (s < nvalid) {
+                    const int idx = rg * NS + s;
+                    const int r = fused::div_kvg(p, idx);
+                    const int hrow = r * p.nh + kvh * p.kvg + (idx - r * p.kvg);          // row within the batch element
+                    if (p.write_partial) {
+                        float *pr = pbase + (size_t)(b * p.S * p.nh + hrow) * (HD + 2);
+                        pr[0] = acc[s];
+                        if (kr == 0) {
+                            pr[HD] = p.export_nat ? rfin[s] * LN2 : rfin[s];
+                            pr[HD + 1] = lfin[s];
+                        }
+                    } else {
+                        const float v = lfin[s] > 0.0f ? acc[s] / lfin[s] : 0.0f;
+                        const long oi = b * p.out_batch_stride + (long)hrow * HD + kr;
+                        if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
+                        else reinterpret_cast<float *>(p.out)[oi] = v;
+                    }
                 }
             }
         }
@@ -744,7 +799,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     TC5_CTA_MARK(5);
     tc_fence_before();
     __syncthreads();
-    if (warp == NSW) tmem_dealloc(tmem_base, TMEM_COLS);
+    if (warp == NSW) tmem_dealloc(tmem_base, C::TMEM_COLS);
     TC5_CTA_MARK(6);
     fused::merge_splits_in_kernel<NS, HD, NTHREADS, 8>(p, sm, b, kvh, rg);
     TC5_CTA_MARK(7);
