@@ -578,7 +578,7 @@ extern "C" __attribute__((visibility("default"))) int nomos_debug_merge(unsigned
     return (int)cudaMemcpyFromSymbol(host_out, fused::g_merge_tl, sizeof(unsigned long long) * 320 * 8);
 }
 extern "C" __attribute__((visibility("default"))) int nomos_debug_tc5_cta(unsigned long long *host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, tc5::g_tc5_cta, sizeof(unsigned long long) * 320 * 8);
+    return (int)cudaMemcpyFromSymbol(host_out, tc5::g_tc5_cta, sizeof(unsigned long long) * 320 * 16);
 }
 extern "C" __attribute__((visibility("default"))) int nomos_debug_tc5_timeline(unsigned long long *host_out) {
     return (int)cudaMemcpyFromSymbol(host_out, tc5::g_tc5_tl, sizeof(unsigned long long) * 320 * 40 * 6);

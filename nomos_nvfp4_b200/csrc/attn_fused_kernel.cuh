@@ -336,13 +336,12 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
         __syncthreads();
         MERGE_MARK(5);
     };
-    auto emit = [&](int sl, int d, float o) {
+    auto emit_ml = [&](int sl, int d, float o, float mstar, float lstar) {
         const long grow = grow_of(sl);
-        const float lstar = s_lstar[sl];
         if (p.partial_export) {
             p.partial_export[(size_t)grow * (HD + 2) + d] = o;
             if (d == 0) {
-                p.partial_export[(size_t)grow * (HD + 2) + HD] = lstar > 0.0f ? s_mstar[sl] * LN2 : 0.0f;
+                p.partial_export[(size_t)grow * (HD + 2) + HD] = lstar > 0.0f ? mstar * LN2 : 0.0f;
                 p.partial_export[(size_t)grow * (HD + 2) + HD + 1] = lstar;
             }
         } else {
@@ -354,29 +353,47 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
             else reinterpret_cast<float *>(p.out)[oi] = v;
         }
     };
-    // Small merges (the common decode case): every thread owns one (row, dim) and requests its
-    // G partial outputs BEFORE the (m, l) staging barrier, so both sets of L2 loads are in flight
-    // together (one round trip instead of two).
-    constexpr int GFAST = 32;
-    if ((G <= GFAST) && (nrows * HD <= NTHR)) {
-        float pre[GFAST];
-        const bool mine = (int)threadIdx.x < nrows * HD;
-        const int sl = mine ? threadIdx.x / HD : 0, d = mine ? threadIdx.x - sl * HD : 0;
-        if (mine) {
-            const float *base = p.partial + (size_t)grow_of(sl) * (HD + 2) + d;
+    auto emit = [&](int sl, int d, float o) { emit_ml(sl, d, o, s_mstar[sl], s_lstar[sl]); };
+    // Small merges (the common decode case): every thread owns one (row, dim) and does the whole merge
+    // of that element by itself -- its row's (m, l) of every split (the same addresses for the 128
+    // threads of a row) and its own partial outputs are all requested at once, one round trip to L2, and
+    // the weights are worked out redundantly per thread: no staging, no barrier.  The capacity (unrolled
+    // loads; clamped instead of predicated so that they batch) follows the number of splits.
+    if (G <= 32 && nrows * HD <= NTHR) {
+        auto fast = [&](auto cap_tag) {
+            constexpr int GC = decltype(cap_tag)::value;
+            if ((int)threadIdx.x >= nrows * HD) return;
+            const int sl = threadIdx.x / HD, d = threadIdx.x - sl * HD;
+            const float *base = p.partial + (size_t)grow_of(sl) * (HD + 2);
+            float2 ml[GC];
+            float o[GC];
 #pragma unroll
-            for (int i = 0; i < GFAST; ++i) pre[i] = __ldcg(base + (size_t)min(i, G - 1) * rstride);   // unconditional: batches freely
-        }
-        stage_weights();
-        if (mine) {
-            float o0 = 0.0f, o1 = 0.0f;
-#pragma unroll
-            for (int k = 0; k < GFAST; k += 2) {
-                if (k < G) o0 = fmaf(ms[sl * G + k], pre[k], o0);
-                if (k + 1 < G) o1 = fmaf(ms[sl * G + k + 1], pre[k + 1], o1);
+            for (int i = 0; i < GC; ++i) {
+                const float *row = base + (size_t)min(i, G - 1) * rstride;
+                ml[i] = __ldcg(reinterpret_cast<const float2 *>(row + HD));
+                o[i] = __ldcg(row + d);
             }
-            emit(sl, d, o0 + o1);
-        }
+            float m = -CUDART_INF_F;
+#pragma unroll
+            for (int i = 0; i < GC; ++i) {
+                ml[i].x = (i < G && ml[i].y > 0.0f) ? ml[i].x : -CUDART_INF_F;    // a split that saw no key, or a clamped repeat
+                m = fmaxf(m, ml[i].x);
+            }
+            if (m == -CUDART_INF_F) m = 0.0f;            // no split saw a key for this row: weights are all 0
+            float l = 0.0f, a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < GC; ++i) {
+                const float w = ex2f(ml[i].x - m);
+                l = fmaf(w, ml[i].y, l);
+                if (i & 1) a1 = fmaf(w, o[i], a1); else a0 = fmaf(w, o[i], a0);
+            }
+            emit_ml(sl, d, a0 + a1, m, l);
+        };
+        if (G <= 8) fast(std::integral_constant<int, 8>{});
+        else if (G <= 16) fast(std::integral_constant<int, 16>{});
+        else if (G <= 24) fast(std::integral_constant<int, 24>{});
+        else fast(std::integral_constant<int, 32>{});
+        MERGE_MARK(6);
         return;
     }
     // General case: a thread takes EL pairs of dims at a time (partial rows are 8-byte aligned) and

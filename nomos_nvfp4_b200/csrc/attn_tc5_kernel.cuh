@@ -63,7 +63,7 @@ __device__ unsigned long long g_tc5_tl[320][40][6];
         const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);         \
         if ((threadIdx.x & 127) == 0 && threadIdx.x < 32 * Cfg<NS>::NSW && cta_ < 320 && (tile) < 40) g_tc5_tl[cta_][tile][slot] = fused::gtime(); \
     } while (0)
-__device__ unsigned long long g_tc5_cta[320][8];
+__device__ unsigned long long g_tc5_cta[320][16];
 #define TC5_CTA_MARK(slot)                                                                       \
     do {                                                                                         \
         const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);         \
@@ -93,11 +93,11 @@ struct Cfg {
     static constexpr int OFF_Q = OFF_SCALES + NSTG * 2 * SCALE_BYTES;
     static constexpr int OFF_P = OFF_Q + QP_BYTES;
     static constexpr int OFF_XCH = OFF_P + NB * QP_BYTES;            // [NG][2][NSP][4] warp maxima
-    static constexpr int OFF_SLOT = OFF_XCH + NG * 2 * NSP * 16;     // qscale[NSP], lo[NSP], hi[NSP]
+    static constexpr int OFF_SLOT = OFF_XCH + NG * 2 * NSP * 16;     // -, lo[NSP], hi[NSP]: first and one-past-last key of each slot
     static constexpr int OFF_SLOTC = (OFF_SLOT + NSP * 12 + 15) / 16 * 16;   // per softmax warp: NSP x (max, weight, alpha, -)
     static constexpr int OFF_BAR = OFF_SLOTC + NSW * NSP * 16;
     static constexpr int NBAR = 2 * NSTG + 4 * NB + 1 + 2 * NG + 2;  // full, empty; s_ready, p_ready, o_ready, o_free (per buffer); q_ready; xch (x2 per group); patched (x2)
-    static constexpr int MRG_BYTES = (NG - 1) * NS * HD * 4;         // output sums of groups 1.. for the merge, over the tile stages
+    static constexpr int MRG_BYTES = NG * (2 * NS * HD + 2 * NSP) * 4;   // the groups' sums for their merge, over the tile stages
     static_assert(MRG_BYTES <= NSTG * 2 * TILE_BYTES, "group merge scratch reuses the tile stages");
     static constexpr int OFF_MISC = (OFF_BAR + NBAR * 8 + 15) / 16 * 16;   // tmem base, abort flag
     static constexpr int OFF_NEW = OFF_MISC + 16;                    // quantize-on-write: [NEW_MAX][K, V] rows of codes + scale
@@ -164,20 +164,20 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, int (&r)[COUNT]) {
                      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                      : "r"(taddr));
 }
-// int -> float for |x| < 2^22 on the integer and FMA pipes (the conversion instruction shares the
-// quarter-rate unit with ex2, the busiest one here): x + 1.5 * 2^23 read as a float, minus 1.5 * 2^23.
-__device__ __forceinline__ float i2f_small(int x) { return __int_as_float(x + 0x4B400000) - 12582912.0f; }
-__device__ __forceinline__ int redux_max(int v) {
-    int r;
-    asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;\n" : "=r"(r) : "r"(v));
+// hi * 2^SH + lo as a float, |hi|, |lo| < 2^22.  int -> float on the integer and FMA pipes: x + 1.5 * 2^23
+// read as a float, minus 1.5 * 2^23 (the conversion instruction itself measured much slower here: it shares
+// the quarter-rate unit with ex2).
+template <int SH>
+__device__ __forceinline__ float limbs2f(int hi, int lo) {
+    const float fh = __int_as_float(hi + 0x4B400000) - 12582912.0f, fl = __int_as_float(lo + 0x4B400000) - 12582912.0f;
+    return fmaf(fh, (float)(1 << SH), fl);
+}
+// Warp-wide maximum of a float in one instruction (sm_100a).
+__device__ __forceinline__ float redux_max(float v) {
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;\n" : "=f"(r) : "f"(v));
     return r;
 }
-// float <-> int with the same ordering (an involution)
-__device__ __forceinline__ int f2ord(float f) {
-    const int k = __float_as_int(f);
-    return k ^ ((k >> 31) & 0x7fffffff);
-}
-__device__ __forceinline__ float ord2f(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
 
 // Shared-memory matrix descriptors (sm_100 format: version 1, 128-byte swizzle, 8-row groups of
 // 128-byte rows 1024 bytes apart).  K-major: rows = M/N index, the 128 bytes of a row = K.
@@ -252,10 +252,9 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t sm_u32 = smem_u32(sm);
-    float *slot_qscale = reinterpret_cast<float *>(sm + C::OFF_SLOT);
     int *slot_lo = reinterpret_cast<int *>(sm + C::OFF_SLOT + NSP * 4);
     int *slot_hi = reinterpret_cast<int *>(sm + C::OFF_SLOT + NSP * 8);
-    int *xch_all = reinterpret_cast<int *>(sm + C::OFF_XCH);                // [NG][2][NSP][4]
+    float *xch_all = reinterpret_cast<float *>(sm + C::OFF_XCH);            // [NG][2][NSP][4]
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(sm + C::OFF_MISC);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(sm + C::OFF_MISC + 4);
     const uint32_t bar0 = sm_u32 + C::OFF_BAR;
@@ -421,7 +420,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         TC5_CTA_MARK(2);
         const int grp = warp >> 2, wq = warp & 3;        // group, and the TMEM lane quarter this warp may read
         const int kr = threadIdx.x & 127;                // key row of S^T, output dim of O^T
-        int *xch = xch_all + grp * 2 * NSP * 4;          // this group's [2][NSP][4] exchange area
+        float *xch = xch_all + grp * 2 * NSP * 4;        // this group's [2][NSP][4] exchange area
         const uint32_t tmem_lane = tmem_base + ((uint32_t)(32 * wq) << 16);
         auto wait_warp = [&](uint32_t bar, uint32_t parity) {
             return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag, p.fault)) != 0;
@@ -440,9 +439,12 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 vs_next = __ldg(gvs + row);
             }
         };
+#ifndef NOMOS_TC5_LATE_SCALES
         fetch_scales(grp);                               // in flight while the query rows are prepared
+#endif
         // ---- query rows -> two int8 limbs each (15-bit fixed point: q ~= sq * (128 hi + lo)).
         // A warp prepares slots warp, warp+4, ...; all their loads are issued before the first use.
+        TC5_CTA_MARK(11);
         constexpr int QPW = (NSP + NSW - 1) / NSW;
         uint32_t qraw[QPW][HD / 32];
         {
@@ -491,6 +493,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 }
             }
         }
+        TC5_CTA_MARK(8);
         float qx[QPW][HD / 32];
 #pragma unroll
         for (int k = 0; k < QPW; ++k) {
@@ -499,6 +502,26 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
 #pragma unroll
             for (int i = 0; i < HD / 32; ++i) qx[k][i] = valid ? __uint_as_float(qraw[k][i]) : 0.0f;
         }
+        TC5_CTA_MARK(12);
+        // One fixed-point scale for all the CTA's query rows (the largest magnitude of any of them): every
+        // logit then has the same absolute resolution, that of the largest row, which is what the softmax
+        // sees, and the loop multiplies by one scale instead of one per slot.
+        float qamax = 0.0f;
+#pragma unroll
+        for (int k = 0; k < QPW; ++k)
+#pragma unroll
+            for (int i = 0; i < HD / 32; ++i) qamax = fmaxf(qamax, fabsf(qx[k][i]));
+        qamax = warp_max(qamax);
+        {
+            float *qmax_w = reinterpret_cast<float *>(sm + C::OFF_SLOTC);     // per-warp maxima; the area is reused from the first tile on
+            if (lane == 0) qmax_w[warp] = qamax;
+            asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
+#pragma unroll
+            for (int w = 0; w < NSW; ++w) qamax = fmaxf(qamax, qmax_w[w]);
+        }
+        const float sq = qamax > 0.0f ? qamax * (1.0f / (float)Q_FIX_MAX) : 1.0f;
+        const float inv = rcpf(sq);
+        const float qscale = sq * p.qk_scale_log2;       // base-2 logit per unit of the integer dot product and of the key's scale
 #pragma unroll
         for (int k = 0; k < QPW; ++k) {
             const int sl = warp + NSW * k;
@@ -506,12 +529,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             const int idx = rg * NS + sl;
             const int r = fused::div_kvg(p, idx);
             const bool valid = sl < NS && r < p.S;
-            float amax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < HD / 32; ++i) amax = fmaxf(amax, fabsf(qx[k][i]));
-            amax = warp_max(amax);
-            const float sq = amax > 0.0f ? amax * (1.0f / (float)Q_FIX_MAX) : 1.0f;
-            const float inv = rcpf(sq);
 #pragma unroll
             for (int i = 0; i < HD / 32; ++i) {
                 int qf = __float2int_rn(qx[k][i] * inv);
@@ -522,12 +539,13 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             }
             if (lane == 0) {
                 const int hi_b = valid ? wg.klen - (p.S - 1 - r) : 0;
-                slot_qscale[sl] = valid ? sq * p.qk_scale_log2 : 0.0f;
                 slot_hi[sl] = hi_b;
                 slot_lo[sl] = (valid && p.window > 0) ? max(0, hi_b - p.window) : 0;
             }
         }
+        TC5_CTA_MARK(9);
         fused::fence_proxy_async();                      // the limbs are read by the tensor core (async proxy)
+        TC5_CTA_MARK(10);
         mbar_arrive(bar_q_ready);
         bool alive = wait_warp(bar_q_ready, 0);          // slot constants of the other warps are visible
         TC5_CTA_MARK(3);
@@ -535,17 +553,18 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         // The loops below are written phase by phase over all slots (loads, then arithmetic, then
         // stores) so that the slots' independent instruction chains overlap: each scheduler of the
         // SM runs a single softmax warp and has nothing else to hide latencies with.
-        float lsum[NSG], acc[NSG], f_prev[NSG];               // over this group's tiles, every slot
+        float lsum[NSG], acc[NSG];                            // over this group's tiles, every slot
         float r_lane = M_INIT;                                // running reference of slot `lane` (lanes < NSG)
+        float fw_lane = 0.0f;                                 // same lane: what a unit of the previous tile's O^T is worth
         float4 *my_consts = reinterpret_cast<float4 *>(sm + C::OFF_SLOTC) + warp * NSP;
         int lo_max = 0, hi_min = 0x7fffffff;
 #pragma unroll
         for (int s = 0; s < NSG; ++s) {
-            lsum[s] = 0.0f; acc[s] = 0.0f; f_prev[s] = 0.0f;
+            lsum[s] = 0.0f; acc[s] = 0.0f;
             if (alive && slot_hi[s] > 0) { lo_max = max(lo_max, slot_lo[s]); hi_min = min(hi_min, slot_hi[s]); }
         }
-        // O^T of tile j: add the exact int32 sums with the tile's weight
-        auto epilogue = [&](int j) -> bool {
+        // O^T of tile j: add the exact int32 sums with the tile's weight fe[slot]
+        auto epilogue = [&](int j, const float (&fe)[NSG]) -> bool {
             const int bf = j % NB;
             if (!wait_warp(bar_o_ready(bf), (j / NB) & 1)) return false;
             tc_fence_after();
@@ -559,13 +578,16 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
 #pragma unroll
             for (int c = 0; c < NCH; ++c)
 #pragma unroll
-                for (int e = 0; e < CH; ++e)      // each limb sum is below 128 * 255 * 127 < 2^22
-                    acc[c * CH + e] = fmaf(fmaf(i2f_small(oh[c][e]), 256.0f, i2f_small(ol[c][e])), f_prev[c * CH + e], acc[c * CH + e]);
+                for (int e = 0; e < CH; ++e)      // each limb sum is below 128 * 255 * 127 < 2^22: the combination fits an int
+                    acc[c * CH + e] = fmaf(limbs2f<8>(oh[c][e], ol[c][e]), fe[c * CH + e], acc[c * CH + e]);
             tc_fence_before();
             mbar_arrive(bar_o_free(bf));
             return true;
         };
 
+#ifdef NOMOS_TC5_LATE_SCALES
+        fetch_scales(grp);
+#endif
         int last_done = -1;                              // this group's last tile whose P was handed to the tensor core
         for (int i = grp; alive && i < my_n; i += NG) {
             const int st = i % NSTG, bf = i % NB;
@@ -612,9 +634,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             }
             const float vs = row_ok ? fmaxf(vs_raw, 5.421011e-20f) : 1.0f;   // floor 2^-64: keeps 1/vs finite
             const float lvs = lg2f(vs), rvs = row_ok ? rcpf(vs) : 0.0f;
-            float qk[NSG];
-#pragma unroll
-            for (int s = 0; s < NSG; ++s) qk[s] = slot_qscale[s] * ks;
+            const float qk = qscale * ks;
             if (!wait_warp(bar_s_ready(bf), (i / NB) & 1)) { alive = false; break; }
             tc_fence_after();
             TC5_MARK(i, 2);
@@ -629,8 +649,8 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             // to the tile's largest, the quantity that goes to the tensor core as 16-bit fixed point
             float u[NSG];
 #pragma unroll
-            for (int s = 0; s < NSG; ++s)         // limb sums are below 128 * 127 * 127 < 2^22
-                u[s] = fmaf(fmaf(i2f_small(sh[s / CH][s % CH]), 128.0f, i2f_small(sl_[s / CH][s % CH])), qk[s], lvs);
+            for (int s = 0; s < NSG; ++s)         // limb sums are below 128 * 127 * 127 < 2^22: the combination fits an int
+                u[s] = fmaf(limbs2f<7>(sh[s / CH][s % CH], sl_[s / CH][s % CH]), qk, lvs);
             if (need_mask) {
 #pragma unroll
                 for (int s = 0; s < NSG; ++s) {
@@ -638,12 +658,12 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                     u[s] = ok ? u[s] : -CUDART_INF_F;
                 }
             }
-            // tile maximum per slot: one warp-wide integer max each, exchanged through shared memory;
+            // tile maximum per slot: one warp-wide max each, exchanged through shared memory;
             // lane s carries slot s's value to a single store
-            int mine = 0;
+            float mine = 0.0f;
 #pragma unroll
             for (int s = 0; s < NSG; ++s) {
-                const int wm = redux_max(f2ord(u[s]));
+                const float wm = redux_max(u[s]);
                 mine = lane == s ? wm : mine;
             }
             if (lane < NSG) xch[(b2 * NSP + lane) * 4 + wq] = mine;
@@ -658,13 +678,16 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             // tile weight 2^d) or it moves to the tile maximum (tile weight 1, alpha = 2^-d).
             bool moved = false;
             if (lane < NSG) {
-                const int4 m4 = *reinterpret_cast<const int4 *>(xch + (b2 * NSP + lane) * 4);
-                const float umax = ord2f(max(max(m4.x, m4.y), max(m4.z, m4.w)));
+                const float4 m4 = *reinterpret_cast<const float4 *>(xch + (b2 * NSP + lane) * 4);
+                const float umax = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w));
                 const float d = umax - r_lane;                           // -inf when every key of the tile is masked
                 moved = d > LAZY_MAX;
                 const float e = ex2f(moved ? -d : d);
                 r_lane = moved ? umax : r_lane;
-                my_consts[lane] = make_float4(umax == -CUDART_INF_F ? 0.0f : umax, moved ? 1.0f : e, moved ? e : 1.0f, 0.0f);
+                const float tw = moved ? 1.0f : e;                      // weight of this tile's sums against the reference
+                const float alpha = moved ? e : 1.0f;                   // what the sums so far are rescaled by
+                my_consts[lane] = make_float4(umax == -CUDART_INF_F ? 0.0f : umax, tw, alpha, fw_lane * alpha);
+                fw_lane = tw * (1.0f / P_FIX);
             }
             const bool any_moved = __any_sync(0xffffffffu, moved);
             __syncwarp();
@@ -672,16 +695,16 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
 #pragma unroll
                 for (int s = 0; s < NSG; ++s) {
                     const float alpha = my_consts[s].z;
-                    lsum[s] *= alpha; acc[s] *= alpha; f_prev[s] *= alpha;
+                    lsum[s] *= alpha; acc[s] *= alpha;
                 }
             }
-            float f_cur[NSG];
+            float fe[NSG];                                               // weight of the previous tile's O^T units
             uint32_t fx[NSG];
 #pragma unroll
             for (int s = 0; s < NSG; ++s) {
-                const float4 c = my_consts[s];                           // (tile max or 0, tile weight, alpha, -)
+                const float4 c = my_consts[s];                           // (tile max or 0, tile weight, alpha, previous tile's unit weight)
                 const float w = ex2f(u[s] - c.x);                        // in [0, 1]
-                f_cur[s] = c.y * (1.0f / P_FIX);
+                fe[s] = c.w;
                 lsum[s] = fmaf(w * c.y, rvs, lsum[s]);                   // 2^(logit - R): the softmax denominator
                 fx[s] = __float_as_uint(fmaf(w, P_FIX, RND_MAGIC));
             }
@@ -699,98 +722,102 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             tc_fence_before();
             mbar_arrive(bar_p_ready(bf));
             TC5_MARK(i, 4);
-            if (last_done >= 0 && !epilogue(last_done)) { alive = false; break; }
+            if (last_done >= 0 && !epilogue(last_done, fe)) { alive = false; break; }
             last_done = i;
             TC5_MARK(i, 5);
-#pragma unroll
-            for (int s = 0; s < NSG; ++s) f_prev[s] = f_cur[s];
         }
-        if (alive && last_done >= 0) alive = epilogue(last_done);
+        if (alive && last_done >= 0) {
+            float fe[NSG];
+            if (lane < NSG) my_consts[lane].w = fw_lane;
+            __syncwarp();
+#pragma unroll
+            for (int s = 0; s < NSG; ++s) fe[s] = my_consts[s].w;
+            alive = epilogue(last_done, fe);
+        }
 
         TC5_CTA_MARK(4);
-        // ---- denominators: sum the per-key partial sums over the group's 128 threads
-        float *lred = reinterpret_cast<float *>(xch);        // [NSP][4] sums, then [NSP][4] references (element 0)
+        const int nvalid = min(NS, p.S * p.kvg - rg * NS);
+        float *pbase = p.partial + ((size_t)split * p.grows) * (HD + 2) + kr;
+        // one slot's row of this thread's dim: the partial (sum, reference, denominator) or the final output
+        auto put_row = [&](int s, float a, float rs, float l) {
+            const int idx = rg * NS + s;
+            const int r = fused::div_kvg(p, idx);
+            const int hrow = r * p.nh + kvh * p.kvg + (idx - r * p.kvg);          // row within the batch element
+            if (p.write_partial) {
+                float *pr = pbase + (size_t)(b * p.S * p.nh + hrow) * (HD + 2);
+                pr[0] = a;
+                if (kr == 0) {
+                    pr[HD] = p.export_nat ? rs * LN2 : rs;
+                    pr[HD + 1] = l;
+                }
+            } else {
+                const float v = l > 0.0f ? a / l : 0.0f;
+                const long oi = b * p.out_batch_stride + (long)hrow * HD + kr;
+                if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
+                else reinterpret_cast<float *>(p.out)[oi] = v;
+            }
+        };
+        if constexpr (NG == 1) {
+            // ---- denominators: sum the per-key partial sums over the 128 threads
+            float *lred = xch;                               // [NSP][4] sums, then [NSP][4] references (element 0)
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
+            for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-            for (int s = 0; s < NSG; ++s) lsum[s] += __shfl_xor_sync(0xffffffffu, lsum[s], o);
-        {
+                for (int s = 0; s < NSG; ++s) lsum[s] += __shfl_xor_sync(0xffffffffu, lsum[s], o);
             float mine_l = 0.0f;
 #pragma unroll
             for (int s = 0; s < NSG; ++s) mine_l = lane == s ? lsum[s] : mine_l;
             if (lane < NSG) lred[lane * 4 + wq] = mine_l;
             if (lane < NSG && wq == 0) lred[(NSP + lane) * 4] = r_lane;
-        }
-        if constexpr (NG == 1) {
             asm volatile("bar.sync 1, 128;\n" ::: "memory");                 // the four softmax warps
-        } else {
-            // Every group has seen its last O^T, so every MMA of the CTA has completed and every tile has
-            // landed: the tile stages are free to carry the other groups' output sums to group 0.
-            asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
-            float *mrg = reinterpret_cast<float *>(sm);                       // [NG-1][NS][128 dims]
-            if (grp > 0) {
-#pragma unroll
-                for (int s = 0; s < NSG; ++s) mrg[((grp - 1) * NS + s) * HD + kr] = acc[s];
-            }
-            asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
-        }
-        if (grp == 0) {
             // ---- outputs: this thread owns dim kr of every slot
-            float lfin[NSG], rfin[NSG];
-#pragma unroll
-            for (int s = 0; s < NSG; ++s) {
-                const float4 l4 = *reinterpret_cast<const float4 *>(lred + s * 4);
-                lfin[s] = (l4.x + l4.y) + (l4.z + l4.w);
-                rfin[s] = lred[(NSP + s) * 4];
-            }
-            if constexpr (NG > 1) {
-                // merge the groups: common reference = the largest, sums rescaled by 2^(own - common)
-#pragma unroll
-                for (int s = 0; s < NSG; ++s) {
-                    float rg_[NG], lg_[NG];
-                    rg_[0] = rfin[s]; lg_[0] = lfin[s];
-                    float rmax = rfin[s];
-#pragma unroll
-                    for (int gg = 1; gg < NG; ++gg) {
-                        const float *lo = reinterpret_cast<const float *>(xch_all + gg * 2 * NSP * 4);
-                        const float4 l4 = *reinterpret_cast<const float4 *>(lo + s * 4);
-                        lg_[gg] = (l4.x + l4.y) + (l4.z + l4.w);
-                        rg_[gg] = lo[(NSP + s) * 4];
-                        rmax = fmaxf(rmax, rg_[gg]);
-                    }
-                    const float *mrg = reinterpret_cast<const float *>(sm);
-                    float a = acc[s] * ex2f(rg_[0] - rmax), l = lg_[0] * ex2f(rg_[0] - rmax);
-#pragma unroll
-                    for (int gg = 1; gg < NG; ++gg) {
-                        const float w = ex2f(rg_[gg] - rmax);            // a group without tiles has sums 0 and the initial reference
-                        a = fmaf(mrg[((gg - 1) * NS + s) * HD + kr], w, a);
-                        l = fmaf(lg_[gg], w, l);
-                    }
-                    acc[s] = a; lfin[s] = l; rfin[s] = rmax;
-                }
-            }
-            const int nvalid = min(NS, p.S * p.kvg - rg * NS);
-            float *pbase = p.partial + ((size_t)split * p.grows) * (HD + 2) + kr;
 #pragma unroll
             for (int s = 0; s < NSG; ++s) {
                 if (s < nvalid) {
-                    const int idx = rg * NS + s;
-                    const int r = fused::div_kvg(p, idx);
-                    const int hrow = r * p.nh + kvh * p.kvg + (idx - r * p.kvg);          // row within the batch element
-                    if (p.write_partial) {
-                        float *pr = pbase + (size_t)(b * p.S * p.nh + hrow) * (HD + 2);
-                        pr[0] = acc[s];
-                        if (kr == 0) {
-                            pr[HD] = p.export_nat ? rfin[s] * LN2 : rfin[s];
-                            pr[HD + 1] = lfin[s];
-                        }
-                    } else {
-                        const float v = lfin[s] > 0.0f ? acc[s] / lfin[s] : 0.0f;
-                        const long oi = b * p.out_batch_stride + (long)hrow * HD + kr;
-                        if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
-                        else reinterpret_cast<float *>(p.out)[oi] = v;
-                    }
+                    const float4 l4 = *reinterpret_cast<const float4 *>(lred + s * 4);
+                    put_row(s, acc[s], lred[(NSP + s) * 4], (l4.x + l4.y) + (l4.z + l4.w));
                 }
+            }
+        } else {
+            // Every group has seen its last O^T, so every MMA of the CTA has completed and every tile has
+            // landed: the tile stages are free to carry the groups' sums.  What follows runs once per CTA,
+            // so it is written as short rolled loops over shared memory rather than unrolled over the slots.
+            asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
+            float *mrg = reinterpret_cast<float *>(sm);                       // [NG][NS][128 dims] output sums
+            float *lsm = mrg + NG * NS * HD;                                  // [NG][NS][128 keys] denominators per key row
+            float *rsm = lsm + NG * NS * KT;                                  // [NG][NSP] running references
+            float *lfs = rsm + NG * NSP;                                      // [NG][NSP] denominators
+#pragma unroll
+            for (int s = 0; s < NSG; ++s) {
+                mrg[(grp * NS + s) * HD + kr] = acc[s];
+                lsm[(grp * NS + s) * KT + kr] = lsum[s];
+            }
+            if (wq == 0 && lane < NSG) rsm[grp * NSP + lane] = r_lane;
+            asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
+#pragma unroll 1
+            for (int idx = warp; idx < NG * NS; idx += NSW) {                 // a warp per (group, slot)
+                const float4 v = reinterpret_cast<const float4 *>(lsm + idx * KT)[lane];
+                float t = (v.x + v.y) + (v.z + v.w);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+                if (lane == 0) lfs[(idx / NS) * NSP + idx % NS] = t;
+            }
+            asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
+            // merge the groups per slot (common reference = the largest, sums rescaled by 2^(own - common));
+            // thread (group, dim) takes slots group, group + NG, ...
+#pragma unroll 1
+            for (int s = grp; s < nvalid; s += NG) {
+                float rmax = rsm[s];
+#pragma unroll
+                for (int gg = 1; gg < NG; ++gg) rmax = fmaxf(rmax, rsm[gg * NSP + s]);
+                float a = 0.0f, l = 0.0f;
+#pragma unroll
+                for (int gg = 0; gg < NG; ++gg) {
+                    const float w = ex2f(rsm[gg * NSP + s] - rmax);      // a group without tiles has sums 0 and the initial reference
+                    a = fmaf(mrg[(gg * NS + s) * HD + kr], w, a);
+                    l = fmaf(lfs[gg * NSP + s], w, l);
+                }
+                put_row(s, a, rmax, l);
             }
         }
     }
