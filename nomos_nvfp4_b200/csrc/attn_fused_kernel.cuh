@@ -238,6 +238,89 @@ __device__ __forceinline__ unsigned long long arrive_add(unsigned long long *ctr
     return old;
 }
 
+// Small merges (the common decode case: at most 32 splits, one (row, dim) element per thread).  Thread
+// `tid` does the whole merge of its element by itself: its row's (m, l) of every split (the same
+// addresses for the 128 threads of a row) and its own partial outputs are all requested at once, one
+// round trip to L2, and the weights are worked out redundantly per thread -- no staging, no barrier.
+// The capacity (unrolled loads; clamped instead of predicated so that they batch) follows the number of
+// splits.  Deliberately not inlined: one copy of the code per head dim serves every kernel, and a warp
+// that has nothing left to do (the TMA producer once its last tile is requested) runs it once with
+// `dry` set -- same loads, nothing stored -- so that the CTA which arrives last, and whose exit the
+// whole grid waits for, does not fetch this code cold from device memory.
+struct SmallMergeArgs {
+    const float *partial;      // split 0 of the workspace partials
+    float *partial_export;     // merged (o, m, l) rows instead of normalised outputs, or nullptr
+    uint8_t *out;
+    long rstride;              // floats between two splits
+    long out_batch_stride;
+    int G, S, nh, kvg, out_type;
+    unsigned int kvg_magic;
+    int b, kvh, first, nrows;  // batch element, KV head, first slot of the row group, its valid slots
+};
+template <int HD>
+__device__ __noinline__ void merge_small(const SmallMergeArgs a, int tid, bool dry) {
+    if (tid >= a.nrows * HD) return;
+    const int sl = tid / HD, d = tid - sl * HD;
+    const int idx = a.first + sl;
+    const int r = a.kvg_magic ? (int)__umulhi((unsigned)idx, a.kvg_magic) : idx;
+    const int hrow = r * a.nh + a.kvh * a.kvg + (idx - r * a.kvg);
+    const long grow = (long)a.b * a.S * a.nh + hrow;
+    const float *base = a.partial + (size_t)grow * (HD + 2);
+    const int G = a.G;
+    auto run = [&](auto cap_tag) {
+        constexpr int GC = decltype(cap_tag)::value;
+        float2 ml[GC];
+        float o[GC];
+#pragma unroll
+        for (int i = 0; i < GC; ++i) {
+            const float *row = base + (size_t)min(i, G - 1) * a.rstride;
+            ml[i] = __ldcg(reinterpret_cast<const float2 *>(row + HD));
+            o[i] = __ldcg(row + d);
+        }
+        float m = -CUDART_INF_F;
+#pragma unroll
+        for (int i = 0; i < GC; ++i) {
+            ml[i].x = (i < G && ml[i].y > 0.0f) ? ml[i].x : -CUDART_INF_F;    // a split that saw no key, or a clamped repeat
+            m = fmaxf(m, ml[i].x);
+        }
+        if (m == -CUDART_INF_F) m = 0.0f;            // no split saw a key for this row: weights are all 0
+        float l = 0.0f, a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < GC; ++i) {
+            const float w = ex2f(ml[i].x - m);
+            l = fmaf(w, ml[i].y, l);
+            if (i & 1) a1 = fmaf(w, o[i], a1); else a0 = fmaf(w, o[i], a0);
+        }
+        const float acc = a0 + a1;
+        if (dry) return;
+        if (a.partial_export) {
+            a.partial_export[(size_t)grow * (HD + 2) + d] = acc;
+            if (d == 0) {
+                a.partial_export[(size_t)grow * (HD + 2) + HD] = l > 0.0f ? m * LN2 : 0.0f;
+                a.partial_export[(size_t)grow * (HD + 2) + HD + 1] = l;
+            }
+        } else {
+            const float v = l > 0.0f ? acc / l : 0.0f;
+            const long oi = a.b * a.out_batch_stride + (long)hrow * HD + d;
+            if (a.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(a.out)[oi] = __float2bfloat16_rn(v);
+            else reinterpret_cast<float *>(a.out)[oi] = v;
+        }
+    };
+    if (G <= 8) run(std::integral_constant<int, 8>{});
+    else if (G <= 16) run(std::integral_constant<int, 16>{});
+    else if (G <= 24) run(std::integral_constant<int, 24>{});
+    else run(std::integral_constant<int, 32>{});
+}
+// Whether a unit's merge takes the small path, and its arguments.
+template <int NSLOT, int HD, int NTHR>
+__device__ __forceinline__ bool small_merge_args(const KParams &p, int b, int kvh, int rg, SmallMergeArgs &a) {
+    a.partial = p.partial; a.partial_export = p.partial_export; a.out = p.out;
+    a.rstride = (long)p.grows * (HD + 2); a.out_batch_stride = p.out_batch_stride;
+    a.G = p.splits; a.S = p.S; a.nh = p.nh; a.kvg = p.kvg; a.out_type = p.out_type; a.kvg_magic = p.kvg_magic;
+    a.b = b; a.kvh = kvh; a.first = rg * NSLOT; a.nrows = min(NSLOT, p.S * p.kvg - rg * NSLOT);
+    return p.counters != nullptr && p.splits <= 32 && a.nrows * HD <= NTHR;
+}
+
 // In-kernel merge across the splits of one (batch, KV head, row group) unit, called by every
 // thread of a CTA after its partial (o, m, l) rows are stored.  The last CTA of the unit to
 // arrive merges the unit's rows; the others return.  `scratch` is shared memory the CTA no
@@ -354,47 +437,13 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
         }
     };
     auto emit = [&](int sl, int d, float o) { emit_ml(sl, d, o, s_mstar[sl], s_lstar[sl]); };
-    // Small merges (the common decode case): every thread owns one (row, dim) and does the whole merge
-    // of that element by itself -- its row's (m, l) of every split (the same addresses for the 128
-    // threads of a row) and its own partial outputs are all requested at once, one round trip to L2, and
-    // the weights are worked out redundantly per thread: no staging, no barrier.  The capacity (unrolled
-    // loads; clamped instead of predicated so that they batch) follows the number of splits.
-    if (G <= 32 && nrows * HD <= NTHR) {
-        auto fast = [&](auto cap_tag) {
-            constexpr int GC = decltype(cap_tag)::value;
-            if ((int)threadIdx.x >= nrows * HD) return;
-            const int sl = threadIdx.x / HD, d = threadIdx.x - sl * HD;
-            const float *base = p.partial + (size_t)grow_of(sl) * (HD + 2);
-            float2 ml[GC];
-            float o[GC];
-#pragma unroll
-            for (int i = 0; i < GC; ++i) {
-                const float *row = base + (size_t)min(i, G - 1) * rstride;
-                ml[i] = __ldcg(reinterpret_cast<const float2 *>(row + HD));
-                o[i] = __ldcg(row + d);
-            }
-            float m = -CUDART_INF_F;
-#pragma unroll
-            for (int i = 0; i < GC; ++i) {
-                ml[i].x = (i < G && ml[i].y > 0.0f) ? ml[i].x : -CUDART_INF_F;    // a split that saw no key, or a clamped repeat
-                m = fmaxf(m, ml[i].x);
-            }
-            if (m == -CUDART_INF_F) m = 0.0f;            // no split saw a key for this row: weights are all 0
-            float l = 0.0f, a0 = 0.0f, a1 = 0.0f;
-#pragma unroll
-            for (int i = 0; i < GC; ++i) {
-                const float w = ex2f(ml[i].x - m);
-                l = fmaf(w, ml[i].y, l);
-                if (i & 1) a1 = fmaf(w, o[i], a1); else a0 = fmaf(w, o[i], a0);
-            }
-            emit_ml(sl, d, a0 + a1, m, l);
-        };
-        if (G <= 8) fast(std::integral_constant<int, 8>{});
-        else if (G <= 16) fast(std::integral_constant<int, 16>{});
-        else if (G <= 24) fast(std::integral_constant<int, 24>{});
-        else fast(std::integral_constant<int, 32>{});
-        MERGE_MARK(6);
-        return;
+    {
+        SmallMergeArgs sa;
+        if (small_merge_args<NSLOT, HD, NTHR>(p, b, kvh, rg, sa)) {
+            merge_small<HD>(sa, threadIdx.x, false);
+            MERGE_MARK(6);
+            return;
+        }
     }
     // General case: a thread takes EL pairs of dims at a time (partial rows are 8-byte aligned) and
     // up to GBW splits of each, every load of such a batch issued before the first use (clamped
