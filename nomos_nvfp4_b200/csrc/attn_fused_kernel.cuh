@@ -311,6 +311,71 @@ __device__ __noinline__ void merge_small(const SmallMergeArgs a, int tid, bool d
     else if (G <= 24) run(std::integral_constant<int, 24>{});
     else run(std::integral_constant<int, 32>{});
 }
+// Merges of more elements than threads with at most 12 splits (speculative verify: 18 rows x 128 dims,
+// 9 splits).  Same idea as merge_small, no staging and no barrier: a thread takes two pairs of dims
+// (partial rows are 8-byte aligned) per round and requests all their splits' outputs together with
+// their rows' (m, l) of every split -- up to 48 independent 8-byte loads, one round trip to L2 -- then
+// works out the weights itself (four pairs per round when there are at most four splits).  A short rolled loop over the rounds, so its code is fetched once.
+template <int HD, int GC>
+__device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int nthr) {
+    constexpr int EL = GC <= 4 ? 4 : 2, HP = HD / 2;
+    const int total = a.nrows * HP, G = a.G;
+#pragma unroll 1
+    for (int e0 = tid; e0 < total; e0 += EL * nthr) {
+        const float *base[EL];
+        long grow[EL];
+        int hrow[EL], dd[EL];
+        float2 v[EL][GC], ml[EL][GC];
+#pragma unroll
+        for (int j = 0; j < EL; ++j) {
+            const int e = min(e0 + j * nthr, total - 1);
+            const int sl = e / HP;
+            dd[j] = 2 * (e - sl * HP);
+            const int idx = a.first + sl;
+            const int r = a.kvg_magic ? (int)__umulhi((unsigned)idx, a.kvg_magic) : idx;
+            hrow[j] = r * a.nh + a.kvh * a.kvg + (idx - r * a.kvg);
+            grow[j] = (long)a.b * a.S * a.nh + hrow[j];
+            base[j] = a.partial + (size_t)grow[j] * (HD + 2);
+        }
+#pragma unroll
+        for (int j = 0; j < EL; ++j)
+#pragma unroll
+            for (int k = 0; k < GC; ++k) {
+                const float *row = base[j] + (size_t)min(k, G - 1) * a.rstride;
+                v[j][k] = __ldcg(reinterpret_cast<const float2 *>(row + dd[j]));
+                ml[j][k] = __ldcg(reinterpret_cast<const float2 *>(row + HD));
+            }
+#pragma unroll
+        for (int j = 0; j < EL; ++j) {
+            float m = -CUDART_INF_F;
+#pragma unroll
+            for (int k = 0; k < GC; ++k) {
+                ml[j][k].x = (k < G && ml[j][k].y > 0.0f) ? ml[j][k].x : -CUDART_INF_F;
+                m = fmaxf(m, ml[j][k].x);
+            }
+            if (m == -CUDART_INF_F) m = 0.0f;
+            float l = 0.0f, ox = 0.0f, oy = 0.0f;
+#pragma unroll
+            for (int k = 0; k < GC; ++k) {
+                const float w = ex2f(ml[j][k].x - m);
+                l = fmaf(w, ml[j][k].y, l);
+                ox = fmaf(w, v[j][k].x, ox);
+                oy = fmaf(w, v[j][k].y, oy);
+            }
+            if (e0 + j * nthr >= total) continue;
+            if (a.partial_export) {
+                float *pe = a.partial_export + (size_t)grow[j] * (HD + 2);
+                *reinterpret_cast<float2 *>(pe + dd[j]) = make_float2(ox, oy);
+                if (dd[j] == 0) *reinterpret_cast<float2 *>(pe + HD) = make_float2(l > 0.0f ? m * LN2 : 0.0f, l);
+            } else {
+                const float vx = l > 0.0f ? ox / l : 0.0f, vy = l > 0.0f ? oy / l : 0.0f;
+                const long oi = a.b * a.out_batch_stride + (long)hrow[j] * HD + dd[j];
+                if (a.out_type == ET_BF16) *reinterpret_cast<__nv_bfloat162 *>(reinterpret_cast<__nv_bfloat16 *>(a.out) + oi) = __floats2bfloat162_rn(vx, vy);
+                else *reinterpret_cast<float2 *>(reinterpret_cast<float *>(a.out) + oi) = make_float2(vx, vy);
+            }
+        }
+    }
+}
 // Whether a unit's merge takes the small path, and its arguments.
 template <int NSLOT, int HD, int NTHR>
 __device__ __forceinline__ bool small_merge_args(const KParams &p, int b, int kvh, int rg, SmallMergeArgs &a) {
@@ -441,6 +506,16 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
         SmallMergeArgs sa;
         if (small_merge_args<NSLOT, HD, NTHR>(p, b, kvh, rg, sa)) {
             merge_small<HD>(sa, threadIdx.x, false);
+            MERGE_MARK(6);
+            return;
+        }
+        // outputs and exported partials must take 8-byte stores for the paired path
+        const bool al8 = ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.partial_export)) & 7) == 0 &&
+                         (p.out_batch_stride & 3) == 0;
+        if (p.splits <= 12 && al8) {
+            if (p.splits <= 4) merge_medium<HD, 4>(sa, threadIdx.x, NTHR);
+            else if (p.splits <= 8) merge_medium<HD, 8>(sa, threadIdx.x, NTHR);
+            else merge_medium<HD, 12>(sa, threadIdx.x, NTHR);
             MERGE_MARK(6);
             return;
         }
