@@ -326,9 +326,9 @@ static int launch_tc5(cudaStream_t st, const AttnArgs &a, bool q, long *ws);
 static bool tc5_eligible(const AttnArgs &a) {
     if (a.kv_fmt != KV_I8 || a.l_hd != 128 || a.no_tma || a.no_tcgen05) return false;
     if (a.new_k != nullptr && (a.n_new > tc5::NEW_MAX || a.cache_hd != a.l_hd)) return false;
-    // more than eight query rows per KV head (verify) currently run faster on the mma.sync kernel
-    static const bool wide = [] { const char *e = std::getenv("NOMOS_ATTN_TCGEN05_VERIFY"); return e && e[0] == '1'; }();
-    if (a.S * a.kvg > 8 && !wide && !a.tcgen05_always) return false;
+    // one CTA serves at most 24 query rows per KV head (9 verify tokens x 2 group heads = 18); more go to the
+    // mma.sync kernel, which cuts them into row groups
+    if (a.S * a.kvg > 24 && !a.tcgen05_always) return false;
     if (tc5_disabled_by_env() || tma_disabled_by_env() || encode_tiled_fn() == nullptr) return false;
     const auto al16 = [](const void *x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
     if (!al16(a.k_cache) || !al16(a.v_cache) || a.cache_hd % 16 != 0) return false;

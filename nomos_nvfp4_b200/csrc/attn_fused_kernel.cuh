@@ -312,20 +312,23 @@ __device__ __noinline__ void merge_small(const SmallMergeArgs a, int tid, bool d
     else run(std::integral_constant<int, 32>{});
 }
 // Merges of more elements than threads with at most 12 splits (speculative verify: 18 rows x 128 dims,
-// 9 splits).  Same idea as merge_small, no staging and no barrier: a thread takes two pairs of dims
-// (partial rows are 8-byte aligned) per round and requests all their splits' outputs together with
-// their rows' (m, l) of every split -- up to 48 independent 8-byte loads, one round trip to L2 -- then
-// works out the weights itself (four pairs per round when there are at most four splits).  A short rolled loop over the rounds, so its code is fetched once.
+// 9 splits).  Same idea as merge_small, no staging and no barrier.  A thread takes four pairs of dims
+// per round (partial rows are 8-byte aligned) and requests all their splits' outputs at once; the 32
+// lanes of a warp hold consecutive pairs of ONE row (a row is HD/2 pairs, a multiple of 32), so the
+// row's weights are worked out across the warp -- lane k fetches (m, l) of split k, two warp reductions
+// give the reference and the denominator -- and handed round by shuffle.  Up to 52 independent loads per
+// thread, one round trip to L2 per round; verify needs a single round.
 template <int HD, int GC>
-__device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int nthr) {
-    constexpr int EL = GC <= 4 ? 4 : 2, HP = HD / 2;
-    const int total = a.nrows * HP, G = a.G;
+__device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int nthr, bool dry) {
+    constexpr int EL = 4, HP = HD / 2;
+    static_assert(HP % 32 == 0 && GC <= 32, "a warp's pairs share a row; one lane per split");
+    const int total = a.nrows * HP, G = a.G, lane = tid & 31;
 #pragma unroll 1
     for (int e0 = tid; e0 < total; e0 += EL * nthr) {
         const float *base[EL];
         long grow[EL];
         int hrow[EL], dd[EL];
-        float2 v[EL][GC], ml[EL][GC];
+        float2 v[EL][GC], ml[EL];
 #pragma unroll
         for (int j = 0; j < EL; ++j) {
             const int e = min(e0 + j * nthr, total - 1);
@@ -338,31 +341,31 @@ __device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int n
             base[j] = a.partial + (size_t)grow[j] * (HD + 2);
         }
 #pragma unroll
-        for (int j = 0; j < EL; ++j)
+        for (int j = 0; j < EL; ++j) {
+            ml[j] = __ldcg(reinterpret_cast<const float2 *>(base[j] + (size_t)min(lane, G - 1) * a.rstride + HD));
 #pragma unroll
-            for (int k = 0; k < GC; ++k) {
-                const float *row = base[j] + (size_t)min(k, G - 1) * a.rstride;
-                v[j][k] = __ldcg(reinterpret_cast<const float2 *>(row + dd[j]));
-                ml[j][k] = __ldcg(reinterpret_cast<const float2 *>(row + HD));
-            }
+            for (int k = 0; k < GC; ++k)
+                v[j][k] = __ldcg(reinterpret_cast<const float2 *>(base[j] + (size_t)min(k, G - 1) * a.rstride + dd[j]));
+        }
+        MERGE_MARK(4);
 #pragma unroll
         for (int j = 0; j < EL; ++j) {
-            float m = -CUDART_INF_F;
-#pragma unroll
-            for (int k = 0; k < GC; ++k) {
-                ml[j][k].x = (k < G && ml[j][k].y > 0.0f) ? ml[j][k].x : -CUDART_INF_F;
-                m = fmaxf(m, ml[j][k].x);
-            }
+            const float mk = (lane < G && ml[j].y > 0.0f) ? ml[j].x : -CUDART_INF_F;   // a split that saw no key, or no split
+            float m = warp_max(mk);
             if (m == -CUDART_INF_F) m = 0.0f;
-            float l = 0.0f, ox = 0.0f, oy = 0.0f;
+            const float wk = ex2f(mk - m);
+            float l = wk * ml[j].y;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+            if (j == 0) MERGE_MARK(5);
+            float ox = 0.0f, oy = 0.0f;
 #pragma unroll
             for (int k = 0; k < GC; ++k) {
-                const float w = ex2f(ml[j][k].x - m);
-                l = fmaf(w, ml[j][k].y, l);
+                const float w = __shfl_sync(0xffffffffu, wk, k);          // 0 from lanes past the last split
                 ox = fmaf(w, v[j][k].x, ox);
                 oy = fmaf(w, v[j][k].y, oy);
             }
-            if (e0 + j * nthr >= total) continue;
+            if (e0 + j * nthr >= total || dry) continue;
             if (a.partial_export) {
                 float *pe = a.partial_export + (size_t)grow[j] * (HD + 2);
                 *reinterpret_cast<float2 *>(pe + dd[j]) = make_float2(ox, oy);
@@ -374,9 +377,10 @@ __device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int n
                 else *reinterpret_cast<float2 *>(reinterpret_cast<float *>(a.out) + oi) = make_float2(vx, vy);
             }
         }
+        if (dry) break;                                  // one round is enough to have fetched the code
     }
 }
-// Whether a unit's merge takes the small path, and its arguments.
+// A unit's merge arguments; true when it takes the small path.
 template <int NSLOT, int HD, int NTHR>
 __device__ __forceinline__ bool small_merge_args(const KParams &p, int b, int kvh, int rg, SmallMergeArgs &a) {
     a.partial = p.partial; a.partial_export = p.partial_export; a.out = p.out;
@@ -384,6 +388,26 @@ __device__ __forceinline__ bool small_merge_args(const KParams &p, int b, int kv
     a.G = p.splits; a.S = p.S; a.nh = p.nh; a.kvg = p.kvg; a.out_type = p.out_type; a.kvg_magic = p.kvg_magic;
     a.b = b; a.kvh = kvh; a.first = rg * NSLOT; a.nrows = min(NSLOT, p.S * p.kvg - rg * NSLOT);
     return p.counters != nullptr && p.splits <= 32 && a.nrows * HD <= NTHR;
+}
+
+// The barrier-free merges: runs the one that fits the unit, if any.  With `dry` (a warp that has nothing
+// left to do, `nthr` = 32) the same code runs once on whatever the partials hold and stores nothing.
+template <int NSLOT, int HD, int NTHR>
+__device__ __forceinline__ bool merge_without_staging(const KParams &p, int b, int kvh, int rg, int tid, int nthr, bool dry) {
+    SmallMergeArgs sa;
+    if (small_merge_args<NSLOT, HD, NTHR>(p, b, kvh, rg, sa)) {
+        merge_small<HD>(sa, tid, dry);
+        return true;
+    }
+    if (p.counters == nullptr) return false;
+    // outputs and exported partials must take 8-byte stores for the paired path
+    const bool al8 = ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.partial_export)) & 7) == 0 &&
+                     (p.out_batch_stride & 3) == 0;
+    if (p.splits > 12 || !al8) return false;
+    if (p.splits <= 4) merge_medium<HD, 4>(sa, tid, nthr, dry);
+    else if (p.splits <= 8) merge_medium<HD, 8>(sa, tid, nthr, dry);
+    else merge_medium<HD, 12>(sa, tid, nthr, dry);
+    return true;
 }
 
 // In-kernel merge across the splits of one (batch, KV head, row group) unit, called by every
@@ -502,23 +526,9 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
         }
     };
     auto emit = [&](int sl, int d, float o) { emit_ml(sl, d, o, s_mstar[sl], s_lstar[sl]); };
-    {
-        SmallMergeArgs sa;
-        if (small_merge_args<NSLOT, HD, NTHR>(p, b, kvh, rg, sa)) {
-            merge_small<HD>(sa, threadIdx.x, false);
-            MERGE_MARK(6);
-            return;
-        }
-        // outputs and exported partials must take 8-byte stores for the paired path
-        const bool al8 = ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.partial_export)) & 7) == 0 &&
-                         (p.out_batch_stride & 3) == 0;
-        if (p.splits <= 12 && al8) {
-            if (p.splits <= 4) merge_medium<HD, 4>(sa, threadIdx.x, NTHR);
-            else if (p.splits <= 8) merge_medium<HD, 8>(sa, threadIdx.x, NTHR);
-            else merge_medium<HD, 12>(sa, threadIdx.x, NTHR);
-            MERGE_MARK(6);
-            return;
-        }
+    if (merge_without_staging<NSLOT, HD, NTHR>(p, b, kvh, rg, threadIdx.x, NTHR, false)) {
+        MERGE_MARK(6);
+        return;
     }
     // General case: a thread takes EL pairs of dims at a time (partial rows are 8-byte aligned) and
     // up to GBW splits of each, every load of such a batch issued before the first use (clamped

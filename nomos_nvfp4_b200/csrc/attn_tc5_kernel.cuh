@@ -238,6 +238,72 @@ struct WindowGeo {
     }
 };
 
+// The end of a CTA that ran several softmax groups: their sums, staged in shared memory (layout below),
+// are merged per slot and stored.  These two steps run once per CTA, straight after its last tile, on the
+// path the whole grid waits for, so they are kept out of line: the TMA warp runs them once with `dry` set
+// (one round on whatever the stage memory holds, nothing written) when its last tile is requested, and the
+// real call does not fetch its code cold from device memory.
+//   mrg [NG][NS][128 dims] output sums | lsm [NG][NS][128 keys] denominators per key row |
+//   rsm [NG][NSP] running references   | lfs [NG][NSP] denominators
+struct TailArgs {
+    float *partial;            // this split's partial rows (row 0 of the batch), or nullptr: write normalised outputs
+    uint8_t *out;
+    long out_batch_stride;
+    int export_nat, out_type, S, nh, kvg;
+    unsigned int kvg_magic;
+    int b, kvh, slot0, nvalid; // batch element, KV head, first slot of the row group, its valid slots
+};
+template <int NS, int NSP, int NG, int NSW>
+__device__ __noinline__ void group_denominators(float *stage, int warp, int lane, bool dry) {
+    const float *lsm = stage + NG * NS * HD;
+    float *lfs = stage + NG * NS * HD + NG * NS * KT + NG * NSP;
+#pragma unroll 1
+    for (int idx = warp; idx < NG * NS; idx += NSW) {                 // a warp per (group, slot)
+        const float4 v = reinterpret_cast<const float4 *>(lsm + idx * KT)[lane];
+        float t = (v.x + v.y) + (v.z + v.w);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (dry) break;
+        if (lane == 0) lfs[(idx / NS) * NSP + idx % NS] = t;
+    }
+}
+template <int NS, int NSP, int NG>
+__device__ __noinline__ void group_outputs(const TailArgs a, const float *stage, int grp, int kr, bool dry) {
+    const float *mrg = stage, *rsm = stage + NG * NS * HD + NG * NS * KT, *lfs = rsm + NG * NSP;
+    // common reference = the largest, sums rescaled by 2^(own - common); thread (group, dim) takes slots
+    // group, group + NG, ...
+#pragma unroll 1
+    for (int s = grp; s < a.nvalid; s += NG) {
+        float rmax = rsm[s];
+#pragma unroll
+        for (int gg = 1; gg < NG; ++gg) rmax = fmaxf(rmax, rsm[gg * NSP + s]);
+        float o = 0.0f, l = 0.0f;
+#pragma unroll
+        for (int gg = 0; gg < NG; ++gg) {
+            const float w = ex2f(rsm[gg * NSP + s] - rmax);          // a group without tiles has sums 0 and the initial reference
+            o = fmaf(mrg[(gg * NS + s) * HD + kr], w, o);
+            l = fmaf(lfs[gg * NSP + s], w, l);
+        }
+        if (dry) break;
+        const int idx = a.slot0 + s;
+        const int r = a.kvg_magic ? (int)__umulhi((unsigned)idx, a.kvg_magic) : idx;
+        const int hrow = r * a.nh + a.kvh * a.kvg + (idx - r * a.kvg);          // row within the batch element
+        if (a.partial) {
+            float *pr = a.partial + (size_t)(a.b * a.S * a.nh + hrow) * (HD + 2) + kr;
+            pr[0] = o;
+            if (kr == 0) {
+                pr[HD] = a.export_nat ? rmax * LN2 : rmax;
+                pr[HD + 1] = l;
+            }
+        } else {
+            const float v = l > 0.0f ? o / l : 0.0f;
+            const long oi = a.b * a.out_batch_stride + (long)hrow * HD + kr;
+            if (a.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(a.out)[oi] = __float2bfloat16_rn(v);
+            else reinterpret_cast<float *>(a.out)[oi] = v;
+        }
+    }
+}
+
 template <int NS>
 __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     attn_tc5_kernel(const KParams p, const __grid_constant__ TmaMaps4 tm) {
@@ -352,6 +418,13 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         __syncthreads();
     }
 
+    TailArgs tail_args;
+    tail_args.partial = p.write_partial ? p.partial + ((size_t)split * p.grows) * (HD + 2) : nullptr;
+    tail_args.out = p.out; tail_args.out_batch_stride = p.out_batch_stride;
+    tail_args.export_nat = p.export_nat; tail_args.out_type = p.out_type; tail_args.S = p.S; tail_args.nh = p.nh;
+    tail_args.kvg = p.kvg; tail_args.kvg_magic = p.kvg_magic;
+    tail_args.b = b; tail_args.kvh = kvh; tail_args.slot0 = rg * NS; tail_args.nvalid = min(NS, p.S * p.kvg - rg * NS);
+
     if (warp == NSW) {
         // =========================================================== TMA producer
         if (lane == 0) {
@@ -377,11 +450,12 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             if (!waited) { fused::pdl_wait(); fused::pdl_launch_dependents(); }
         }
         __syncwarp();
-        {
-            // every tile is requested: warm the code of the split merge (see merge_small)
-            fused::SmallMergeArgs sa;
-            if (fused::small_merge_args<NS, HD, NTHREADS>(p, b, kvh, rg, sa)) fused::merge_small<HD>(sa, lane, true);
+        // every tile is requested: warm the code of the CTA's last steps (see group_outputs, merge_small)
+        if constexpr (NG > 1) {
+            group_denominators<NS, NSP, NG, NSW>(reinterpret_cast<float *>(sm), 0, lane, true);
+            group_outputs<NS, NSP, NG>(tail_args, reinterpret_cast<const float *>(sm), 0, lane, true);
         }
+        fused::merge_without_staging<NS, HD, NTHREADS>(p, b, kvh, rg, lane, 32, true);
     } else if (warp == NSW + 1) {
         // =========================================================== MMA issuer
         if (lane == 0) {
@@ -453,6 +527,8 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         // (measured: about 3 us less on the verify kernel).  Nothing but shared-memory scratch is written
         // in the first pass.
         float qscale = 0.0f;                             // base-2 logit per unit of the integer dot product and of the key's scale
+        float lsum[NSG], acc[NSG];                       // denominators and output sums over this group's tiles, every slot
+        int lo_max = 0, hi_min = 0x7fffffff;             // keys in [lo_max, hi_min) are visible to every query row
 #pragma unroll 1
         for (int pass = dry_first ? 0 : 1; pass < 2; ++pass) {
             if (pass == 1 && dry_first) {
@@ -561,28 +637,27 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                     slot_lo[sl] = (valid && p.window > 0) ? max(0, hi_b - p.window) : 0;
                 }
             }
-            if (pass == 0) asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");   // scratch is rewritten by the next pass
+            fused::fence_proxy_async();                  // the limbs are read by the tensor core (async proxy)
+            // every softmax warp's slot constants are visible (and the scratch may be rewritten by the next pass)
+            asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
+            lo_max = 0; hi_min = 0x7fffffff;
+#pragma unroll
+            for (int s = 0; s < NSG; ++s) {
+                lsum[s] = 0.0f; acc[s] = 0.0f;
+                if (slot_hi[s] > 0) { lo_max = max(lo_max, slot_lo[s]); hi_min = min(hi_min, slot_hi[s]); }
+            }
         }
-        TC5_CTA_MARK(9);
-        fused::fence_proxy_async();                      // the limbs are read by the tensor core (async proxy)
         TC5_CTA_MARK(10);
-        mbar_arrive(bar_q_ready);
-        bool alive = wait_warp(bar_q_ready, 0);          // slot constants of the other warps are visible
+        mbar_arrive(bar_q_ready);                        // the MMA issuer starts on the first tile
+        bool alive = wait_warp(bar_q_ready, 0);
         TC5_CTA_MARK(3);
 
         // The loops below are written phase by phase over all slots (loads, then arithmetic, then
         // stores) so that the slots' independent instruction chains overlap: each scheduler of the
         // SM runs a single softmax warp and has nothing else to hide latencies with.
-        float lsum[NSG], acc[NSG];                            // over this group's tiles, every slot
         float r_lane = M_INIT;                                // running reference of slot `lane` (lanes < NSG)
         float fw_lane = 0.0f;                                 // same lane: what a unit of the previous tile's O^T is worth
         float4 *my_consts = reinterpret_cast<float4 *>(sm + C::OFF_SLOTC) + warp * NSP;
-        int lo_max = 0, hi_min = 0x7fffffff;
-#pragma unroll
-        for (int s = 0; s < NSG; ++s) {
-            lsum[s] = 0.0f; acc[s] = 0.0f;
-            if (alive && slot_hi[s] > 0) { lo_max = max(lo_max, slot_lo[s]); hi_min = min(hi_min, slot_hi[s]); }
-        }
         // O^T of tile j: add the exact int32 sums with the tile's weight fe[slot]
         auto epilogue = [&](int j, const float (&fe)[NSG]) -> bool {
             const int bf = j % NB;
@@ -811,31 +886,9 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             }
             if (wq == 0 && lane < NSG) rsm[grp * NSP + lane] = r_lane;
             asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
-#pragma unroll 1
-            for (int idx = warp; idx < NG * NS; idx += NSW) {                 // a warp per (group, slot)
-                const float4 v = reinterpret_cast<const float4 *>(lsm + idx * KT)[lane];
-                float t = (v.x + v.y) + (v.z + v.w);
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-                if (lane == 0) lfs[(idx / NS) * NSP + idx % NS] = t;
-            }
+            group_denominators<NS, NSP, NG, NSW>(mrg, warp, lane, false);
             asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
-            // merge the groups per slot (common reference = the largest, sums rescaled by 2^(own - common));
-            // thread (group, dim) takes slots group, group + NG, ...
-#pragma unroll 1
-            for (int s = grp; s < nvalid; s += NG) {
-                float rmax = rsm[s];
-#pragma unroll
-                for (int gg = 1; gg < NG; ++gg) rmax = fmaxf(rmax, rsm[gg * NSP + s]);
-                float a = 0.0f, l = 0.0f;
-#pragma unroll
-                for (int gg = 0; gg < NG; ++gg) {
-                    const float w = ex2f(rsm[gg * NSP + s] - rmax);      // a group without tiles has sums 0 and the initial reference
-                    a = fmaf(mrg[(gg * NS + s) * HD + kr], w, a);
-                    l = fmaf(lfs[gg * NSP + s], w, l);
-                }
-                put_row(s, a, rmax, l);
-            }
+            group_outputs<NS, NSP, NG>(tail_args, mrg, grp, kr, false);
         }
     }
 
