@@ -314,8 +314,9 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
 }
 
 // ------------------------------------------------------------------ tcgen05 path
-// int8 KV, head_dim 128, no fused append: the contraction runs on tcgen05 with accumulators in
-// tensor memory (attn_tc5_kernel.cuh).  Everything else stays on the kernel above.
+// int8 KV, head_dim 128, up to 24 query rows per KV head (decode and verify), with or without fused
+// quantize-on-write: the contraction runs on tcgen05 with accumulators in tensor memory
+// (attn_tc5_kernel.cuh).  Everything else stays on the kernel above.
 static bool tc5_disabled_by_env() {
     static const bool off = [] { const char *e = std::getenv("NOMOS_ATTN_NO_TCGEN05"); return e && e[0] == '1'; }();
     return off;
