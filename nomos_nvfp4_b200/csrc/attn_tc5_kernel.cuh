@@ -93,7 +93,7 @@ struct Cfg {
     static constexpr int OFF_Q = OFF_SCALES + NSTG * 2 * SCALE_BYTES;
     static constexpr int OFF_P = OFF_Q + QP_BYTES;
     static constexpr int OFF_XCH = OFF_P + NB * QP_BYTES;            // [NG][2][NSP][4] warp maxima
-    static constexpr int OFF_SLOT = OFF_XCH + NG * 2 * NSP * 16;     // -, lo[NSP], hi[NSP]: first and one-past-last key of each slot
+    static constexpr int OFF_SLOT = OFF_XCH + NG * 2 * NSP * 16;     // qscale[NSP], lo[NSP], hi[NSP]: query scale, first and one-past-last key of each slot
     static constexpr int OFF_SLOTC = (OFF_SLOT + NSP * 12 + 15) / 16 * 16;   // per softmax warp: NSP x (max, weight, alpha, -)
     static constexpr int OFF_BAR = OFF_SLOTC + NSW * NSP * 16;
     static constexpr int NBAR = 2 * NSTG + 4 * NB + 1 + 2 * NG + 2;  // full, empty; s_ready, p_ready, o_ready, o_free (per buffer); q_ready; xch (x2 per group); patched (x2)
@@ -318,6 +318,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t sm_u32 = smem_u32(sm);
+    float *slot_qscale = reinterpret_cast<float *>(sm + C::OFF_SLOT);      // base-2 logit per unit of the integer dot product and of the key's scale
     int *slot_lo = reinterpret_cast<int *>(sm + C::OFF_SLOT + NSP * 4);
     int *slot_hi = reinterpret_cast<int *>(sm + C::OFF_SLOT + NSP * 8);
     float *xch_all = reinterpret_cast<float *>(sm + C::OFF_XCH);            // [NG][2][NSP][4]
@@ -526,7 +527,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         // idle behind its predecessor, so that the pass that counts, after the wait, is not fetched cold
         // (measured: about 3 us less on the verify kernel).  Nothing but shared-memory scratch is written
         // in the first pass.
-        float qscale = 0.0f;                             // base-2 logit per unit of the integer dot product and of the key's scale
         float lsum[NSG], acc[NSG];                       // denominators and output sums over this group's tiles, every slot
         int lo_max = 0, hi_min = 0x7fffffff;             // keys in [lo_max, hi_min) are visible to every query row
 #pragma unroll 1
@@ -597,25 +597,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 for (int i = 0; i < HD / 32; ++i) qx[k][i] = valid ? __uint_as_float(qraw[k][i]) : 0.0f;
             }
             TC5_CTA_MARK(12);
-            // One fixed-point scale for all the CTA's query rows (the largest magnitude of any of them): every
-            // logit then has the same absolute resolution, that of the largest row, which is what the softmax
-            // sees, and the loop multiplies by one scale instead of one per slot.
-            float qamax = 0.0f;
-    #pragma unroll
-            for (int k = 0; k < QPW; ++k)
-    #pragma unroll
-                for (int i = 0; i < HD / 32; ++i) qamax = fmaxf(qamax, fabsf(qx[k][i]));
-            qamax = warp_max(qamax);
-            {
-                float *qmax_w = reinterpret_cast<float *>(sm + C::OFF_SLOTC);     // per-warp maxima; the area is reused from the first tile on
-                if (lane == 0) qmax_w[warp] = qamax;
-                asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
-    #pragma unroll
-                for (int w = 0; w < NSW; ++w) qamax = fmaxf(qamax, qmax_w[w]);
-            }
-            const float sq = qamax > 0.0f ? qamax * (1.0f / (float)Q_FIX_MAX) : 1.0f;
-            const float inv = rcpf(sq);
-            qscale = sq * p.qk_scale_log2;
     #pragma unroll
             for (int k = 0; k < QPW; ++k) {
                 const int sl = warp + NSW * k;
@@ -623,6 +604,12 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 const int idx = rg * NS + sl;
                 const int r = fused::div_kvg(p, idx);
                 const bool valid = sl < NS && r < p.S;
+                float amax = 0.0f;
+    #pragma unroll
+                for (int i = 0; i < HD / 32; ++i) amax = fmaxf(amax, fabsf(qx[k][i]));
+                amax = warp_max(amax);
+                const float sq = amax > 0.0f ? amax * (1.0f / (float)Q_FIX_MAX) : 1.0f;   // each row its own scale
+                const float inv = rcpf(sq);
     #pragma unroll
                 for (int i = 0; i < HD / 32; ++i) {
                     int qf = __float2int_rn(qx[k][i] * inv);
@@ -633,6 +620,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 }
                 if (lane == 0) {
                     const int hi_b = valid ? wg.klen - (p.S - 1 - r) : 0;
+                    slot_qscale[sl] = valid ? sq * p.qk_scale_log2 : 0.0f;
                     slot_hi[sl] = hi_b;
                     slot_lo[sl] = (valid && p.window > 0) ? max(0, hi_b - p.window) : 0;
                 }
@@ -726,7 +714,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             }
             const float vs = row_ok ? fmaxf(vs_raw, 5.421011e-20f) : 1.0f;   // floor 2^-64: keeps 1/vs finite
             const float lvs = lg2f(vs), rvs = row_ok ? rcpf(vs) : 0.0f;
-            const float qk = qscale * ks;
             if (!wait_warp(bar_s_ready(bf), (i / NB) & 1)) { alive = false; break; }
             tc_fence_after();
             TC5_MARK(i, 2);
@@ -742,7 +729,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             float u[NSG];
 #pragma unroll
             for (int s = 0; s < NSG; ++s)         // limb sums are below 128 * 127 * 127 < 2^22: the combination fits an int
-                u[s] = fmaf(limbs2f<7>(sh[s / CH][s % CH], sl_[s / CH][s % CH]), qk, lvs);
+                u[s] = fmaf(limbs2f<7>(sh[s / CH][s % CH], sl_[s / CH][s % CH]), slot_qscale[s] * ks, lvs);
             if (need_mask) {
 #pragma unroll
                 for (int s = 0; s < NSG; ++s) {

@@ -11,7 +11,7 @@ import pytest
 import torch
 
 from nomos_nvfp4_b200 import ops
-from tests._cases import KVCache, bf16_normal, k_with_outliers
+from tests._cases import KVCache, bf16_normal, k_with_outliers, orc
 from tests._gpu import DEV, bf16_dev, dev, host, within
 
 pytestmark = pytest.mark.gpu
@@ -446,3 +446,48 @@ def test_many_verify_rows(oracle, S, kvg):
     for r in range(S):
         ok, rel = within(got[r], want[r], TOL)
         assert ok, f"row {r}: {rel:.2e} x RMS"
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 5, 8, 9, 12, 13, 17])
+def test_verify_forced_splits_cover_every_merge_path(oracle, splits):
+    """18 query rows per KV head merged from 1..17 splits: no merge, the barrier-free paired merge with
+    capacities 4 / 8 / 12 and the staged merge (more than 12 splits); the tile counts per CTA (and per
+    softmax group of the tcgen05 kernel, which takes tiles in turn) are odd, even and 1."""
+    rng = np.random.default_rng(500 + splits)
+    nh, nkv, hd, S, T0 = 4, 2, 128, 9, 2300
+    T = T0 + S
+    c = build_cache("i8", rng, T, nkv, hd)
+    q = bf16_normal(rng, (S, nh, hd))
+    scale = 1.0 / np.sqrt(128.0)
+    want = exact(oracle, c, q, S=S, klen=T, scale=scale)
+    got, _ = fused(c, q, S=S, klen=T, scale=scale, q_type=ops.BF16, force_splits=splits)
+    for r in range(S):
+        ok, rel = within(got[r], want[r], TOL)
+        assert ok, f"row {r}: {rel:.2e} x RMS"
+    gotb, _ = fused(c, q, S=S, klen=T, scale=scale, q_type=ops.BF16, out_type=ops.BF16, force_splits=splits)
+    # the bf16 store of the same path: the fp32 result rounded once
+    assert np.all(np.abs(gotb - got) <= np.abs(got) * 2.0 ** -8 + 1e-30)
+
+
+@pytest.mark.parametrize("S,big", [(1, 30.0), (9, 30.0), (9, 1e-3), (3, 200.0)])
+def test_query_rows_of_very_different_magnitude(oracle, S, big):
+    """Query rows that share a CTA (the heads of a GQA group, the tokens of a verify step) but differ in
+    magnitude by 30x .. 1000x: every row is quantised with its own fixed-point scale, so each must pass the
+    gate separately, against its own RMS.  The softmax scale keeps the largest rows' logits moderate
+    (standard deviation about 7): beyond that the 15-bit query itself limits any kernel."""
+    rng = np.random.default_rng(int(S * 1000 + big))
+    nh, nkv, hd, T0 = 4, 2, 128, 1500
+    T = T0 + S
+    c = build_cache("i8", rng, T, nkv, hd)
+    q = bf16_normal(rng, (S, nh, hd))
+    q[:, 0::2, :] *= np.float32(big)                          # one head of every GQA pair (and every token of it)
+    if S > 1:
+        q[S // 2, 1, :] *= np.float32(big)                    # and one token of the other head
+    q = orc.bf16_round(q)
+    scale = 0.6 / max(big, 1.0)
+    want = exact(oracle, c, q, S=S, klen=T, scale=scale)
+    got, _ = fused(c, q, S=S, klen=T, scale=scale)
+    for r in range(S):
+        for h in range(nh):
+            ok, rel = within(got[r][h], want[r][h], TOL)
+            assert ok, f"row {r} head {h}: {rel:.2e} x RMS"
