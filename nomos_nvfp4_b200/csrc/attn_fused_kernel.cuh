@@ -112,6 +112,7 @@ struct KParams {
     int max_pages;
     unsigned int kvg_magic;  // ceil(2^32 / kvg), 0 for kvg == 1: idx / kvg = umulhi(idx, kvg_magic)
     int use_tma;             // bit 0: whole tiles come by TMA; bit 1: their scales by bulk copy
+    int dry_pass;            // 1: the whole grid is resident at once, so a CTA may start before its stream predecessor is done
     unsigned int *fault;     // sticky device word: bit 0 = a tile never arrived within the wait limit
 };
 
@@ -243,10 +244,9 @@ __device__ __forceinline__ unsigned long long arrive_add(unsigned long long *ctr
 // addresses for the 128 threads of a row) and its own partial outputs are all requested at once, one
 // round trip to L2, and the weights are worked out redundantly per thread -- no staging, no barrier.
 // The capacity (unrolled loads; clamped instead of predicated so that they batch) follows the number of
-// splits.  Deliberately not inlined: one copy of the code per head dim serves every kernel, and a warp
-// that has nothing left to do (the TMA producer once its last tile is requested) runs it once with
-// `dry` set -- same loads, nothing stored -- so that the CTA which arrives last, and whose exit the
-// whole grid waits for, does not fetch this code cold from device memory.
+// splits.  Not inlined: it runs once, in the one CTA per unit that arrives last.  (Having an idle warp run it
+// ahead of time to warm the instruction caches was tried: the merge itself got no faster -- it waits on
+// L2, not on its code -- and the decode call 1.2 us slower.)
 struct SmallMergeArgs {
     const float *partial;      // split 0 of the workspace partials
     float *partial_export;     // merged (o, m, l) rows instead of normalised outputs, or nullptr
@@ -258,7 +258,7 @@ struct SmallMergeArgs {
     int b, kvh, first, nrows;  // batch element, KV head, first slot of the row group, its valid slots
 };
 template <int HD>
-__device__ __noinline__ void merge_small(const SmallMergeArgs a, int tid, bool dry) {
+__device__ __noinline__ void merge_small(const SmallMergeArgs a, int tid) {
     if (tid >= a.nrows * HD) return;
     const int sl = tid / HD, d = tid - sl * HD;
     const int idx = a.first + sl;
@@ -292,7 +292,6 @@ __device__ __noinline__ void merge_small(const SmallMergeArgs a, int tid, bool d
             if (i & 1) a1 = fmaf(w, o[i], a1); else a0 = fmaf(w, o[i], a0);
         }
         const float acc = a0 + a1;
-        if (dry) return;
         if (a.partial_export) {
             a.partial_export[(size_t)grow * (HD + 2) + d] = acc;
             if (d == 0) {
@@ -319,7 +318,7 @@ __device__ __noinline__ void merge_small(const SmallMergeArgs a, int tid, bool d
 // give the reference and the denominator -- and handed round by shuffle.  Up to 52 independent loads per
 // thread, one round trip to L2 per round; verify needs a single round.
 template <int HD, int GC>
-__device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int nthr, bool dry) {
+__device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int nthr) {
     constexpr int EL = 4, HP = HD / 2;
     static_assert(HP % 32 == 0 && GC <= 32, "a warp's pairs share a row; one lane per split");
     const int total = a.nrows * HP, G = a.G, lane = tid & 31;
@@ -365,7 +364,7 @@ __device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int n
                 ox = fmaf(w, v[j][k].x, ox);
                 oy = fmaf(w, v[j][k].y, oy);
             }
-            if (e0 + j * nthr >= total || dry) continue;
+            if (e0 + j * nthr >= total) continue;
             if (a.partial_export) {
                 float *pe = a.partial_export + (size_t)grow[j] * (HD + 2);
                 *reinterpret_cast<float2 *>(pe + dd[j]) = make_float2(ox, oy);
@@ -377,7 +376,6 @@ __device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int n
                 else *reinterpret_cast<float2 *>(reinterpret_cast<float *>(a.out) + oi) = make_float2(vx, vy);
             }
         }
-        if (dry) break;                                  // one round is enough to have fetched the code
     }
 }
 // A unit's merge arguments; true when it takes the small path.
@@ -390,13 +388,12 @@ __device__ __forceinline__ bool small_merge_args(const KParams &p, int b, int kv
     return p.counters != nullptr && p.splits <= 32 && a.nrows * HD <= NTHR;
 }
 
-// The barrier-free merges: runs the one that fits the unit, if any.  With `dry` (a warp that has nothing
-// left to do, `nthr` = 32) the same code runs once on whatever the partials hold and stores nothing.
+// The barrier-free merges: runs the one that fits the unit, if any.
 template <int NSLOT, int HD, int NTHR>
-__device__ __forceinline__ bool merge_without_staging(const KParams &p, int b, int kvh, int rg, int tid, int nthr, bool dry) {
+__device__ __forceinline__ bool merge_without_staging(const KParams &p, int b, int kvh, int rg, int tid, int nthr) {
     SmallMergeArgs sa;
     if (small_merge_args<NSLOT, HD, NTHR>(p, b, kvh, rg, sa)) {
-        merge_small<HD>(sa, tid, dry);
+        merge_small<HD>(sa, tid);
         return true;
     }
     if (p.counters == nullptr) return false;
@@ -404,9 +401,9 @@ __device__ __forceinline__ bool merge_without_staging(const KParams &p, int b, i
     const bool al8 = ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.partial_export)) & 7) == 0 &&
                      (p.out_batch_stride & 3) == 0;
     if (p.splits > 12 || !al8) return false;
-    if (p.splits <= 4) merge_medium<HD, 4>(sa, tid, nthr, dry);
-    else if (p.splits <= 8) merge_medium<HD, 8>(sa, tid, nthr, dry);
-    else merge_medium<HD, 12>(sa, tid, nthr, dry);
+    if (p.splits <= 4) merge_medium<HD, 4>(sa, tid, nthr);
+    else if (p.splits <= 8) merge_medium<HD, 8>(sa, tid, nthr);
+    else merge_medium<HD, 12>(sa, tid, nthr);
     return true;
 }
 
@@ -526,7 +523,7 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
         }
     };
     auto emit = [&](int sl, int d, float o) { emit_ml(sl, d, o, s_mstar[sl], s_lstar[sl]); };
-    if (merge_without_staging<NSLOT, HD, NTHR>(p, b, kvh, rg, threadIdx.x, NTHR, false)) {
+    if (merge_without_staging<NSLOT, HD, NTHR>(p, b, kvh, rg, threadIdx.x, NTHR)) {
         MERGE_MARK(6);
         return;
     }
@@ -754,34 +751,12 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
     // before that wait, so the pipeline fill overlaps the predecessor's tail.
     int early_n = 0;
     while (early_n < NSTAGE - 1 && early_n < my_count && (my_first + early_n * NWARP + 1) * TILE <= p.early_rows) issue(early_n++);
-    pdl_wait();
-    pdl_launch_dependents();
-    NOMOS_MARK(1);
-
-    // ------------------------------------------------------------ Q prologue
-    // Slot sl of this CTA = local row index rg*NSLOT + sl = (query row r, group head j).
-    // The query loads go out first, then the first cache tiles are requested, so the (tiny) query
-    // is not queued behind megabytes of prefetch and the pipeline fill overlaps its preparation.
-    constexpr int QITER = (C::NSLOT + NWARP - 1) / NWARP;
-    float qx[QITER][HD / 32];
-#pragma unroll
-    for (int qi = 0; qi < QITER; ++qi) {
-        const int sl = warp + qi * NWARP;
-        const int idx = rg * C::NSLOT + sl;
-        const int r = div_kvg(p, idx), j = idx - r * p.kvg;
-        const bool valid = sl < C::NSLOT && r < p.S;
-#pragma unroll
-        for (int i = 0; i < HD / 32; ++i)
-            qx[qi][i] = valid ? load_q(p.q, p.q_type, b * p.q_batch_stride + ((long)r * p.nh + kvh * p.kvg + j) * HD + lane + 32 * i) : 0.0f;
-    }
-    for (int s = early_n; s < NSTAGE - 1; ++s) issue(s);
-
     // ------------------------------------------- fused quantize-on-write of the new keys
     // The newest n_new keys arrive as fp32 rows.  A warp quantises one (row, plane) with the row codec
     // of the append kernels (bit for bit) into its scratch row [codes | scales]; for row group 0 and
     // head-dim slice 0 -- so exactly once per KV head -- it also copies bytes and scales into the
     // ring for later calls.  Returns the block-32 row's cached q8 scale (unused otherwise).
-    auto quantize_new = [&](int i, int kv, uint8_t *scr) {
+    auto quantize_new = [&](int i, int kv, uint8_t *scr, bool store) {
         const float *src = (kv ? p.new_v : p.new_k) + ((size_t)b * p.n_new + i) * p.new_stride + kvh * HD;
         const size_t crow = (size_t)kvh * p.cache_cap + (size_t)((p.new_base_pos + i) % p.cache_cap);
         float q8s = 0.0f;
@@ -794,7 +769,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
             q8s = quant_row_i4_block32(src, HD, scr, reinterpret_cast<__half *>(scr + C::ROWB), lane);
         }
         __syncwarp();
-        if (rg == 0 && dsl == 0) {
+        if (rg == 0 && dsl == 0 && store) {
             uint8_t *g_rows = (kv ? p.v_cache_w : p.k_cache_w) + b * p.kv_batch_stride + crow * row_stride;
             uint8_t *g_sc = (kv ? p.v_scales_w : p.k_scales_w) + b * p.scale_batch_stride;
             // the row, zero-padded to the cache row width like the append kernels do (block-32 rows are never wider)
@@ -816,61 +791,96 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
     const bool early_new = p.new_k != nullptr && p.n_new == 1 && NWARP >= 2 && new_tile >= tile_begin && new_tile < tile_end;
     const int new_owner = early_new ? (new_tile - tile_begin) % NWARP : -1;
     const int new_helper = early_new ? (new_owner + 1) % NWARP : -1;
-    if (warp == new_owner) quantize_new(0, 0, append_scratch + warp * (C::ROWB + 64));
-    if (warp == new_helper) quantize_new(0, 1, append_scratch + warp * (C::ROWB + 64));
 
-    // Each row becomes 15-bit fixed point: q ~= sq * (128*hi + lo), hi/lo int8.
-#pragma unroll
-    for (int qi = 0; qi < QITER; ++qi) {
-        const int sl = warp + qi * NWARP;
-        if (sl >= C::NSLOT) break;
-        const int idx = rg * C::NSLOT + sl;
-        const int r = div_kvg(p, idx);
-        const bool valid = r < p.S;
-        float amax = 0.0f;
-#pragma unroll
-        for (int i = 0; i < HD / 32; ++i) amax = fmaxf(amax, fabsf(qx[qi][i]));
-        amax = warp_max(amax);
-        const float sq = amax > 0.0f ? amax * (1.0f / (float)Q_FIX_MAX) : 1.0f;
-        const float inv = rcpf(sq);
-        int qblk[HD / 32];
-#pragma unroll
-        for (int i = 0; i < HD / 32; ++i) {
-            qblk[i] = 0;
-            int qf = __float2int_rn(qx[qi][i] * inv);
-            qf = max(-Q_FIX_MAX, min(Q_FIX_MAX, qf));
-            const int hi = (qf + 64) >> 7;
-            const int lo = qf - (hi << 7);
-            int pos = lane + 32 * i;
+    // The query preparation (and the early quantisation of a single new row) runs twice.  The first pass
+    // starts before the stream-order wait, on whatever the buffers hold at that moment, and its results are
+    // thrown away (only shared-memory scratch is written): it brings this straight-line code into the
+    // instruction caches while the CTA would otherwise idle behind its predecessor -- every launch streams far
+    // more than L2 holds, so code a CTA runs once is otherwise fetched from device memory.
+#pragma unroll 1
+    // (a grid of several waves would only pay for the first pass; not compiled in for 512-wide heads, where the
+    // pass is long and measured a loss)
+    for (int pass = (HD <= 256 && p.dry_pass) ? 0 : 1; pass < 2; ++pass) {
+        if (pass == 1) {
+            pdl_wait();
+            pdl_launch_dependents();
+            NOMOS_MARK(1);
+        }
+        // ------------------------------------------------------------ Q prologue
+        // Slot sl of this CTA = local row index rg*NSLOT + sl = (query row r, group head j).
+        // The query loads go out first, then the first cache tiles are requested, so the (tiny) query
+        // is not queued behind megabytes of prefetch and the pipeline fill overlaps its preparation.
+        constexpr int QITER = (C::NSLOT + NWARP - 1) / NWARP;
+        float qx[QITER][HD / 32];
+    #pragma unroll
+        for (int qi = 0; qi < QITER; ++qi) {
+            const int sl = warp + qi * NWARP;
+            const int idx = rg * C::NSLOT + sl;
+            const int r = div_kvg(p, idx), j = idx - r * p.kvg;
+            const bool valid = sl < C::NSLOT && r < p.S;
+    #pragma unroll
+            for (int i = 0; i < HD / 32; ++i)
+                qx[qi][i] = valid ? load_q(p.q, p.q_type, b * p.q_batch_stride + ((long)r * p.nh + kvh * p.kvg + j) * HD + lane + 32 * i) : 0.0f;
+        }
+        if (pass == 1)
+            for (int s = early_n; s < NSTAGE - 1; ++s) issue(s);
+        if (warp == new_owner) quantize_new(0, 0, append_scratch + warp * (C::ROWB + 64), pass == 1);
+        if (warp == new_helper) quantize_new(0, 1, append_scratch + warp * (C::ROWB + 64), pass == 1);
+
+        // Each row becomes 15-bit fixed point: q ~= sq * (128*hi + lo), hi/lo int8.
+    #pragma unroll
+        for (int qi = 0; qi < QITER; ++qi) {
+            const int sl = warp + qi * NWARP;
+            if (sl >= C::NSLOT) break;
+            const int idx = rg * C::NSLOT + sl;
+            const int r = div_kvg(p, idx);
+            const bool valid = r < p.S;
+            float amax = 0.0f;
+    #pragma unroll
+            for (int i = 0; i < HD / 32; ++i) amax = fmaxf(amax, fabsf(qx[qi][i]));
+            amax = warp_max(amax);
+            const float sq = amax > 0.0f ? amax * (1.0f / (float)Q_FIX_MAX) : 1.0f;
+            const float inv = rcpf(sq);
+            int qblk[HD / 32];
+    #pragma unroll
+            for (int i = 0; i < HD / 32; ++i) {
+                qblk[i] = 0;
+                int qf = __float2int_rn(qx[qi][i] * inv);
+                qf = max(-Q_FIX_MAX, min(Q_FIX_MAX, qf));
+                const int hi = (qf + 64) >> 7;
+                const int lo = qf - (hi << 7);
+                int pos = lane + 32 * i;
+                if constexpr (FMT != KV_I8) {
+                    // int4 tiles hand element 32b+8t+2j+par of a row to MMA k slot 16*par+4t+j of step b
+                    pos = 32 * i + ((lane & 1) << 4) + ((lane >> 3) << 2) + ((lane >> 1) & 3);
+                    int bs = qf;                                        // sum of the block's fixed-point values
+    #pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
+                    qblk[i] = bs;
+                }
+                // rows are stored with their 16-byte chunks XOR-swizzled by the slot index, so that the
+                // ldmatrix that builds an A fragment (8 slots x one chunk) is free of bank conflicts
+                const int spos = ((((pos >> 4) ^ (sl & 7)) << 4) | (pos & 15));
+                q_limbs[sl * HD + spos] = (int8_t)hi;
+                q_limbs[(C::NSLOT + sl) * HD + spos] = (int8_t)lo;
+            }
             if constexpr (FMT != KV_I8) {
-                // int4 tiles hand element 32b+8t+2j+par of a row to MMA k slot 16*par+4t+j of step b
-                pos = 32 * i + ((lane & 1) << 4) + ((lane >> 3) << 2) + ((lane >> 1) & 3);
-                int bs = qf;                                        // sum of the block's fixed-point values
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
-                qblk[i] = bs;
+                if (lane == 0) {
+                    int tot = 0;
+    #pragma unroll
+                    for (int i = 0; i < HD / 32; ++i) tot += qblk[i];
+    #pragma unroll
+                    for (int i = 0; i < HD / 32; ++i) slot_qsum[sl * C::NBLK + i] = 8 * (FMT == KV_I4 ? tot : qblk[i]);
+                }
             }
-            // rows are stored with their 16-byte chunks XOR-swizzled by the slot index, so that the
-            // ldmatrix that builds an A fragment (8 slots x one chunk) is free of bank conflicts
-            const int spos = ((((pos >> 4) ^ (sl & 7)) << 4) | (pos & 15));
-            q_limbs[sl * HD + spos] = (int8_t)hi;
-            q_limbs[(C::NSLOT + sl) * HD + spos] = (int8_t)lo;
-        }
-        if constexpr (FMT != KV_I8) {
             if (lane == 0) {
-                int tot = 0;
-#pragma unroll
-                for (int i = 0; i < HD / 32; ++i) tot += qblk[i];
-#pragma unroll
-                for (int i = 0; i < HD / 32; ++i) slot_qsum[sl * C::NBLK + i] = 8 * (FMT == KV_I4 ? tot : qblk[i]);
+                const int hi_b = valid ? p.klen - (p.S - 1 - r) : 0;
+                slot_qscale[sl] = valid ? sq * p.qk_scale_log2 : 0.0f;
+                slot_hi[sl] = hi_b;
+                slot_lo[sl] = (valid && p.window > 0) ? max(0, hi_b - p.window) : 0;
             }
         }
-        if (lane == 0) {
-            const int hi_b = valid ? p.klen - (p.S - 1 - r) : 0;
-            slot_qscale[sl] = valid ? sq * p.qk_scale_log2 : 0.0f;
-            slot_hi[sl] = hi_b;
-            slot_lo[sl] = (valid && p.window > 0) ? max(0, hi_b - p.window) : 0;
-        }
+        if (pass == 0) __syncwarp();
     }
     __syncthreads();
 
@@ -971,7 +981,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                     if (wi < tok0 || wi >= tok0 + TILE) continue;
 #pragma unroll
                     for (int kv = 0; kv < 2; ++kv) {
-                        quantize_new(i, kv, scr);
+                        quantize_new(i, kv, scr, true);
                         patch(wi - tok0, kv, scr);
                     }
                 }

@@ -54,6 +54,9 @@ constexpr int MAX_PAGED_TILES = 256;         // paged caches: most tiles (pages)
 #ifndef NOMOS_TC5_NG
 #define NOMOS_TC5_NG 2                       // softmax warp groups (tiles in flight) when a CTA serves more than eight slots
 #endif
+#ifndef NOMOS_TC5_WIDE_FROM
+#define NOMOS_TC5_WIDE_FROM 9                // slots from which a CTA runs several groups, one CTA per SM; below: one group, two CTAs per SM
+#endif
 
 #ifdef NOMOS_TIMELINE
 // Debug builds only: per-CTA, per-tile wall-clock marks (ns) of the softmax role.
@@ -78,10 +81,11 @@ template <int NS>
 struct Cfg {
     static constexpr int NSP = (NS + 7) / 8 * 8;                     // slots padded to the MMA's N granularity
     static constexpr int N = 2 * NSP;
-    static constexpr int NSTG = NS <= 8 ? 3 : 5;                     // 3 stages: two CTAs per SM
-    static constexpr int MIN_CTAS = NS <= 8 ? 2 : 1;
-    static constexpr int NG = NS <= 8 ? 1 : NOMOS_TC5_NG;            // softmax warp groups; group g owns tiles g, g+NG, ...
-    static constexpr int NB = NS <= 8 ? 2 : 4;                       // buffers of S^T, P and O^T (tile i uses buffer i % NB)
+    static constexpr bool WIDE = NS >= NOMOS_TC5_WIDE_FROM;
+    static constexpr int NSTG = WIDE ? 5 : 3;                        // 3 stages: two CTAs per SM
+    static constexpr int MIN_CTAS = WIDE ? 1 : 2;
+    static constexpr int NG = WIDE ? NOMOS_TC5_NG : 1;               // softmax warp groups; group g owns tiles g, g+NG, ...
+    static constexpr int NB = WIDE ? 4 : 2;                          // buffers of S^T, P and O^T (tile i uses buffer i % NB)
     static constexpr int LAG = NG;                                   // the issuer sends PV(i - LAG) after QK(i)
     static constexpr int TMEM_COLS = 128 * NB;                       // S buffers, then O buffers, 64 columns each
     static constexpr int NSW = 4 * NG;                               // softmax warps; then the TMA warp, then the MMA warp
@@ -239,10 +243,7 @@ struct WindowGeo {
 };
 
 // The end of a CTA that ran several softmax groups: their sums, staged in shared memory (layout below),
-// are merged per slot and stored.  These two steps run once per CTA, straight after its last tile, on the
-// path the whole grid waits for, so they are kept out of line: the TMA warp runs them once with `dry` set
-// (one round on whatever the stage memory holds, nothing written) when its last tile is requested, and the
-// real call does not fetch its code cold from device memory.
+// are merged per slot and stored.  Short rolled loops, kept out of line (they run once per CTA).
 //   mrg [NG][NS][128 dims] output sums | lsm [NG][NS][128 keys] denominators per key row |
 //   rsm [NG][NSP] running references   | lfs [NG][NSP] denominators
 struct TailArgs {
@@ -254,7 +255,7 @@ struct TailArgs {
     int b, kvh, slot0, nvalid; // batch element, KV head, first slot of the row group, its valid slots
 };
 template <int NS, int NSP, int NG, int NSW>
-__device__ __noinline__ void group_denominators(float *stage, int warp, int lane, bool dry) {
+__device__ __noinline__ void group_denominators(float *stage, int warp, int lane) {
     const float *lsm = stage + NG * NS * HD;
     float *lfs = stage + NG * NS * HD + NG * NS * KT + NG * NSP;
 #pragma unroll 1
@@ -263,12 +264,11 @@ __device__ __noinline__ void group_denominators(float *stage, int warp, int lane
         float t = (v.x + v.y) + (v.z + v.w);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-        if (dry) break;
         if (lane == 0) lfs[(idx / NS) * NSP + idx % NS] = t;
     }
 }
 template <int NS, int NSP, int NG>
-__device__ __noinline__ void group_outputs(const TailArgs a, const float *stage, int grp, int kr, bool dry) {
+__device__ __noinline__ void group_outputs(const TailArgs a, const float *stage, int grp, int kr) {
     const float *mrg = stage, *rsm = stage + NG * NS * HD + NG * NS * KT, *lfs = rsm + NG * NSP;
     // common reference = the largest, sums rescaled by 2^(own - common); thread (group, dim) takes slots
     // group, group + NG, ...
@@ -284,7 +284,6 @@ __device__ __noinline__ void group_outputs(const TailArgs a, const float *stage,
             o = fmaf(mrg[(gg * NS + s) * HD + kr], w, o);
             l = fmaf(lfs[gg * NSP + s], w, l);
         }
-        if (dry) break;
         const int idx = a.slot0 + s;
         const int r = a.kvg_magic ? (int)__umulhi((unsigned)idx, a.kvg_magic) : idx;
         const int hrow = r * a.nh + a.kvh * a.kvg + (idx - r * a.kvg);          // row within the batch element
@@ -404,7 +403,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     // this grid's own dependents be scheduled.  The producer thread first requests the tiles the
     // caller declared settled, and the softmax warps first run their query preparation once on
     // whatever the query buffer holds (see below); both wait further down.
-    const bool dry_first = !paged && warp < NSW;
+    const bool dry_first = !paged && warp < NSW && p.dry_pass;
     if (!((warp == NSW && lane == 0) || dry_first) || paged) {
         fused::pdl_wait();
         fused::pdl_launch_dependents();
@@ -419,12 +418,15 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         __syncthreads();
     }
 
-    TailArgs tail_args;
-    tail_args.partial = p.write_partial ? p.partial + ((size_t)split * p.grows) * (HD + 2) : nullptr;
-    tail_args.out = p.out; tail_args.out_batch_stride = p.out_batch_stride;
-    tail_args.export_nat = p.export_nat; tail_args.out_type = p.out_type; tail_args.S = p.S; tail_args.nh = p.nh;
-    tail_args.kvg = p.kvg; tail_args.kvg_magic = p.kvg_magic;
-    tail_args.b = b; tail_args.kvh = kvh; tail_args.slot0 = rg * NS; tail_args.nvalid = min(NS, p.S * p.kvg - rg * NS);
+    auto make_tail_args = [&]() {
+        TailArgs t;
+        t.partial = p.write_partial ? p.partial + ((size_t)split * p.grows) * (HD + 2) : nullptr;
+        t.out = p.out; t.out_batch_stride = p.out_batch_stride;
+        t.export_nat = p.export_nat; t.out_type = p.out_type; t.S = p.S; t.nh = p.nh;
+        t.kvg = p.kvg; t.kvg_magic = p.kvg_magic;
+        t.b = b; t.kvh = kvh; t.slot0 = rg * NS; t.nvalid = min(NS, p.S * p.kvg - rg * NS);
+        return t;
+    };
 
     if (warp == NSW) {
         // =========================================================== TMA producer
@@ -451,12 +453,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             if (!waited) { fused::pdl_wait(); fused::pdl_launch_dependents(); }
         }
         __syncwarp();
-        // every tile is requested: warm the code of the CTA's last steps (see group_outputs, merge_small)
-        if constexpr (NG > 1) {
-            group_denominators<NS, NSP, NG, NSW>(reinterpret_cast<float *>(sm), 0, lane, true);
-            group_outputs<NS, NSP, NG>(tail_args, reinterpret_cast<const float *>(sm), 0, lane, true);
-        }
-        fused::merge_without_staging<NS, HD, NTHREADS>(p, b, kvh, rg, lane, 32, true);
     } else if (warp == NSW + 1) {
         // =========================================================== MMA issuer
         if (lane == 0) {
@@ -625,7 +621,9 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                     slot_lo[sl] = (valid && p.window > 0) ? max(0, hi_b - p.window) : 0;
                 }
             }
-            fused::fence_proxy_async();                  // the limbs are read by the tensor core (async proxy)
+            // the limbs are read by the tensor core (async proxy).  Not in the warming pass: with tile copies in
+            // flight the fence takes as long as they do (measured +1 us on the decode call).
+            if (pass == 1) fused::fence_proxy_async();
             // every softmax warp's slot constants are visible (and the scratch may be rewritten by the next pass)
             asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
             lo_max = 0; hi_min = 0x7fffffff;
@@ -873,9 +871,9 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             }
             if (wq == 0 && lane < NSG) rsm[grp * NSP + lane] = r_lane;
             asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
-            group_denominators<NS, NSP, NG, NSW>(mrg, warp, lane, false);
+            group_denominators<NS, NSP, NG, NSW>(mrg, warp, lane);
             asm volatile("bar.sync 1, %0;\n" ::"n"(32 * NSW) : "memory");
-            group_outputs<NS, NSP, NG>(tail_args, mrg, grp, kr, false);
+            group_outputs<NS, NSP, NG>(make_tail_args(), mrg, grp, kr);
         }
     }
 
