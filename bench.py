@@ -283,15 +283,17 @@ def run_ours(args) -> dict:
         zc_s = float(tt.item())
 
     peak, peak_src = measured_peak_gbs()
-    tc5 = os.environ.get("NOMOS_ATTN_NO_TCGEN05", "0") != "1" and os.environ.get("NOMOS_ATTN_NO_TMA", "0") != "1"
-    kernel_name = "attn_tc5_kernel<2> (tcgen05 + TMEM + TMA)" if tc5 else "attn_fused_kernel<int8,128,1> (mma.sync)"
+    tc5 = ops.attn_kernel_choice(layer_args[0]) == 1          # which of the two kernels the library runs for this call
+    kernel_name = ("attn_tc5_kernel<2> (tcgen05 + TMEM + TMA)" if tc5
+                   else "attn_fused_kernel<int8,128,1> (int8 mma.sync + TMA tiles + mbarrier ring)")
     # roofline: algorithmic bytes / average launch duration over the timed region (launches run
     # back to back there, as they do in a decode loop); the event-bracketed single launch is kept too
     achieved = step_bytes_rank / (ms_per_step * 1e-3) / 1e9
     result = {
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": N, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": round(ms_per_step, 6), "us_per_layer": round(ms_per_step * 1000, 3), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "int8 (KV bytes x fixed-point Q / softmax weights on tcgen05 int8 tensor cores, int32 in tensor memory, fp32 running sums)",
+        "scaling": "weak", "vs_baseline": None, "dtype": ("int8 (KV bytes x fixed-point Q / softmax weights on tcgen05 int8 tensor cores, int32 in tensor memory, fp32 running sums)" if tc5
+                                                          else "int8 (KV bytes x fixed-point Q / softmax weights on int8 tensor cores, int32 accumulators, fp32 running sums)"),
         "data": "synthetic",
         "config": {"workload": f"C2 decode layer: {N} seq x 32768 cached keys, 32q/16kv heads x 128, int8 row-scale KV, "
                                f"bf16 Q/out, sharded by KV-head groups ({nkv_l} heads x {seqs} seq per GPU)",

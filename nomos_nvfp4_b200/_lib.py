@@ -80,6 +80,7 @@ PROTOTYPES = {
     "nomos_attn_decode_bf16": (i32, [vp] + [u64] * 7 + [i32] * 7),
     "nomos_attn_prefix_batched_dense": (i32, [vp] + [u64] * 5 + [i32] * 12),
     "nomos_attn_workspace_bytes": (i64, [C.POINTER(AttnArgs)]),
+    "nomos_attn_kernel_choice": (i32, [C.POINTER(AttnArgs)]),
     "nomos_attn_fused": (i32, [vp, C.POINTER(AttnArgs)]),
     "nomos_attn_fused_static_ws": (i32, [vp, C.POINTER(AttnArgs)]),
     "nomos_attn_merge_partials": (i32, [vp, u64, i32, i32, i32, u64, i32]),

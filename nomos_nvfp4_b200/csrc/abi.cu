@@ -414,6 +414,15 @@ NOMOS_EXPORT int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args) {
     return attn_workspace_bytes(a);
 }
 
+NOMOS_EXPORT int32_t nomos_attn_kernel_choice(const nomos_attn_args_t *args) {
+    AttnArgs a;
+    int rc = unpack_args(args, a, "nomos_attn_kernel_choice");
+    if (rc) return rc;
+    if ((rc = check_attn_geometry("nomos_attn_kernel_choice", a.nh, a.nkv, a.l_hd, a.cache_hd, a.kvg))) return rc;
+    if (a.batch <= 0 || a.S <= 0 || a.klen <= 0) { set_error("nomos_attn_kernel_choice: bad batch/S/klen"); return NOMOS_EBADARG; }
+    return attn_kernel_choice(a);
+}
+
 NOMOS_EXPORT int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *args) {
     AttnArgs a;
     int rc = unpack_args(args, a, "nomos_attn_fused");

@@ -530,6 +530,18 @@ static int dispatch_mma(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
     }
 }
 
+// Calls both kernels can serve, decode shapes (up to 8 query rows per KV head).  Measured on B200 with both on
+// one box: the tcgen05 kernel streams faster (batch 8 x 131072 keys 619 vs 641 us, 524288 keys 325 vs 346 us:
+// about 7.0 against 6.6 TB/s), the mma.sync kernel has about 2 us less fixed cost per call (one CTA per SM, half
+// as many partials to merge: 32768 keys 26.9 vs 27.7 us, the two-launch decode step 31.5 vs 32.2 us).  Two
+// straight lines, 8.0 us + bytes / 7.0 TB/s and 5.9 us + bytes / 6.6 TB/s, cross at about 240 MB of cache.
+static bool prefers_mma(const AttnArgs &a) {
+    if (a.tcgen05_always || a.block_table != nullptr || a.S * a.kvg > 8) return false;
+    const int keys = a.window > 0 ? std::min(a.klen, a.window + a.S - 1) : a.klen;
+    const double bytes = (double)a.batch * a.nkv * keys * (2.0 * a.cache_hd + 8.0);
+    return bytes < 240e6;
+}
+
 static int dispatch(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
     if (!tc5_eligible(a)) return dispatch_mma(st, a, q, ws);
     if (q) {
@@ -542,11 +554,14 @@ static int dispatch(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
         *ws = rc1 == NOMOS_OK ? std::max(w_tc, w_mma) : w_mma;
         return NOMOS_OK;
     }
+    if (prefers_mma(a)) return dispatch_mma(st, a, false, nullptr);
     const int rc = launch_tc5(st, a, false, nullptr);
     return rc == 1 ? dispatch_mma(st, a, false, nullptr) : rc;
 }
 
 }  // namespace
+
+int attn_kernel_choice(const AttnArgs &a) { return tc5_eligible(a) && !prefers_mma(a) ? 1 : 0; }
 
 long attn_workspace_bytes(const AttnArgs &a) {
     long ws = 0;

@@ -68,6 +68,7 @@ struct AttnArgs {
 };
 
 long attn_workspace_bytes(const AttnArgs &a);
+int attn_kernel_choice(const AttnArgs &a);     // 1: the tcgen05 kernel would serve the call, 0: the mma.sync kernel
 int launch_attn_fused(cudaStream_t st, const AttnArgs &a);
 long attn_paged_workspace_bytes(const AttnArgs &a);
 int launch_attn_paged(cudaStream_t st, const AttnArgs &a);

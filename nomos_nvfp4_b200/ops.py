@@ -245,6 +245,14 @@ def attn_workspace_bytes(args: AttnArgs) -> int:
     return int(n)
 
 
+def attn_kernel_choice(args: AttnArgs) -> int:
+    """1 when `attn_fused` would run the tcgen05 kernel for these arguments, 0 for the mma.sync kernel."""
+    n = _lib.lib().nomos_attn_kernel_choice(C.byref(args))
+    if n < 0:
+        _check(int(n))
+    return int(n)
+
+
 def attn_fused(stream, args: AttnArgs) -> None:
     """Append (optional) + attention over the packed ring in one call; replaces the
     reference's per-layer append -> window reader -> attention sequence

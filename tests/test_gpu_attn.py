@@ -491,3 +491,22 @@ def test_query_rows_of_very_different_magnitude(oracle, S, big):
         for h in range(nh):
             ok, rel = within(got[r][h], want[r][h], TOL)
             assert ok, f"row {r} head {h}: {rel:.2e} x RMS"
+
+
+def test_kernel_choice_follows_the_cost_model(kernel_path):
+    """nomos_attn_kernel_choice: short decode calls go to the mma.sync kernel, verify and calls streaming more
+    than about 240 MB to the tcgen05 kernel; the flag bits override; int4 caches have one kernel."""
+    def choice(S, klen, batch=1, fmt=ops.KV_I8, flags=0, hd=128):
+        a = ops.make_args(q=0x1000, k_cache=0x10000, v_cache=0x20000, k_scales=0x30000, v_scales=0x40000, out=0x50000,
+                          kv_fmt=fmt, q_type=ops.BF16, out_type=ops.BF16, batch=batch, S=S, nh=32, nkv=16, kvg=2, l_hd=hd,
+                          cache_hd=hd, cache_cap=klen, klen=klen, softmax_scale=0.1, flags=flags)
+        return ops.attn_kernel_choice(a)
+    assert choice(1, 32768) == 0
+    assert choice(1, 32768, flags=ops.TCGEN05_ALWAYS) == 1
+    assert choice(1, 131072) == 1
+    assert choice(1, 131072, flags=ops.NO_TCGEN05) == 0
+    assert choice(1, 131072, batch=8) == 1
+    assert choice(9, 16393) == 1
+    assert choice(9, 16393, flags=ops.NO_TCGEN05) == 0
+    assert choice(1, 32768, fmt=ops.KV_I4B32) == 0
+    assert choice(1, 32768, hd=256) == 0
