@@ -314,8 +314,8 @@ def run_ours(args) -> dict:
     if N == 1:
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the ncu
         # captures summarised in profiles/attn_tc5_int8_hd128_decode_c2.md (138.71 MB + 4.77 MB) and, for the
-        # mma.sync kernel, profiles/attn_fused_int8_hd128_decode_c2.md (138.49 MB + 3.45 MB)
-        result["roofline"]["traffic"] = 143.48e6 if tc5 else 141.94e6
+        # mma.sync kernel, profiles/attn_fused_int8_hd128_decode_c2.md (138.50 MB + 3.50 MB)
+        result["roofline"]["traffic"] = 143.48e6 if tc5 else 142.00e6
 
     if rank == 0 and N == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_reference_leg(sample_heads=16, repeats=4, threads=None)
