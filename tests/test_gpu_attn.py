@@ -21,7 +21,7 @@ SENTINEL = -1.0e30
 
 # Every test that goes through fused() runs three times: on the kernel the library picks, pinned
 # to the mma.sync kernel, and on the tcgen05 kernel wherever it supports the call (int8 KV,
-# head_dim 128, no fused append).
+# head_dim 128, with or without fused append).
 EXTRA_FLAGS = 0
 
 
