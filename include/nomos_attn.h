@@ -62,8 +62,12 @@ const char *nomos_attn_last_error(void);
 /* Device-side fault bits of the current device, accumulated since the last clearing read.
  * The kernels never wait without a limit; a wait that ran out ORs a bit in here and the
  * launch carries on (its output is then undefined).  Bit 0: a tile requested from the cache
- * did not arrive within about two seconds.  Synchronises the device; a health check between
- * steps, not a per-call status.  `clear` != 0 resets the word after reading.
+ * did not arrive within about two seconds (mma.sync kernel).  Bit 1: a hand-off between the
+ * roles of the tcgen05 kernel (copy engine, tensor core, softmax warps) ran out of time.
+ * Bit 2: a peer GPU's partial result did not arrive (nomos_attn_seq_sharded_*).  After a
+ * fault the split workspace of the call may hold arrival counts of the unfinished launch:
+ * zero it (cudaMemsetAsync) before using it again.  Synchronises the device; a health check
+ * between steps, not a per-call status.  `clear` != 0 resets the word after reading.
  * No counterpart in the reference (its kernels have no waits). */
 int32_t nomos_attn_device_faults(uint32_t *out_bits, int32_t clear);
 
@@ -167,12 +171,24 @@ int32_t nomos_attn_decode_multirow_i8(void *stream, uint64_t q_b, uint64_t score
                                       int32_t query_base_pos);
 
 /* attention_prefill_prefix_batched_int8, lib/attention_gpu_int8.mojo:844-887.
- * q_t / attn_t are the reference's transpose scratches (accepted, unused). */
+ * q_t / attn_t are the reference's transpose scratches (accepted, unused).  K / V / scale
+ * pointers may be pre-offset by key_base_pos rows, exactly as the engine passes them on
+ * sliding layers (lib/engine_prefill.mojo:926-941): key t of the arrays is absolute position
+ * key_base_pos + t, row s attends [max(0, q_abs-window+1) - key_base_pos, q_abs - key_base_pos]
+ * clipped to [0, key_len), q_abs = query_base_pos + s. */
 int32_t nomos_attn_prefix_batched_i8(void *stream, uint64_t q_b, uint64_t q_t, uint64_t scores, uint64_t attn_t,
                                      uint64_t attn_b, uint64_t k_i8, uint64_t v_i8, uint64_t k_scale, uint64_t v_scale,
                                      int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
                                      int32_t S, int32_t key_len, int32_t kvg, int32_t window,
                                      int32_t query_base_pos, int32_t key_base_pos);
+
+/* attention_prefill_batched_int8, lib/attention_gpu_int8.mojo:804-841: the square causal
+ * prefill (S query rows over the S keys at positions 0..S-1), without its [nkv, S*kvg, S]
+ * score matrix. */
+int32_t nomos_attn_prefill_batched_i8(void *stream, uint64_t q_b, uint64_t q_t, uint64_t scores, uint64_t attn_t,
+                                      uint64_t attn_b, uint64_t k_i8, uint64_t v_i8, uint64_t k_scale, uint64_t v_scale,
+                                      int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
+                                      int32_t S, int32_t kvg, int32_t window);
 
 /* attention_gpu_fp32_dev, lib/attention_gpu.mojo:165-204 (cuBLAS handle dropped). */
 int32_t nomos_attn_decode_fp32(void *stream, uint64_t q, uint64_t k_cache, uint64_t v_cache, uint64_t scores_scratch,
@@ -186,8 +202,31 @@ int32_t nomos_attn_decode_bf16(void *stream, uint64_t q, uint64_t k_cache, uint6
                                int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
                                int32_t seq_len, int32_t kvg);
 
-/* attention_prefill_prefix_batched_fp32 / _bf16, lib/batched_attn_gpu.mojo:499-548,
- * 613-666.  kv_is_bf16 selects the cache element type. */
+/* attention_prefill_prefix_batched_fp32, lib/batched_attn_gpu.mojo:499-548 (cuBLAS handle
+ * dropped; q_t / attn_t transpose scratches accepted, unused). */
+int32_t nomos_attn_prefix_batched_fp32(void *stream, uint64_t q_b, uint64_t q_t, uint64_t scores, uint64_t attn_t,
+                                       uint64_t attn_b, uint64_t k_cache, uint64_t v_cache,
+                                       int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
+                                       int32_t S, int32_t key_len, int32_t kvg, int32_t window,
+                                       int32_t query_base_pos, int32_t key_base_pos);
+/* attention_prefill_prefix_batched_bf16, lib/batched_attn_gpu.mojo:613-666 (bf16 caches; the
+ * q_t, q_t_bf16, scores_bf16 and attn_t scratches are accepted, unused). */
+int32_t nomos_attn_prefix_batched_bf16(void *stream, uint64_t q_b, uint64_t q_t, uint64_t q_t_bf16, uint64_t scores,
+                                       uint64_t scores_bf16, uint64_t attn_t, uint64_t attn_b, uint64_t k_cache,
+                                       uint64_t v_cache, int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd,
+                                       int32_t max_seq, int32_t S, int32_t key_len, int32_t kvg, int32_t window,
+                                       int32_t query_base_pos, int32_t key_base_pos);
+/* attention_prefill_batched_fp32 / _bf16, lib/batched_attn_gpu.mojo:448-496, 558-610: the
+ * square causal forms (key_len = S, both bases 0). */
+int32_t nomos_attn_prefill_batched_fp32(void *stream, uint64_t q_b, uint64_t q_t, uint64_t scores, uint64_t attn_t,
+                                        uint64_t attn_b, uint64_t k_cache, uint64_t v_cache,
+                                        int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
+                                        int32_t S, int32_t kvg, int32_t window);
+int32_t nomos_attn_prefill_batched_bf16(void *stream, uint64_t q_b, uint64_t q_t, uint64_t q_t_bf16, uint64_t scores,
+                                        uint64_t scores_bf16, uint64_t attn_t, uint64_t attn_b, uint64_t k_cache,
+                                        uint64_t v_cache, int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd,
+                                        int32_t max_seq, int32_t S, int32_t kvg, int32_t window);
+/* The shared body of the four operators above; kv_is_bf16 selects the cache element type. */
 int32_t nomos_attn_prefix_batched_dense(void *stream, uint64_t q_b, uint64_t scores, uint64_t attn_b,
                                         uint64_t k_cache, uint64_t v_cache,
                                         int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq,
@@ -232,20 +271,22 @@ typedef struct nomos_attn_args {
     int64_t flags;              /* NOMOS_ATTN_* bits below                                */
 } nomos_attn_args_t;
 
-/* flags bit: the caller guarantees that every cache row (and scale) OLDER than the S query
- * rows was written by work that completed before the kernel immediately preceding this call
- * in the stream was launched -- true for a decode/verify loop, where only the append of the
- * current rows touches the cache.  The library may then start streaming those older rows
- * while that preceding kernel is still finishing (the query, the S newest rows and every
- * output are still ordered after it). */
+/* flags bit: the caller guarantees that every cache row (and scale) older than the newest
+ * 2 * max(S, n_new) keys of the window was written by work that completed before the kernel
+ * immediately preceding this call in the stream was launched.  True for a decode / verify
+ * loop: the preceding kernel is either the append of this call's own rows or the previous
+ * step's attention call with its fused append, and both only touch rows inside that margin
+ * (a verify step that kept a of its VB rows is followed by a step whose rows start a
+ * positions later).  The library may then start streaming the older rows while that
+ * preceding kernel is still finishing (the query, the newest rows and every output are still
+ * ordered after it).  Do not set it when the preceding kernel may have written older rows of
+ * this cache (a prefill chunk, a KV-reuse copy). */
 #define NOMOS_ATTN_SETTLED_CACHE 1
 /* flags bit: fetch every tile with 16-byte cp.async copies instead of TMA tensor copies.
- * Same results bit for bit; for comparing the two copy paths (the environment variable
- * NOMOS_ATTN_NO_TMA=1 does the same for a whole process). */
+ * Same results bit for bit; for comparing the two copy paths. */
 #define NOMOS_ATTN_NO_TMA 2
 /* flags bit: keep int8 / head_dim 128 calls on the mma.sync kernel instead of the tcgen05 one
- * (both pass the same accuracy gate; their roundings differ).  The environment variable
- * NOMOS_ATTN_NO_TCGEN05=1 does the same for a whole process. */
+ * (both pass the same accuracy gate; their roundings differ). */
 #define NOMOS_ATTN_NO_TCGEN05 4
 /* flags bit: take the tcgen05 kernel for every call it supports, also where the library's
  * own choice would be the mma.sync kernel (for comparing the two). */
@@ -375,6 +416,43 @@ int32_t nomos_attn_paged_decode_i8(void *stream, uint64_t q, uint64_t k_pool, ui
 int32_t nomos_kv_paged_append_quant_i8(void *stream, uint64_t src_k, uint64_t src_v, uint64_t k_pool, uint64_t v_pool,
                                        uint64_t ks_pool, uint64_t vs_pool, uint64_t block_table, uint64_t positions,
                                        int32_t batch, int32_t nkv, int32_t l_hd, int32_t l_kvd, int32_t max_pages);
+
+/* ------------------------------------------------------------------------- *
+ *  Sequence-sharded decode across the GPUs of one node (no counterpart in the reference, which runs on   *
+ *  one GPU, lib/gemma4_engine.mojo:229)                                                                  *
+ * ------------------------------------------------------------------------- *
+ * A long context is cut into `world` contiguous chunks, one per GPU (one process per GPU).  Every rank
+ * calls nomos_attn_seq_sharded with ITS chunk as the window (args->klen = keys of the chunk) and the same
+ * query; each call is ONE kernel launch that streams the chunk, merges its splits, stores the chunk's
+ * un-normalised (o, m, l) rows straight into every peer's mailbox over NVLink (plain stores to peer-mapped
+ * memory, a release stamp per row), waits -- with a limit -- for the peers' rows in its own mailbox, and
+ * writes the final normalised output of every query row into args->out on every rank.  No collective
+ * library call, no second launch, nothing multicast.
+ *
+ * Set-up, once: every rank creates a mailbox (nomos_attn_peer_mailbox_create: the one call of this library
+ * that allocates device memory; zero-filled), passes the 64-byte handle to the other ranks by any host-side
+ * means, and opens theirs (nomos_attn_peer_mailbox_open).  mailbox[g] is rank g's mailbox as addressable
+ * from THIS process (mailbox[rank] = the pointer create returned).
+ * Per call: `step` must be the same on every rank and grow by one with every call (start at 1); every rank
+ * must make every call, with the same batch, S, nh and l_hd.  A rank may be at most one call ahead of its
+ * peers (the mailboxes hold two steps).  timeout_us (0 = one second) bounds the wait for a peer: when it
+ * runs out the kernel raises bit 2 of the device fault word and returns without writing the output;
+ * nomos_attn_seq_sharded_status (synchronises the stream) then answers NOMOS_ATTN_ENOTWRITTEN.  After such
+ * a failure the ranks must agree on a new step number on the host before they go on. */
+typedef struct nomos_attn_peer {
+    uint64_t struct_bytes;      /* sizeof(nomos_attn_peer_t)                                              */
+    int64_t rank, world;        /* this shard's index, number of shards (1..8; 1 = plain nomos_attn_fused) */
+    uint64_t mailbox[8];        /* device addresses of every rank's mailbox in this process               */
+    int64_t mailbox_bytes;      /* size of each, >= nomos_attn_peer_mailbox_bytes(world, batch*S*nh, l_hd) */
+    uint64_t step;              /* call counter, identical on every rank, never 0                          */
+    int64_t timeout_us;         /* wait limit for a peer's rows; 0 = 1 000 000                             */
+} nomos_attn_peer_t;
+int64_t nomos_attn_peer_mailbox_bytes(int32_t world, int32_t rows, int32_t l_hd);
+int32_t nomos_attn_peer_mailbox_create(int64_t bytes, uint64_t *dev_ptr, void *handle64);
+int32_t nomos_attn_peer_mailbox_open(const void *handle64, uint64_t *dev_ptr);
+int32_t nomos_attn_peer_mailbox_close(uint64_t dev_ptr, int32_t own);
+int32_t nomos_attn_seq_sharded(void *stream, const nomos_attn_args_t *args, const nomos_attn_peer_t *peer);
+int32_t nomos_attn_seq_sharded_status(void *stream, int32_t clear);
 
 /* Merge G partial triples (as written through partial_out, gathered from G
  * sequence shards) into a normalised output.  partials: fp32 [G][rows][l_hd+2];

@@ -36,6 +36,12 @@ class AttnArgs(C.Structure):
     ]
 
 
+class AttnPeer(C.Structure):
+    """Mirror of ``nomos_attn_peer_t``."""
+    _fields_ = [("struct_bytes", u64), ("rank", i64), ("world", i64), ("mailbox", u64 * 8), ("mailbox_bytes", i64),
+                ("step", u64), ("timeout_us", i64)]
+
+
 class KvRing(C.Structure):
     """Mirror of ``nomos_kv_ring_t``."""
     _fields_ = [("struct_bytes", i64), ("cache_cap", i64), ("window", i64), ("max_rows", i64), ("len", i64),
@@ -79,11 +85,22 @@ PROTOTYPES = {
     "nomos_attn_decode_fp32": (i32, [vp] + [u64] * 5 + [i32] * 7),
     "nomos_attn_decode_bf16": (i32, [vp] + [u64] * 7 + [i32] * 7),
     "nomos_attn_prefix_batched_dense": (i32, [vp] + [u64] * 5 + [i32] * 12),
+    "nomos_attn_prefill_batched_i8": (i32, [vp] + [u64] * 9 + [i32] * 8),
+    "nomos_attn_prefix_batched_fp32": (i32, [vp] + [u64] * 7 + [i32] * 11),
+    "nomos_attn_prefix_batched_bf16": (i32, [vp] + [u64] * 9 + [i32] * 11),
+    "nomos_attn_prefill_batched_fp32": (i32, [vp] + [u64] * 7 + [i32] * 8),
+    "nomos_attn_prefill_batched_bf16": (i32, [vp] + [u64] * 9 + [i32] * 8),
     "nomos_attn_workspace_bytes": (i64, [C.POINTER(AttnArgs)]),
     "nomos_attn_kernel_choice": (i32, [C.POINTER(AttnArgs)]),
     "nomos_attn_fused": (i32, [vp, C.POINTER(AttnArgs)]),
     "nomos_attn_fused_static_ws": (i32, [vp, C.POINTER(AttnArgs)]),
     "nomos_attn_merge_partials": (i32, [vp, u64, i32, i32, i32, u64, i32]),
+    "nomos_attn_peer_mailbox_bytes": (i64, [i32, i32, i32]),
+    "nomos_attn_peer_mailbox_create": (i32, [i64, C.POINTER(u64), vp]),
+    "nomos_attn_peer_mailbox_open": (i32, [vp, C.POINTER(u64)]),
+    "nomos_attn_peer_mailbox_close": (i32, [u64, i32]),
+    "nomos_attn_seq_sharded": (i32, [vp, C.POINTER(AttnArgs), C.POINTER(AttnPeer)]),
+    "nomos_attn_seq_sharded_status": (i32, [vp, i32]),
 }
 
 

@@ -275,6 +275,9 @@ static int run_fused(cudaStream_t st, AttnArgs &a, const char *who) {
     return launch_attn_fused(st, a);
 }
 
+static int run_prefill_general(cudaStream_t st, AttnArgs &a, const char *who, int S, int key_len, int window, int query_base_pos,
+                               int key_base_pos);
+
 static void fill_thin(AttnArgs &a, uint64_t q, uint64_t k, uint64_t v, uint64_t ks, uint64_t vs, uint64_t scratch,
                       long scratch_floats, uint64_t out, int nh, int nkv, int l_hd, int cache_hd, int max_seq, int kvg) {
     memset(&a, 0, sizeof(a));
@@ -309,22 +312,52 @@ NOMOS_EXPORT int32_t nomos_attn_decode_multirow_i8(void *stream, uint64_t q_b, u
     return run_fused(as_stream(stream), a, "nomos_attn_decode_multirow_i8");
 }
 
+// Key range of the prefix-batched operators expressed for the fused kernel.  The operators' row s sees keys
+// [max(0, lo_abs - key_base_pos), min(q_abs - key_base_pos, key_len - 1)] of the array handed in, q_abs =
+// query_base_pos + s (lib/batched_attn_gpu.mojo:314-326); the fused kernel's row s sees window indices up to
+// klen - S + s.  The two agree when the array ends at the last query row: klen = query_base_pos - key_base_pos + S.
+// Keys beyond that are never attended, so a longer key_len is cut down to it.  Returns klen, or a negative status
+// for the ranges the fused kernel cannot express (a key array that ends before the last query row, queries
+// before the first key): those take the general prefill kernel.
+static int prefix_klen(int S, int key_len, int query_base_pos, int key_base_pos) {
+    if (query_base_pos < key_base_pos) return -1;
+    const long full = (long)query_base_pos - key_base_pos + S;
+    return key_len >= full ? (int)full : -1;
+}
+
 NOMOS_EXPORT int32_t nomos_attn_prefix_batched_i8(void *stream, uint64_t q_b, uint64_t, uint64_t scores, uint64_t,
                                                   uint64_t attn_b, uint64_t k_i8, uint64_t v_i8, uint64_t k_scale,
                                                   uint64_t v_scale, int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd,
                                                   int32_t max_seq, int32_t S, int32_t key_len, int32_t kvg, int32_t window,
                                                   int32_t query_base_pos, int32_t key_base_pos) {
+    const char *who = "nomos_attn_prefix_batched_i8";
     if (nh <= 0 || S <= 0 || key_len <= 0) return NOMOS_OK;
-    // The fused kernel expresses "row s sees keys up to its own position": the key
-    // range handed in must end exactly at the last query row.
-    if (key_base_pos != 0 || key_len != query_base_pos + S) {
-        set_error("nomos_attn_prefix_batched_i8: only key_base_pos=0 and key_len=query_base_pos+S are supported");
-        return NOMOS_EUNSUPPORTED;
-    }
+    REQUIRE(query_base_pos >= 0 && key_base_pos >= 0 && window >= 0, "%s: negative position or window", who);
+    if (key_len > max_seq) { set_error("%s: key_len %d exceeds the row pitch %d", who, key_len, max_seq); return NOMOS_ECAPACITY; }
     AttnArgs a;
     fill_thin(a, q_b, k_i8, v_i8, k_scale, v_scale, scores, (long)S * nh * key_len, attn_b, nh, nkv, l_hd, cache_hd, max_seq, kvg);
-    a.S = S; a.klen = key_len; a.window = window;
-    return run_fused(as_stream(stream), a, "nomos_attn_prefix_batched_i8");
+    // The engine pre-offsets the K / V / scale pointers by key_base_pos rows (lib/engine_prefill.mojo:926-941), so
+    // window index t of the array is absolute position key_base_pos + t and the sliding window needs no base.
+    const int klen = prefix_klen(S, key_len, query_base_pos, key_base_pos);
+    if (klen < 0) return run_prefill_general(as_stream(stream), a, who, S, key_len, window, query_base_pos, key_base_pos);
+    a.S = S; a.klen = klen; a.window = window;
+    return run_fused(as_stream(stream), a, who);
+}
+
+/* attention_prefill_batched_int8, lib/attention_gpu_int8.mojo:804-841: the square causal form. */
+NOMOS_EXPORT int32_t nomos_attn_prefill_batched_i8(void *stream, uint64_t q_b, uint64_t q_t, uint64_t scores, uint64_t attn_t,
+                                                   uint64_t attn_b, uint64_t k_i8, uint64_t v_i8, uint64_t k_scale,
+                                                   uint64_t v_scale, int32_t nh, int32_t nkv, int32_t l_hd, int32_t cache_hd,
+                                                   int32_t max_seq, int32_t S, int32_t kvg, int32_t window) {
+    return nomos_attn_prefix_batched_i8(stream, q_b, q_t, scores, attn_t, attn_b, k_i8, v_i8, k_scale, v_scale, nh, nkv, l_hd,
+                                        cache_hd, max_seq, S, S, kvg, window, 0, 0);
+}
+
+// Prefix ranges the decode-order kernels cannot express (see prefix_klen).
+static int run_prefill_general(cudaStream_t, AttnArgs &, const char *who, int S, int key_len, int, int query_base_pos, int key_base_pos) {
+    set_error("%s: key range [%d, %d) must reach the last query row (position %d) and start at or before the first", who, key_base_pos,
+              key_base_pos + key_len, query_base_pos + S - 1);
+    return NOMOS_EUNSUPPORTED;
 }
 
 static int run_dense(cudaStream_t st, const char *who, uint64_t q, uint64_t k, uint64_t v, uint64_t scratch, long scratch_floats,
@@ -366,9 +399,41 @@ NOMOS_EXPORT int32_t nomos_attn_prefix_batched_dense(void *stream, uint64_t q_b,
                                                      int32_t key_len, int32_t kvg, int32_t window, int32_t query_base_pos,
                                                      int32_t key_base_pos, int32_t kv_is_bf16) {
     if (nh <= 0 || S <= 0 || key_len <= 0) return NOMOS_OK;
+    REQUIRE(query_base_pos >= 0 && key_base_pos >= 0 && window >= 0, "nomos_attn_prefix_batched_dense: negative position or window");
     return run_dense(as_stream(stream), "nomos_attn_prefix_batched_dense", q_b, k_cache, v_cache, scores, (long)S * nh * key_len,
                      attn_b, nh, nkv, l_hd, cache_hd, max_seq, S, key_len, kvg, window, query_base_pos, key_base_pos,
                      kv_is_bf16 != 0);
+}
+
+// The four operators of lib/batched_attn_gpu.mojo with their own argument lists (the cuBLAS handle dropped, the
+// transpose / cast scratches accepted and unused): one body, nomos_attn_prefix_batched_dense.
+NOMOS_EXPORT int32_t nomos_attn_prefix_batched_fp32(void *stream, uint64_t q_b, uint64_t, uint64_t scores, uint64_t, uint64_t attn_b,
+                                                    uint64_t k_cache, uint64_t v_cache, int32_t nh, int32_t nkv, int32_t l_hd,
+                                                    int32_t cache_hd, int32_t max_seq, int32_t S, int32_t key_len, int32_t kvg,
+                                                    int32_t window, int32_t query_base_pos, int32_t key_base_pos) {
+    return nomos_attn_prefix_batched_dense(stream, q_b, scores, attn_b, k_cache, v_cache, nh, nkv, l_hd, cache_hd, max_seq, S,
+                                           key_len, kvg, window, query_base_pos, key_base_pos, 0);
+}
+NOMOS_EXPORT int32_t nomos_attn_prefix_batched_bf16(void *stream, uint64_t q_b, uint64_t, uint64_t, uint64_t scores, uint64_t,
+                                                    uint64_t, uint64_t attn_b, uint64_t k_cache, uint64_t v_cache, int32_t nh,
+                                                    int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq, int32_t S,
+                                                    int32_t key_len, int32_t kvg, int32_t window, int32_t query_base_pos,
+                                                    int32_t key_base_pos) {
+    return nomos_attn_prefix_batched_dense(stream, q_b, scores, attn_b, k_cache, v_cache, nh, nkv, l_hd, cache_hd, max_seq, S,
+                                           key_len, kvg, window, query_base_pos, key_base_pos, 1);
+}
+NOMOS_EXPORT int32_t nomos_attn_prefill_batched_fp32(void *stream, uint64_t q_b, uint64_t, uint64_t scores, uint64_t, uint64_t attn_b,
+                                                     uint64_t k_cache, uint64_t v_cache, int32_t nh, int32_t nkv, int32_t l_hd,
+                                                     int32_t cache_hd, int32_t max_seq, int32_t S, int32_t kvg, int32_t window) {
+    return nomos_attn_prefix_batched_dense(stream, q_b, scores, attn_b, k_cache, v_cache, nh, nkv, l_hd, cache_hd, max_seq, S, S, kvg,
+                                           window, 0, 0, 0);
+}
+NOMOS_EXPORT int32_t nomos_attn_prefill_batched_bf16(void *stream, uint64_t q_b, uint64_t, uint64_t, uint64_t scores, uint64_t,
+                                                     uint64_t, uint64_t attn_b, uint64_t k_cache, uint64_t v_cache, int32_t nh,
+                                                     int32_t nkv, int32_t l_hd, int32_t cache_hd, int32_t max_seq, int32_t S,
+                                                     int32_t kvg, int32_t window) {
+    return nomos_attn_prefix_batched_dense(stream, q_b, scores, attn_b, k_cache, v_cache, nh, nkv, l_hd, cache_hd, max_seq, S, S, kvg,
+                                           window, 0, 0, 1);
 }
 
 // -------------------------------------------------------------------- fused
@@ -410,7 +475,7 @@ NOMOS_EXPORT int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args) {
     int rc = unpack_args(args, a, "nomos_attn_workspace_bytes");
     if (rc) return rc;
     if ((rc = check_attn_geometry("nomos_attn_workspace_bytes", a.nh, a.nkv, a.l_hd, a.cache_hd, a.kvg))) return rc;
-    if (a.batch <= 0 || a.S <= 0 || a.klen <= 0) { set_error("nomos_attn_workspace_bytes: bad batch/S/klen"); return NOMOS_EBADARG; }
+    if (a.batch <= 0 || a.S <= 0 || a.klen <= 0 || a.cache_cap <= 0 || a.win_start < 0) { set_error("nomos_attn_workspace_bytes: bad batch/S/klen/cache_cap/win_start"); return NOMOS_EBADARG; }
     return attn_workspace_bytes(a);
 }
 
@@ -419,7 +484,7 @@ NOMOS_EXPORT int32_t nomos_attn_kernel_choice(const nomos_attn_args_t *args) {
     int rc = unpack_args(args, a, "nomos_attn_kernel_choice");
     if (rc) return rc;
     if ((rc = check_attn_geometry("nomos_attn_kernel_choice", a.nh, a.nkv, a.l_hd, a.cache_hd, a.kvg))) return rc;
-    if (a.batch <= 0 || a.S <= 0 || a.klen <= 0) { set_error("nomos_attn_kernel_choice: bad batch/S/klen"); return NOMOS_EBADARG; }
+    if (a.batch <= 0 || a.S <= 0 || a.klen <= 0 || a.cache_cap <= 0 || a.win_start < 0) { set_error("nomos_attn_kernel_choice: bad batch/S/klen/cache_cap/win_start"); return NOMOS_EBADARG; }
     return attn_kernel_choice(a);
 }
 
@@ -439,23 +504,16 @@ NOMOS_EXPORT int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *arg
     return run_fused(as_stream(stream), a, "nomos_attn_fused");
 }
 
-// Device-visible address of a pinned host buffer (0 if the GPU cannot address it).  The last answers
-// are remembered per thread: a decode loop passes the same two buffers every step.
+// Device-visible address of a pinned host buffer (0 if the GPU cannot address it).  Asked of the runtime on
+// every call: a remembered answer would go stale when the caller frees or unregisters the buffer and the
+// address comes back as pageable memory, and the question costs well under a microsecond next to the
+// stream synchronise of the same call.
 static uint64_t device_view_of_host(uint64_t host) {
-    struct Entry { uint64_t host = 0, dev = 0; };
-    thread_local Entry cache[4];
-    thread_local int next = 0;
-    for (const Entry &c : cache)
-        if (c.host == host) return c.dev;
     cudaPointerAttributes at;
-    uint64_t dev = 0;
     if (cudaPointerGetAttributes(&at, ptr(host)) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer != nullptr)
-        dev = (uint64_t)(uintptr_t)at.devicePointer;
-    else
-        cudaGetLastError();                       // not an error of the call: just not mapped
-    cache[next].host = host; cache[next].dev = dev;
-    next = (next + 1) % 4;
-    return dev;
+        return (uint64_t)(uintptr_t)at.devicePointer;
+    cudaGetLastError();                           // not an error of the call: just not mapped
+    return 0;
 }
 
 NOMOS_EXPORT int32_t nomos_attn_fused_host(void *stream, const nomos_attn_args_t *args, uint64_t host_in, uint64_t dev_in,
@@ -571,6 +629,98 @@ NOMOS_EXPORT int32_t nomos_attn_merge_partials(void *stream, uint64_t partials, 
     return launch_merge_partials(as_stream(stream), static_cast<const float *>(ptr(partials)), G, rows, l_hd, ptr(out), out_type);
 }
 
+// ------------------------------------------------- sequence-sharded decode across the GPUs of one node
+
+NOMOS_EXPORT int64_t nomos_attn_peer_mailbox_bytes(int32_t world, int32_t rows, int32_t l_hd) {
+    if (world < 1 || world > 8 || rows <= 0 || l_hd <= 0) { set_error("nomos_attn_peer_mailbox_bytes: bad world/rows/l_hd"); return NOMOS_EBADARG; }
+    return attn_peer_mailbox_bytes(world, rows, l_hd);
+}
+
+// Set-up, not the hot path: the one place the library allocates device memory, because the mailbox must be an
+// allocation of its own (its interprocess handle names the whole allocation) and must start zeroed.
+NOMOS_EXPORT int32_t nomos_attn_peer_mailbox_create(int64_t bytes, uint64_t *dev_ptr, void *handle64) {
+    const char *who = "nomos_attn_peer_mailbox_create";
+    REQUIRE(bytes > 0 && dev_ptr != nullptr, "%s: bad argument", who);
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 opaque bytes");
+    void *m = nullptr;
+    cudaError_t e = cudaMalloc(&m, (size_t)bytes);
+    if (e == cudaSuccess) e = cudaMemset(m, 0, (size_t)bytes);
+    if (e == cudaSuccess && handle64 != nullptr) e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t *>(handle64), m);
+    if (e != cudaSuccess) {
+        set_error("%s: %s", who, cudaGetErrorString(e));
+        if (m) cudaFree(m);
+        return NOMOS_ECUDA;
+    }
+    *dev_ptr = (uint64_t)(uintptr_t)m;
+    return NOMOS_OK;
+}
+
+NOMOS_EXPORT int32_t nomos_attn_peer_mailbox_open(const void *handle64, uint64_t *dev_ptr) {
+    const char *who = "nomos_attn_peer_mailbox_open";
+    REQUIRE(handle64 != nullptr && dev_ptr != nullptr, "%s: null pointer", who);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    void *m = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&m, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) { set_error("%s: %s", who, cudaGetErrorString(e)); return NOMOS_ECUDA; }
+    *dev_ptr = (uint64_t)(uintptr_t)m;
+    return NOMOS_OK;
+}
+
+NOMOS_EXPORT int32_t nomos_attn_peer_mailbox_close(uint64_t dev_ptr, int32_t own) {
+    if (dev_ptr == 0) return NOMOS_OK;
+    cudaError_t e = own ? cudaFree(ptr(dev_ptr)) : cudaIpcCloseMemHandle(ptr(dev_ptr));
+    if (e != cudaSuccess) { set_error("nomos_attn_peer_mailbox_close: %s", cudaGetErrorString(e)); return NOMOS_ECUDA; }
+    return NOMOS_OK;
+}
+
+NOMOS_EXPORT int32_t nomos_attn_seq_sharded(void *stream, const nomos_attn_args_t *args, const nomos_attn_peer_t *peer) {
+    const char *who = "nomos_attn_seq_sharded";
+    AttnArgs a;
+    int rc = unpack_args(args, a, who);
+    if (rc) return rc;
+    REQUIRE(peer != nullptr && peer->struct_bytes == sizeof(nomos_attn_peer_t), "%s: null peer block or struct_bytes mismatch", who);
+    REQUIRE(peer->world >= 1 && peer->world <= 8 && peer->rank >= 0 && peer->rank < peer->world, "%s: rank %lld of %lld", who,
+            (long long)peer->rank, (long long)peer->world);
+    if (a.nh <= 0) return NOMOS_OK;
+    REQUIRE(a.klen > 0, "%s: every shard must hold at least one key of the window", who);
+    REQUIRE(a.out != nullptr && a.partial_out == nullptr, "%s: the call writes the final output (out) and exports no partials", who);
+    if (a.new_k || a.new_v) {
+        REQUIRE(a.new_k && a.new_v && a.n_new > 0, "%s: new_k/new_v/n_new inconsistent", who);
+        REQUIRE(a.new_base_pos + a.n_new == a.win_start + a.klen, "%s: the new rows must be the last keys of the shard", who);
+        if (a.new_stride == 0) a.new_stride = a.nkv * a.l_hd;
+        REQUIRE(a.n_new <= a.klen && a.n_new <= a.cache_cap, "%s: n_new %d exceeds the window", who, a.n_new);
+    }
+    if (peer->world == 1) return run_fused(as_stream(stream), a, who);
+    REQUIRE(peer->step != 0, "%s: step numbers start at 1 (a zeroed mailbox reads as step 0)", who);
+    REQUIRE(a.batch > 0 && a.S > 0, "%s: bad batch/S", who);
+    const long need = attn_peer_mailbox_bytes((int)peer->world, (long)a.batch * a.S * a.nh, a.l_hd);
+    if (peer->mailbox_bytes < need) {
+        set_error("%s: mailboxes hold %lld bytes, this call needs %ld", who, (long long)peer->mailbox_bytes, need);
+        return NOMOS_ECAPACITY;
+    }
+    for (int g = 0; g < peer->world; ++g) {
+        REQUIRE(peer->mailbox[g] != 0 && aligned(peer->mailbox[g], 16), "%s: mailbox %d null or misaligned", who, g);
+        a.peer_box[g] = ptr(peer->mailbox[g]);
+    }
+    a.peer_rank = (int)peer->rank; a.peer_world = (int)peer->world; a.peer_seq = peer->step; a.peer_timeout_us = (long)peer->timeout_us;
+    return run_fused(as_stream(stream), a, who);
+}
+
+NOMOS_EXPORT int32_t nomos_attn_seq_sharded_status(void *stream, int32_t clear) {
+    cudaError_t e = cudaStreamSynchronize(as_stream(stream));
+    if (e != cudaSuccess) { set_error("nomos_attn_seq_sharded_status: %s", cudaGetErrorString(e)); return NOMOS_ECUDA; }
+    uint32_t bits = 0;
+    int rc = nomos::read_attn_faults(&bits, false);
+    if (rc) return rc;
+    if (bits & 4u) {
+        if (clear) nomos::clear_attn_fault_bits(4u);
+        set_error("nomos_attn_seq_sharded: a peer's partial result did not arrive within the time limit; no output was written");
+        return NOMOS_ENOTWRITTEN;
+    }
+    return NOMOS_OK;
+}
+
 // ------------------------------------------------- fused call without a caller workspace
 //
 // Some callers of this library cannot give it a workspace: the Nomos engine hands its whole
@@ -584,8 +734,9 @@ NOMOS_EXPORT int32_t nomos_attn_merge_partials(void *stream, uint64_t partials, 
 //   * every GPU that loads the library holds NOMOS_STATIC_WS_BYTES (4 MiB) until the process exits;
 //   * a call whose split scratch would be larger is refused with NOMOS_ECAPACITY;
 //   * all calls on one device share the array, which keeps the previous call's contents.  Nothing in
-//     it has to start at zero: the arrival counters carry a per-launch tag and the partial results are
-//     fully rewritten before they are read, so no clearing pass is needed.  Two calls that overlap
+//     it has to start at zero: the arrival counters carry a tag the library recognises (an untagged word reads
+//     as "no arrivals yet"; the merging CTA leaves the word tagged with a zero count) and the partial results
+//     are fully rewritten before they are read, so no clearing pass is needed.  Two calls that overlap
 //     on the GPU (different streams) would overwrite each other's partial results: callers must
 //     keep calls to this entry point ordered on a device, e.g. by using one stream.
 //   * the first call on each device looks the array's device address up (cudaGetSymbolAddress);
@@ -623,7 +774,7 @@ NOMOS_EXPORT int32_t nomos_attn_fused_static_ws(void *stream, const nomos_attn_a
     if (a.nh <= 0 || a.klen <= 0) return NOMOS_OK;
     REQUIRE(a.new_k == nullptr && a.new_v == nullptr, "nomos_attn_fused_static_ws: fused append is not offered here; append first");
     if ((rc = check_attn_geometry("nomos_attn_fused_static_ws", a.nh, a.nkv, a.l_hd, a.cache_hd, a.kvg))) return rc;
-    REQUIRE(a.batch > 0 && a.S > 0, "nomos_attn_fused_static_ws: bad batch/S");
+    REQUIRE(a.batch > 0 && a.S > 0 && a.cache_cap > 0 && a.win_start >= 0, "nomos_attn_fused_static_ws: bad batch/S/cache_cap/win_start");
     const long need = attn_workspace_bytes(a);
     if (need < 0) return (int32_t)need;
     if (need > NOMOS_STATIC_WS_BYTES) {

@@ -17,7 +17,7 @@
 //   mbarrier); ragged or ring-wrapping tiles and wider rows use 16-byte cp.async copies.
 // Arithmetic per warp tile (all contractions on the tensor cores, no integer->float
 // conversion of cache bytes anywhere)
-//   QK:  int8 MMA m16n8k32.  A = the query rows as two int8 limbs of a 15-bit fixed
+//   QK:  int8 MMA m16n8k32.  A = the query rows as two int8 limbs of a 16-bit fixed
 //        point (rows g / g+8 of the M tile = high / low limb of slot g), B = the K
 //        bytes exactly as stored.  The int32 result is exact; one fp32 multiply per
 //        (token, slot) applies q_scale * k_scale.
@@ -31,9 +31,6 @@
 // inside the same launch by the last CTA of the (batch, head, row group) to arrive
 // (merge_splits_in_kernel), or exported for the multi-GPU all-gather (merge_kernel runs after it).
 #include <algorithm>
-#include <atomic>
-#include <chrono>
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -83,10 +80,6 @@ static EncodeTiledFn encode_tiled_fn() {
         return reinterpret_cast<EncodeTiledFn>(sym);
     }();
     return fn;
-}
-static bool tma_disabled_by_env() {
-    static const bool off = [] { const char *e = std::getenv("NOMOS_ATTN_NO_TMA"); return e && e[0] == '1'; }();
-    return off;
 }
 
 // kind 0: {row bytes, rows, batch} view of one byte plane of the cache, box = box_rows rows,
@@ -152,17 +145,34 @@ static unsigned int *fault_word() {
     return cached[dev];
 }
 
-// Launch epochs: unique 48-bit values per process, seeded from the clock, so the arrival
-// counters in a caller-owned workspace never need zeroing.
-static unsigned long long next_epoch() {
-    static std::atomic<unsigned long long> epoch{
-        (unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count() * 0x9E3779B97F4A7C15ull};
-    return (epoch.fetch_add(1) + 1) & ((1ull << 48) - 1);
-}
-
 struct Plan {
     int mt, row_groups, tile0, ntiles, splits, tiles_per_split, grows;
 };
+
+// Peer fields of a sequence-sharded call; returns where this rank's own merged rows go.
+static float *fill_peer_params(KParams &p, const AttnArgs &a, long grows) {
+    p.peer_world = a.peer_world > 1 ? a.peer_world : 0;
+    p.peer_rank = a.peer_rank; p.peer_seq = a.peer_seq;
+    p.peer_timeout_ns = (unsigned long long)(a.peer_timeout_us > 0 ? a.peer_timeout_us : 1000000) * 1000ull;
+    for (int g = 0; g < 8; ++g) { p.peer_rows[g] = nullptr; p.peer_flags[g] = nullptr; }
+    if (p.peer_world == 0) return nullptr;
+    const long rows_bytes = attn_peer_mailbox_rows_bytes(a.peer_world, grows, a.l_hd);
+    for (int g = 0; g < a.peer_world; ++g) {
+        p.peer_rows[g] = static_cast<float *>(a.peer_box[g]);
+        p.peer_flags[g] = reinterpret_cast<unsigned long long *>(static_cast<char *>(a.peer_box[g]) + rows_bytes);
+    }
+    const size_t blk = (size_t)grows * (a.l_hd + 2);
+    return p.peer_rows[a.peer_rank] + ((size_t)(a.peer_seq & 1ull) * a.peer_world + a.peer_rank) * blk;
+}
+
+// Window rows [0, settled_rows) may be requested before the stream-order wait when the caller set
+// NOMOS_ATTN_SETTLED_CACHE.  The newest 2 x max(S, n_new) rows are left out: this call's own rows, and as many
+// before them, which is where the preceding call of a decode / verify loop on the same cache (same batch size,
+// any number of accepted rows) wrote the rows it appended -- whether through its own fused append or through an
+// append kernel ordered before it.
+static int settled_rows(const AttnArgs &a) {
+    return a.settled_cache ? std::max(0, a.klen - 2 * std::max(a.S, a.n_new)) : 0;
+}
 
 template <int FMT, int HD, int MT, int DS>
 static int kernel_occupancy() {
@@ -236,29 +246,32 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     const Plan pl = make_plan(a, occ, HD, C::NW, DS);
     const long units = (long)a.nkv * a.batch * pl.row_groups;
     const long part_bytes = (((long)pl.splits * pl.grows * (HD + 2) * 4) + 15) / 16 * 16;
-    const long need = pl.splits > 1 ? part_bytes + units * 8 : 0;
+    // a sequence-sharded call always ends in the unit's merging CTA (it runs the exchange), also with one split
+    const bool in_kernel_merge = pl.splits > 1 || a.peer_world > 1;
+    const long need = in_kernel_merge ? part_bytes + units * 8 : 0;
     if (query_ws) { *ws_needed = need; return NOMOS_OK; }
     if (need > a.ws_bytes || (need > 0 && a.workspace == nullptr)) {
         set_error("attention workspace too small: need %ld bytes, have %ld", need, a.ws_bytes);
         return NOMOS_ECAPACITY;
     }
     KParams p;
+    std::memset(&p, 0, sizeof(p));
     p.q = static_cast<const uint8_t *>(a.q);
     p.k_cache = static_cast<const uint8_t *>(a.k_cache);
     p.v_cache = static_cast<const uint8_t *>(a.v_cache);
     p.k_scales = static_cast<const uint8_t *>(a.k_scales);
     p.v_scales = static_cast<const uint8_t *>(a.v_scales);
     p.out = static_cast<uint8_t *>(a.out);
-    const bool direct_export = (pl.splits == 1 && a.partial_out != nullptr);
+    const bool direct_export = (!in_kernel_merge && a.partial_out != nullptr);
     p.partial = direct_export ? a.partial_out : static_cast<float *>(a.workspace);
-    p.write_partial = (pl.splits > 1 || direct_export) ? 1 : 0;
+    p.write_partial = (in_kernel_merge || direct_export) ? 1 : 0;
     p.export_nat = direct_export ? 1 : 0;
-    p.counters = pl.splits > 1 ? reinterpret_cast<unsigned long long *>(static_cast<char *>(a.workspace) + part_bytes) : nullptr;
-    p.epoch = next_epoch();
+    p.counters = in_kernel_merge ? reinterpret_cast<unsigned long long *>(static_cast<char *>(a.workspace) + part_bytes) : nullptr;
     p.splits = pl.splits;
     p.arrivals = pl.splits * DS;
     p.partial_export = a.partial_out;
-    p.early_rows = a.settled_cache ? std::max(0, a.klen - std::max(a.S, a.n_new)) : 0;
+    if (float *own = fill_peer_params(p, a, pl.grows)) p.partial_export = own;
+    p.early_rows = settled_rows(a);
     p.new_k = a.new_k; p.new_v = a.new_v;
     p.n_new = a.new_k ? a.n_new : 0; p.new_stride = a.new_stride; p.new_base_pos = a.new_base_pos;
     p.k_cache_w = const_cast<uint8_t *>(p.k_cache); p.v_cache_w = const_cast<uint8_t *>(p.v_cache);
@@ -280,7 +293,7 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     TmaMaps tm;
     std::memset(&tm, 0, sizeof(tm));
     p.use_tma = 0;
-    if (C::TMA_OK && !a.no_tma && !tma_disabled_by_env()) {
+    if (C::TMA_OK && !a.no_tma) {
         const int row_stride = (FMT == KV_I8) ? a.cache_hd : a.cache_hd / 2;
         const auto al16 = [](const void *x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
         const long rows = (long)a.nkv * a.cache_cap;
@@ -320,10 +333,6 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
 // int8 KV, head_dim 128, up to 24 query rows per KV head (decode and verify), with or without fused
 // quantize-on-write: the contraction runs on tcgen05 with accumulators in tensor memory
 // (attn_tc5_kernel.cuh).  Everything else stays on the kernel above.
-static bool tc5_disabled_by_env() {
-    static const bool off = [] { const char *e = std::getenv("NOMOS_ATTN_NO_TCGEN05"); return e && e[0] == '1'; }();
-    return off;
-}
 static bool tc5_eligible(const AttnArgs &a);
 static int launch_tc5(cudaStream_t st, const AttnArgs &a, bool q, long *ws);
 
@@ -333,7 +342,7 @@ static bool tc5_eligible(const AttnArgs &a) {
     // one CTA serves at most 24 query rows per KV head (9 verify tokens x 2 group heads = 18); more go to the
     // mma.sync kernel, which cuts them into row groups
     if (a.S * a.kvg > 24 && !a.tcgen05_always) return false;
-    if (tc5_disabled_by_env() || tma_disabled_by_env() || encode_tiled_fn() == nullptr) return false;
+    if (encode_tiled_fn() == nullptr) return false;
     const auto al16 = [](const void *x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
     if (!al16(a.k_cache) || !al16(a.v_cache) || a.cache_hd % 16 != 0) return false;
     if (a.batch > 1 && a.kv_batch_stride % 16 != 0) return false;
@@ -356,11 +365,29 @@ static int tc5_occupancy() {
         cudaFuncSetAttribute(tc5::attn_tc5_kernel<NS>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         int n = 0;
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, tc5::attn_tc5_kernel<NS>, tc5::Cfg<NS>::NTHREADS, tc5::Cfg<NS>::SMEM_BYTES);
-        // two CTAs of 256 tensor-memory columns each is all an SM holds
-        // The occupancy query answers 1 for this kernel although two CTAs of 111 KB shared memory,
-        // 256 threads x <=128 registers and 256 tensor-memory columns each do run side by side on an
-        // SM (seen in per-CTA start times); plan with the residency the launch bounds were written for.
-        occ[dev] = std::max(n > 0 ? n : 1, tc5::Cfg<NS>::MIN_CTAS);
+        n = n > 0 ? n : 1;
+        // The occupancy query has answered 1 for the decode instances although two of their CTAs (111 KB of
+        // shared memory, 256 threads x <= 128 registers, 256 tensor-memory columns each) do run side by side
+        // on an SM.  The plan uses the residency the launch bounds were written for only when this device's own
+        // limits and this build's resource use say that it fits; otherwise the query's answer stands.
+        if (n < tc5::Cfg<NS>::MIN_CTAS) {
+            cudaFuncAttributes fa;
+            int smem_sm = 0, smem_rsv = 0, regs_sm = 0, thr_sm = 0;
+            const int want = tc5::Cfg<NS>::MIN_CTAS;
+            const bool known = cudaFuncGetAttributes(&fa, tc5::attn_tc5_kernel<NS>) == cudaSuccess &&
+                               cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess &&
+                               cudaDeviceGetAttribute(&smem_rsv, cudaDevAttrReservedSharedMemoryPerBlock, dev) == cudaSuccess &&
+                               cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, dev) == cudaSuccess &&
+                               cudaDeviceGetAttribute(&thr_sm, cudaDevAttrMaxThreadsPerMultiProcessor, dev) == cudaSuccess;
+            if (known) {
+                const long smem_cta = (long)tc5::Cfg<NS>::SMEM_BYTES + (long)fa.sharedSizeBytes + smem_rsv;
+                const long regs_cta = (long)((fa.numRegs + 7) / 8 * 8) * tc5::Cfg<NS>::NTHREADS;   // registers are granted in units of 8 per thread
+                const bool fits = want * smem_cta <= smem_sm && want * regs_cta <= regs_sm && want * tc5::Cfg<NS>::NTHREADS <= thr_sm &&
+                                  want * tc5::Cfg<NS>::TMEM_COLS <= 512;
+                if (fits) n = want;
+            }
+        }
+        occ[dev] = n;
     }
     return occ[dev];
 }
@@ -417,7 +444,8 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     const Tc5Plan pl = tc5_plan(a, NS, tc5_occupancy<NS>());
     const long units = (long)a.nkv * a.batch * pl.row_groups;
     const long part_bytes = (((long)pl.splits * pl.grows * (a.l_hd + 2) * 4) + 15) / 16 * 16;
-    const long need = pl.splits > 1 ? part_bytes + units * 8 : 0;
+    const bool in_kernel_merge = pl.splits > 1 || a.peer_world > 1;
+    const long need = in_kernel_merge ? part_bytes + units * 8 : 0;
     if (query_ws) { *ws_needed = need; return NOMOS_OK; }
     if (need > a.ws_bytes || (need > 0 && a.workspace == nullptr)) {
         set_error("attention workspace too small: need %ld bytes, have %ld", need, a.ws_bytes);
@@ -445,16 +473,16 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     p.v_scales = static_cast<const uint8_t *>(a.v_scales);
     p.q = static_cast<const uint8_t *>(a.q);
     p.out = static_cast<uint8_t *>(a.out);
-    const bool direct_export = (pl.splits == 1 && a.partial_out != nullptr);
+    const bool direct_export = (!in_kernel_merge && a.partial_out != nullptr);
     p.partial = direct_export ? a.partial_out : static_cast<float *>(a.workspace);
-    p.write_partial = (pl.splits > 1 || direct_export) ? 1 : 0;
+    p.write_partial = (in_kernel_merge || direct_export) ? 1 : 0;
     p.export_nat = direct_export ? 1 : 0;
-    p.counters = pl.splits > 1 ? reinterpret_cast<unsigned long long *>(static_cast<char *>(a.workspace) + part_bytes) : nullptr;
-    p.epoch = next_epoch();
+    p.counters = in_kernel_merge ? reinterpret_cast<unsigned long long *>(static_cast<char *>(a.workspace) + part_bytes) : nullptr;
     p.splits = pl.splits;
     p.arrivals = pl.splits;
     p.partial_export = a.partial_out;
-    p.early_rows = (a.settled_cache && !paged) ? std::max(0, a.klen - std::max(a.S, a.n_new)) : 0;
+    if (float *own = fill_peer_params(p, a, pl.grows)) p.partial_export = own;
+    p.early_rows = paged ? 0 : settled_rows(a);
     p.block_table = a.block_table; p.seq_lens = a.seq_lens; p.max_pages = a.max_pages;
     p.q_type = a.q_type; p.out_type = a.out_type;
     p.S = a.S; p.nh = a.nh; p.nkv = a.nkv; p.kvg = a.kvg; p.cache_hd = a.cache_hd; p.cache_cap = a.cache_cap;
@@ -561,6 +589,13 @@ static int dispatch(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
 
 }  // namespace
 
+long attn_peer_mailbox_rows_bytes(int world, long grows, int l_hd) {
+    return ((2L * world * grows * (l_hd + 2) * 4) + 15) / 16 * 16;
+}
+long attn_peer_mailbox_bytes(int world, long grows, int l_hd) {
+    return attn_peer_mailbox_rows_bytes(world, grows, l_hd) + 2L * world * grows * 8;
+}
+
 int attn_kernel_choice(const AttnArgs &a) { return tc5_eligible(a) && !prefers_mma(a) ? 1 : 0; }
 
 long attn_workspace_bytes(const AttnArgs &a) {
@@ -593,20 +628,16 @@ int read_attn_faults(unsigned int *out, bool clear) {
     return NOMOS_OK;
 }
 
-#ifdef NOMOS_TIMELINE
-extern "C" __attribute__((visibility("default"))) int nomos_debug_merge(unsigned long long *host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, fused::g_merge_tl, sizeof(unsigned long long) * 320 * 8);
+
+__global__ void clear_fault_bits_kernel(unsigned int *w, unsigned int bits) { atomicAnd(w, ~bits); }
+int clear_attn_fault_bits(unsigned int bits) {
+    unsigned int *w = fault_word();
+    if (w == nullptr) { set_error("device fault word unavailable"); return NOMOS_ECUDA; }
+    clear_fault_bits_kernel<<<1, 1>>>(w, bits);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) { set_error("fault word clear: %s", cudaGetErrorString(e)); return NOMOS_ECUDA; }
+    return NOMOS_OK;
 }
-extern "C" __attribute__((visibility("default"))) int nomos_debug_tc5_cta(unsigned long long *host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, tc5::g_tc5_cta, sizeof(unsigned long long) * 320 * 16);
-}
-extern "C" __attribute__((visibility("default"))) int nomos_debug_tc5_timeline(unsigned long long *host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, tc5::g_tc5_tl, sizeof(unsigned long long) * 320 * 40 * 6);
-}
-extern "C" __attribute__((visibility("default"))) int nomos_debug_timeline(unsigned long long *host_out, int n_ctas) {
-    return (int)cudaMemcpyFromSymbol(host_out, fused::g_timeline, sizeof(unsigned long long) * 6 * n_ctas);
-}
-#endif
 
 int launch_merge_partials(cudaStream_t st, const float *partials, int G, int rows, int l_hd, void *out, int out_type) {
     merge_kernel<<<rows, 128, 0, st>>>(partials, G, rows, l_hd, out, out_type, 1, nullptr);

@@ -32,7 +32,7 @@ constexpr int NSTAGE = NOMOS_NSTAGE;     // tile stages per warp
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float M_INIT = -1.0e30f;       // finite "minus infinity" for the running max
-constexpr int Q_FIX_MAX = 16256;         // 127 * 128: two int8 limbs, hi in [-127,127], lo in [-64,63]
+constexpr int Q_FIX_MAX = 32639;         // 127 * 256 + 127: two int8 limbs, hi in [-127,127], lo in [-128,127]
 constexpr float P_FIX = 65535.0f;        // probabilities reach the tensor core as 16-bit fixed point (two u8 limbs)
 constexpr float LAZY_MAX = 8.0f;         // base-2 slack before the running softmax reference is moved
 constexpr float RND_MAGIC = 8388608.0f;  // 2^23: adding it leaves round-to-nearest(x) in the low mantissa bits
@@ -96,8 +96,7 @@ struct KParams {
     int tile0, ntiles, tiles_per_split, row_groups, grows;
     float qk_scale_log2;     // softmax_scale * log2(e)
     // in-kernel split merge: the last CTA of a (batch, kv head, row group) unit to finish merges
-    unsigned long long *counters;   // one word per unit: (epoch << 16) | arrivals; nullptr = no in-kernel merge
-    unsigned long long epoch;       // unique per launch, so stale or uninitialised words read as "0 arrivals"
+    unsigned long long *counters;   // one word per unit: (tag << 16) | arrivals, see merge_splits_in_kernel; nullptr = no in-kernel merge
     int splits;
     int arrivals;                   // CTAs per unit that arrive before the merge: splits x head-dim slices
     float *partial_export;          // optional exported (o, m, l) per row, m in natural-log units
@@ -110,10 +109,18 @@ struct KParams {
     const int *block_table;  // paged caches (tcgen05 kernel): [batch][max_pages] page of each 128-key tile; nullptr = contiguous
     const int *seq_lens;     // paged caches: keys of each sequence
     int max_pages;
+    // sequence-sharded decode across GPUs (peer_world > 1): the CTA that merges a unit's splits pushes the unit's
+    // (o, m, l) rows into every peer's mailbox, waits for the peers' rows in its own and writes the final output
+    float *peer_rows[8];                // rank g's mailbox rows [2 step slots][world][grows][HD+2], as mapped in this process
+    unsigned long long *peer_flags[8];  // rank g's arrival stamps [2][world][grows]: the step number once the row is complete
+    int peer_rank, peer_world;
+    unsigned long long peer_seq;        // step number, the same on every rank, never 0
+    unsigned long long peer_timeout_ns; // how long a CTA waits for a peer's rows before it gives up (fault bit 2)
     unsigned int kvg_magic;  // ceil(2^32 / kvg), 0 for kvg == 1: idx / kvg = umulhi(idx, kvg_magic)
     int use_tma;             // bit 0: whole tiles come by TMA; bit 1: their scales by bulk copy
     int dry_pass;            // 1: the whole grid is resident at once, so a CTA may start before its stream predecessor is done
-    unsigned int *fault;     // sticky device word: bit 0 = a tile never arrived within the wait limit
+    unsigned int *fault;     // sticky device word: bit 0 = a tile never arrived within the wait limit (mma.sync kernel),
+                             // bit 1 = a hand-off of the tcgen05 kernel ran out of time, bit 2 = a peer's partial never arrived
 };
 
 // idx / kvg for the small non-negative indices used here, without the division routine.
@@ -121,9 +128,12 @@ __device__ __forceinline__ int div_kvg(const KParams &p, int idx) {
     return p.kvg_magic ? (int)__umulhi((unsigned)idx, p.kvg_magic) : idx;
 }
 
+// Query elements are read through L2 only (ld.global.cg): the warming pass reads them before the
+// stream-order wait, while the stream predecessor may still be writing them, and the pass that
+// counts must not find such a line in the L1 or in the read-only path.
 __device__ __forceinline__ float load_q(const uint8_t *q, int q_type, long idx) {
-    return q_type == ET_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(q)[idx])
-                             : reinterpret_cast<const float *>(q)[idx];
+    return q_type == ET_BF16 ? __uint_as_float((uint32_t)__ldcg(reinterpret_cast<const unsigned short *>(q) + idx) << 16)
+                             : __ldcg(reinterpret_cast<const float *>(q) + idx);
 }
 
 // D(16x8,s32) = A(16x32,u8,row) * B(32x8,s8,col), no accumulator input.
@@ -135,33 +145,6 @@ __device__ __forceinline__ void mma_u8s8_zero(int (&d)[4], uint32_t a0, uint32_t
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
 }
 
-#ifdef NOMOS_TIMELINE
-// Debug builds only: per-CTA wall-clock marks (ns) read back by nomos_debug_timeline().
-__device__ unsigned long long g_timeline[4096][6];
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define NOMOS_MARK(slot)                                                                                    \
-    do {                                                                                                    \
-        if (threadIdx.x == 0) {                                                                             \
-            const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                 \
-            if (cta < 4096) g_timeline[cta][slot] = gtime();                                                \
-        }                                                                                                   \
-    } while (0)
-__device__ unsigned long long g_merge_tl[320][8];
-#define MERGE_MARK(slot)                                                                                    \
-    do {                                                                                                    \
-        if (threadIdx.x == 0) {                                                                             \
-            const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                 \
-            if (cta < 320) g_merge_tl[cta][slot] = gtime();                                                 \
-        }                                                                                                   \
-    } while (0)
-#else
-#define NOMOS_MARK(slot) do {} while (0)
-#define MERGE_MARK(slot) do {} while (0)
-#endif
 
 __device__ __forceinline__ void mma_u8u8_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                               uint32_t b1) {
@@ -346,7 +329,6 @@ __device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int n
             for (int k = 0; k < GC; ++k)
                 v[j][k] = __ldcg(reinterpret_cast<const float2 *>(base[j] + (size_t)min(k, G - 1) * a.rstride + dd[j]));
         }
-        MERGE_MARK(4);
 #pragma unroll
         for (int j = 0; j < EL; ++j) {
             const float mk = (lane < G && ml[j].y > 0.0f) ? ml[j].x : -CUDART_INF_F;   // a split that saw no key, or no split
@@ -356,7 +338,6 @@ __device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int n
             float l = wk * ml[j].y;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-            if (j == 0) MERGE_MARK(5);
             float ox = 0.0f, oy = 0.0f;
 #pragma unroll
             for (int k = 0; k < GC; ++k) {
@@ -411,16 +392,15 @@ __device__ __forceinline__ bool merge_without_staging(const KParams &p, int b, i
 // thread of a CTA after its partial (o, m, l) rows are stored.  The last CTA of the unit to
 // arrive merges the unit's rows; the others return.  `scratch` is shared memory the CTA no
 // longer needs, at least 8 * NSLOT * splits bytes.
+// Returns true in the CTA that merged the unit's rows (the last one to arrive).
 template <int NSLOT, int HD, int NTHR, int GB = 8>
-__device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t *scratch, int b, int kvh, int rg) {
-    if (p.counters == nullptr) return;
+__device__ __forceinline__ bool merge_unit_splits(const KParams &p, uint8_t *scratch, int b, int kvh, int rg) {
+    if (p.counters == nullptr) return false;
 
     // ------------------------------------------- in-kernel merge across the splits
     // Arrival counting without a zeroed workspace (see the tag below).
     __shared__ int s_last;
-    MERGE_MARK(0);
     __syncthreads();                      // all partial stores of this CTA are issued
-    MERGE_MARK(1);
     if (threadIdx.x == 0) {
         // The arrival is one acquire-release atomic at GPU scope: release makes the whole CTA's partial
         // stores (ordered before it by the barrier above) visible before the count, acquire orders the
@@ -454,10 +434,7 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
         s_last = (arrived == p.arrivals);
     }
     __syncthreads();
-    MERGE_MARK(2);
-    if (!s_last) return;
-    NOMOS_MARK(5);
-    MERGE_MARK(3);
+    if (!s_last) return false;
 
     // The last CTA of the unit merges its rows.  Phase A stages every split's (m, l) in shared
     // memory; phase B (a warp per row) turns them into weights 2^(m_i - m*) and the merged
@@ -485,7 +462,6 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
             ms[sl * G + i] = ml.y > 0.0f ? ml.x : -CUDART_INF_F;
         }
         __syncthreads();
-        MERGE_MARK(4);
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         for (int sl = warp; sl < nrows; sl += NTHR / 32) {
             float m = -CUDART_INF_F;
@@ -503,7 +479,6 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
             if (lane == 0) { s_mstar[sl] = m; s_lstar[sl] = lp; }
         }
         __syncthreads();
-        MERGE_MARK(5);
     };
     auto emit_ml = [&](int sl, int d, float o, float mstar, float lstar) {
         const long grow = grow_of(sl);
@@ -523,10 +498,7 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
         }
     };
     auto emit = [&](int sl, int d, float o) { emit_ml(sl, d, o, s_mstar[sl], s_lstar[sl]); };
-    if (merge_without_staging<NSLOT, HD, NTHR>(p, b, kvh, rg, threadIdx.x, NTHR)) {
-        MERGE_MARK(6);
-        return;
-    }
+    if (merge_without_staging<NSLOT, HD, NTHR>(p, b, kvh, rg, threadIdx.x, NTHR)) return true;
     // General case: a thread takes EL pairs of dims at a time (partial rows are 8-byte aligned) and
     // up to GBW splits of each, every load of such a batch issued before the first use (clamped
     // instead of predicated, so they batch freely); the first batch is requested before the (m, l)
@@ -590,7 +562,119 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
     if (G <= 4) general(std::integral_constant<int, 4>{});
     else if (G <= 8) general(std::integral_constant<int, 8>{});
     else general(std::integral_constant<int, 12>{});
-    MERGE_MARK(6);
+    return true;
+}
+
+// ---- sequence shards on several GPUs: exchange of the merged rows through peer memory
+__device__ __forceinline__ void st_release_sys(unsigned long long *addr, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;\n" ::"l"(addr), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *addr) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];\n" : "=l"(v) : "l"(addr) : "memory");
+    return v;
+}
+
+// Called by every thread of the CTA that merged a unit's splits into this rank's own mailbox rows
+// (p.partial_export points at them; m in natural-log units).  Three steps, one launch, no collective library:
+//   1. push: the unit's rows are copied into the same place of every peer's mailbox with plain stores to
+//      peer-mapped memory (NVLink), then each row's stamp is released at system scope with the step number;
+//   2. wait: thread (peer, row) polls this rank's own mailbox for the peer's stamp of this step, for at most
+//      peer_timeout_ns; a peer that never shows up raises fault bit 2 and the CTA returns without an output;
+//   3. merge: the world's rows of each query row are combined exactly like split partials and normalised.
+// Mailboxes have two step slots (step & 1): a rank can be at most one step ahead of a peer it exchanged with,
+// so the slot a push overwrites was consumed two steps ago.  Nothing here is multicast, and no thread waits
+// without a limit.
+template <int NSLOT, int HD, int NTHR>
+__device__ __noinline__ void peer_exchange_and_merge(const KParams &p, int b, int kvh, int rg) {
+    __shared__ int s_peer_ok;
+    const int G = p.peer_world, me = p.peer_rank, tid = threadIdx.x;
+    const int slot = (int)(p.peer_seq & 1ull);
+    const int first = rg * NSLOT;
+    const int nrows = min(NSLOT, p.S * p.kvg - first);
+    const size_t blk = (size_t)p.grows * (HD + 2);                   // floats of one (slot, source rank) block
+    auto grow_of = [&](int sl) {
+        const int idx = first + sl;
+        const int r = div_kvg(p, idx);
+        return ((long)b * p.S + r) * p.nh + kvh * p.kvg + (idx - r * p.kvg);
+    };
+    if (tid == 0) s_peer_ok = 1;
+    __syncthreads();                                                 // this CTA's merged rows are written
+    // ---- 1. push
+    constexpr int RP = (HD + 2) / 2;                                 // float2 per row
+    const int per_peer = nrows * RP;
+    for (int e = tid; e < per_peer * (G - 1); e += NTHR) {
+        const int gi = e / per_peer, rem = e - gi * per_peer;
+        const int g = gi + (gi >= me ? 1 : 0);
+        const int sl = rem / RP, c = rem - sl * RP;
+        const size_t off = ((size_t)slot * G + me) * blk + (size_t)grow_of(sl) * (HD + 2) + 2 * c;
+        const float2 v = __ldcg(reinterpret_cast<const float2 *>(p.peer_rows[me] + off));
+        *reinterpret_cast<float2 *>(p.peer_rows[g] + off) = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    for (int e = tid; e < nrows * (G - 1); e += NTHR) {
+        const int gi = e / nrows, sl = e - gi * nrows;
+        const int g = gi + (gi >= me ? 1 : 0);
+        st_release_sys(p.peer_flags[g] + ((size_t)slot * G + me) * p.grows + grow_of(sl), p.peer_seq);
+    }
+    // ---- 2. wait
+    for (int e = tid; e < nrows * (G - 1); e += NTHR) {
+        const int gi = e / nrows, sl = e - gi * nrows;
+        const int g = gi + (gi >= me ? 1 : 0);
+        const unsigned long long *f = p.peer_flags[me] + ((size_t)slot * G + g) * p.grows + grow_of(sl);
+        unsigned long long t0, t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        bool seen = ld_acquire_sys(f) == p.peer_seq;
+        while (!seen) {
+#pragma unroll 1
+            for (int k = 0; k < 16 && !seen; ++k) { __nanosleep(40); seen = ld_acquire_sys(f) == p.peer_seq; }
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (!seen && t1 - t0 > p.peer_timeout_ns) break;
+        }
+        if (!seen) { s_peer_ok = 0; atomicOr(p.fault, 4u); }
+    }
+    __syncthreads();
+    if (!s_peer_ok) return;
+    // ---- 3. merge the world's rows (rank me's own rows included) and write the normalised output
+    for (int e = tid; e < nrows * HD; e += NTHR) {
+        const int sl = e / HD, d = e - sl * HD;
+        const long grow = grow_of(sl);
+        const float *base = p.peer_rows[me] + (size_t)slot * G * blk + (size_t)grow * (HD + 2);
+        float m = -CUDART_INF_F;
+        float mg[8], lg[8], og[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const float *row = base + (size_t)min(g, G - 1) * blk;
+            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(row + HD));
+            og[g] = __ldcg(row + d);
+            lg[g] = g < G ? ml.y : 0.0f;
+            mg[g] = (g < G && ml.y > 0.0f) ? ml.x * LOG2E : -CUDART_INF_F;       // exported m is in natural-log units
+            m = fmaxf(m, mg[g]);
+        }
+        if (m == -CUDART_INF_F) m = 0.0f;
+        float l = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const float w = ex2f(mg[g] - m);
+            l = fmaf(w, lg[g], l);
+            acc = fmaf(w, og[g], acc);
+        }
+        const float v = l > 0.0f ? acc / l : 0.0f;
+        const int idx = first + sl;
+        const int r = div_kvg(p, idx);
+        const long oi = b * p.out_batch_stride + ((long)r * p.nh + kvh * p.kvg + (idx - r * p.kvg)) * HD + d;
+        if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
+        else reinterpret_cast<float *>(p.out)[oi] = v;
+    }
+}
+
+// In-kernel tail of every attention CTA: the split merge and, on a sequence-sharded call, the exchange with the
+// other GPUs' shards.
+template <int NSLOT, int HD, int NTHR, int GB = 8>
+__device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t *scratch, int b, int kvh, int rg) {
+    const bool merged = merge_unit_splits<NSLOT, HD, NTHR, GB>(p, scratch, b, kvh, rg);
+    if (merged && p.peer_world > 1) peer_exchange_and_merge<NSLOT, HD, NTHR>(p, b, kvh, rg);
 }
 
 template <int FMT, int HD, int MT, int DS = 1>
@@ -746,7 +830,6 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
     // the stream was still running: wait for the predecessor's memory (the query, freshly
     // appended cache rows, the shared split workspace) before the first global access.  Then let
     // the split-merge grid be set up right away; it blocks the same way until this grid is done.
-    NOMOS_MARK(0);
     // Cache rows the caller declared settled (not written by the stream predecessor) are requested
     // before that wait, so the pipeline fill overlaps the predecessor's tail.
     int early_n = 0;
@@ -761,12 +844,12 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
         const size_t crow = (size_t)kvh * p.cache_cap + (size_t)((p.new_base_pos + i) % p.cache_cap);
         float q8s = 0.0f;
         if constexpr (FMT == KV_I8) {
-            quant_row_i8(src, HD, HD, reinterpret_cast<int8_t *>(scr), reinterpret_cast<float *>(scr + C::ROWB), lane);
+            quant_row_i8_cg(src, HD, HD, reinterpret_cast<int8_t *>(scr), reinterpret_cast<float *>(scr + C::ROWB), lane);
         } else if constexpr (FMT == KV_I4) {
-            const float sc = quant_row_i4(src, HD, HD, scr, nullptr, lane);
+            const float sc = quant_row_i4<true>(src, HD, HD, scr, nullptr, lane);
             if (lane == 0) *reinterpret_cast<float *>(scr + C::ROWB) = sc;
         } else {
-            q8s = quant_row_i4_block32(src, HD, scr, reinterpret_cast<__half *>(scr + C::ROWB), lane);
+            q8s = quant_row_i4_block32<true>(src, HD, scr, reinterpret_cast<__half *>(scr + C::ROWB), lane);
         }
         __syncwarp();
         if (rg == 0 && dsl == 0 && store) {
@@ -804,7 +887,6 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
         if (pass == 1) {
             pdl_wait();
             pdl_launch_dependents();
-            NOMOS_MARK(1);
         }
         // ------------------------------------------------------------ Q prologue
         // Slot sl of this CTA = local row index rg*NSLOT + sl = (query row r, group head j).
@@ -827,7 +909,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
         if (warp == new_owner) quantize_new(0, 0, append_scratch + warp * (C::ROWB + 64), pass == 1);
         if (warp == new_helper) quantize_new(0, 1, append_scratch + warp * (C::ROWB + 64), pass == 1);
 
-        // Each row becomes 15-bit fixed point: q ~= sq * (128*hi + lo), hi/lo int8.
+        // Each row becomes 16-bit fixed point: q ~= sq * (256*hi + lo), hi/lo int8.
     #pragma unroll
         for (int qi = 0; qi < QITER; ++qi) {
             const int sl = warp + qi * NWARP;
@@ -847,8 +929,8 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                 qblk[i] = 0;
                 int qf = __float2int_rn(qx[qi][i] * inv);
                 qf = max(-Q_FIX_MAX, min(Q_FIX_MAX, qf));
-                const int hi = (qf + 64) >> 7;
-                const int lo = qf - (hi << 7);
+                const int hi = (qf + 128) >> 8;
+                const int lo = qf - (hi << 8);
                 int pos = lane + 32 * i;
                 if constexpr (FMT != KV_I8) {
                     // int4 tiles hand element 32b+8t+2j+par of a row to MMA k slot 16*par+4t+j of step b
@@ -918,7 +1000,6 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
         }
     };
 
-    NOMOS_MARK(2);
     // ------------------------------------------------------------ running state
     float M[MT], l[MT];
     float acc[MT][C::NT][2];              // [slot tile][8-dim tile][2 dims] of slot g
@@ -1024,8 +1105,8 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                 const float2 kk = *reinterpret_cast<const float2 *>(ksm + (8 * n + 2 * t) * 4);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    s2[mt][n][0] = (float)(c[mt][n][0] * 128 + c[mt][n][2]) * (qscale[mt] * kk.x);
-                    s2[mt][n][1] = (float)(c[mt][n][1] * 128 + c[mt][n][3]) * (qscale[mt] * kk.y);
+                    s2[mt][n][0] = (float)(c[mt][n][0] * 256 + c[mt][n][2]) * (qscale[mt] * kk.x);
+                    s2[mt][n][1] = (float)(c[mt][n][1] * 256 + c[mt][n][3]) * (qscale[mt] * kk.y);
                 }
             }
         } else {
@@ -1066,8 +1147,8 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                                 const int bias = slot_qsum[(mt * 8 + g) * C::NBLK + blk];
                                 const float f0 = __half2float(*reinterpret_cast<const __half *>(ksm + ((8 * n + 2 * t) * C::NBLK + blk) * 2));
                                 const float f1 = __half2float(*reinterpret_cast<const __half *>(ksm + ((8 * n + 2 * t + 1) * C::NBLK + blk) * 2));
-                                sblk[mt][0] = fmaf((float)(cb[0] * 128 + cb[2] - bias), f0, sblk[mt][0]);
-                                sblk[mt][1] = fmaf((float)(cb[1] * 128 + cb[3] - bias), f1, sblk[mt][1]);
+                                sblk[mt][0] = fmaf((float)(cb[0] * 256 + cb[2] - bias), f0, sblk[mt][0]);
+                                sblk[mt][1] = fmaf((float)(cb[1] * 256 + cb[3] - bias), f1, sblk[mt][1]);
                             }
                         }
                     }
@@ -1077,8 +1158,8 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
                         const int bias = slot_qsum[(mt * 8 + g) * C::NBLK];          // 8 * sum over the whole row
-                        s2[mt][n][0] = (float)(c[mt][0] * 128 + c[mt][2] - bias) * (qscale[mt] * kk.x);
-                        s2[mt][n][1] = (float)(c[mt][1] * 128 + c[mt][3] - bias) * (qscale[mt] * kk.y);
+                        s2[mt][n][0] = (float)(c[mt][0] * 256 + c[mt][2] - bias) * (qscale[mt] * kk.x);
+                        s2[mt][n][1] = (float)(c[mt][1] * 256 + c[mt][3] - bias) * (qscale[mt] * kk.y);
                     }
                 } else {
 #pragma unroll
@@ -1235,7 +1316,6 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
         __syncwarp();
     }
     cp_async_wait<0>();
-    if (warp == 0) NOMOS_MARK(3);
 
     // ---------------------------------------------------- merge warps in shared
 #pragma unroll
@@ -1300,7 +1380,6 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
             pr[HD + 1] = lstar;
         }
     }
-    NOMOS_MARK(4);
     merge_splits_in_kernel<C::NSLOT, HD, NWARP * 32>(p, pipe, b, kvh, rg);
 }
 

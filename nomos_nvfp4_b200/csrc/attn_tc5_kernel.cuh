@@ -10,7 +10,7 @@
 //                            bytes TMA wrote, read transposed by the tensor core)
 //                            x Plimbs[N x 128 keys]   (B, K-major)
 // N = 2 x (padded slots): column s holds the high limb of slot s (a query row x group head),
-// column NSP+s the low limb, for the 15-bit fixed-point query and the 16-bit fixed-point softmax
+// column NSP+s the low limb, for the 16-bit fixed-point query and the 16-bit fixed-point softmax
 // weights alike, so every product is an exact int32.
 // Accumulators live in tensor memory: a softmax warp reads the TMEM lanes 32(w%4)..32(w%4)+31,
 // i.e. thread = one key of the tile for S^T, thread = one output dim for O^T.
@@ -58,24 +58,6 @@ constexpr int MAX_PAGED_TILES = 256;         // paged caches: most tiles (pages)
 #define NOMOS_TC5_WIDE_FROM 9                // slots from which a CTA runs several groups, one CTA per SM; below: one group, two CTAs per SM
 #endif
 
-#ifdef NOMOS_TIMELINE
-// Debug builds only: per-CTA, per-tile wall-clock marks (ns) of the softmax role.
-__device__ unsigned long long g_tc5_tl[320][40][6];
-#define TC5_MARK(tile, slot)                                                                     \
-    do {                                                                                         \
-        const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);         \
-        if ((threadIdx.x & 127) == 0 && threadIdx.x < 32 * Cfg<NS>::NSW && cta_ < 320 && (tile) < 40) g_tc5_tl[cta_][tile][slot] = fused::gtime(); \
-    } while (0)
-__device__ unsigned long long g_tc5_cta[320][16];
-#define TC5_CTA_MARK(slot)                                                                       \
-    do {                                                                                         \
-        const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);         \
-        if (threadIdx.x == 0 && cta_ < 320) g_tc5_cta[cta_][slot] = fused::gtime();              \
-    } while (0)
-#else
-#define TC5_MARK(tile, slot) do {} while (0)
-#define TC5_CTA_MARK(slot) do {} while (0)
-#endif
 
 template <int NS>
 struct Cfg {
@@ -339,7 +321,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, kvh = blockIdx.y;
     const int b = blockIdx.z / p.row_groups, rg = blockIdx.z % p.row_groups;
-    TC5_CTA_MARK(0);
 
     // ------------------------------------------------------------ window and tile schedule
     WindowGeo wg;
@@ -398,7 +379,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    TC5_CTA_MARK(1);
     // Programmatic dependent launch: every thread waits for the stream predecessor before it lets
     // this grid's own dependents be scheduled.  The producer thread first requests the tiles the
     // caller declared settled, and the softmax warps first run their query preparation once on
@@ -495,7 +475,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         __syncwarp();
     } else if (warp < NSW) {
         // =========================================================== softmax warps
-        TC5_CTA_MARK(2);
         const int grp = warp >> 2, wq = warp & 3;        // group, and the TMEM lane quarter this warp may read
         const int kr = threadIdx.x & 127;                // key row of S^T, output dim of O^T
         float *xch = xch_all + grp * 2 * NSP * 4;        // this group's [2][NSP][4] exchange area
@@ -513,8 +492,8 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
         auto fetch_scales = [&](int i) {
             if (!scales_by_tma && i < my_n) {
                 const int row = min(row_base + wg.tile(tile_begin + i).slot0 + kr, last_row);   // rows past the cache are masked anyway
-                ks_next = __ldg(gks + row);
-                vs_next = __ldg(gvs + row);
+                ks_next = __ldcg(gks + row);                 // through L2: the newest rows' scales may have been written
+                vs_next = __ldcg(gvs + row);                 // by the stream predecessor after the warming pass read them
             }
         };
         // The query preparation runs twice.  The first pass starts before the stream-order wait, on
@@ -532,9 +511,8 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 fused::pdl_launch_dependents();
             }
             fetch_scales(grp);                               // in flight while the query rows are prepared
-            // ---- query rows -> two int8 limbs each (15-bit fixed point: q ~= sq * (128 hi + lo)).
+            // ---- query rows -> two int8 limbs each (16-bit fixed point: q ~= sq * (256 hi + lo)).
             // A warp prepares slots warp, warp+4, ...; all their loads are issued before the first use.
-            TC5_CTA_MARK(11);
             constexpr int QPW = (NSP + NSW - 1) / NSW;
             uint32_t qraw[QPW][HD / 32];
             {
@@ -546,17 +524,19 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                     const bool valid = warp + NSW * k < NS && r < p.S;
                     qoff[k] = b * p.q_batch_stride + (valid ? ((long)r * p.nh + kvh * p.kvg + j) * HD : (long)(kvh * p.kvg) * HD) + lane;
                 }
-                // raw bits first, conversions afterwards: every load is in flight before the first use
+                // raw bits first, conversions afterwards: every load is in flight before the first use.  The loads go
+                // through L2 only (ld.global.cg, never the read-only path): the warming pass reads the query while the
+                // stream predecessor (e.g. the producer epilogue rewriting it in place) may still be running.
                 if (p.q_type == ET_BF16) {
     #pragma unroll
                     for (int k = 0; k < QPW; ++k)
     #pragma unroll
-                        for (int i = 0; i < HD / 32; ++i) qraw[k][i] = (uint32_t)__ldg(reinterpret_cast<const uint16_t *>(p.q) + qoff[k] + 32 * i) << 16;
+                        for (int i = 0; i < HD / 32; ++i) qraw[k][i] = (uint32_t)__ldcg(reinterpret_cast<const uint16_t *>(p.q) + qoff[k] + 32 * i) << 16;
                 } else {
     #pragma unroll
                     for (int k = 0; k < QPW; ++k)
     #pragma unroll
-                        for (int i = 0; i < HD / 32; ++i) qraw[k][i] = __ldg(reinterpret_cast<const uint32_t *>(p.q) + qoff[k] + 32 * i);
+                        for (int i = 0; i < HD / 32; ++i) qraw[k][i] = __ldcg(reinterpret_cast<const uint32_t *>(p.q) + qoff[k] + 32 * i);
                 }
             }
             // ---- fused quantize-on-write, early: while the query and the first tiles are in flight, the softmax
@@ -570,7 +550,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                     const int n = pidx >> 1, kv = pidx & 1;
                     uint8_t *scr = sm + C::OFF_NEW + pidx * 144;
                     const float *src = (kv ? p.new_v : p.new_k) + ((size_t)b * p.n_new + n) * p.new_stride + kvh * HD;
-                    quant_row_i8(src, HD, HD, reinterpret_cast<int8_t *>(scr), reinterpret_cast<float *>(scr + 128), lane);
+                    quant_row_i8_cg(src, HD, HD, reinterpret_cast<int8_t *>(scr), reinterpret_cast<float *>(scr + 128), lane);
                     __syncwarp();
                     const float sc_row = *reinterpret_cast<const float *>(scr + 128);
                     if (lane == 0) new_sc[kv * NEW_MAX + n] = sc_row;
@@ -583,7 +563,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                     }
                 }
             }
-            TC5_CTA_MARK(8);
             float qx[QPW][HD / 32];
     #pragma unroll
             for (int k = 0; k < QPW; ++k) {
@@ -592,7 +571,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     #pragma unroll
                 for (int i = 0; i < HD / 32; ++i) qx[k][i] = valid ? __uint_as_float(qraw[k][i]) : 0.0f;
             }
-            TC5_CTA_MARK(12);
     #pragma unroll
             for (int k = 0; k < QPW; ++k) {
                 const int sl = warp + NSW * k;
@@ -610,7 +588,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 for (int i = 0; i < HD / 32; ++i) {
                     int qf = __float2int_rn(qx[k][i] * inv);
                     qf = max(-Q_FIX_MAX, min(Q_FIX_MAX, qf));
-                    const int hi = (qf + 64) >> 7, lo = qf - (hi << 7);
+                    const int hi = (qf + 128) >> 8, lo = qf - (hi << 8);
                     sm[C::OFF_Q + at(sl, lane + 32 * i)] = (uint8_t)(int8_t)hi;
                     sm[C::OFF_Q + at(NSP + sl, lane + 32 * i)] = (uint8_t)(int8_t)lo;
                 }
@@ -633,10 +611,8 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 if (slot_hi[s] > 0) { lo_max = max(lo_max, slot_lo[s]); hi_min = min(hi_min, slot_hi[s]); }
             }
         }
-        TC5_CTA_MARK(10);
         mbar_arrive(bar_q_ready);                        // the MMA issuer starts on the first tile
         bool alive = wait_warp(bar_q_ready, 0);
-        TC5_CTA_MARK(3);
 
         // The loops below are written phase by phase over all slots (loads, then arithmetic, then
         // stores) so that the slots' independent instruction chains overlap: each scheduler of the
@@ -673,9 +649,7 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             const TileGeo g = wg.tile(tile_begin + i);
             const float ks_ld = ks_next, vs_ld = vs_next;
             fetch_scales(i + NG);
-            TC5_MARK(i, 0);
             if (!wait_warp(bar_full(st), (i / NSTG) & 1)) { alive = false; break; }
-            TC5_MARK(i, 1);
             const float *sc = reinterpret_cast<const float *>(sm + C::OFF_SCALES + st * 2 * SCALE_BYTES);
             const int t = g.t0 + kr;
             const bool row_ok = t >= g.t_lo && t < g.t_hi;
@@ -714,7 +688,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             const float lvs = lg2f(vs), rvs = row_ok ? rcpf(vs) : 0.0f;
             if (!wait_warp(bar_s_ready(bf), (i / NB) & 1)) { alive = false; break; }
             tc_fence_after();
-            TC5_MARK(i, 2);
             int sh[NCH][CH], sl_[NCH][CH];
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
@@ -726,8 +699,8 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             // to the tile's largest, the quantity that goes to the tensor core as 16-bit fixed point
             float u[NSG];
 #pragma unroll
-            for (int s = 0; s < NSG; ++s)         // limb sums are below 128 * 127 * 127 < 2^22: the combination fits an int
-                u[s] = fmaf(limbs2f<7>(sh[s / CH][s % CH], sl_[s / CH][s % CH]), slot_qscale[s] * ks, lvs);
+            for (int s = 0; s < NSG; ++s)         // limb sums are below 128 * 128 * 127 < 2^22: the combination fits an int
+                u[s] = fmaf(limbs2f<8>(sh[s / CH][s % CH], sl_[s / CH][s % CH]), slot_qscale[s] * ks, lvs);
             if (need_mask) {
 #pragma unroll
                 for (int s = 0; s < NSG; ++s) {
@@ -746,7 +719,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             if (lane < NSG) xch[(b2 * NSP + lane) * 4 + wq] = mine;
             mbar_arrive(bar_xch(grp, b2));
             if (!wait_warp(bar_xch(grp, b2), xph)) { alive = false; break; }
-            TC5_MARK(i, 3);
             // Per-slot constants of the tile are the same for every key: lane s of each warp works them
             // out for slot s (the running reference R of that slot lives in that lane) and the warp
             // shares them through shared memory, instead of every thread repeating them for every slot.
@@ -798,10 +770,8 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             fused::fence_proxy_async();
             tc_fence_before();
             mbar_arrive(bar_p_ready(bf));
-            TC5_MARK(i, 4);
             if (last_done >= 0 && !epilogue(last_done, fe)) { alive = false; break; }
             last_done = i;
-            TC5_MARK(i, 5);
         }
         if (alive && last_done >= 0) {
             float fe[NSG];
@@ -812,7 +782,6 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
             alive = epilogue(last_done, fe);
         }
 
-        TC5_CTA_MARK(4);
         const int nvalid = min(NS, p.S * p.kvg - rg * NS);
         float *pbase = p.partial + ((size_t)split * p.grows) * (HD + 2) + kr;
         // one slot's row of this thread's dim: the partial (sum, reference, denominator) or the final output
@@ -878,13 +847,10 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
     }
 
     // ------------------------------------------------------------ tear-down
-    TC5_CTA_MARK(5);
     tc_fence_before();
     __syncthreads();
     if (warp == NSW) tmem_dealloc(tmem_base, C::TMEM_COLS);
-    TC5_CTA_MARK(6);
     fused::merge_splits_in_kernel<NS, HD, NTHREADS, 8>(p, sm, b, kvh, rg);
-    TC5_CTA_MARK(7);
 }
 
 }  // namespace tc5

@@ -59,6 +59,12 @@ struct AttnArgs {
     const int *block_table;
     const int *seq_lens;
     int max_pages, n_pages;
+    // sequence-sharded decode across GPUs (peer_world > 1, see nomos_attn_seq_sharded): every rank's mailbox as mapped
+    // in this process, this rank's index, the step number and the wait limit
+    void *peer_box[8];
+    int peer_rank, peer_world;
+    unsigned long long peer_seq;
+    long peer_timeout_us;
     int force_splits;       // 0 = choose; >0 = use exactly this many splits (tests)
     int no_tma;             // 1: keep every tile on the cp.async path
     int no_tcgen05;         // 1: never take the tcgen05 kernel
@@ -67,6 +73,10 @@ struct AttnArgs {
     int fit_splits_to_ws;   // 1: use fewer splits rather than fail when the workspace is small (thin entry points)
 };
 
+// Bytes of one rank's mailbox for `world` sequence shards of `grows` query rows (batch x S x nh) of head dim l_hd:
+// [2 step slots][world][grows][l_hd + 2] fp32 rows, then [2][world][grows] 64-bit stamps.
+long attn_peer_mailbox_rows_bytes(int world, long grows, int l_hd);
+long attn_peer_mailbox_bytes(int world, long grows, int l_hd);
 long attn_workspace_bytes(const AttnArgs &a);
 int attn_kernel_choice(const AttnArgs &a);     // 1: the tcgen05 kernel would serve the call, 0: the mma.sync kernel
 int launch_attn_fused(cudaStream_t st, const AttnArgs &a);
@@ -74,6 +84,7 @@ long attn_paged_workspace_bytes(const AttnArgs &a);
 int launch_attn_paged(cudaStream_t st, const AttnArgs &a);
 // Reads (and optionally clears) the device word the kernels OR into when a bounded wait runs out.
 int read_attn_faults(unsigned int *out, bool clear);
+int clear_attn_fault_bits(unsigned int bits);
 // partials [G][rows][l_hd+2] = (o.., m, l) with m in natural-log units (the exported form)
 int launch_merge_partials(cudaStream_t st, const float *partials, int G, int rows, int l_hd, void *out, int out_type);
 // same, m in log2 units (in-library split partials), fp32 output

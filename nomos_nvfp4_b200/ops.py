@@ -205,22 +205,49 @@ def attention_gpu_bf16_dev(stream, handle, d_q_gpu, d_k_cache_layer, d_v_cache_l
         _addr(d_q_bf16), _addr(d_scores_bf16), _addr(d_attn_out_scratch), nh, nkv, l_hd, cache_hd, max_seq, seq_len, kvg))
 
 
+def attention_prefill_batched_int8(stream, d_q_b, d_q_t, d_scores, d_attn_t, d_attn_b, d_k_i8, d_v_i8, d_k_scale,
+                                   d_v_scale, nh, nkv, l_hd, cache_hd, max_seq, S, kvg, window):
+    """lib/attention_gpu_int8.mojo:804"""
+    _check(_lib.lib().nomos_attn_prefill_batched_i8(
+        _stream(stream), _addr(d_q_b), _addr(d_q_t), _addr(d_scores), _addr(d_attn_t), _addr(d_attn_b),
+        _addr(d_k_i8), _addr(d_v_i8), _addr(d_k_scale), _addr(d_v_scale), nh, nkv, l_hd, cache_hd, max_seq, S, kvg, window))
+
+
 def attention_prefill_prefix_batched_fp32(stream, handle, d_q_b, d_q_t, d_scores, d_attn_t, d_attn_b,
                                           d_k_cache_layer, d_v_cache_layer, nh, nkv, l_hd, cache_hd, max_seq, S,
                                           key_len, kvg, window, query_base_pos, key_base_pos):
-    """lib/batched_attn_gpu.mojo:499"""
-    _check(_lib.lib().nomos_attn_prefix_batched_dense(
-        _stream(stream), _addr(d_q_b), _addr(d_scores), _addr(d_attn_b), _addr(d_k_cache_layer), _addr(d_v_cache_layer),
-        nh, nkv, l_hd, cache_hd, max_seq, S, key_len, kvg, window, query_base_pos, key_base_pos, 0))
+    """lib/batched_attn_gpu.mojo:499 (the cuBLAS ``handle`` is accepted and ignored)"""
+    _check(_lib.lib().nomos_attn_prefix_batched_fp32(
+        _stream(stream), _addr(d_q_b), _addr(d_q_t), _addr(d_scores), _addr(d_attn_t), _addr(d_attn_b),
+        _addr(d_k_cache_layer), _addr(d_v_cache_layer),
+        nh, nkv, l_hd, cache_hd, max_seq, S, key_len, kvg, window, query_base_pos, key_base_pos))
 
 
 def attention_prefill_prefix_batched_bf16(stream, handle, d_q_b, d_q_t, d_q_t_bf16, d_scores, d_scores_bf16, d_attn_t,
                                           d_attn_b, d_k_cache_layer, d_v_cache_layer, nh, nkv, l_hd, cache_hd, max_seq,
                                           S, key_len, kvg, window, query_base_pos, key_base_pos):
     """lib/batched_attn_gpu.mojo:613"""
-    _check(_lib.lib().nomos_attn_prefix_batched_dense(
-        _stream(stream), _addr(d_q_b), _addr(d_scores), _addr(d_attn_b), _addr(d_k_cache_layer), _addr(d_v_cache_layer),
-        nh, nkv, l_hd, cache_hd, max_seq, S, key_len, kvg, window, query_base_pos, key_base_pos, 1))
+    _check(_lib.lib().nomos_attn_prefix_batched_bf16(
+        _stream(stream), _addr(d_q_b), _addr(d_q_t), _addr(d_q_t_bf16), _addr(d_scores), _addr(d_scores_bf16),
+        _addr(d_attn_t), _addr(d_attn_b), _addr(d_k_cache_layer), _addr(d_v_cache_layer),
+        nh, nkv, l_hd, cache_hd, max_seq, S, key_len, kvg, window, query_base_pos, key_base_pos))
+
+
+def attention_prefill_batched_fp32(stream, handle, d_q_b, d_q_t, d_scores, d_attn_t, d_attn_b, d_k_cache_layer,
+                                   d_v_cache_layer, nh, nkv, l_hd, cache_hd, max_seq, S, kvg, window):
+    """lib/batched_attn_gpu.mojo:448"""
+    _check(_lib.lib().nomos_attn_prefill_batched_fp32(
+        _stream(stream), _addr(d_q_b), _addr(d_q_t), _addr(d_scores), _addr(d_attn_t), _addr(d_attn_b),
+        _addr(d_k_cache_layer), _addr(d_v_cache_layer), nh, nkv, l_hd, cache_hd, max_seq, S, kvg, window))
+
+
+def attention_prefill_batched_bf16(stream, handle, d_q_b, d_q_t, d_q_t_bf16, d_scores, d_scores_bf16, d_attn_t, d_attn_b,
+                                   d_k_cache_layer, d_v_cache_layer, nh, nkv, l_hd, cache_hd, max_seq, S, kvg, window):
+    """lib/batched_attn_gpu.mojo:558"""
+    _check(_lib.lib().nomos_attn_prefill_batched_bf16(
+        _stream(stream), _addr(d_q_b), _addr(d_q_t), _addr(d_q_t_bf16), _addr(d_scores), _addr(d_scores_bf16),
+        _addr(d_attn_t), _addr(d_attn_b), _addr(d_k_cache_layer), _addr(d_v_cache_layer),
+        nh, nkv, l_hd, cache_hd, max_seq, S, kvg, window))
 
 
 # ----------------------------------------------------------------------- fused

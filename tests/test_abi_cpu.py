@@ -125,3 +125,33 @@ def test_fused_args_validation(lib):
     with pytest.raises(ops.NomosError) as e:
         ops.attn_fused(0, a)
     assert e.value.status == -1
+
+
+def test_planning_calls_refuse_a_zero_capacity(lib):
+    """A zero-initialised argument block (cache_cap = 0) is a bad argument for the planning entry points and for
+    the workspace-free call, not a division by zero inside the planner."""
+    from nomos_nvfp4_b200 import ops
+    a = ops.make_args(q=0x1000, k_cache=0x10000, v_cache=0x20000, k_scales=0x30000, v_scales=0x40000, out=0x50000,
+                      nh=32, nkv=16, kvg=2, l_hd=128, cache_hd=128, cache_cap=0, klen=2048)
+    for call in (ops.attn_workspace_bytes, ops.attn_kernel_choice, lambda x: ops.attn_fused_static_ws(0, x),
+                 lambda x: ops.attn_fused(0, x)):
+        with pytest.raises(ops.NomosError) as e:
+            call(a)
+        assert e.value.status == -1
+    a.cache_cap, a.win_start = 4096, -1
+    with pytest.raises(ops.NomosError) as e:
+        ops.attn_workspace_bytes(a)
+    assert e.value.status == -1
+
+
+def test_prefix_operator_ranges(lib):
+    """The prefix-batched int8 operator: ranges the decode-order kernel cannot express are refused with -2 rather
+    than computed wrongly; negative positions are bad arguments."""
+    from nomos_nvfp4_b200 import ops
+    P = 0x1000
+    with pytest.raises(ops.NomosError) as e:   # key array longer than the row pitch
+        ops.attention_prefill_prefix_batched_int8(0, P, 0, P, 0, P, P, P, P, P, 8, 4, 128, 128, 64, 4, 65, 2, 0, 61, 0)
+    assert e.value.status == -3
+    with pytest.raises(ops.NomosError) as e:
+        ops.attention_prefill_prefix_batched_int8(0, P, 0, P, 0, P, P, P, P, P, 8, 4, 128, 128, 64, 4, 20, 2, 0, -1, 0)
+    assert e.value.status == -1

@@ -163,7 +163,7 @@ def test_decode_i8_peaked_and_flat_softmax(oracle):
     nh, nkv, hd, T = 8, 4, 128, 3000
     c = build_cache("i8", rng, T, nkv, hd)
     # gain 1: unscaled N(0,1) logits (std ~11, one key dominates); gain 1e-3: flat softmax.
-    # gain 3 (logit std ~34) is far outside anything the model produces; there the 15-bit
+    # gain 3 (logit std ~34) is far outside anything the model produces; there the 16-bit
     # fixed-point query (relative step 2^-15 of the row maximum) shows, so the bar is looser.
     for gain, tol in ((1.0, TOL), (1e-3, TOL), (3.0, 1e-2)):
         q = bf16_normal(rng, (1, nh, hd)) * np.float32(gain)
@@ -474,7 +474,7 @@ def test_query_rows_of_very_different_magnitude(oracle, S, big):
     """Query rows that share a CTA (the heads of a GQA group, the tokens of a verify step) but differ in
     magnitude by 30x .. 1000x: every row is quantised with its own fixed-point scale, so each must pass the
     gate separately, against its own RMS.  The softmax scale keeps the largest rows' logits moderate
-    (standard deviation about 7): beyond that the 15-bit query itself limits any kernel."""
+    (standard deviation about 7): beyond that the 16-bit query itself limits any kernel."""
     rng = np.random.default_rng(int(S * 1000 + big))
     nh, nkv, hd, T0 = 4, 2, 128, 1500
     T = T0 + S

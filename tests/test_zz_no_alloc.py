@@ -3,10 +3,11 @@
 Some callers of the library have no buffer to pass as split workspace: an engine that hands its
 whole device-memory budget out at start-up, or a decode loop that must never call the allocator.
 For them the library carries a fixed 4 MiB scratch array.  This file checks, through the C ABI,
-that the workspace-free call gives the same attention output as the regular call (same 2e-3 x RMS
-bar as the other GPU tests, against the regular entry point's output), twice in a row so that the
-second call runs over the scratch contents the first one left behind, and that an oversized
-request is refused instead of overrunning the array.  It is named to be collected last.
+that the workspace-free call gives the same attention output as the regular call and as the CPU
+oracle's exact attention over the same cache (the 2e-3 x RMS bar of the other GPU tests, both
+times), twice in a row so that the second call runs over the scratch contents the first one left
+behind, and that an oversized request is refused instead of overrunning the array.  It is named
+to be collected last.
 """
 import numpy as np
 import pytest
@@ -15,7 +16,7 @@ import torch
 from nomos_nvfp4_b200 import ops
 from tests._cases import bf16_normal
 from tests._gpu import DEV, dev, host, within
-from tests.test_gpu_attn import build_cache
+from tests.test_gpu_attn import build_cache, exact
 
 pytestmark = pytest.mark.gpu
 
@@ -29,7 +30,7 @@ def _args(c, q, out, T, scale):
     return a, keep
 
 
-def test_static_workspace_matches_regular_entry_point_twice():
+def test_static_workspace_matches_regular_entry_point_twice(oracle):
     rng = np.random.default_rng(4242)
     nh, nkv, hd = 32, 16, 128
     for call, T in enumerate((6000, 3500)):               # two calls in a row; both split the sequence
@@ -49,6 +50,8 @@ def test_static_workspace_matches_regular_entry_point_twice():
         torch.cuda.synchronize()
         ok, rel = within(host(got), host(want), 2e-3)
         assert ok, f"call {call}: static-workspace output differs by {rel:.2e} x RMS"
+        ok, rel = within(host(got), exact(oracle, c, q, klen=T, scale=scale), 2e-3)
+        assert ok, f"call {call}: static-workspace output is {rel:.2e} x RMS from the oracle"
         assert not np.any(host(got) == -1e30), "output not fully written"
 
 
