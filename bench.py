@@ -406,6 +406,13 @@ def run_ours(args) -> dict:
         result["cpu_baseline"] = cpu_reference_leg()
     if not args.no_extras:
         result["extras"] = extras(torch, dist, ops, dev, rank, world)
+        # the two long-context curves of configuration 5 at the top level: c5a has no collective (KV-head groups),
+        # c5b exchanges (o, m, l) between the ranks inside the timed step (strong scaling: the job is fixed)
+        for key, name in (("c5a_batch8_131k_head_sharded", "c5a"), ("c5b_seq_sharded_512k", "c5b")):
+            e = result["extras"].get(key, {})
+            if "us_per_layer" in e:
+                result[name] = {"us_per_layer": e["us_per_layer"], "n_gpus": N, "scaling": "strong",
+                                "GBps_aggregate": e.get("GBps_aggregate")}
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -456,6 +463,16 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
         by = algorithmic_bytes(NKV, NH // NKV, T4, HD, 1, S)
         out["c4_verify_vb9_16k"] = {"us_per_layer": round(us, 2), "GBps": round(by / us / 1e3, 1),
                                     "attn_only_tok_per_s_60_layers": round(S / (60 * us * 1e-6), 1)}
+        if rank == 0:          # parity of the timed call (fp32 output, layer 0) against the oracle, every row against its own RMS
+            from oracle import oracle as orc
+            o32 = torch.zeros((1, S, NH, HD), dtype=torch.float32, device=dev)
+            al[0].out, al[0].out_type = o32.data_ptr(), ops.F32
+            ops.attn_fused(stream, al[0]); torch.cuda.synchronize()
+            k0, v0, ks0, vs0 = (t[0].cpu().numpy() for t in caches[0])
+            want = orc.attn_exact(q[0].float().cpu().numpy(), k0, v0, ks0, vs0, orc.KV_I8, NH, NKV, HD, HD, T4, S=S,
+                                  query_base_pos=T4 - S, softmax_scale=float(SOFTMAX_SCALE))
+            got = o32[0].cpu().numpy()
+            out["c4_verify_vb9_16k"]["parity_rel_err"] = float(f"{max(rel_err(got[r], want[r]) for r in range(S)):.3e}")
         del caches, ws
     except Exception as e:   # report, never hide
         out["c4_verify_vb9_16k"] = {"error": str(e)}
@@ -636,40 +653,98 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
         del kp, vp, ksp, vsp, ws
     except Exception as e:
         out["c5a_paged_batch8_131k"] = {"error": str(e)}
-    # configuration 5b: batch 1 x 524288 keys, sharded by sequence chunks, (o, m, l) all-gathered and merged
+    # configuration 5b: batch 1 x 524288 keys, sharded by sequence chunks.  Two realisations of the exchange:
+    #   "nccl": attention exports (o, m, l), NCCL all-gather of 16.6 KB per rank (torch.distributed), merge kernel;
+    #   "peer": nomos_attn_seq_sharded -- one launch per rank: the attention kernel stores its rows into the peers'
+    #           mailboxes over NVLink, waits for theirs and merges.
+    # Both are checked against the oracle: every rank computes the exact fp64 partial of its own chunk on the host,
+    # the partials are gathered on the host and merged by the oracle.
     try:
+        from nomos_nvfp4_b200.sharding import SeqShardGroup
         T5 = 524288 // world
         cache = make_layer_cache(torch, ops, dev, 1, NKV, T5, HD, 1005 + rank)
-        q = torch.randn((1, 1, NH, HD), device=dev).to(torch.bfloat16)
-        if world > 1:
-            dist.broadcast(q, 0)
+        qh = np.random.default_rng(5005).standard_normal((1, 1, NH, HD), dtype=np.float32)
+        q = torch.from_numpy(qh).to(dev).to(torch.bfloat16)
         o = torch.zeros((NH, HD), dtype=torch.bfloat16, device=dev)
         part = torch.zeros((NH, HD + 2), dtype=torch.float32, device=dev)
         gathered = torch.zeros((world, NH, HD + 2), dtype=torch.float32, device=dev)
         k, v, ks, vs = cache
-        a = ops.make_args(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, partial_out=part, kv_fmt=ops.KV_I8,
-                          q_type=ops.BF16, nh=NH, nkv=NKV, kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=T5, klen=T5,
-                          softmax_scale=SOFTMAX_SCALE)
+        common = dict(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, kv_fmt=ops.KV_I8, q_type=ops.BF16, nh=NH, nkv=NKV,
+                      kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=T5, klen=T5, softmax_scale=SOFTMAX_SCALE, flags=ops.SETTLED_CACHE)
+        a = ops.make_args(partial_out=part, **common)
         wsb = ops.attn_workspace_bytes(a)
         ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
         a.workspace, a.ws_bytes = ws.data_ptr(), wsb
 
-        def fn():
-            ops.attn_fused(stream, a)
+        def gather():
             if world > 1:
                 dist.all_gather_into_tensor(gathered, part)
             else:
                 gathered.copy_(part.unsqueeze(0))
+
+        def fn():
+            ops.attn_fused(stream, a)
+            gather()
             ops.attn_merge_partials(stream, gathered, world, NH, HD, o, ops.BF16)
 
-        us = time_call(torch, fn, max(10, iters // 4))
+        n5 = max(10, iters // 4)
+        us = time_call(torch, fn, n5)
+        # the three phases bracketed by events (this serialises them; the sum can exceed the pipelined step time)
+        ph = np.zeros(3)
+        for _ in range(n5):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record(); ops.attn_fused(stream, a); ev[1].record(); gather(); ev[2].record()
+            ops.attn_merge_partials(stream, gathered, world, NH, HD, o, ops.BF16); ev[3].record()
+            torch.cuda.synchronize()
+            ph += np.array([ev[i].elapsed_time(ev[i + 1]) for i in range(3)]) * 1000.0 / n5
+        # peer-memory variant
+        o2 = torch.zeros((NH, HD), dtype=torch.bfloat16, device=dev)
+        a2 = ops.make_args(out=o2, out_type=ops.BF16, **common)
+        a2.workspace, a2.ws_bytes = ws.data_ptr(), wsb
+
+        def agb(b):
+            if world == 1:
+                return [b]
+            lst = [None] * world
+            dist.all_gather_object(lst, b)
+            return lst
+
+        group = SeqShardGroup(rank, world, NH, HD, agb)
         if world > 1:
-            tt = torch.tensor([us], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX); us = float(tt.item())
+            dist.barrier()
+        us_peer = time_call(torch, lambda: group.decode(stream, a2), n5)
+        peer_rc = group.status(stream)
+        if world > 1:
+            tt = torch.tensor([us, us_peer, *ph], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            us, us_peer, ph = float(tt[0]), float(tt[1]), tt[2:].cpu().numpy()
+        # parity of both variants (fp32 outputs of one more step each) against the oracle
+        o32 = torch.zeros((NH, HD), dtype=torch.float32, device=dev); o32p = torch.zeros_like(o32)
+        ops.attn_fused(stream, a); gather(); ops.attn_merge_partials(stream, gathered, world, NH, HD, o32, ops.F32)
+        a2.out, a2.out_type = o32p.data_ptr(), ops.F32
+        group.decode(stream, a2)
+        peer_rc = peer_rc or group.status(stream)
+        from oracle import oracle as orc
+        orc.set_threads(max(1, (os.cpu_count() or 1) // world))
+        _, pe = orc.attn_exact(orc.bf16_round(qh[0]), k[0].cpu().numpy(), v[0].cpu().numpy(), ks[0].cpu().numpy(), vs[0].cpu().numpy(),
+                               orc.KV_I8, NH, NKV, HD, HD, T5, query_base_pos=T5 - 1, softmax_scale=float(SOFTMAX_SCALE), want_partial=True)
+        parts = [pe]
+        if world > 1:
+            parts = [None] * world
+            dist.all_gather_object(parts, pe)
+        want = orc.merge_partials(np.stack(parts), HD)
         by = algorithmic_bytes(NKV, NH // NKV, 524288, HD)
-        out["c5b_seq_sharded_512k"] = {"us_per_layer": round(us, 2), "GBps_aggregate": round(by / us / 1e3, 1), "gpus": world}
+        out["c5b_seq_sharded_512k"] = {
+            "us_per_layer": round(min(us, us_peer), 2), "GBps_aggregate": round(by / min(us, us_peer) / 1e3, 1), "gpus": world,
+            "nccl_allgather_plus_merge": {"us_per_layer": round(us, 2), "phases_us": {"attention": round(float(ph[0]), 2),
+                                          "all_gather": round(float(ph[1]), 2), "merge": round(float(ph[2]), 2)},
+                                          "parity_rel_err": float(f"{rel_err(o32.cpu().numpy(), want):.3e}")},
+            "peer_stores_one_launch": {"us_per_layer": round(us_peer, 2), "status": int(peer_rc),
+                                       "parity_rel_err": float(f"{rel_err(o32p.cpu().numpy(), want):.3e}")},
+            "parity_bar": 2e-3}
+        group.close()
         del cache, ws
     except Exception as e:
-        out["c5b_seq_sharded_512k"] = {"error": str(e)}
+        out["c5b_seq_sharded_512k"] = {"error": repr(e)}
     return out
 
 

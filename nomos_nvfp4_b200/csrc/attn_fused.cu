@@ -249,7 +249,7 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     // a sequence-sharded call always ends in the unit's merging CTA (it runs the exchange), also with one split
     const bool in_kernel_merge = pl.splits > 1 || a.peer_world > 1;
     const long need = in_kernel_merge ? part_bytes + units * 8 : 0;
-    if (query_ws) { *ws_needed = need; return NOMOS_OK; }
+    if (query_ws) { *ws_needed = part_bytes + units * 8; return NOMOS_OK; }   // also enough for a sequence-sharded call, which merges in the kernel even with one split
     if (need > a.ws_bytes || (need > 0 && a.workspace == nullptr)) {
         set_error("attention workspace too small: need %ld bytes, have %ld", need, a.ws_bytes);
         return NOMOS_ECAPACITY;
@@ -446,7 +446,7 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     const long part_bytes = (((long)pl.splits * pl.grows * (a.l_hd + 2) * 4) + 15) / 16 * 16;
     const bool in_kernel_merge = pl.splits > 1 || a.peer_world > 1;
     const long need = in_kernel_merge ? part_bytes + units * 8 : 0;
-    if (query_ws) { *ws_needed = need; return NOMOS_OK; }
+    if (query_ws) { *ws_needed = part_bytes + units * 8; return NOMOS_OK; }   // also enough for a sequence-sharded call, which merges in the kernel even with one split
     if (need > a.ws_bytes || (need > 0 && a.workspace == nullptr)) {
         set_error("attention workspace too small: need %ld bytes, have %ld", need, a.ws_bytes);
         return NOMOS_ECAPACITY;

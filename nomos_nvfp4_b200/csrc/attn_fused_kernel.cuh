@@ -585,6 +585,8 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
 // Mailboxes have two step slots (step & 1): a rank can be at most one step ahead of a peer it exchanged with,
 // so the slot a push overwrites was consumed two steps ago.  Nothing here is multicast, and no thread waits
 // without a limit.
+// (p is the kernels' __grid_constant__ parameter block: its address can be handed to this out-of-line function
+// without the compiler keeping a per-thread copy of it.)
 template <int NSLOT, int HD, int NTHR>
 __device__ __noinline__ void peer_exchange_and_merge(const KParams &p, int b, int kvh, int rg) {
     __shared__ int s_peer_ok;
@@ -595,7 +597,7 @@ __device__ __noinline__ void peer_exchange_and_merge(const KParams &p, int b, in
     const size_t blk = (size_t)p.grows * (HD + 2);                   // floats of one (slot, source rank) block
     auto grow_of = [&](int sl) {
         const int idx = first + sl;
-        const int r = div_kvg(p, idx);
+        const int r = p.kvg_magic ? (int)__umulhi((unsigned)idx, p.kvg_magic) : idx;
         return ((long)b * p.S + r) * p.nh + kvh * p.kvg + (idx - r * p.kvg);
     };
     if (tid == 0) s_peer_ok = 1;
@@ -662,7 +664,7 @@ __device__ __noinline__ void peer_exchange_and_merge(const KParams &p, int b, in
         }
         const float v = l > 0.0f ? acc / l : 0.0f;
         const int idx = first + sl;
-        const int r = div_kvg(p, idx);
+        const int r = p.kvg_magic ? (int)__umulhi((unsigned)idx, p.kvg_magic) : idx;
         const long oi = b * p.out_batch_stride + ((long)r * p.nh + kvh * p.kvg + (idx - r * p.kvg)) * HD + d;
         if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
         else reinterpret_cast<float *>(p.out)[oi] = v;
@@ -679,7 +681,7 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
 
 template <int FMT, int HD, int MT, int DS = 1>
 __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
-    attn_fused_kernel(const KParams p, const __grid_constant__ TmaMaps tm) {
+    attn_fused_kernel(const __grid_constant__ KParams p, const __grid_constant__ TmaMaps tm) {
     using C = Cfg<FMT, HD, MT, DS>;
     constexpr int HDV = C::HDV;
     constexpr int NWARP = C::NW;

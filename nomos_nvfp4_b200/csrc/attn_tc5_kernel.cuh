@@ -287,7 +287,7 @@ __device__ __noinline__ void group_outputs(const TailArgs a, const float *stage,
 
 template <int NS>
 __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
-    attn_tc5_kernel(const KParams p, const __grid_constant__ TmaMaps4 tm) {
+    attn_tc5_kernel(const __grid_constant__ KParams p, const __grid_constant__ TmaMaps4 tm) {
     using C = Cfg<NS>;
     constexpr int NSP = C::NSP, NSTG = C::NSTG;
     constexpr int NG = C::NG, NB = C::NB, LAG = C::LAG, NSW = C::NSW, NTHREADS = C::NTHREADS;

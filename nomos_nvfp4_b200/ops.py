@@ -15,7 +15,7 @@ from __future__ import annotations
 import ctypes as C
 
 from . import _lib
-from ._lib import AttnArgs
+from ._lib import AttnArgs, AttnPeer
 
 KV_I8, KV_I4, KV_I4B32 = 0, 1, 2
 F32, BF16 = 0, 1
@@ -358,3 +358,54 @@ def attn_fused_static_ws(stream, args: AttnArgs) -> None:
 
 def attn_merge_partials(stream, partials, G, rows, l_hd, out, out_type=F32) -> None:
     _check(_lib.lib().nomos_attn_merge_partials(_stream(stream), _addr(partials), G, rows, l_hd, _addr(out), out_type))
+
+
+# ------------------------------------------------- sequence-sharded decode across GPUs
+
+def attn_peer_mailbox_bytes(world: int, rows: int, l_hd: int) -> int:
+    n = _lib.lib().nomos_attn_peer_mailbox_bytes(world, rows, l_hd)
+    if n < 0:
+        _check(int(n))
+    return int(n)
+
+
+def attn_peer_mailbox_create(nbytes: int) -> tuple[int, bytes]:
+    """Allocates and zeroes one rank's mailbox; returns (device address, 64-byte interprocess handle)."""
+    ptr = C.c_uint64(0)
+    handle = C.create_string_buffer(64)
+    _check(_lib.lib().nomos_attn_peer_mailbox_create(int(nbytes), C.byref(ptr), handle))
+    return int(ptr.value), handle.raw
+
+
+def attn_peer_mailbox_open(handle: bytes) -> int:
+    ptr = C.c_uint64(0)
+    buf = C.create_string_buffer(handle, 64)
+    _check(_lib.lib().nomos_attn_peer_mailbox_open(buf, C.byref(ptr)))
+    return int(ptr.value)
+
+
+def attn_peer_mailbox_close(ptr: int, own: bool) -> None:
+    _check(_lib.lib().nomos_attn_peer_mailbox_close(int(ptr), 1 if own else 0))
+
+
+def make_peer(rank: int, world: int, mailboxes, mailbox_bytes: int, step: int, timeout_us: int = 0) -> AttnPeer:
+    p = AttnPeer()
+    p.struct_bytes = C.sizeof(AttnPeer)
+    p.rank, p.world, p.mailbox_bytes, p.step, p.timeout_us = rank, world, mailbox_bytes, step, timeout_us
+    for g, m in enumerate(mailboxes):
+        p.mailbox[g] = _addr(m)
+    return p
+
+
+def attn_seq_sharded(stream, args: AttnArgs, peer: AttnPeer) -> None:
+    """One rank's call of the sequence-sharded decode: attention over this rank's chunk, exchange of the (o, m, l)
+    rows through the peers' mailboxes and the final merge, in one launch (include/nomos_attn.h)."""
+    _check(_lib.lib().nomos_attn_seq_sharded(_stream(stream), C.byref(args), C.byref(peer)))
+
+
+def attn_seq_sharded_status(stream, clear: bool = False) -> int:
+    """Synchronises the stream; 0, or -4 when a peer's rows did not arrive in time (raises for other errors)."""
+    rc = _lib.lib().nomos_attn_seq_sharded_status(_stream(stream), 1 if clear else 0)
+    if rc not in (0, -4):
+        _check(rc)
+    return int(rc)

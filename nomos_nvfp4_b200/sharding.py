@@ -5,9 +5,11 @@ The reference is single-GPU; these two partitions are the multi-GPU surface of t
 * KV-head groups: rank g owns ``nkv/G`` KV heads (and their ``kvg`` query heads) of every
   sequence.  Outputs are disjoint slices of ``[nh, l_hd]``; no collective is needed.
 * Sequence chunks (batch 1, long context): rank g owns a contiguous run of cached positions and
-  produces un-normalised partials ``(o, m, l)`` per query head; the partials are all-gathered and
-  merged (``nomos_attn_merge_partials``).  Chunk boundaries fall on multiples of 32 positions so
-  every rank's kernel streams whole tiles.
+  produces un-normalised partials ``(o, m, l)`` per query head.  Either the partials are all-gathered
+  by a collective library and merged by ``nomos_attn_merge_partials``, or -- ``SeqShardGroup`` -- every
+  rank's attention kernel stores them into the peers' mailboxes itself and merges what arrives
+  (``nomos_attn_seq_sharded``: one launch per rank and step).  Chunk boundaries fall on multiples of
+  32 positions so every rank's kernel streams whole tiles.
 """
 from __future__ import annotations
 
@@ -50,3 +52,37 @@ def sequence_shard(klen: int, world: int, rank: int, align: int = 32) -> tuple[i
     begin = min(klen, rank * per * align)
     end = min(klen, (rank + 1) * per * align)
     return begin, end - begin
+
+
+class SeqShardGroup:
+    """Mailboxes and step counter of one sequence-sharded decode group (one process per GPU).
+
+    ``all_gather_bytes(b: bytes) -> list[bytes]`` exchanges a byte string between the ranks on the host, in rank
+    order (e.g. ``torch.distributed.all_gather_object``); it is used once, to pass the mailbox handles round.
+    Every rank must make every ``decode`` call: the step counter advances in lockstep."""
+
+    def __init__(self, rank: int, world: int, rows: int, l_hd: int, all_gather_bytes, timeout_us: int = 0):
+        from . import ops
+        self._ops, self.rank, self.world, self.timeout_us = ops, rank, world, timeout_us
+        self.step = 0
+        self.mailbox_bytes = ops.attn_peer_mailbox_bytes(world, rows, l_hd)
+        self.own, handle = ops.attn_peer_mailbox_create(self.mailbox_bytes)
+        handles = all_gather_bytes(handle)
+        if len(handles) != world:
+            raise ValueError(f"expected {world} mailbox handles, got {len(handles)}")
+        self.mailboxes = [self.own if g == rank else ops.attn_peer_mailbox_open(handles[g]) for g in range(world)]
+
+    def decode(self, stream, args) -> None:
+        """Attention over this rank's chunk + exchange + merge; the final output lands in ``args.out`` on every rank."""
+        self.step += 1
+        peer = self._ops.make_peer(self.rank, self.world, self.mailboxes, self.mailbox_bytes, self.step, self.timeout_us)
+        self._ops.attn_seq_sharded(stream, args, peer)
+
+    def status(self, stream, clear: bool = False) -> int:
+        return self._ops.attn_seq_sharded_status(stream, clear)
+
+    def close(self) -> None:
+        for g, m in enumerate(self.mailboxes):
+            if m:
+                self._ops.attn_peer_mailbox_close(m, g == self.rank)
+        self.mailboxes = []
