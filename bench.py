@@ -56,6 +56,14 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
+def measured_peak_tflops() -> float:
+    p = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(p.read_text())["bf16_tflops"])
+    except Exception:
+        return 1590.0
+
+
 # --------------------------------------------------------------------- clocks
 
 class ClockSampler:
@@ -476,6 +484,45 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
         del caches, ws
     except Exception as e:   # report, never hide
         out["c4_verify_vb9_16k"] = {"error": str(e)}
+    # prefill: 2048 prompt tokens, 32q/16kv x 128, int8 KV already appended; causal attention over the quantised
+    # cache on the query-major tcgen05 kernel (no S x S score matrix), and the same call as mma.sync row groups
+    try:
+        Sp = 2048
+        cache = make_layer_cache(torch, ops, dev, 1, NKV, Sp, HD, 1404)
+        qh = np.random.default_rng(1404).standard_normal((1, Sp, NH, HD), dtype=np.float32)
+        q = torch.from_numpy(qh).to(dev).to(torch.bfloat16)
+        o = torch.zeros((1, Sp, NH, HD), dtype=torch.bfloat16, device=dev)
+        k, v, ks, vs = cache
+        res = {}
+        for name, fl in (("tcgen05_query_major", 0), ("mma_sync_row_groups", ops.NO_TCGEN05)):
+            a = ops.make_args(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=o, kv_fmt=ops.KV_I8, q_type=ops.BF16,
+                              out_type=ops.BF16, S=Sp, nh=NH, nkv=NKV, kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=Sp, klen=Sp,
+                              softmax_scale=SOFTMAX_SCALE, flags=fl)
+            wsb = ops.attn_workspace_bytes(a)
+            ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+            a.workspace, a.ws_bytes = ws.data_ptr(), wsb
+            us = time_call(torch, lambda: ops.attn_fused(stream, a), max(10, iters // 8))
+            flops = 4.0 * NH * HD * (Sp * (Sp + 1) / 2.0)           # QK and PV over the causal half
+            res[name] = {"us": round(us, 1), "TFLOPs_causal": round(flops / us / 1e6, 1), "kernel_choice": ops.attn_kernel_choice(a)}
+            if rank == 0 and fl == 0:
+                from oracle import oracle as orc
+                o32 = torch.zeros((1, Sp, NH, HD), dtype=torch.float32, device=dev)
+                a.out, a.out_type = o32.data_ptr(), ops.F32
+                ops.attn_fused(stream, a); torch.cuda.synchronize()
+                a.out, a.out_type = o.data_ptr(), ops.BF16
+                got = o32[0].cpu().numpy()
+                hk, hv, hks, hvs = (t[0].cpu().numpy() for t in cache)
+                worst = 0.0
+                for srow in (0, 1, 63, 64, 127, 128, 1000, 1023, 1024, 2047):
+                    want = orc.attn_exact(orc.bf16_round(qh[0, srow:srow + 1]), hk, hv, hks, hvs, orc.KV_I8, NH, NKV, HD, HD, Sp, S=1,
+                                          query_base_pos=srow, softmax_scale=float(SOFTMAX_SCALE))
+                    worst = max(worst, rel_err(got[srow], want[0]))
+                res[name]["parity_rel_err_sampled_rows"] = float(f"{worst:.3e}")
+        res["tensor_peak_fraction"] = round(res["tcgen05_query_major"]["TFLOPs_causal"] / measured_peak_tflops(), 4)
+        out["prefill_s2048_i8"] = res
+        del cache
+    except Exception as e:
+        out["prefill_s2048_i8"] = {"error": repr(e)}
     # configuration 3: sliding-window layer, ring of 1024 at position 8191, int4 block-32, fused append
     try:
         W, pos = 1024, 8191

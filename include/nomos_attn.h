@@ -360,11 +360,14 @@ int32_t nomos_kv_ring_fill_args(const nomos_kv_ring_t *ring, const nomos_kv_step
 
 /* Bytes of workspace the call needs (>= 0), or a negative status. */
 int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args);
-/* Which kernel nomos_attn_fused would run for these arguments: 1 = the tcgen05 / tensor-memory kernel,
- * 0 = the mma.sync kernel, negative = status.  Both serve int8 caches at head_dim 128; the library picks by
- * a measured cost model (the tcgen05 kernel for verify, paged caches and calls streaming more than about
- * 240 MB; the other for shorter decode calls), and the NOMOS_ATTN_NO_TCGEN05 / NOMOS_ATTN_TCGEN05_ALWAYS flag
- * bits override it.  No reference counterpart (lib/attention_gpu_int8.mojo has a single kernel chain). */
+/* Which kernel nomos_attn_fused would run for these arguments: 2 = the query-major prefill kernel (tcgen05, 128
+ * query rows per CTA: int8 caches at head_dim 128 with more than 24 query rows per KV head), 1 = the tcgen05 /
+ * tensor-memory decode and verify kernel, 0 = the mma.sync kernel, negative = status.  Kernels 1 and 0 both serve
+ * int8 caches at head_dim 128 for up to 24 rows per KV head; the library picks by a measured cost model (the tcgen05
+ * kernel for verify, paged caches and calls streaming more than about 240 MB; the other for shorter decode calls), and
+ * the NOMOS_ATTN_NO_TCGEN05 / NOMOS_ATTN_TCGEN05_ALWAYS flag bits override it (NO_TCGEN05 also keeps prefill-sized calls
+ * on the mma.sync kernel, as row groups).  No reference counterpart (lib/attention_gpu_int8.mojo has a single kernel
+ * chain). */
 int32_t nomos_attn_kernel_choice(const nomos_attn_args_t *args);
 /* Run it. */
 int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *args);

@@ -353,11 +353,22 @@ NOMOS_EXPORT int32_t nomos_attn_prefill_batched_i8(void *stream, uint64_t q_b, u
                                         cache_hd, max_seq, S, S, kvg, window, 0, 0);
 }
 
-// Prefix ranges the decode-order kernels cannot express (see prefix_klen).
-static int run_prefill_general(cudaStream_t, AttnArgs &, const char *who, int S, int key_len, int, int query_base_pos, int key_base_pos) {
-    set_error("%s: key range [%d, %d) must reach the last query row (position %d) and start at or before the first", who, key_base_pos,
-              key_base_pos + key_len, query_base_pos + S - 1);
-    return NOMOS_EUNSUPPORTED;
+// Prefix ranges the decode-order kernels cannot express (see prefix_klen): the query-major prefill kernel takes
+// the operator's bounds as they are (row s attends key indices up to min(d0 + s, key_len - 1), d0 = query_base_pos -
+// key_base_pos, possibly negative; rows without a key get zeros).
+static int run_prefill_general(cudaStream_t st, AttnArgs &a, const char *who, int S, int key_len, int window, int query_base_pos,
+                               int key_base_pos) {
+    a.S = S; a.klen = key_len; a.window = window;
+    a.d0_set = 1; a.d0 = query_base_pos - key_base_pos;
+    int rc = check_attn_geometry(who, a.nh, a.nkv, a.l_hd, a.cache_hd, a.kvg);
+    if (rc) return rc;
+    REQUIRE(a.q && a.k_cache && a.v_cache && a.k_scales && a.v_scales && a.out, "%s: null pointer", who);
+    if (a.kv_fmt != KV_I8 || a.l_hd != 128) {
+        set_error("%s: key range [%d, %d) must reach the last query row (position %d) and start at or before the first for this "
+                  "cache format / head dim", who, key_base_pos, key_base_pos + key_len, query_base_pos + S - 1);
+        return NOMOS_EUNSUPPORTED;
+    }
+    return launch_attn_fused(st, a);
 }
 
 static int run_dense(cudaStream_t st, const char *who, uint64_t q, uint64_t k, uint64_t v, uint64_t scratch, long scratch_floats,

@@ -38,6 +38,7 @@
 
 #include "attn_fused_kernel.cuh"
 #include "attn_tc5_kernel.cuh"
+#include "attn_prefill_kernel.cuh"
 
 #ifndef NOMOS_DS512
 #define NOMOS_DS512 4
@@ -563,6 +564,74 @@ static int dispatch_mma(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
 // about 7.0 against 6.6 TB/s), the mma.sync kernel has about 2 us less fixed cost per call (one CTA per SM, half
 // as many partials to merge: 32768 keys 26.9 vs 27.7 us, the two-launch decode step 31.5 vs 32.2 us).  Two
 // straight lines, 8.0 us + bytes / 7.0 TB/s and 5.9 us + bytes / 6.6 TB/s, cross at about 240 MB of cache.
+// ------------------------------------------------------------------ query-major prefill (attn_prefill_kernel.cuh)
+// int8 KV, head_dim 128, more query rows per KV head than the decode / verify kernels serve in one CTA (24), a
+// window that does not wrap the ring, no fused append and no partial export.  Everything else -- int4 caches, wider
+// heads, wrapped rings -- runs as row groups of the mma.sync kernel (also without any S x key_len scratch).
+static bool prefill_eligible(const AttnArgs &a) {
+    if (a.kv_fmt != KV_I8 || a.l_hd != 128 || a.no_tma || a.no_tcgen05 || a.block_table != nullptr) return false;
+    if (a.new_k != nullptr || a.partial_out != nullptr || a.out == nullptr || a.peer_world > 1) return false;
+    if (!a.d0_set && a.S * a.kvg <= 24) return false;
+    if (a.kvg != 1 && a.kvg != 2 && a.kvg != 4 && a.kvg != 8) return false;
+    if ((long)(a.win_start % a.cache_cap) + a.klen > a.cache_cap) return false;
+    if (encode_tiled_fn() == nullptr) return false;
+    const auto al16 = [](const void *x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
+    if (!al16(a.k_cache) || !al16(a.v_cache) || !al16(a.q) || !al16(a.out) || a.cache_hd % 16 != 0) return false;
+    if (a.q_batch_stride % 8 != 0 || a.out_batch_stride % 8 != 0 || a.scale_batch_stride % 4 != 0) return false;
+    if (a.batch > 1 && a.kv_batch_stride % 16 != 0) return false;
+    if ((long)a.nkv * a.cache_cap >= (1l << 31)) return false;
+    return true;
+}
+
+static int launch_prefill(cudaStream_t st, const AttnArgs &a) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!attr_set[dev]) {
+        cudaFuncSetAttribute(pf::attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::SMEM_BYTES);
+        attr_set[dev] = true;
+    }
+    pf::PMaps tm;
+    const int rows = a.nkv * a.cache_cap;
+    const MapKey mk{a.k_cache, 0, 128, a.cache_hd, rows, a.batch, pf::KT, a.kv_batch_stride};
+    const MapKey mv{a.v_cache, 0, 128, a.cache_hd, rows, a.batch, pf::KT, a.kv_batch_stride};
+    if (!encode_plane(mk, &tm.k) || !encode_plane(mv, &tm.v)) return 1;
+    pf::PParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.q = static_cast<const uint8_t *>(a.q);
+    p.out = static_cast<uint8_t *>(a.out);
+    p.k_scales = static_cast<const float *>(a.k_scales);
+    p.v_scales = static_cast<const float *>(a.v_scales);
+    p.q_type = a.q_type; p.out_type = a.out_type;
+    p.S = a.S; p.nh = a.nh; p.nkv = a.nkv; p.kvg = a.kvg; p.cache_cap = a.cache_cap;
+    p.row0 = a.win_start % a.cache_cap;
+    p.key_len = a.klen;
+    p.d0 = a.d0_set ? a.d0 : a.klen - a.S;
+    p.window = a.window;
+    p.pos_per_cta = pf::MR / a.kvg;
+    p.q_blocks = (a.S + p.pos_per_cta - 1) / p.pos_per_cta;
+    p.q_scale = a.softmax_scale * LOG2E;
+    p.q_batch_stride = a.q_batch_stride; p.out_batch_stride = a.out_batch_stride; p.scale_batch_stride = a.scale_batch_stride;
+    p.scales_vec = ((reinterpret_cast<uintptr_t>(a.k_scales) | reinterpret_cast<uintptr_t>(a.v_scales)) % 16 == 0 && a.cache_cap % 4 == 0 &&
+                    p.row0 % 4 == 0 && a.scale_batch_stride % 16 == 0) ? 1 : 0;
+    p.fault = fault_word();
+    if (p.fault == nullptr) { set_error("attn_prefill: device fault word unavailable"); return NOMOS_ECUDA; }
+    if (p.q_blocks > 65535 * 32 || a.batch > 65535) { set_error("attn_prefill: too many query blocks"); return NOMOS_EUNSUPPORTED; }
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.q_blocks, a.nkv, a.batch);
+    cfg.blockDim = dim3(pf::NTHREADS);
+    cfg.dynamicSmemBytes = pf::SMEM_BYTES;
+    cfg.stream = st;
+    cfg.attrs = pdl; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, pf::attn_prefill_kernel, p, tm);
+    if (e != cudaSuccess) { set_error("attn_prefill launch: %s", cudaGetErrorString(e)); return NOMOS_ECUDA; }
+    return NOMOS_OK;
+}
+
 static bool prefers_mma(const AttnArgs &a) {
     if (a.tcgen05_always || a.block_table != nullptr || a.S * a.kvg > 8) return false;
     const int keys = a.window > 0 ? std::min(a.klen, a.window + a.S - 1) : a.klen;
@@ -571,6 +640,11 @@ static bool prefers_mma(const AttnArgs &a) {
 }
 
 static int dispatch(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
+    if (!q && prefill_eligible(a)) {
+        const int rc = launch_prefill(st, a);
+        if (rc != 1) return rc;                    // 1: the tensor maps could not be encoded, use the other kernels
+    }
+    if (a.d0_set) { set_error("this key range needs the prefill kernel (int8 KV, head_dim 128, 16-byte aligned buffers)"); return NOMOS_EUNSUPPORTED; }
     if (!tc5_eligible(a)) return dispatch_mma(st, a, q, ws);
     if (q) {
         // a later call with the same geometry may carry new rows to append and take the other
@@ -596,7 +670,7 @@ long attn_peer_mailbox_bytes(int world, long grows, int l_hd) {
     return attn_peer_mailbox_rows_bytes(world, grows, l_hd) + 2L * world * grows * 8;
 }
 
-int attn_kernel_choice(const AttnArgs &a) { return tc5_eligible(a) && !prefers_mma(a) ? 1 : 0; }
+int attn_kernel_choice(const AttnArgs &a) { return prefill_eligible(a) ? 2 : (tc5_eligible(a) && !prefers_mma(a) ? 1 : 0); }
 
 long attn_workspace_bytes(const AttnArgs &a) {
     long ws = 0;

@@ -65,6 +65,10 @@ struct AttnArgs {
     int peer_rank, peer_world;
     unsigned long long peer_seq;
     long peer_timeout_us;
+    // general prefix bounds (prefill kernel only): when d0_set, query row s may attend window indices <= d0 + s
+    // (clipped to klen - 1; d0 may be negative, rows before the first key see nothing) instead of the default
+    // d0 = klen - S ("the query rows are the last S keys")
+    int d0_set, d0;
     int force_splits;       // 0 = choose; >0 = use exactly this many splits (tests)
     int no_tma;             // 1: keep every tile on the cp.async path
     int no_tcgen05;         // 1: never take the tcgen05 kernel
@@ -78,7 +82,7 @@ struct AttnArgs {
 long attn_peer_mailbox_rows_bytes(int world, long grows, int l_hd);
 long attn_peer_mailbox_bytes(int world, long grows, int l_hd);
 long attn_workspace_bytes(const AttnArgs &a);
-int attn_kernel_choice(const AttnArgs &a);     // 1: the tcgen05 kernel would serve the call, 0: the mma.sync kernel
+int attn_kernel_choice(const AttnArgs &a);     // 2: the query-major prefill kernel, 1: the tcgen05 decode / verify kernel, 0: the mma.sync kernel
 int launch_attn_fused(cudaStream_t st, const AttnArgs &a);
 long attn_paged_workspace_bytes(const AttnArgs &a);
 int launch_attn_paged(cudaStream_t st, const AttnArgs &a);
