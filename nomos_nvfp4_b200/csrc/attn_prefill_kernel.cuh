@@ -24,10 +24,12 @@
 // The cache stays int8 in device memory and on the way in: TMA boxes of 128 rows x 128 bytes, one tensor map per
 // plane over this GPU's own memory, no cluster, nothing multicast.
 //
-// Roles (320 threads): warps 0-3 softmax (thread = query row = TMEM lane: the row maximum and sum need no
-// shuffles), warps 4-7 dequant (thread = key row of the V tile), warp 8 lane 0 TMA producer (+ TMEM allocation),
-// warp 9 lane 0 MMA issuer.  A softmax thread pulls its row of S into registers and releases S at once, so QK of
-// tile i+1 runs while the softmax warps work on tile i; O stays in tensor memory across tiles and is rescaled in
+// Roles (384 threads): warps 0-7 softmax -- query row r = TMEM lane r is shared by two threads, lane r % 32 of warps
+// r / 32 and r / 32 + 4 (both may read that lane quarter), each taking 64 of the tile's 128 keys: two warps per
+// scheduler hide each other's latencies (one warp per scheduler measured 0.16 instructions per cycle), the row
+// maximum crosses the pair through shared memory once per tile; warps 8-9 dequant (a thread converts two key rows of
+// the V tile), warp 10 lane 0 TMA producer (+ TMEM allocation), warp 11 lane 0 MMA issuer.  The softmax threads pull
+// S into registers and release it at once, so QK of tile i+1 runs while they work on tile i; O stays in tensor memory across tiles and is rescaled in
 // place only when a row's running maximum moves by more than 2^8 (a handful of times per row).  Every wait is an
 // mbarrier wait with a time limit; a wait that runs out raises the CTA's abort flag and bit 1 of the device fault
 // word, every role leaves its loop, tensor memory is freed and the CTA exits.
@@ -57,11 +59,14 @@ constexpr int OFF_P16 = OFF_Q8 + 2 * RAW_TILE;   // weight limbs: high, then low
 constexpr int OFF_BAR = OFF_P16 + 2 * H_TILE; // 196608
 constexpr int NBAR = 16;
 constexpr int OFF_MISC = OFF_BAR + NBAR * 8;  // tmem base, abort flag
-constexpr int SMEM_BYTES = 1024 + OFF_MISC + 64;
-constexpr int NTHREADS = 320;
+constexpr int OFF_SC = OFF_MISC + 64;         // [2 stages][K scales | V scales] fp32, 128 each, bulk-copied with the tile
+constexpr int OFF_XCH = OFF_SC + 2 * 2 * KT * 4;        // [3][2 halves][128 rows] fp32: row maxima by tile parity; region 2: query maxima, then denominators
+constexpr int SMEM_BYTES = 1024 + OFF_XCH + 3 * 2 * 128 * 4;
+constexpr int NTHREADS = 384;
 constexpr int TMEM_COLS = 512;                // S_hi at column 0, S_lo at 128, O at 256
 constexpr int Q_FIX_MAX = fused::Q_FIX_MAX;   // 16-bit fixed-point query, two int8 limbs
 static_assert(OFF_V16 % 1024 == 0 && OFF_Q8 % 1024 == 0 && OFF_P16 % 1024 == 0, "operand tiles sit on swizzle-pattern boundaries");
+static_assert(OFF_SC % 16 == 0, "bulk copies land on 16-byte boundaries");
 static_assert(SMEM_BYTES <= 232448, "shared memory budget of a CTA");
 
 struct PParams {
@@ -166,16 +171,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
     const uint32_t sm_u32 = smem_u32(sm);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(sm + OFF_MISC);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(sm + OFF_MISC + 4);
+    float *xch = reinterpret_cast<float *>(sm + OFF_XCH);              // [3][2][128]
     const uint32_t bar0 = sm_u32 + OFF_BAR;
     auto bar_raw_full = [&](int s) { return bar0 + 8 * s; };            // TMA -> dequant and MMA (tx bytes)
-    auto bar_raw_empty = [&](int s) { return bar0 + 8 * (2 + s); };     // dequant (128, V converted) + commit after QK (1) -> TMA
-    const uint32_t bar_v16_full = bar0 + 8 * 4;                         // dequant (128) -> MMA
+    auto bar_raw_empty = [&](int s) { return bar0 + 8 * (2 + s); };     // dequant (64, V converted) + commit after QK (1) + softmax (256, scales used) -> TMA
+    const uint32_t bar_v16_full = bar0 + 8 * 4;                         // dequant (64) -> MMA
     const uint32_t bar_v16_empty = bar0 + 8 * 5;                        // commit after PV -> dequant
     const uint32_t bar_s_full = bar0 + 8 * 6;                           // commit after QK -> softmax
-    const uint32_t bar_s_empty = bar0 + 8 * 7;                          // softmax (128): S is in registers -> MMA
-    const uint32_t bar_p_full = bar0 + 8 * 8;                           // softmax (128) -> MMA
+    const uint32_t bar_s_empty = bar0 + 8 * 7;                          // softmax (256): S is in registers -> MMA
+    const uint32_t bar_p_full = bar0 + 8 * 8;                           // softmax (256) -> MMA
     const uint32_t bar_o_done = bar0 + 8 * 9;                           // commit after PV -> softmax
-    const uint32_t bar_q_ready = bar0 + 8 * 10;                         // softmax (128) -> MMA
+    const uint32_t bar_q_ready = bar0 + 8 * 10;                         // softmax (256) -> MMA
+    const uint32_t bar_xch = bar0 + 8 * 11;                             // softmax (256): the two halves of every row have written their exchange slot
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heavy blocks (late query positions: the most key tiles) are scheduled first
@@ -193,15 +200,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         fused::mbar_init(bar_raw_full(0), 1); fused::mbar_init(bar_raw_full(1), 1);
-        fused::mbar_init(bar_raw_empty(0), 129); fused::mbar_init(bar_raw_empty(1), 129);
-        fused::mbar_init(bar_v16_full, 128); fused::mbar_init(bar_v16_empty, 1);
-        fused::mbar_init(bar_s_full, 1); fused::mbar_init(bar_s_empty, 128);
-        fused::mbar_init(bar_p_full, 128); fused::mbar_init(bar_o_done, 1);
-        fused::mbar_init(bar_q_ready, 128);
+        fused::mbar_init(bar_raw_empty(0), 321); fused::mbar_init(bar_raw_empty(1), 321);
+        fused::mbar_init(bar_v16_full, 64); fused::mbar_init(bar_v16_empty, 1);
+        fused::mbar_init(bar_s_full, 1); fused::mbar_init(bar_s_empty, 256);
+        fused::mbar_init(bar_p_full, 256); fused::mbar_init(bar_o_done, 1);
+        fused::mbar_init(bar_q_ready, 256);
+        fused::mbar_init(bar_xch, 256);
         fused::fence_mbar_init();
     }
-    if (warp == 9 && lane == 0) { fused::prefetch_tensormap(&tm.k); fused::prefetch_tensormap(&tm.v); }
-    if (warp == 8) {
+    // the scale stages start as zeros: a partial copy at the end of the key array then leaves finite values behind
+    for (int e = threadIdx.x; e < 2 * 2 * KT; e += NTHREADS) reinterpret_cast<float *>(sm + OFF_SC)[e] = 0.0f;
+    fused::fence_proxy_async();
+    if (warp == 11 && lane == 0) { fused::prefetch_tensormap(&tm.k); fused::prefetch_tensormap(&tm.v); }
+    if (warp == 10) {
         tc5::tmem_alloc(sm_u32 + OFF_MISC, TMEM_COLS);
         tc5::tmem_relinquish();
     }
@@ -212,7 +223,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
     fused::pdl_wait();                         // the query and the cache rows may come from the stream predecessor
     fused::pdl_launch_dependents();
 
-    if (warp == 8) {
+    if (warp == 10) {
         // =========================================================== TMA producer
         if (lane == 0) {
             for (int i = 0; i < n_tiles; ++i) {
@@ -220,13 +231,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
                 if (i >= 2 && !wait_or_abort(bar_raw_empty(st), ((i >> 1) - 1) & 1, abort_flag, p.fault)) break;
                 const uint32_t dst = sm_u32 + OFF_RAW + st * 2 * RAW_TILE;
                 const int row = map_row0 + (tile_lo + i) * KT;
-                fused::mbar_expect_tx(bar_raw_full(st), 2 * RAW_TILE);
+                // the tile's fp32 row scales ride along as two bulk copies (whole 16-byte units inside the key array)
+                const int t0 = (tile_lo + i) * KT;
+                const uint32_t sc_bytes = p.scales_vec ? (uint32_t)(min(KT, p.key_len - t0) & ~3) * 4u : 0u;
+                fused::mbar_expect_tx(bar_raw_full(st), 2 * RAW_TILE + 2 * sc_bytes);
                 fused::tma_load_tile(dst, &tm.k, row, b, bar_raw_full(st));
                 fused::tma_load_tile(dst + RAW_TILE, &tm.v, row, b, bar_raw_full(st));
+                if (sc_bytes) {
+                    const size_t so = b * (p.scale_batch_stride / 4) + (size_t)kvh * p.cache_cap + p.row0 + t0;
+                    fused::bulk_load(sm_u32 + OFF_SC + st * 2 * KT * 4, p.k_scales + so, sc_bytes, bar_raw_full(st));
+                    fused::bulk_load(sm_u32 + OFF_SC + st * 2 * KT * 4 + KT * 4, p.v_scales + so, sc_bytes, bar_raw_full(st));
+                }
             }
         }
         __syncwarp();
-    } else if (warp == 9) {
+    } else if (warp == 11) {
         // =========================================================== MMA issuer
         if (lane == 0) {
             const uint32_t idesc_qk = tc5::make_idesc(KT, true, true, false);
@@ -275,46 +294,60 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
             }
         }
         __syncwarp();
-    } else if (warp >= 4) {
-        // =========================================================== dequant warps: thread = key row of the V tile
-        const int r = threadIdx.x - 128;
+    } else if (warp >= 8) {
+        // =========================================================== dequant warps: a thread converts key rows t, t + 64 of the V tile
+        const int t = threadIdx.x - 256;
         for (int i = 0; i < n_tiles; ++i) {
             const int st = i & 1;
             const uint8_t *raw = sm + OFF_RAW + st * 2 * RAW_TILE + RAW_TILE;
             if (!__all_sync(0xffffffffu, wait_or_abort(bar_raw_full(st), (i >> 1) & 1, abort_flag, p.fault))) break;
             if (i >= 1 && !__all_sync(0xffffffffu, wait_or_abort(bar_v16_empty, (i - 1) & 1, abort_flag, p.fault))) break;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {                              // 16 codes per step -> two 16-byte chunks of fp16
-                const uint4 x = *reinterpret_cast<const uint4 *>(raw + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
-                uint4 y0, y1;
-                cvt4(x.x, y0.x, y0.y); cvt4(x.y, y0.z, y0.w);
-                cvt4(x.z, y1.x, y1.y); cvt4(x.w, y1.z, y1.w);
-                *reinterpret_cast<uint4 *>(sm + OFF_V16 + h_off(r, 2 * c)) = y0;
-                *reinterpret_cast<uint4 *>(sm + OFF_V16 + h_off(r, 2 * c + 1)) = y1;
+            for (int rr = 0; rr < 2; ++rr) {
+                const int r = t + 64 * rr;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {                          // 16 codes per step -> two 16-byte chunks of fp16
+                    const uint4 x = *reinterpret_cast<const uint4 *>(raw + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
+                    uint4 y0, y1;
+                    cvt4(x.x, y0.x, y0.y); cvt4(x.y, y0.z, y0.w);
+                    cvt4(x.z, y1.x, y1.y); cvt4(x.w, y1.z, y1.w);
+                    *reinterpret_cast<uint4 *>(sm + OFF_V16 + h_off(r, 2 * c)) = y0;
+                    *reinterpret_cast<uint4 *>(sm + OFF_V16 + h_off(r, 2 * c + 1)) = y1;
+                }
             }
             fused::fence_proxy_async();
             tc5::mbar_arrive(bar_v16_full);
             tc5::mbar_arrive(bar_raw_empty(st));
         }
     } else {
-        // =========================================================== softmax warps: thread = query row = TMEM lane
-        const int r = threadIdx.x;
+        // =========================================================== softmax warps: two threads per query row
+        const int half = warp >> 2;                                    // which 64 keys of a tile (and which 64 dims of Q / O) this thread takes
+        const int r = 32 * (warp & 3) + lane;                          // query row = TMEM lane
         const int s = s_first + r / p.kvg, j = r - (r / p.kvg) * p.kvg;
         const bool valid = r < p.pos_per_cta * p.kvg && s < p.S;
         const int hi_r = valid ? min(p.d0 + s, p.key_len - 1) : -1;                     // inclusive
         const int lo_r = (valid && p.window > 0) ? max(0, p.d0 + s - p.window + 1) : 0;
-        const uint32_t tmem_lane = tmem_base + ((uint32_t)(32 * warp) << 16);
+        const uint32_t tmem_lane = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16);
         auto wait_warp = [&](uint32_t bar, uint32_t parity) {
             return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag, p.fault)) != 0;
         };
+        // Meeting point of the 256 softmax threads: an mbarrier with the same time limit as every other wait (a
+        // hardware barrier would wait forever for a warp that had given up).  false = abandoned.
+        uint32_t xphase = 0;
+        auto pair_sync = [&]() {
+            tc5::mbar_arrive(bar_xch);
+            const bool ok = wait_warp(bar_xch, xphase);
+            xphase ^= 1u;
+            return ok;
+        };
         // ---- the query row -> 16-bit fixed point of its own maximum, two int8 limbs (q ~= sq * (256 hi + lo)),
-        // stored K-major in the 128-byte swizzle pattern
+        // stored K-major in the 128-byte swizzle pattern; this thread converts dims 64 half .. 64 half + 63
         float qscale_r;                          // base-2 logit per unit of the integer dot product and of the key's scale
         {
-            const long qoff = b * p.q_batch_stride + ((long)(valid ? s : 0) * p.nh + kvh * p.kvg + (valid ? j : 0)) * HD;
-            float x[HD];
+            const long qoff = b * p.q_batch_stride + ((long)(valid ? s : 0) * p.nh + kvh * p.kvg + (valid ? j : 0)) * HD + 64 * half;
+            float x[64];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
+            for (int c = 0; c < 8; ++c) {
                 if (p.q_type == ET_BF16) {
                     const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(p.q) + qoff) + c);
                     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -329,12 +362,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
             }
             float amax = 0.0f;
 #pragma unroll
-            for (int d = 0; d < HD; ++d) amax = fmaxf(amax, fabsf(x[d]));
+            for (int d = 0; d < 64; ++d) amax = fmaxf(amax, fabsf(x[d]));
+            xch[(4 + half) * 128 + r] = amax;
+            pair_sync();
+            amax = fmaxf(amax, xch[(4 + 1 - half) * 128 + r]);
             const float sq = (valid && amax > 0.0f) ? amax * (1.0f / (float)Q_FIX_MAX) : 1.0f;
             const float inv = 1.0f / sq;
             qscale_r = valid ? sq * p.q_scale : 0.0f;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {                              // 16 dims per 16-byte chunk
+            for (int c = 0; c < 4; ++c) {                              // 16 dims per 16-byte chunk
                 uint32_t wh[4], wl[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -349,7 +385,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
                     }
                     wh[e] = ph; wl[e] = pl;
                 }
-                const int off = (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
+                const int off = (r >> 3) * 1024 + (r & 7) * 128 + (((4 * half + c) ^ (r & 7)) << 4);
                 *reinterpret_cast<uint4 *>(sm + OFF_Q8 + off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
                 *reinterpret_cast<uint4 *>(sm + OFF_Q8 + RAW_TILE + off) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
             }
@@ -359,28 +395,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
         // fp32 row scales of the keys, read per tile by every thread (the same 1 KB for the whole CTA: L1 hits)
         const float *gks = p.k_scales + b * (p.scale_batch_stride / 4) + (size_t)kvh * p.cache_cap + p.row0;
         const float *gvs = p.v_scales + b * (p.scale_batch_stride / 4) + (size_t)kvh * p.cache_cap + p.row0;
-        float m = M_INIT, l = 0.0f;
+        float m = M_INIT, l = 0.0f;              // running maximum of the row (both halves agree), this half's share of the denominator
         bool alive = true;
         for (int i = 0; alive && i < n_tiles; ++i) {
-            const int t0 = (tile_lo + i) * KT;
-            const bool need_mask = t0 < lo_r || t0 + KT - 1 > hi_r;   // rows outside [lo_r, hi_r] see nothing of the key (a select, never a multiply)
-            const bool whole = p.scales_vec && t0 + KT <= p.key_len;   // 16-byte loads: every column's scale exists and is aligned
+            const int t0 = (tile_lo + i) * KT + 64 * half;             // first key of this thread's half of the tile
+            const bool need_mask = t0 < lo_r || t0 + 63 > hi_r;       // rows outside [lo_r, hi_r] see nothing of the key (a select, never a multiply)
+            const int st = i & 1;
+            // scales of this half's keys: in shared memory when they could ride the bulk copies (the copy covers whole
+            // 16-byte units inside the key array: a ragged tail is read from global memory), else from global memory
+            const bool whole = p.scales_vec && (((tile_lo + i) * KT + (min(KT, p.key_len - (tile_lo + i) * KT) & ~3)) >= t0 + 64);
+            const float *sks = reinterpret_cast<const float *>(sm + OFF_SC + st * 2 * KT * 4) + 64 * half - t0;      // used when `whole`
+            const float *svs = reinterpret_cast<const float *>(sm + OFF_SC + st * 2 * KT * 4 + KT * 4) + 64 * half - t0;
             const int tl = p.key_len - 1;
+            if (!wait_warp(bar_raw_full(st), (i >> 1) & 1)) { alive = false; break; }   // the scales have landed
             if (!wait_warp(bar_s_full, i & 1)) { alive = false; break; }
             tc5::tc_fence_after();
-            float sv[4][32];                                           // base-2 logits of this row against the tile's keys
+            float sv[2][32];                                           // base-2 logits of this row against its 64 keys
             float tmax = -CUDART_INF_F;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 int sh[32], sl[32];
-                tmem_ld32i(tmem_lane + 32 * c, sh);
-                tmem_ld32i(tmem_lane + 128 + 32 * c, sl);
+                tmem_ld32i(tmem_lane + 64 * half + 32 * c, sh);
+                tmem_ld32i(tmem_lane + 128 + 64 * half + 32 * c, sl);
                 tc5::tmem_wait_ld();
 #pragma unroll
                 for (int e4 = 0; e4 < 32; e4 += 4) {
                     float4 k4;
                     if (whole) {
-                        k4 = *reinterpret_cast<const float4 *>(gks + t0 + 32 * c + e4);
+                        k4 = *reinterpret_cast<const float4 *>(sks + t0 + 32 * c + e4);
                     } else {
                         k4 = make_float4(gks[min(t0 + 32 * c + e4, tl)], gks[min(t0 + 32 * c + e4 + 1, tl)], gks[min(t0 + 32 * c + e4 + 2, tl)],
                                          gks[min(t0 + 32 * c + e4 + 3, tl)]);
@@ -401,72 +443,83 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
             }
             tc5::tc_fence_before();
             tc5::mbar_arrive(bar_s_empty);                             // S is in registers: QK of the next tile may overwrite it
+            // the row's tile maximum: the two halves meet through shared memory (double-buffered by tile parity)
+            xch[((i & 1) * 2 + half) * 128 + r] = tmax;
+            if (!pair_sync()) { alive = false; break; }
+            tmax = fmaxf(tmax, xch[((i & 1) * 2 + 1 - half) * 128 + r]);
             // the running maximum only moves when the tile exceeds it by more than 2^8: the weights stay below 2^8 and
             // the accumulator in tensor memory is rescaled a handful of times per row instead of once per tile
             const bool moved = tmax > m + LAZY;
             const float m_new = moved ? tmax : m;
             const float alpha = moved ? ex2f(m - m_new) : 1.0f;
             m = m_new;
+            // P is single-buffered and O lives in tensor memory: both wait for the previous tile's PV product
+            if (i >= 1 && !wait_warp(bar_o_done, (i - 1) & 1)) { alive = false; break; }
+            if (i >= 1 && __any_sync(0xffffffffu, moved)) {            // this thread rescales its 64 dims of O
+                tc5::tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    float o[32];
+                    tmem_ld32(tmem_lane + 256 + 64 * half + 32 * c, o);
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[e] *= alpha;
+                    tmem_st32(tmem_lane + 256 + 64 * half + 32 * c, o);
+                }
+                tmem_wait_st();
+            }
+            // weights of this thread's 64 keys = key block `half` of the P tiles: weight x value scale as fp16 hi + lo
             float lsum = 0.0f;
-            uint32_t ph[64], pl[64];                                   // weight x value scale as fp16 hi + lo, two keys per word
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 2; ++c)
 #pragma unroll
-                for (int e4 = 0; e4 < 32; e4 += 4) {
-                    float4 v4;
+                for (int e8 = 0; e8 < 32; e8 += 8) {
+                    float vv[8];
                     if (whole) {
-                        v4 = *reinterpret_cast<const float4 *>(gvs + t0 + 32 * c + e4);
+                        const float4 a4 = *reinterpret_cast<const float4 *>(svs + t0 + 32 * c + e8);
+                        const float4 b4 = *reinterpret_cast<const float4 *>(svs + t0 + 32 * c + e8 + 4);
+                        vv[0] = a4.x; vv[1] = a4.y; vv[2] = a4.z; vv[3] = a4.w; vv[4] = b4.x; vv[5] = b4.y; vv[6] = b4.z; vv[7] = b4.w;
                     } else {
-                        v4 = make_float4(gvs[min(t0 + 32 * c + e4, tl)], gvs[min(t0 + 32 * c + e4 + 1, tl)], gvs[min(t0 + 32 * c + e4 + 2, tl)],
-                                         gvs[min(t0 + 32 * c + e4 + 3, tl)]);
-                    }
-                    const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
-                    for (int e = 0; e < 4; e += 2) {
-                        const float p0 = ex2f(sv[c][e4 + e] - m), p1 = ex2f(sv[c][e4 + e + 1] - m);
+                        for (int e = 0; e < 8; ++e) vv[e] = gvs[min(t0 + 32 * c + e8 + e, tl)];
+                    }
+                    uint32_t wh[4], wl[4];
+#pragma unroll
+                    for (int e = 0; e < 8; e += 2) {
+                        const float p0 = ex2f(sv[c][e8 + e] - m), p1 = ex2f(sv[c][e8 + e + 1] - m);
                         lsum += p0 + p1;
                         const float w0 = p0 * vv[e], w1 = p1 * vv[e + 1];
                         const __half2 h = __floats2half2_rn(w0, w1);
                         const __half2 hl = __floats2half2_rn(w0 - __low2float(h), w1 - __high2float(h));
-                        ph[16 * c + ((e4 + e) >> 1)] = *reinterpret_cast<const uint32_t *>(&h);
-                        pl[16 * c + ((e4 + e) >> 1)] = *reinterpret_cast<const uint32_t *>(&hl);
+                        wh[e >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+                        wl[e >> 1] = *reinterpret_cast<const uint32_t *>(&hl);
                     }
+                    const int chunk = 8 * half + 4 * c + (e8 >> 3);    // 16-byte chunk (8 keys) of the row
+                    *reinterpret_cast<uint4 *>(sm + OFF_P16 + h_off(r, chunk)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                    *reinterpret_cast<uint4 *>(sm + OFF_P16 + H_TILE + h_off(r, chunk)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 }
             l = fmaf(l, alpha, lsum);
-            // P is single-buffered and O lives in tensor memory: both wait for the previous tile's PV product
-            if (i >= 1 && !wait_warp(bar_o_done, (i - 1) & 1)) { alive = false; break; }
-            if (i >= 1 && __any_sync(0xffffffffu, moved)) {
-                tc5::tc_fence_after();
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    float o[32];
-                    tmem_ld32(tmem_lane + 256 + 32 * c, o);
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) o[e] *= alpha;
-                    tmem_st32(tmem_lane + 256 + 32 * c, o);
-                }
-                tmem_wait_st();
-            }
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                *reinterpret_cast<uint4 *>(sm + OFF_P16 + h_off(r, c)) = make_uint4(ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
-                *reinterpret_cast<uint4 *>(sm + OFF_P16 + H_TILE + h_off(r, c)) = make_uint4(pl[4 * c], pl[4 * c + 1], pl[4 * c + 2], pl[4 * c + 3]);
-            }
+            tc5::mbar_arrive(bar_raw_empty(st));                       // done with the stage's scales
             fused::fence_proxy_async();
             tc5::tc_fence_before();
             tc5::mbar_arrive(bar_p_full);
         }
-        // ---- output: O / l (rows without any key are exact zeros, lib/batched_attn_gpu.mojo:329-409)
+        // ---- output: O / l (rows without any key are exact zeros, lib/batched_attn_gpu.mojo:329-409); this thread
+        // writes dims 64 half .. 64 half + 63 of its row
         if (alive && n_tiles > 0) alive = wait_warp(bar_o_done, (n_tiles - 1) & 1);
+        if (alive) {
+            xch[(4 + half) * 128 + r] = l;
+            alive = pair_sync();
+            l += xch[(4 + 1 - half) * 128 + r];
+        }
         if (alive) {
             tc5::tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            const long oi = b * p.out_batch_stride + ((long)(valid ? s : 0) * p.nh + kvh * p.kvg + (valid ? j : 0)) * HD;
+            const long oi = b * p.out_batch_stride + ((long)(valid ? s : 0) * p.nh + kvh * p.kvg + (valid ? j : 0)) * HD + 64 * half;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 float o[32];
                 if (n_tiles > 0) {
-                    tmem_ld32(tmem_lane + 256 + 32 * c, o);
+                    tmem_ld32(tmem_lane + 256 + 64 * half + 32 * c, o);
                 } else {
 #pragma unroll
                     for (int e = 0; e < 32; ++e) o[e] = 0.0f;
@@ -497,7 +550,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
     // ------------------------------------------------------------ tear-down
     tc5::tc_fence_before();
     __syncthreads();
-    if (warp == 8) tc5::tmem_dealloc(tmem_base, TMEM_COLS);
+    if (warp == 10) tc5::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 }  // namespace pf
