@@ -399,7 +399,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
         bool alive = true;
         for (int i = 0; alive && i < n_tiles; ++i) {
             const int t0 = (tile_lo + i) * KT + 64 * half;             // first key of this thread's half of the tile
-            const bool need_mask = t0 < lo_r || t0 + 63 > hi_r;       // rows outside [lo_r, hi_r] see nothing of the key (a select, never a multiply)
+            // rows outside [lo_r, hi_r] see nothing of the key (a select, never a multiply); decided per warp, so that
+            // whole tiles in the middle of every row's range carry no masking instructions at all
+            const bool need_mask = __any_sync(0xffffffffu, t0 < lo_r || t0 + 63 > hi_r);
             const int st = i & 1;
             // scales of this half's keys: in shared memory when they could ride the bulk copies (the copy covers whole
             // 16-byte units inside the key array: a ragged tail is read from global memory), else from global memory
