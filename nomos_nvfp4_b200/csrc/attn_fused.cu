@@ -175,17 +175,17 @@ static int settled_rows(const AttnArgs &a) {
     return a.settled_cache ? std::max(0, a.klen - 2 * std::max(a.S, a.n_new)) : 0;
 }
 
-template <int FMT, int HD, int MT, int DS>
+template <int FMT, int HD, int MT, int DS, int QS>
 static int kernel_occupancy() {
     static int occ[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (occ[dev] == 0) {
-        using C = Cfg<FMT, HD, MT, DS>;
-        cudaFuncSetAttribute(attn_fused_kernel<FMT, HD, MT, DS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        using C = Cfg<FMT, HD, MT, DS, QS>;
+        cudaFuncSetAttribute(attn_fused_kernel<FMT, HD, MT, DS, QS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         int n = 0;
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_fused_kernel<FMT, HD, MT, DS>, C::NW * 32, C::SMEM_BYTES);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_fused_kernel<FMT, HD, MT, DS, QS>, C::NW * 32, C::SMEM_BYTES);
         occ[dev] = n > 0 ? n : 1;
     }
     return occ[dev];
@@ -240,11 +240,11 @@ static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp, int d
     return pl;
 }
 
-template <int FMT, int HD, int MT, int DS = 1>
+template <int FMT, int HD, int MT, int DS = 1, int QS = 1>
 static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *ws_needed) {
-    using C = Cfg<FMT, HD, MT, DS>;
-    const int occ = kernel_occupancy<FMT, HD, MT, DS>();
-    const Plan pl = make_plan(a, occ, HD, C::NW, DS);
+    using C = Cfg<FMT, HD, MT, DS, QS>;
+    const int occ = kernel_occupancy<FMT, HD, MT, DS, QS>();
+    const Plan pl = make_plan(a, occ, HD, C::NQ, DS);          // C::NQ tile streams per CTA (warps, or quads of QS warps)
     const long units = (long)a.nkv * a.batch * pl.row_groups;
     const long part_bytes = (((long)pl.splits * pl.grows * (HD + 2) * 4) + 15) / 16 * 16;
     // a sequence-sharded call always ends in the unit's merging CTA (it runs the exchange), also with one split
@@ -325,7 +325,7 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     cudaLaunchConfig_t mcfg = {};
     mcfg.gridDim = grid; mcfg.blockDim = dim3(C::NW * 32); mcfg.dynamicSmemBytes = C::SMEM_BYTES; mcfg.stream = st;
     mcfg.attrs = pdl; mcfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&mcfg, attn_fused_kernel<FMT, HD, MT, DS>, p, tm);
+    cudaError_t e = cudaLaunchKernelEx(&mcfg, attn_fused_kernel<FMT, HD, MT, DS, QS>, p, tm);
     if (e != cudaSuccess) { set_error("attn_fused launch: %s", cudaGetErrorString(e)); return NOMOS_ECUDA; }
     return NOMOS_OK;
 }
@@ -536,16 +536,25 @@ template <int FMT>
 static int dispatch_hd(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
     switch (a.l_hd) {
         case 128: return dispatch_mt<FMT, 128>(st, a, q, ws);
-        // Wider heads: one 8-row tile per CTA (more query rows are covered by row groups), and the PV
-        // product split over CTAs that each hold a 128-dim slice of the output (they all compute the
-        // full QK; K is read from HBM once and served to the other slices from L2).  Calls that append
-        // rows in the same launch keep the unsplit kernel.
+        // Wider heads: one 8-row tile per CTA (more query rows are covered by row groups), and quads of 2 / 4 warps
+        // that take every tile together, each warp owning a 128-dim slice of K, V and the output (see Cfg).  Calls
+        // that append rows in the same launch keep the unsliced kernel.  NOMOS_WIDE_BY_CTA selects the earlier
+        // scheme (the PV product split over CTAs, the QK product repeated by each) for comparison builds.
+#ifdef NOMOS_WIDE_BY_CTA
         case 256:
             if (a.new_k == nullptr && FMT == KV_I8) return launch_inst<FMT, 256, 1, 2>(st, a, q, ws);
             return launch_inst<FMT, 256, 1>(st, a, q, ws);
         case 512:
             if (a.new_k == nullptr) return launch_inst<FMT, 512, 1, NOMOS_DS512>(st, a, q, ws);
             return launch_inst<FMT, 512, 1>(st, a, q, ws);
+#else
+        case 256:
+            if (a.new_k == nullptr) return launch_inst<FMT, 256, 1, 1, 2>(st, a, q, ws);
+            return launch_inst<FMT, 256, 1>(st, a, q, ws);
+        case 512:
+            if (a.new_k == nullptr) return launch_inst<FMT, 512, 1, 1, 4>(st, a, q, ws);
+            return launch_inst<FMT, 512, 1>(st, a, q, ws);
+#endif
         default: set_error("head_dim %d unsupported (128, 256, 512)", a.l_hd); return NOMOS_EUNSUPPORTED;
     }
 }

@@ -37,23 +37,36 @@ constexpr float P_FIX = 65535.0f;        // probabilities reach the tensor core 
 constexpr float LAZY_MAX = 8.0f;         // base-2 slack before the running softmax reference is moved
 constexpr float RND_MAGIC = 8388608.0f;  // 2^23: adding it leaves round-to-nearest(x) in the low mantissa bits
 
-// DS > 1 splits the head dimension of the PV product over DS CTAs: each of them computes the full
-// QK (it reads all of K, the others' copies come from L2) but holds only HD / DS output dims and
-// streams only that slice of every V row.  Wide heads then keep as many warps per SM as head_dim 128.
-template <int FMT, int HD, int MT, int DS = 1>
+// Wide heads are cut into head-dim slices in one of two ways.
+// QS > 1 (the default for head_dim 256 / 512): QS warps of a CTA -- a "quad" -- take every tile TOGETHER.  Warp j of
+//   the quad owns dims [j HD/QS, (j+1) HD/QS): it streams only those byte columns of the K and V rows (and of the
+//   block scales), computes the partial logits of its dims, the quad adds the partials up through shared memory (one
+//   named barrier per tile), every warp works out the same softmax weights, and warp j accumulates its slice of the
+//   output.  K and V leave HBM once and every product is computed once; per warp the loop is the head_dim 128 loop.
+// DS > 1 (kept for comparison): the PV product is split over DS CTAs that each compute the full QK (all of K is read
+//   by every slice, from L2 after the first) and hold HD / DS output dims.
+template <int FMT, int HD, int MT, int DS = 1, int QS = 1>
 struct Cfg {
-    static constexpr int HDV = HD / DS;                                       // output dims of this CTA
+    static_assert(DS == 1 || QS == 1, "one way of slicing at a time");
+    static constexpr int QSL = QS;
+    static constexpr int HDK = HD / QS;                                       // dims whose QK partial a warp computes
+    static constexpr int HDV = HD / (DS * QS);                                // output dims of a warp
     static constexpr int ROWB = (FMT == KV_I8) ? HD : HD / 2;                 // cache bytes per token row
-    static constexpr int ROWBV = ROWB / DS;                                   // bytes of a V row this CTA reads
+    static constexpr int ROWBK = ROWB / QS;                                   // bytes of a K row a warp reads
+    static constexpr int ROWBV = ROWB / (DS * QS);                            // bytes of a V row a warp reads
     static constexpr int CHUNKS = ROWB / 16;                                  // 16-byte chunks per row
+    static constexpr int CHUNKSK = ROWBK / 16;
     static constexpr int CHUNKSV = ROWBV / 16;
     static constexpr int NBLK = HD / 32;
+    static constexpr int NBLKK = NBLK / QS;
     static constexpr int NBLKV = HDV / 32;
-    static constexpr int SCB = (FMT == KV_I4B32) ? NBLK * 2 : 4;              // scale bytes per token
-    static constexpr int KV_BYTES = TILE * ROWB;                              // K tile
+    static constexpr int SCB = (FMT == KV_I4B32) ? NBLK * 2 : 4;              // scale bytes per token in the cache
+    static constexpr int SCBW = (FMT == KV_I4B32) ? NBLKK * 2 : 4;            // scale bytes per token a warp keeps
+    static constexpr int KV_BYTES = TILE * ROWBK;                             // K tile (slice)
     static constexpr int V_BYTES = TILE * ROWBV;                              // V tile (slice)
     static constexpr int ST_BYTES = KV_BYTES + V_BYTES;                       // tiles of one stage
-    static constexpr int SC_BYTES = TILE * SCB;
+    static constexpr int SC_BYTES = TILE * SCBW;
+    static_assert(ROWBK >= 64 && ROWBK % 64 == 0 && HDK % 128 == 0, "a K slice is whole 128-dim groups");
     static constexpr int STAGE_BYTES = ST_BYTES + 2 * SC_BYTES;
     static constexpr int NSLOT = 8 * MT;                                      // query rows (row x group head) per CTA
     static constexpr int NT = HDV / 8;                                        // PV N tiles (8 output dims each)
@@ -62,8 +75,12 @@ struct Cfg {
     static constexpr int SLOT_BYTES = NSLOT * 16 + NSLOT * NBLK * 4;          // qscale, lo, hi, pad; 8*sum(q) per block
     // warps per CTA: as many as the register file and ~200 KB of pipeline memory allow
     static constexpr int NW_REG = (MT == 1 && HDV <= 256) ? NOMOS_NWARP : NOMOS_NWARP_MULTI;
-    static constexpr int NW_MEM = (200 * 1024) / (NSTAGE * STAGE_BYTES);
-    static constexpr int NW = NW_REG < NW_MEM ? NW_REG : (NW_MEM < 1 ? 1 : NW_MEM);
+    static constexpr int XCH_WARP_BYTES = QS > 1 ? 2 * MT * 8 * 32 * 4 : 0;  // a warp's share of the quads' partial-logit buffers
+    static constexpr int NW_MEM = (200 * 1024) / (NSTAGE * STAGE_BYTES + XCH_WARP_BYTES);
+    static constexpr int NW_MIN = NW_REG < NW_MEM ? NW_REG : (NW_MEM < 1 ? 1 : NW_MEM);
+    static constexpr int NW = (NW_MIN / QS) * QS;                            // whole quads
+    static constexpr int NQ = NW / QS;                                       // tile streams per CTA
+    static_assert(NW >= QS, "a CTA holds at least one quad");
     static constexpr int APPEND_BYTES = NW * (ROWB + 64);                     // per warp: one quantised row + its scales
     // Shared-memory map: [K/V tiles of every warp and stage | scales | query limbs | slot
     // constants | append scratch | mbarriers].  The tile region starts on a 1024-byte boundary
@@ -73,10 +90,12 @@ struct Cfg {
     static constexpr int MERGE_BYTES = NW * NSLOT * (HDV + 2) * 4;
     static constexpr int REGION0_BYTES = ((TILES_BYTES > MERGE_BYTES ? TILES_BYTES : MERGE_BYTES) + 15) / 16 * 16;
     static constexpr int BAR_BYTES = NW * NSTAGE * 8;
-    static constexpr int SMEM_BYTES = 1024 + REGION0_BYTES + SCALES_BYTES + Q_BYTES + SLOT_BYTES + APPEND_BYTES + BAR_BYTES;
+    static constexpr int XCH_BYTES = NW * XCH_WARP_BYTES;                      // partial logits: [quad][tile parity][warp of the quad][MT*8][32 lanes] fp32
+    static constexpr int SMEM_BYTES = 1024 + REGION0_BYTES + SCALES_BYTES + Q_BYTES + SLOT_BYTES + APPEND_BYTES + BAR_BYTES + XCH_BYTES;
+    static_assert(SMEM_BYTES <= 232448, "shared memory budget of a CTA");
     // Rows of 64 / 128 bytes map one-to-one onto the TMA 64B / 128B swizzle patterns, which are
     // the XOR layouts swz_chunk() defines; wider rows stay on the cp.async path.
-    static constexpr bool TMA_OK = (ROWB == 64 || ROWB == 128) && DS == 1;
+    static constexpr bool TMA_OK = (ROWB == 64 || ROWB == 128) && DS == 1 && QS == 1;
 };
 
 // Tensor maps of the K and V byte planes: {row bytes, nkv * cache_cap rows, batch}.
@@ -679,12 +698,13 @@ __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t
     if (merged && p.peer_world > 1) peer_exchange_and_merge<NSLOT, HD, NTHR>(p, b, kvh, rg);
 }
 
-template <int FMT, int HD, int MT, int DS = 1>
-__global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
+template <int FMT, int HD, int MT, int DS = 1, int QS = 1>
+__global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS, QS>::NW * 32)
     attn_fused_kernel(const __grid_constant__ KParams p, const __grid_constant__ TmaMaps tm) {
-    using C = Cfg<FMT, HD, MT, DS>;
+    using C = Cfg<FMT, HD, MT, DS, QS>;
     constexpr int HDV = C::HDV;
     constexpr int NWARP = C::NW;
+    constexpr int NQ = C::NQ;                 // tile streams of the CTA: one per warp, or one per quad of QS warps
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *pipe = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // K/V tiles [NW][NSTAGE][2]
     uint8_t *sc_region = pipe + C::REGION0_BYTES;                                  // scales  [NW][NSTAGE][2]
@@ -696,23 +716,26 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
     int *slot_qsum = reinterpret_cast<int *>(qreg + C::Q_BYTES + C::NSLOT * 16);   // [NSLOT][NBLK]
     uint8_t *append_scratch = qreg + C::Q_BYTES + C::SLOT_BYTES;                  // [NW][ROWB + 64]
     const uint32_t bars_u32 = smem_u32(append_scratch + C::APPEND_BYTES);         // [NW][NSTAGE] mbarriers
+    float *xch_region = reinterpret_cast<float *>(append_scratch + C::APPEND_BYTES + C::BAR_BYTES);   // quads' partial logits
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    const int quad = warp / QS, wj = warp % QS;                                     // tile stream of this warp, its slice in the quad
     const int split = blockIdx.x / DS, dsl = blockIdx.x % DS, kvh = blockIdx.y;     // dsl: head-dim slice of this CTA
     const int b = blockIdx.z / p.row_groups, rg = blockIdx.z % p.row_groups;
 
     // ------------------------------------------------------------ tile schedule
     const int tile_begin = p.tile0 + split * p.tiles_per_split;
     const int tile_end = min(p.tile0 + p.ntiles, tile_begin + p.tiles_per_split);
-    const int my_first = tile_begin + warp;
-    const int my_count = my_first < tile_end ? (tile_end - my_first + NWARP - 1) / NWARP : 0;
+    const int my_first = tile_begin + quad;
+    const int my_count = my_first < tile_end ? (tile_end - my_first + NQ - 1) / NQ : 0;
 
     const int row_stride = (FMT == KV_I8) ? p.cache_hd : p.cache_hd / 2;   // bytes between consecutive token rows
-    const uint8_t *kbase = p.k_cache + b * p.kv_batch_stride + (size_t)kvh * p.cache_cap * (size_t)row_stride;
-    const uint8_t *vbase = p.v_cache + b * p.kv_batch_stride + (size_t)kvh * p.cache_cap * (size_t)row_stride + dsl * C::ROWBV;
-    const uint8_t *ksbase = p.k_scales + b * p.scale_batch_stride + (size_t)kvh * p.cache_cap * C::SCB;
-    const uint8_t *vsbase = p.v_scales + b * p.scale_batch_stride + (size_t)kvh * p.cache_cap * C::SCB;
+    const uint8_t *kbase = p.k_cache + b * p.kv_batch_stride + (size_t)kvh * p.cache_cap * (size_t)row_stride + wj * C::ROWBK;
+    const uint8_t *vbase = p.v_cache + b * p.kv_batch_stride + (size_t)kvh * p.cache_cap * (size_t)row_stride + (dsl * QS + wj) * C::ROWBV;
+    constexpr int SC_SLICE = (FMT == KV_I4B32) ? C::SCBW : 0;                // block scales are sliced with the dims, row scales are not
+    const uint8_t *ksbase = p.k_scales + b * p.scale_batch_stride + (size_t)kvh * p.cache_cap * C::SCB + wj * SC_SLICE;
+    const uint8_t *vsbase = p.v_scales + b * p.scale_batch_stride + (size_t)kvh * p.cache_cap * C::SCB + wj * SC_SLICE;
 
     uint8_t *my_pipe = pipe + warp * NSTAGE * C::ST_BYTES;           // stage s: K tile, V tile (slice)
     uint8_t *my_sc = sc_region + warp * NSTAGE * 2 * C::SC_BYTES;    // stage s: K scales, V scales
@@ -734,12 +757,12 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
     }
 
     // Copy geometry: per cp.async instruction the warp covers 8 rows x 64 bytes; lane = (row r, chunk c0).
-    constexpr int HPASS = C::CHUNKS / 4;                     // 64-byte column groups per row
+    constexpr int HPASS = C::CHUNKSK / 4;                    // 64-byte column groups per row (of this warp's K slice)
     const int cr = lane >> 2, cc0 = lane & 3;
     const size_t lane_goff = (size_t)cr * row_stride + cc0 * 16;
     uint32_t lane_soff[HPASS];
 #pragma unroll
-    for (int h = 0; h < HPASS; ++h) lane_soff[h] = cr * C::ROWB + swz_chunk<C::ROWB>(cr, cc0 + 4 * h) * 16;
+    for (int h = 0; h < HPASS; ++h) lane_soff[h] = cr * C::ROWBK + swz_chunk<C::ROWBK>(cr, cc0 + 4 * h) * 16;
     constexpr int HPASSV = C::CHUNKSV / 4;
     uint32_t lane_soffv[HPASSV];
 #pragma unroll
@@ -747,16 +770,16 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
 
     // one token's scale bytes (4: fp32 row scale; 2 per block of 32 for the block-32 layout)
     auto copy_scales = [&](uint32_t dst, const uint8_t *src, bool ok) {
-        if constexpr (C::SCB == 4) cp_async4(dst, src, ok ? 4 : 0);
-        else if constexpr (C::SCB == 8) cp_async8(dst, src, ok ? 8 : 0);
+        if constexpr (C::SCBW == 4) cp_async4(dst, src, ok ? 4 : 0);
+        else if constexpr (C::SCBW == 8) cp_async8(dst, src, ok ? 8 : 0);
         else {
 #pragma unroll
-            for (int o = 0; o < C::SCB; o += 16) cp_async16(dst + o, src + o, ok ? 16 : 0);
+            for (int o = 0; o < C::SCBW; o += 16) cp_async16(dst + o, src + o, ok ? 16 : 0);
         }
     };
     auto issue = [&](int it) {
         if (it < my_count) {
-            const int tok0 = (my_first + it * NWARP) * TILE;
+            const int tok0 = (my_first + it * NQ) * TILE;
             const int stg = it % NSTAGE;
             const uint32_t st = my_pipe_u32 + stg * C::ST_BYTES;
             const uint32_t ss = my_sc_u32 + stg * 2 * C::SC_BYTES;
@@ -781,8 +804,8 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                 }
                 if (!bulk_sc) {
                     const size_t sg = (size_t)(slot0 + lane) * C::SCB;
-                    copy_scales(ss + lane * C::SCB, ksbase + sg, true);
-                    copy_scales(ss + C::SC_BYTES + lane * C::SCB, vsbase + sg, true);
+                    copy_scales(ss + lane * C::SCBW, ksbase + sg, true);
+                    copy_scales(ss + C::SC_BYTES + lane * C::SCBW, vsbase + sg, true);
                 }
                 tma_mask |= 1u << stg;
             } else if (whole) {
@@ -793,14 +816,14 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                 for (int i = 0; i < 4; ++i) {
 #pragma unroll
                     for (int h = 0; h < HPASS; ++h)
-                        cp_async16(st + lane_soff[h] + 8 * i * C::ROWB, gk + (size_t)(8 * i) * row_stride + 64 * h, 16);
+                        cp_async16(st + lane_soff[h] + 8 * i * C::ROWBK, gk + (size_t)(8 * i) * row_stride + 64 * h, 16);
 #pragma unroll
                     for (int h = 0; h < HPASSV; ++h)
                         cp_async16(st + C::KV_BYTES + lane_soffv[h] + 8 * i * C::ROWBV, gv + (size_t)(8 * i) * row_stride + 64 * h, 16);
                 }
                 const size_t sg = (size_t)(slot0 + lane) * C::SCB;
-                copy_scales(ss + lane * C::SCB, ksbase + sg, true);
-                copy_scales(ss + C::SC_BYTES + lane * C::SCB, vsbase + sg, true);
+                copy_scales(ss + lane * C::SCBW, ksbase + sg, true);
+                copy_scales(ss + C::SC_BYTES + lane * C::SCBW, vsbase + sg, true);
             } else {
                 // ragged tile: wraps the ring or runs past the window; rows past the end are zero-filled
 #pragma unroll
@@ -811,7 +834,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                     const bool ok = tok < p.klen;
                     const size_t go = (size_t)(ok ? slot : 0) * row_stride + cc0 * 16;
 #pragma unroll
-                    for (int h = 0; h < HPASS; ++h) cp_async16(st + lane_soff[h] + 8 * i * C::ROWB, kbase + go + 64 * h, ok ? 16 : 0);
+                    for (int h = 0; h < HPASS; ++h) cp_async16(st + lane_soff[h] + 8 * i * C::ROWBK, kbase + go + 64 * h, ok ? 16 : 0);
 #pragma unroll
                     for (int h = 0; h < HPASSV; ++h)
                         cp_async16(st + C::KV_BYTES + lane_soffv[h] + 8 * i * C::ROWBV, vbase + go + 64 * h, ok ? 16 : 0);
@@ -821,8 +844,8 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                 slot = slot >= p.cache_cap ? slot - p.cache_cap : slot;
                 const bool ok = tok < p.klen;
                 const size_t sg = (size_t)(ok ? slot : 0) * C::SCB;
-                copy_scales(ss + lane * C::SCB, ksbase + sg, ok);
-                copy_scales(ss + C::SC_BYTES + lane * C::SCB, vsbase + sg, ok);
+                copy_scales(ss + lane * C::SCBW, ksbase + sg, ok);
+                copy_scales(ss + C::SC_BYTES + lane * C::SCBW, vsbase + sg, ok);
             }
         }
         cp_async_commit();
@@ -835,7 +858,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
     // Cache rows the caller declared settled (not written by the stream predecessor) are requested
     // before that wait, so the pipeline fill overlaps the predecessor's tail.
     int early_n = 0;
-    while (early_n < NSTAGE - 1 && early_n < my_count && (my_first + early_n * NWARP + 1) * TILE <= p.early_rows) issue(early_n++);
+    while (early_n < NSTAGE - 1 && early_n < my_count && (my_first + early_n * NQ + 1) * TILE <= p.early_rows) issue(early_n++);
     // ------------------------------------------- fused quantize-on-write of the new keys
     // The newest n_new keys arrive as fp32 rows.  A warp quantises one (row, plane) with the row codec
     // of the append kernels (bit for bit) into its scratch row [codes | scales]; for row group 0 and
@@ -954,7 +977,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
     #pragma unroll
                     for (int i = 0; i < HD / 32; ++i) tot += qblk[i];
     #pragma unroll
-                    for (int i = 0; i < HD / 32; ++i) slot_qsum[sl * C::NBLK + i] = 8 * (FMT == KV_I4 ? tot : qblk[i]);
+                    for (int i = 0; i < HD / 32; ++i) slot_qsum[sl * C::NBLK + i] = 8 * ((FMT == KV_I4 && QS == 1) ? tot : qblk[i]);
                 }
             }
             if (lane == 0) {
@@ -978,8 +1001,9 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
     }
     // Q A-fragments (rows g = high limb, rows g+8 = low limb of slot g): registers for
     // one M tile, re-read from shared memory otherwise.
-    constexpr bool Q_IN_REGS = (MT == 1) && (HD <= 256);
-    uint32_t qa[Q_IN_REGS ? HD / 32 : 1][4];
+    constexpr bool Q_IN_REGS = (MT == 1) && (C::HDK <= 256);
+    constexpr int KS0_STEP = C::HDK / 32;            // k steps (32 dims) of this warp's slice; its first global step is wj * KS0_STEP
+    uint32_t qa[Q_IN_REGS ? C::HDK / 32 : 1][4];
     // A fragment of k step ks for M tile mt in one ldmatrix.x4: matrices = (high limb, chunk 2ks),
     // (low limb, chunk 2ks), (high, 2ks+1), (low, 2ks+1) of slots 8mt..8mt+7  ->  a0, a1, a2, a3.
     const uint32_t q_u32 = smem_u32(q_limbs);
@@ -991,14 +1015,15 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
     };
     if constexpr (Q_IN_REGS) {
 #pragma unroll
-        for (int ks = 0; ks < HD / 32; ++ks) load_qa(qa[ks], 0, ks);
+        for (int ks = 0; ks < C::HDK / 32; ++ks) load_qa(qa[ks], 0, wj * KS0_STEP + ks);
     }
+    // ks counts the k steps of this warp's slice
     auto get_qa = [&](uint32_t(&a)[4], int mt, int ks) {
         if constexpr (Q_IN_REGS) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) a[i] = qa[ks][i];
         } else {
-            load_qa(a, mt, ks);
+            load_qa(a, mt, wj * KS0_STEP + ks);
         }
     };
 
@@ -1033,7 +1058,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
         }
         __syncwarp();
 
-        const int tok0 = (my_first + it * NWARP) * TILE;
+        const int tok0 = (my_first + it * NQ) * TILE;
         const uint32_t st = my_pipe_u32 + stg * C::ST_BYTES;
         const bool need_mask = (tok0 + TILE > hi_min) || (tok0 < lo_max);
         const uint8_t *ksm = my_sc + stg * 2 * C::SC_BYTES;         // K scales of the tile, token-major
@@ -1084,13 +1109,13 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) c[mt][n][i] = 0;
 #pragma unroll
-            for (int half = 0; half < HD / 64; ++half) {
+            for (int half = 0; half < C::HDK / 64; ++half) {
                 uint32_t kb[4][4];        // K bytes of the four 8-token groups, chunks 4half..4half+3
 #pragma unroll
                 for (int n = 0; n < 4; ++n) {
                     const int row = 8 * n + (lane & 7);
                     const int ch = 4 * half + (lane >> 3);
-                    ldmatrix_x4(kb[n], st + row * C::ROWB + swz_chunk<C::ROWB>(row, ch) * 16);
+                    ldmatrix_x4(kb[n], st + row * C::ROWBK + swz_chunk<C::ROWBK>(row, ch) * 16);
                 }
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
@@ -1126,11 +1151,11 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                     sblk[mt][0] = 0.0f; sblk[mt][1] = 0.0f;
                 }
 #pragma unroll
-                for (int grp = 0; grp < HD / 128; ++grp) {
+                for (int grp = 0; grp < C::HDK / 128; ++grp) {
                     uint32_t kr[4];
                     const int row = 8 * n + (lane & 7);
                     const int ch = 4 * grp + (lane >> 3);
-                    ldmatrix_x4(kr, st + row * C::ROWB + swz_chunk<C::ROWB>(row, ch) * 16);
+                    ldmatrix_x4(kr, st + row * C::ROWBK + swz_chunk<C::ROWBK>(row, ch) * 16);
 #pragma unroll
                     for (int m = 0; m < 4; ++m) {
                         const int blk = 4 * grp + m;
@@ -1146,9 +1171,9 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                                 int cb[4] = {0, 0, 0, 0};
                                 mma_s8u8(cb, a, lo, hi);
                                 // fp16 block scales of tokens 8n+2t and 8n+2t+1
-                                const int bias = slot_qsum[(mt * 8 + g) * C::NBLK + blk];
-                                const float f0 = __half2float(*reinterpret_cast<const __half *>(ksm + ((8 * n + 2 * t) * C::NBLK + blk) * 2));
-                                const float f1 = __half2float(*reinterpret_cast<const __half *>(ksm + ((8 * n + 2 * t + 1) * C::NBLK + blk) * 2));
+                                const int bias = slot_qsum[(mt * 8 + g) * C::NBLK + wj * C::NBLKK + blk];
+                                const float f0 = __half2float(*reinterpret_cast<const __half *>(ksm + ((8 * n + 2 * t) * C::NBLKK + blk) * 2));
+                                const float f1 = __half2float(*reinterpret_cast<const __half *>(ksm + ((8 * n + 2 * t + 1) * C::NBLKK + blk) * 2));
                                 sblk[mt][0] = fmaf((float)(cb[0] * 256 + cb[2] - bias), f0, sblk[mt][0]);
                                 sblk[mt][1] = fmaf((float)(cb[1] * 256 + cb[3] - bias), f1, sblk[mt][1]);
                             }
@@ -1159,7 +1184,12 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                     const float2 kk = *reinterpret_cast<const float2 *>(ksm + (8 * n + 2 * t) * 4);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        const int bias = slot_qsum[(mt * 8 + g) * C::NBLK];          // 8 * sum over the whole row
+                        int bias = slot_qsum[(mt * 8 + g) * C::NBLK];                // 8 * sum over the whole row ...
+                        if constexpr (QS > 1) {                                      // ... or over this warp's blocks
+                            bias = 0;
+#pragma unroll
+                            for (int bk = 0; bk < C::NBLKK; ++bk) bias += slot_qsum[(mt * 8 + g) * C::NBLK + wj * C::NBLKK + bk];
+                        }
                         s2[mt][n][0] = (float)(c[mt][0] * 256 + c[mt][2] - bias) * (qscale[mt] * kk.x);
                         s2[mt][n][1] = (float)(c[mt][1] * 256 + c[mt][3] - bias) * (qscale[mt] * kk.y);
                     }
@@ -1171,6 +1201,31 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                     }
                 }
             }
+        }
+        if constexpr (QS > 1) {
+            // ---- the quad adds up its partial logits.  Every warp writes its 8 MT values per lane, the quad meets at its
+            // named barrier (one per tile; the buffer alternates with the tile's parity, so the next tile's writes cannot
+            // overtake a warp still reading), and every warp sums the QS partials in the same order: the four warps hold
+            // bit-identical logits, hence identical softmax references, weights and denominators.
+            float *xq = xch_region + (size_t)((quad * 2 + (it & 1)) * QS) * (MT * 8 * 32);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int n = 0; n < 4; ++n)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) xq[(wj * MT * 8 + (mt * 4 + n) * 2 + e) * 32 + lane] = s2[mt][n][e];
+            asm volatile("bar.sync %0, %1;\n" ::"r"(1 + quad), "n"(QS * 32) : "memory");
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int n = 0; n < 4; ++n)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        float acc_s = 0.0f;
+#pragma unroll
+                        for (int jj = 0; jj < QS; ++jj) acc_s += xq[(jj * MT * 8 + (mt * 4 + n) * 2 + e) * 32 + lane];
+                        s2[mt][n][e] = acc_s;
+                    }
         }
         if (need_mask) {
 #pragma unroll
@@ -1197,7 +1252,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
                 for (int e = 0; e < 2; ++e)
 #pragma unroll
                     for (int vb = 0; vb < NVB; ++vb)
-                        vsc[n][e][vb] = __half2float(*reinterpret_cast<const __half *>(vsm + ((8 * n + 2 * t + e) * C::NBLK + dsl * C::NBLKV + vb) * 2));
+                        vsc[n][e][vb] = __half2float(*reinterpret_cast<const __half *>(vsm + ((8 * n + 2 * t + e) * C::NBLKK + (QS > 1 ? 0 : dsl * C::NBLKV) + vb) * 2));
             } else {
                 const float2 vv = *reinterpret_cast<const float2 *>(vsm + (8 * n + 2 * t) * 4);
                 vsc[n][0][0] = vv.x; vsc[n][1][0] = vv.y;
@@ -1352,26 +1407,28 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS>::NW * 32)
         const int idx = rg * C::NSLOT + sl;
         const int r = div_kvg(p, idx), j = idx - r * p.kvg;
         if (r >= p.S) break;
+        // one (m, l, o) per tile stream: the warps of a quad hold the same (m, l) and different dims
         float mstar = M_INIT;
 #pragma unroll
-        for (int w = 0; w < NWARP; ++w) mstar = fmaxf(mstar, mbuf[((size_t)w * C::NSLOT + sl) * (HDV + 2) + HDV]);
-        float wgt[NWARP], lstar = 0.0f;
+        for (int w = 0; w < NQ; ++w) mstar = fmaxf(mstar, mbuf[((size_t)(w * QS) * C::NSLOT + sl) * (HDV + 2) + HDV]);
+        float wgt[NQ], lstar = 0.0f;
 #pragma unroll
-        for (int w = 0; w < NWARP; ++w) {
-            const float *rw = mbuf + ((size_t)w * C::NSLOT + sl) * (HDV + 2);
+        for (int w = 0; w < NQ; ++w) {
+            const float *rw = mbuf + ((size_t)(w * QS) * C::NSLOT + sl) * (HDV + 2);
             wgt[w] = ex2f(rw[HDV] - mstar);
             lstar += wgt[w] * rw[HDV + 1];
         }
         const long grow = ((long)b * p.S + r) * p.nh + kvh * p.kvg + j;
-        for (int d = threadIdx.x; d < HDV; d += NWARP * 32) {
+        for (int dq = threadIdx.x; dq < HDV * QS; dq += NWARP * 32) {
+            const int sj = dq / HDV, d = dq - sj * HDV;            // slice of the quad that holds the dim, dim inside the slice
             float o = 0.0f;
 #pragma unroll
-            for (int w = 0; w < NWARP; ++w) o += wgt[w] * mbuf[((size_t)w * C::NSLOT + sl) * (HDV + 2) + d];
+            for (int w = 0; w < NQ; ++w) o += wgt[w] * mbuf[((size_t)(w * QS + sj) * C::NSLOT + sl) * (HDV + 2) + d];
             if (p.write_partial) {
-                p.partial[((size_t)split * p.grows + grow) * (HD + 2) + dsl * HDV + d] = o;
+                p.partial[((size_t)split * p.grows + grow) * (HD + 2) + dsl * HDV * QS + dq] = o;
             } else {
                 const float v = lstar > 0.0f ? o / lstar : 0.0f;
-                const long oi = b * p.out_batch_stride + ((long)r * p.nh + kvh * p.kvg + j) * HD + dsl * HDV + d;
+                const long oi = b * p.out_batch_stride + ((long)r * p.nh + kvh * p.kvg + j) * HD + dsl * HDV * QS + dq;
                 if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(v);
                 else reinterpret_cast<float *>(p.out)[oi] = v;
             }

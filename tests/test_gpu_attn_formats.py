@@ -87,3 +87,43 @@ def test_verify_rows_wider_heads(oracle, fmt):
     for r in range(S):
         ok, rel = within(got[r], want[r], TOL)
         assert ok, f"row {r}: {rel:.2e} x RMS"
+
+
+@pytest.mark.parametrize("fmt", ["i8", "i4", "i4b32"])
+@pytest.mark.parametrize("hd,nkv,kvg", [(512, 2, 8), (256, 4, 2)])
+@pytest.mark.parametrize("T,cap,splits", [(33, 64, 0), (4097, 4100, 0), (3000, 1024, 0), (6000, 6000, 5), (2500, 2500, 1)])
+def test_wider_heads_lengths_rings_and_splits(oracle, fmt, hd, nkv, kvg, T, cap, splits):
+    """Head dims 256 / 512 (warps of a quad own 128-dim slices of K, V and the output and add their partial
+    logits up): ragged lengths, a wrapped ring read from an odd slot, many tiles per quad, forced split counts."""
+    rng = np.random.default_rng(hd + T + splits)
+    nh = nkv * kvg
+    c = build_cache(fmt, rng, T, nkv, hd, cap=cap)
+    q = bf16_normal(rng, (1, nh, hd))
+    scale = 1.0 / np.sqrt(hd)
+    klen = min(T, cap) - (3 if cap < T else 0)
+    win_start = T - klen
+    want = exact(oracle, c, q, klen=klen, win_start=win_start, scale=scale)
+    got, _ = fused(c, q, klen=klen, win_start=win_start, scale=scale, force_splits=splits)
+    ok, rel = within(got, want, TOL)
+    assert ok, f"{fmt} hd={hd} T={T}: {rel:.2e} x RMS"
+    assert not np.any(got == SENTINEL)
+
+
+@pytest.mark.parametrize("fmt,hd", [("i4b32", 512), ("i8", 256)])
+def test_wider_heads_partial_export_merges_to_full(oracle, fmt, hd):
+    """Two sequence shards of a wide-head cache export (o, m, l); their merge equals full attention."""
+    import torch
+    from tests._gpu import DEV, dev, host
+    rng = np.random.default_rng(hd)
+    nkv, kvg, T = 2, 4, 2048
+    nh = nkv * kvg
+    c = build_cache(fmt, rng, T, nkv, hd)
+    q = bf16_normal(rng, (1, nh, hd))
+    scale = 1.0 / np.sqrt(hd)
+    want = exact(oracle, c, q, klen=T, scale=scale)
+    parts = [fused(c, q, klen=T // 2, win_start=g * (T // 2), scale=scale, partial=True)[0] for g in range(2)]
+    out = torch.full((nh, hd), SENTINEL, dtype=torch.float32, device=DEV)
+    ops.attn_merge_partials(None, dev(np.stack(parts)), 2, nh, hd, out)
+    torch.cuda.synchronize()
+    ok, rel = within(host(out)[None], want, TOL)
+    assert ok, f"{rel:.2e} x RMS"
