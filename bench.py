@@ -756,11 +756,15 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
             dist.all_gather_object(lst, b)
             return lst
 
-        group = SeqShardGroup(rank, world, NH, HD, agb)
+        group = SeqShardGroup(rank, world, NH, HD, agb, timeout_us=200000)
         if world > 1:
             dist.barrier()
-        us_peer = time_call(torch, lambda: group.decode(stream, a2), n5)
+        group.decode(stream, a2)                        # one step first: a group that cannot exchange is not timed
         peer_rc = group.status(stream)
+        if world > 1:
+            tt = torch.tensor([float(peer_rc)], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MIN); peer_rc = int(tt.item())
+        us_peer = time_call(torch, lambda: group.decode(stream, a2), n5) if peer_rc == 0 else float("inf")
+        peer_rc = peer_rc or group.status(stream)
         if world > 1:
             tt = torch.tensor([us, us_peer, *ph], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             us, us_peer, ph = float(tt[0]), float(tt[1]), tt[2:].cpu().numpy()
@@ -768,8 +772,9 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
         o32 = torch.zeros((NH, HD), dtype=torch.float32, device=dev); o32p = torch.zeros_like(o32)
         ops.attn_fused(stream, a); gather(); ops.attn_merge_partials(stream, gathered, world, NH, HD, o32, ops.F32)
         a2.out, a2.out_type = o32p.data_ptr(), ops.F32
-        group.decode(stream, a2)
-        peer_rc = peer_rc or group.status(stream)
+        if peer_rc == 0:
+            group.decode(stream, a2)
+            peer_rc = group.status(stream)
         from oracle import oracle as orc
         orc.set_threads(max(1, (os.cpu_count() or 1) // world))
         _, pe = orc.attn_exact(orc.bf16_round(qh[0]), k[0].cpu().numpy(), v[0].cpu().numpy(), ks[0].cpu().numpy(), vs[0].cpu().numpy(),
@@ -782,10 +787,11 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
         by = algorithmic_bytes(NKV, NH // NKV, 524288, HD)
         out["c5b_seq_sharded_512k"] = {
             "us_per_layer": round(min(us, us_peer), 2), "GBps_aggregate": round(by / min(us, us_peer) / 1e3, 1), "gpus": world,
+            "exchange": "peer stores, one launch per rank" if us_peer <= us else "NCCL all-gather + merge launch",
             "nccl_allgather_plus_merge": {"us_per_layer": round(us, 2), "phases_us": {"attention": round(float(ph[0]), 2),
                                           "all_gather": round(float(ph[1]), 2), "merge": round(float(ph[2]), 2)},
                                           "parity_rel_err": float(f"{rel_err(o32.cpu().numpy(), want):.3e}")},
-            "peer_stores_one_launch": {"us_per_layer": round(us_peer, 2), "status": int(peer_rc),
+            "peer_stores_one_launch": {"us_per_layer": round(us_peer, 2) if us_peer != float("inf") else None, "status": int(peer_rc),
                                        "parity_rel_err": float(f"{rel_err(o32p.cpu().numpy(), want):.3e}")},
             "parity_bar": 2e-3}
         group.close()
