@@ -632,7 +632,9 @@ __device__ __noinline__ void peer_exchange_and_merge(const KParams &p, int b, in
         const float2 v = __ldcg(reinterpret_cast<const float2 *>(p.peer_rows[me] + off));
         *reinterpret_cast<float2 *>(p.peer_rows[g] + off) = v;
     }
-    __threadfence_system();
+    // The stamps are released at system scope by the threads that write them; the CTA barrier in front orders every
+    // thread's row stores before them (release is cumulative over what the barrier made visible to the releasing
+    // thread), so no thread pays for a system-wide fence of its own.
     __syncthreads();
     for (int e = tid; e < nrows * (G - 1); e += NTHR) {
         const int gi = e / nrows, sl = e - gi * nrows;
