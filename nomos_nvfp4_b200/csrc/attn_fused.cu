@@ -150,6 +150,20 @@ struct Plan {
     int mt, row_groups, tile0, ntiles, splits, tiles_per_split, grows;
 };
 
+// Whether every CTA of a unit merges a share of the unit's rows (merge_coop) instead of the last one merging all of
+// them.  Worth it when the partials of a unit are large (a verify call: 84 KB; a 512-wide head: 600 KB through one SM
+// took several microseconds), allowed when the whole grid is resident at once (a CTA then waits for CTAs that are
+// running, not for ones that have no SM yet), the outputs take 8-byte stores and no peer exchange follows.
+static bool use_coop_merge(const AttnArgs &a, int splits, int arrivals, long ctas, int occupancy, int rows_per_unit, int hd) {
+    if (splits < 2 || splits > 64 || arrivals != splits || a.peer_world > 1) return false;
+    if (ctas > (long)device_info().sm_count * occupancy) return false;
+    // (at 84 KB -- nine splits of a verify call -- it measured a loss, 27.5 -> 34 us: every CTA then stays on its SM
+    // until the last one has arrived, which keeps the next launch's CTAs from starting under this launch's tail)
+    if ((long)splits * rows_per_unit * (hd + 2) * 4 < 256 * 1024) return false;
+    const bool al8 = ((reinterpret_cast<uintptr_t>(a.out) | reinterpret_cast<uintptr_t>(a.partial_out)) & 7) == 0 && (a.out_batch_stride & 3) == 0;
+    return al8;
+}
+
 // Peer fields of a sequence-sharded call; returns where this rank's own merged rows go.
 static float *fill_peer_params(KParams &p, const AttnArgs &a, long grows) {
     p.peer_world = a.peer_world > 1 ? a.peer_world : 0;
@@ -219,7 +233,7 @@ static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp, int d
         int max_splits = std::min(pl.ntiles, 512);
         if (a.fit_splits_to_ws) {
             const long per_split = (long)pl.grows * (hd + 2) * 4;
-            const long fixed = 16 + 8L * units;                     // alignment slack + arrival counters
+            const long fixed = 16 + 16L * units;                    // alignment slack + arrival and departure counters
             max_splits = (int)std::max<long>(1, std::min<long>(max_splits, a.workspace ? (a.ws_bytes - fixed) / per_split : 0));
         }
         for (int n = 1; n <= max_splits; ++n) {
@@ -249,8 +263,9 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     const long part_bytes = (((long)pl.splits * pl.grows * (HD + 2) * 4) + 15) / 16 * 16;
     // a sequence-sharded call always ends in the unit's merging CTA (it runs the exchange), also with one split
     const bool in_kernel_merge = pl.splits > 1 || a.peer_world > 1;
-    const long need = in_kernel_merge ? part_bytes + units * 8 : 0;
-    if (query_ws) { *ws_needed = part_bytes + units * 8; return NOMOS_OK; }   // also enough for a sequence-sharded call, which merges in the kernel even with one split
+    // two counter words per unit: arrivals, and (cooperative merge) departures
+    const long need = in_kernel_merge ? part_bytes + units * 16 : 0;
+    if (query_ws) { *ws_needed = part_bytes + units * 16; return NOMOS_OK; }   // also enough for a sequence-sharded call, which merges in the kernel even with one split
     if (need > a.ws_bytes || (need > 0 && a.workspace == nullptr)) {
         set_error("attention workspace too small: need %ld bytes, have %ld", need, a.ws_bytes);
         return NOMOS_ECAPACITY;
@@ -270,6 +285,8 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     p.counters = in_kernel_merge ? reinterpret_cast<unsigned long long *>(static_cast<char *>(a.workspace) + part_bytes) : nullptr;
     p.splits = pl.splits;
     p.arrivals = pl.splits * DS;
+    p.departures = p.counters ? p.counters + units : nullptr;
+    p.coop_merge = use_coop_merge(a, pl.splits, p.arrivals, (long)pl.splits * DS * units, occ, std::min(C::NSLOT, a.S * a.kvg), HD) ? 1 : 0;
     p.partial_export = a.partial_out;
     if (float *own = fill_peer_params(p, a, pl.grows)) p.partial_export = own;
     p.early_rows = settled_rows(a);
@@ -419,7 +436,7 @@ static Tc5Plan tc5_plan(const AttnArgs &a, int ns, int occupancy) {
         int max_splits = std::min(pl.ntiles, 512);
         if (a.fit_splits_to_ws) {
             const long per_split = (long)pl.grows * (a.l_hd + 2) * 4;
-            const long fixed = 16 + 8L * units;
+            const long fixed = 16 + 16L * units;
             max_splits = (int)std::max<long>(1, std::min<long>(max_splits, a.workspace ? (a.ws_bytes - fixed) / per_split : 0));
         }
         for (int n = 1; n <= max_splits; ++n) {
@@ -446,8 +463,8 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     const long units = (long)a.nkv * a.batch * pl.row_groups;
     const long part_bytes = (((long)pl.splits * pl.grows * (a.l_hd + 2) * 4) + 15) / 16 * 16;
     const bool in_kernel_merge = pl.splits > 1 || a.peer_world > 1;
-    const long need = in_kernel_merge ? part_bytes + units * 8 : 0;
-    if (query_ws) { *ws_needed = part_bytes + units * 8; return NOMOS_OK; }   // also enough for a sequence-sharded call, which merges in the kernel even with one split
+    const long need = in_kernel_merge ? part_bytes + units * 16 : 0;
+    if (query_ws) { *ws_needed = part_bytes + units * 16; return NOMOS_OK; }   // also enough for a sequence-sharded call, which merges in the kernel even with one split
     if (need > a.ws_bytes || (need > 0 && a.workspace == nullptr)) {
         set_error("attention workspace too small: need %ld bytes, have %ld", need, a.ws_bytes);
         return NOMOS_ECAPACITY;
@@ -481,6 +498,8 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     p.counters = in_kernel_merge ? reinterpret_cast<unsigned long long *>(static_cast<char *>(a.workspace) + part_bytes) : nullptr;
     p.splits = pl.splits;
     p.arrivals = pl.splits;
+    p.departures = p.counters ? p.counters + units : nullptr;
+    p.coop_merge = (!paged && use_coop_merge(a, pl.splits, p.arrivals, (long)pl.splits * units, /* one CTA per SM, whatever the plan assumes */ 1, std::min(NS, a.S * a.kvg), a.l_hd)) ? 1 : 0;
     p.partial_export = a.partial_out;
     if (float *own = fill_peer_params(p, a, pl.grows)) p.partial_export = own;
     p.early_rows = paged ? 0 : settled_rows(a);

@@ -118,6 +118,9 @@ struct KParams {
     unsigned long long *counters;   // one word per unit: (tag << 16) | arrivals, see merge_splits_in_kernel; nullptr = no in-kernel merge
     int splits;
     int arrivals;                   // CTAs per unit that arrive before the merge: splits x head-dim slices
+    unsigned long long *departures; // coop_merge: one more tagged word per unit, counting the CTAs that finished their share
+    int coop_merge;                 // 1: every CTA of a unit merges a share of the unit's rows once all have arrived (the whole
+                                    //    grid is resident at once, so waiting for the others cannot starve them)
     float *partial_export;          // optional exported (o, m, l) per row, m in natural-log units
     int early_rows;                 // window rows [0, early_rows) may be read before griddepcontrol.wait
     // fused quantize-on-write: the last n_new keys of the window are given as fp32 rows
@@ -411,10 +414,163 @@ __device__ __forceinline__ bool merge_without_staging(const KParams &p, int b, i
 // thread of a CTA after its partial (o, m, l) rows are stored.  The last CTA of the unit to
 // arrive merges the unit's rows; the others return.  `scratch` is shared memory the CTA no
 // longer needs, at least 8 * NSLOT * splits bytes.
+// One arrival on a tagged counter word; returns how many have arrived including this one, or -1 if the word could
+// not be brought under the tag within the try limit.  The word is (tag << 16 | arrivals): the CTA that closes a round
+// leaves it tagged with zero arrivals, so the common case is a single atomic add.  A word without the tag has never
+// been used by this library (the workspace is caller-owned and arrives uninitialised): the add went to garbage, and
+// the arrivals that find garbage install a tagged word with compare-and-swap, which only fails when another arrival
+// made progress.
+constexpr unsigned long long ARRIVE_TAG = 0x6e6f6d6f7341ull;
+__device__ __forceinline__ int tagged_arrive(unsigned long long *ctr) {
+    unsigned long long old = arrive_add(ctr);
+    if ((old >> 16) == ARRIVE_TAG) return (int)(old & 0xffffull) + 1;
+    for (int tries = 0; tries < (1 << 16); ++tries) {            // bounded: gives up rather than spin forever
+        const unsigned long long cur = *reinterpret_cast<volatile unsigned long long *>(ctr);
+        if ((cur >> 16) == ARRIVE_TAG) {
+            old = arrive_add(ctr);
+            if ((old >> 16) == ARRIVE_TAG) return (int)(old & 0xffffull) + 1;
+        } else {
+            __threadfence();          // rare path: plain fences around the compare-and-swap
+            const bool won = atomicCAS(ctr, cur, (ARRIVE_TAG << 16) | 1ull) == cur;
+            __threadfence();
+            if (won) return 1;
+        }
+    }
+    return -1;
+}
+__device__ __forceinline__ unsigned long long ld_acquire_gpu(const unsigned long long *addr) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];\n" : "=l"(v) : "l"(addr) : "memory");
+    return v;
+}
+
+// Cooperative merge: CTA number `share` of the G that make up a unit merges pairs [share * per, (share + 1) * per) of
+// the unit's nrows * HD / 2 output pairs, instead of the last CTA merging all of them through one SM (84 KB of
+// partials for a verify call, 600 KB for a 512-wide head).  A warp takes EL pairs at a time; lane k fetches split k's
+// (m, l) and partial outputs of those pairs (a second round for splits 32..63), so every load of the warp is in
+// flight at once; the reference, the denominator and the sums are warp reductions.
+template <int HD>
+__device__ __noinline__ void merge_coop(const SmallMergeArgs a, int share, int tid, int nthr) {
+    constexpr int EL = 4, HP = HD / 2;
+    const int G = a.G, lane = tid & 31, warp = tid >> 5, nwarp = nthr >> 5;
+    const int total = a.nrows * HP;
+    const int per = (total + G - 1) / G;
+    const int begin = share * per, end = min(total, begin + per);
+#pragma unroll 1
+    for (int e0 = begin + warp * EL; e0 < end; e0 += nwarp * EL) {
+        float2 ml[2][EL], v[2][EL];
+        long grow[EL];
+        int hrow[EL], dd[EL];
+#pragma unroll
+        for (int j = 0; j < EL; ++j) {
+            const int e = min(e0 + j, end - 1);
+            const int sl = e / HP;
+            dd[j] = 2 * (e - sl * HP);
+            const int idx = a.first + sl;
+            const int r = a.kvg_magic ? (int)__umulhi((unsigned)idx, a.kvg_magic) : idx;
+            hrow[j] = r * a.nh + a.kvh * a.kvg + (idx - r * a.kvg);
+            grow[j] = (long)a.b * a.S * a.nh + hrow[j];
+        }
+#pragma unroll
+        for (int rd = 0; rd < 2; ++rd) {
+            const int k = min(lane + 32 * rd, G - 1);
+            if (rd == 1 && G <= 32) break;
+#pragma unroll
+            for (int j = 0; j < EL; ++j) {
+                const float *row = a.partial + (size_t)k * a.rstride + (size_t)grow[j] * (HD + 2);
+                ml[rd][j] = __ldcg(reinterpret_cast<const float2 *>(row + HD));
+                v[rd][j] = __ldcg(reinterpret_cast<const float2 *>(row + dd[j]));
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < EL; ++j) {
+            float mk[2], m = -CUDART_INF_F;
+#pragma unroll
+            for (int rd = 0; rd < 2; ++rd) {
+                const bool live = (rd == 0 || G > 32) && lane + 32 * rd < G && ml[rd][j].y > 0.0f;   // a split that saw a key
+                mk[rd] = live ? ml[rd][j].x : -CUDART_INF_F;
+                m = fmaxf(m, mk[rd]);
+            }
+            m = warp_max(m);
+            if (m == -CUDART_INF_F) m = 0.0f;
+            float l = 0.0f, ox = 0.0f, oy = 0.0f;
+#pragma unroll
+            for (int rd = 0; rd < 2; ++rd) {
+                if (rd == 1 && G <= 32) break;
+                const float w = ex2f(mk[rd] - m);                  // 0 for dead lanes
+                l = fmaf(w, ml[rd][j].y, l);
+                ox = fmaf(w, v[rd][j].x, ox);
+                oy = fmaf(w, v[rd][j].y, oy);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                l += __shfl_xor_sync(0xffffffffu, l, o);
+                ox += __shfl_xor_sync(0xffffffffu, ox, o);
+                oy += __shfl_xor_sync(0xffffffffu, oy, o);
+            }
+            if (lane != 0 || e0 + j >= end) continue;
+            if (a.partial_export) {
+                float *pe = a.partial_export + (size_t)grow[j] * (HD + 2);
+                *reinterpret_cast<float2 *>(pe + dd[j]) = make_float2(ox, oy);
+                if (dd[j] == 0) *reinterpret_cast<float2 *>(pe + HD) = make_float2(l > 0.0f ? m * LN2 : 0.0f, l);
+            } else {
+                const float vx = l > 0.0f ? ox / l : 0.0f, vy = l > 0.0f ? oy / l : 0.0f;
+                const long oi = a.b * a.out_batch_stride + (long)hrow[j] * HD + dd[j];
+                if (a.out_type == ET_BF16) *reinterpret_cast<__nv_bfloat162 *>(reinterpret_cast<__nv_bfloat16 *>(a.out) + oi) = __floats2bfloat162_rn(vx, vy);
+                else *reinterpret_cast<float2 *>(reinterpret_cast<float *>(a.out) + oi) = make_float2(vx, vy);
+            }
+        }
+    }
+}
+
+// The cooperative form of the unit merge, out of line (it runs once per CTA; p is the kernels' __grid_constant__
+// parameter block): arrive, wait -- with a time limit -- until every CTA of the unit has arrived, merge this CTA's
+// share, leave.  The whole grid is resident at once (host-checked), so the CTAs waited for are running.
+template <int NSLOT, int HD, int NTHR>
+__device__ __noinline__ void coop_merge_unit(const KParams &p, int b, int kvh, int rg) {
+    __shared__ int s_go, s_share;
+    unsigned long long *ctr = p.counters + ((size_t)blockIdx.z * gridDim.y + blockIdx.y);
+    __syncthreads();                      // all partial stores of this CTA are issued
+    if (threadIdx.x == 0) {
+        const int arrived = tagged_arrive(ctr);
+        s_share = arrived - 1;
+        bool all = arrived == p.arrivals;
+        if (arrived > 0 && !all) {
+            unsigned long long t0, t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            for (;;) {
+                const unsigned long long cur = ld_acquire_gpu(ctr);
+                if ((cur >> 16) == ARRIVE_TAG && (int)(cur & 0xffffull) == p.arrivals) { all = true; break; }
+                __nanosleep(100);
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                if (t1 - t0 > 1000000000ull) { atomicOr(p.fault, 1u); break; }
+            }
+        }
+        s_go = all ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_go) return;
+    SmallMergeArgs sa;
+    small_merge_args<NSLOT, HD, NTHR>(p, b, kvh, rg, sa);
+    merge_coop<HD>(sa, s_share, threadIdx.x, NTHR);
+    __syncthreads();                      // this CTA's share is stored
+    if (threadIdx.x == 0) {
+        unsigned long long *dep = p.departures + ((size_t)blockIdx.z * gridDim.y + blockIdx.y);
+        if (tagged_arrive(dep) == p.arrivals) {                        // the last one out leaves both words clean
+            *dep = ARRIVE_TAG << 16;
+            *ctr = ARRIVE_TAG << 16;
+        }
+    }
+}
+
 // Returns true in the CTA that merged the unit's rows (the last one to arrive).
 template <int NSLOT, int HD, int NTHR, int GB = 8>
 __device__ __forceinline__ bool merge_unit_splits(const KParams &p, uint8_t *scratch, int b, int kvh, int rg) {
     if (p.counters == nullptr) return false;
+    if (p.coop_merge) {                   // (no single CTA then holds the unit's merged rows)
+        coop_merge_unit<NSLOT, HD, NTHR>(p, b, kvh, rg);
+        return false;
+    }
 
     // ------------------------------------------- in-kernel merge across the splits
     // Arrival counting without a zeroed workspace (see the tag below).
@@ -425,36 +581,12 @@ __device__ __forceinline__ bool merge_unit_splits(const KParams &p, uint8_t *scr
         // stores (ordered before it by the barrier above) visible before the count, acquire orders the
         // merging CTA's loads (all its threads, through the barrier below) after every other arrival.
         unsigned long long *ctr = p.counters + ((size_t)blockIdx.z * gridDim.y + blockIdx.y);
-        // The word is (tag << 16 | arrivals).  The merging CTA leaves it tagged with zero arrivals, so
-        // the common case is a single atomic add.  A word without the tag has never been used by this
-        // library (the workspace is caller-owned and arrives uninitialised): the add went to garbage,
-        // and the arrivals that find garbage install a tagged word with compare-and-swap, which only
-        // fails when another arrival made progress.
-        constexpr unsigned long long TAG = 0x6e6f6d6f7341ull;
-        unsigned long long old = arrive_add(ctr);
-        int arrived = -1;
-        if ((old >> 16) == TAG) {
-            arrived = (int)(old & 0xffffull) + 1;
-        } else {
-            for (int tries = 0; tries < (1 << 16); ++tries) {    // bounded: gives up rather than spin forever
-                const unsigned long long cur = *reinterpret_cast<volatile unsigned long long *>(ctr);
-                if ((cur >> 16) == TAG) {
-                    old = arrive_add(ctr);
-                    if ((old >> 16) == TAG) { arrived = (int)(old & 0xffffull) + 1; break; }
-                } else {
-                    __threadfence();          // rare path: plain fences around the compare-and-swap
-                    const bool won = atomicCAS(ctr, cur, (TAG << 16) | 1ull) == cur;
-                    __threadfence();
-                    if (won) { arrived = 1; break; }
-                }
-            }
-        }
-        if (arrived == p.arrivals) *ctr = TAG << 16;                // clean for the next launch on this workspace
+        const int arrived = tagged_arrive(ctr);
+        if (arrived == p.arrivals) *ctr = ARRIVE_TAG << 16;             // clean for the next launch on this workspace
         s_last = (arrived == p.arrivals);
     }
     __syncthreads();
     if (!s_last) return false;
-
     // The last CTA of the unit merges its rows.  Phase A stages every split's (m, l) in shared
     // memory; phase B (a warp per row) turns them into weights 2^(m_i - m*) and the merged
     // denominator; phase C gives each thread (row, dim) elements and streams the splits' partial
