@@ -442,119 +442,128 @@ def time_call(torch, fn, iters: int, warm: int = 5) -> float:
     return a.elapsed_time(b) / iters * 1000.0       # us
 
 
-def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
-    """Secondary configurations, bounded in time.  Not the headline; reported for context."""
+def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> dict:
+    """Secondary configurations, bounded in time.  Not the headline; reported for context.
+    `only`: names of the cases to run (profiler captures run one case by itself)."""
     out = {}
+
+    def want(*names):
+        return only is None or any(n in only for n in names)
     stream = torch.cuda.current_stream().cuda_stream
     # configuration 4: verify, VB = 9 rows against 16384 cached keys (+9 new), int8 KV.
     # Four layer caches are cycled (278 MB > L2), as a 60-layer verify pass would.
-    try:
-        S, T4 = 9, 16384 + 9
-        caches = [make_layer_cache(torch, ops, dev, 1, NKV, T4, HD, 1004 + i) for i in range(NLAYERS)]
-        q = torch.randn((1, S, NH, HD), device=dev).to(torch.bfloat16)
-        o = torch.zeros((1, S, NH, HD), dtype=torch.bfloat16, device=dev)
-        al = []
-        for k, v, ks, vs in caches:
-            al.append(ops.make_args(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=o, kv_fmt=ops.KV_I8,
-                                    q_type=ops.BF16, out_type=ops.BF16, S=S, nh=NH, nkv=NKV, kvg=NH // NKV, l_hd=HD,
-                                    cache_hd=HD, cache_cap=T4, klen=T4, softmax_scale=SOFTMAX_SCALE))
-        wsb = ops.attn_workspace_bytes(al[0])
-        ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
-        for a in al:
-            a.workspace, a.ws_bytes = ws.data_ptr(), wsb
-        ctr = [0]
+    if want("c4_verify_vb9_16k"):
+        try:
+            S, T4 = 9, 16384 + 9
+            caches = [make_layer_cache(torch, ops, dev, 1, NKV, T4, HD, 1004 + i) for i in range(NLAYERS)]
+            q = torch.randn((1, S, NH, HD), device=dev).to(torch.bfloat16)
+            o = torch.zeros((1, S, NH, HD), dtype=torch.bfloat16, device=dev)
+            al = []
+            for k, v, ks, vs in caches:
+                al.append(ops.make_args(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=o, kv_fmt=ops.KV_I8,
+                                        q_type=ops.BF16, out_type=ops.BF16, S=S, nh=NH, nkv=NKV, kvg=NH // NKV, l_hd=HD,
+                                        cache_hd=HD, cache_cap=T4, klen=T4, softmax_scale=SOFTMAX_SCALE))
+            wsb = ops.attn_workspace_bytes(al[0])
+            ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+            for a in al:
+                a.workspace, a.ws_bytes = ws.data_ptr(), wsb
+            ctr = [0]
 
-        def fn4():
-            ops.attn_fused(stream, al[ctr[0] % NLAYERS]); ctr[0] += 1
+            def fn4():
+                ops.attn_fused(stream, al[ctr[0] % NLAYERS]); ctr[0] += 1
 
-        us = time_call(torch, fn4, iters)
-        by = algorithmic_bytes(NKV, NH // NKV, T4, HD, 1, S)
-        out["c4_verify_vb9_16k"] = {"us_per_layer": round(us, 2), "GBps": round(by / us / 1e3, 1),
-                                    "attn_only_tok_per_s_60_layers": round(S / (60 * us * 1e-6), 1)}
-        if rank == 0:          # parity of the timed call (fp32 output, layer 0) against the oracle, every row against its own RMS
-            from oracle import oracle as orc
-            o32 = torch.zeros((1, S, NH, HD), dtype=torch.float32, device=dev)
-            al[0].out, al[0].out_type = o32.data_ptr(), ops.F32
-            ops.attn_fused(stream, al[0]); torch.cuda.synchronize()
-            k0, v0, ks0, vs0 = (t[0].cpu().numpy() for t in caches[0])
-            want = orc.attn_exact(q[0].float().cpu().numpy(), k0, v0, ks0, vs0, orc.KV_I8, NH, NKV, HD, HD, T4, S=S,
-                                  query_base_pos=T4 - S, softmax_scale=float(SOFTMAX_SCALE))
-            got = o32[0].cpu().numpy()
-            out["c4_verify_vb9_16k"]["parity_rel_err"] = float(f"{max(rel_err(got[r], want[r]) for r in range(S)):.3e}")
-        del caches, ws
-    except Exception as e:   # report, never hide
-        out["c4_verify_vb9_16k"] = {"error": str(e)}
+            us = time_call(torch, fn4, iters)
+            by = algorithmic_bytes(NKV, NH // NKV, T4, HD, 1, S)
+            out["c4_verify_vb9_16k"] = {"us_per_layer": round(us, 2), "GBps": round(by / us / 1e3, 1),
+                                        "attn_only_tok_per_s_60_layers": round(S / (60 * us * 1e-6), 1)}
+            if rank == 0:          # parity of the timed call (fp32 output, layer 0) against the oracle, every row against its own RMS
+                from oracle import oracle as orc
+                o32 = torch.zeros((1, S, NH, HD), dtype=torch.float32, device=dev)
+                al[0].out, al[0].out_type = o32.data_ptr(), ops.F32
+                ops.attn_fused(stream, al[0]); torch.cuda.synchronize()
+                k0, v0, ks0, vs0 = (t[0].cpu().numpy() for t in caches[0])
+                want = orc.attn_exact(q[0].float().cpu().numpy(), k0, v0, ks0, vs0, orc.KV_I8, NH, NKV, HD, HD, T4, S=S,
+                                      query_base_pos=T4 - S, softmax_scale=float(SOFTMAX_SCALE))
+                got = o32[0].cpu().numpy()
+                out["c4_verify_vb9_16k"]["parity_rel_err"] = float(f"{max(rel_err(got[r], want[r]) for r in range(S)):.3e}")
+            del caches, ws
+        except Exception as e:   # report, never hide
+            out["c4_verify_vb9_16k"] = {"error": str(e)}
     # prefill: 2048 prompt tokens, 32q/16kv x 128, int8 KV already appended; causal attention over the quantised
     # cache on the query-major tcgen05 kernel (no S x S score matrix), and the same call as mma.sync row groups
-    try:
-        Sp = 2048
-        cache = make_layer_cache(torch, ops, dev, 1, NKV, Sp, HD, 1404)
-        qh = np.random.default_rng(1404).standard_normal((1, Sp, NH, HD), dtype=np.float32)
-        q = torch.from_numpy(qh).to(dev).to(torch.bfloat16)
-        o = torch.zeros((1, Sp, NH, HD), dtype=torch.bfloat16, device=dev)
-        k, v, ks, vs = cache
-        res = {}
-        for name, fl in (("tcgen05_query_major", 0), ("mma_sync_row_groups", ops.NO_TCGEN05)):
-            a = ops.make_args(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=o, kv_fmt=ops.KV_I8, q_type=ops.BF16,
-                              out_type=ops.BF16, S=Sp, nh=NH, nkv=NKV, kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=Sp, klen=Sp,
-                              softmax_scale=SOFTMAX_SCALE, flags=fl)
+    if want("prefill_s2048_i8"):
+        try:
+            Sp = 2048
+            cache = make_layer_cache(torch, ops, dev, 1, NKV, Sp, HD, 1404)
+            qh = np.random.default_rng(1404).standard_normal((1, Sp, NH, HD), dtype=np.float32)
+            q = torch.from_numpy(qh).to(dev).to(torch.bfloat16)
+            o = torch.zeros((1, Sp, NH, HD), dtype=torch.bfloat16, device=dev)
+            k, v, ks, vs = cache
+            res = {}
+            for name, fl in (("tcgen05_query_major", 0), ("mma_sync_row_groups", ops.NO_TCGEN05)):
+                a = ops.make_args(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=o, kv_fmt=ops.KV_I8, q_type=ops.BF16,
+                                  out_type=ops.BF16, S=Sp, nh=NH, nkv=NKV, kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=Sp, klen=Sp,
+                                  softmax_scale=SOFTMAX_SCALE, flags=fl)
+                wsb = ops.attn_workspace_bytes(a)
+                ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+                a.workspace, a.ws_bytes = ws.data_ptr(), wsb
+                us = time_call(torch, lambda: ops.attn_fused(stream, a), max(10, iters // 8))
+                flops = 4.0 * NH * HD * (Sp * (Sp + 1) / 2.0)           # QK and PV over the causal half
+                res[name] = {"us": round(us, 1), "TFLOPs_causal": round(flops / us / 1e6, 1), "kernel_choice": ops.attn_kernel_choice(a)}
+                if rank == 0 and fl == 0:
+                    from oracle import oracle as orc
+                    o32 = torch.zeros((1, Sp, NH, HD), dtype=torch.float32, device=dev)
+                    a.out, a.out_type = o32.data_ptr(), ops.F32
+                    ops.attn_fused(stream, a); torch.cuda.synchronize()
+                    a.out, a.out_type = o.data_ptr(), ops.BF16
+                    got = o32[0].cpu().numpy()
+                    hk, hv, hks, hvs = (t[0].cpu().numpy() for t in cache)
+                    worst = 0.0
+                    for srow in (0, 1, 63, 64, 127, 128, 1000, 1023, 1024, 2047):
+                        want = orc.attn_exact(orc.bf16_round(qh[0, srow:srow + 1]), hk, hv, hks, hvs, orc.KV_I8, NH, NKV, HD, HD, Sp, S=1,
+                                              query_base_pos=srow, softmax_scale=float(SOFTMAX_SCALE))
+                        worst = max(worst, rel_err(got[srow], want[0]))
+                    res[name]["parity_rel_err_sampled_rows"] = float(f"{worst:.3e}")
+            res["tensor_peak_fraction"] = round(res["tcgen05_query_major"]["TFLOPs_causal"] / measured_peak_tflops(), 4)
+            out["prefill_s2048_i8"] = res
+            del cache
+        except Exception as e:
+            out["prefill_s2048_i8"] = {"error": repr(e)}
+    # configuration 3: sliding-window layer, ring of 1024 at position 8191, int4 block-32, fused append
+    if want("c3_swa_ring_i4b32_fused_append"):
+        try:
+            W, pos = 1024, 8191
+            nb = HD // 32
+            rows = NKV * W
+            k = torch.zeros((NKV, W, HD // 2), dtype=torch.uint8, device=dev); v = torch.zeros_like(k)
+            ks = torch.zeros(rows * nb * 2 + rows * 4, dtype=torch.uint8, device=dev); vs = torch.zeros_like(ks)
+            g = torch.Generator(device=dev); g.manual_seed(1003)
+            for base in range(0, pos, 1024):
+                n = min(1024, pos - base)
+                kk = torch.randn((n, NKV, HD), generator=g, device=dev).to(torch.bfloat16).float().contiguous()
+                vv = torch.randn((n, NKV, HD), generator=g, device=dev).to(torch.bfloat16).float().contiguous()
+                ops.gpu_append_quant_kv_i4(None, kk, vv, k, v, ks, vs, n, NKV, HD, NKV * HD, W, HD, base, nb)
+            q = torch.randn((1, 1, NH, HD), device=dev).to(torch.bfloat16)
+            o = torch.zeros((1, 1, NH, HD), dtype=torch.bfloat16, device=dev)
+            nk = torch.randn((1, NKV, HD), device=dev); nv = torch.randn((1, NKV, HD), device=dev)
+            a = ops.make_args(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=o, kv_fmt=ops.KV_I4B32, q_type=ops.BF16,
+                              out_type=ops.BF16, nh=NH, nkv=NKV, kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=W,
+                              win_start=pos + 1 - W, klen=W, softmax_scale=SOFTMAX_SCALE, new_k=nk, new_v=nv, n_new=1,
+                              new_base_pos=pos)
             wsb = ops.attn_workspace_bytes(a)
             ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
             a.workspace, a.ws_bytes = ws.data_ptr(), wsb
-            us = time_call(torch, lambda: ops.attn_fused(stream, a), max(10, iters // 8))
-            flops = 4.0 * NH * HD * (Sp * (Sp + 1) / 2.0)           # QK and PV over the causal half
-            res[name] = {"us": round(us, 1), "TFLOPs_causal": round(flops / us / 1e6, 1), "kernel_choice": ops.attn_kernel_choice(a)}
-            if rank == 0 and fl == 0:
-                from oracle import oracle as orc
-                o32 = torch.zeros((1, Sp, NH, HD), dtype=torch.float32, device=dev)
-                a.out, a.out_type = o32.data_ptr(), ops.F32
-                ops.attn_fused(stream, a); torch.cuda.synchronize()
-                a.out, a.out_type = o.data_ptr(), ops.BF16
-                got = o32[0].cpu().numpy()
-                hk, hv, hks, hvs = (t[0].cpu().numpy() for t in cache)
-                worst = 0.0
-                for srow in (0, 1, 63, 64, 127, 128, 1000, 1023, 1024, 2047):
-                    want = orc.attn_exact(orc.bf16_round(qh[0, srow:srow + 1]), hk, hv, hks, hvs, orc.KV_I8, NH, NKV, HD, HD, Sp, S=1,
-                                          query_base_pos=srow, softmax_scale=float(SOFTMAX_SCALE))
-                    worst = max(worst, rel_err(got[srow], want[0]))
-                res[name]["parity_rel_err_sampled_rows"] = float(f"{worst:.3e}")
-        res["tensor_peak_fraction"] = round(res["tcgen05_query_major"]["TFLOPs_causal"] / measured_peak_tflops(), 4)
-        out["prefill_s2048_i8"] = res
-        del cache
-    except Exception as e:
-        out["prefill_s2048_i8"] = {"error": repr(e)}
-    # configuration 3: sliding-window layer, ring of 1024 at position 8191, int4 block-32, fused append
-    try:
-        W, pos = 1024, 8191
-        nb = HD // 32
-        rows = NKV * W
-        k = torch.zeros((NKV, W, HD // 2), dtype=torch.uint8, device=dev); v = torch.zeros_like(k)
-        ks = torch.zeros(rows * nb * 2 + rows * 4, dtype=torch.uint8, device=dev); vs = torch.zeros_like(ks)
-        g = torch.Generator(device=dev); g.manual_seed(1003)
-        for base in range(0, pos, 1024):
-            n = min(1024, pos - base)
-            kk = torch.randn((n, NKV, HD), generator=g, device=dev).to(torch.bfloat16).float().contiguous()
-            vv = torch.randn((n, NKV, HD), generator=g, device=dev).to(torch.bfloat16).float().contiguous()
-            ops.gpu_append_quant_kv_i4(None, kk, vv, k, v, ks, vs, n, NKV, HD, NKV * HD, W, HD, base, nb)
-        q = torch.randn((1, 1, NH, HD), device=dev).to(torch.bfloat16)
-        o = torch.zeros((1, 1, NH, HD), dtype=torch.bfloat16, device=dev)
-        nk = torch.randn((1, NKV, HD), device=dev); nv = torch.randn((1, NKV, HD), device=dev)
-        a = ops.make_args(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=o, kv_fmt=ops.KV_I4B32, q_type=ops.BF16,
-                          out_type=ops.BF16, nh=NH, nkv=NKV, kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=W,
-                          win_start=pos + 1 - W, klen=W, softmax_scale=SOFTMAX_SCALE, new_k=nk, new_v=nv, n_new=1,
-                          new_base_pos=pos)
-        wsb = ops.attn_workspace_bytes(a)
-        ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
-        a.workspace, a.ws_bytes = ws.data_ptr(), wsb
-        us = time_call(torch, lambda: ops.attn_fused(stream, a), iters)
-        out["c3_swa_ring_i4b32_fused_append"] = {"us_per_layer": round(us, 2), "bytes": 2394368,
-                                                 "note": "2.4 MB per call: launch-latency-bound, L2-resident"}
-    except Exception as e:
-        out["c3_swa_ring_i4b32_fused_append"] = {"error": str(e)}
+            us = time_call(torch, lambda: ops.attn_fused(stream, a), iters)
+            out["c3_swa_ring_i4b32_fused_append"] = {"us_per_layer": round(us, 2), "bytes": 2394368,
+                                                     "note": "2.4 MB per call: launch-latency-bound, L2-resident"}
+        except Exception as e:
+            out["c3_swa_ring_i4b32_fused_append"] = {"error": str(e)}
     # the reference model's real layer geometry (Gemma-4-31B, lib/gemma4_engine.mojo:371-392), int4 block-32 KV:
     # sliding layers 32q/16kv x 256 with a 1024-slot ring, full layers 32q/4kv x 512 at 32768 keys
     for name, nkv_g, hd_g, t_g, cap_g in (("g4_sliding_hd256_i4b32_w1024", 16, 256, 1024, 1024),
                                           ("g4_full_hd512_i4b32_32k", 4, 512, 32768, 32768)):
+        if not want(name):
+            continue
         try:
             nb = hd_g // 32
             rows = nkv_g * cap_g
@@ -595,6 +604,8 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
             ("producer_c2_hd128_i8", NH, NKV, HD, ops.KV_I8, 32768, 10000.0, HD),
             ("producer_g4_sliding_hd256_i4b32", NH, 16, 256, ops.KV_I4B32, 1024, 10000.0, 256),
             ("producer_g4_full_hd512_i4b32", NH, 4, 512, ops.KV_I4B32, 32768, 1000000.0, 128)):
+        if not want(name):
+            continue
         try:
             row_b = hd_p if fmt_p == ops.KV_I8 else hd_p // 2
             nb = hd_p // 32
@@ -619,185 +630,189 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200) -> dict:
             out[name] = {"error": str(e)}
     # one decode step of a layer's attention path at configuration 2: producer epilogue (norms, RoPE, quantize-on-write
     # of the new token) then attention over the 32768 keys -- two launches chained by programmatic dependent launch
-    try:
-        caches = [make_layer_cache(torch, ops, dev, 1, NKV, T, HD, 1302 + i) for i in range(NLAYERS)]
-        qf = torch.randn((1, NH, HD), device=dev); kf = torch.randn((1, NKV, HD), device=dev); vf = torch.randn((1, NKV, HD), device=dev)
-        qw = torch.ones(HD, device=dev); kw = torch.ones(HD, device=dev)
-        o = torch.zeros((1, 1, NH, HD), dtype=torch.bfloat16, device=dev)
-        al = []
-        for k, v, ks, vs in caches:
-            al.append((ops.make_args(q=qf, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=o, kv_fmt=ops.KV_I8, q_type=ops.F32,
-                                     out_type=ops.BF16, nh=NH, nkv=NKV, kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=T, klen=T,
-                                     softmax_scale=SOFTMAX_SCALE, flags=ops.SETTLED_CACHE), (k, v, ks, vs)))
-        wsb = ops.attn_workspace_bytes(al[0][0])
-        ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
-        for a_, _ in al:
-            a_.workspace, a_.ws_bytes = ws.data_ptr(), wsb
-        ctr2 = [0]
+    if want("decode_step_c2_producer_plus_attention"):
+        try:
+            caches = [make_layer_cache(torch, ops, dev, 1, NKV, T, HD, 1302 + i) for i in range(NLAYERS)]
+            qf = torch.randn((1, NH, HD), device=dev); kf = torch.randn((1, NKV, HD), device=dev); vf = torch.randn((1, NKV, HD), device=dev)
+            qw = torch.ones(HD, device=dev); kw = torch.ones(HD, device=dev)
+            o = torch.zeros((1, 1, NH, HD), dtype=torch.bfloat16, device=dev)
+            al = []
+            for k, v, ks, vs in caches:
+                al.append((ops.make_args(q=qf, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=o, kv_fmt=ops.KV_I8, q_type=ops.F32,
+                                         out_type=ops.BF16, nh=NH, nkv=NKV, kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=T, klen=T,
+                                         softmax_scale=SOFTMAX_SCALE, flags=ops.SETTLED_CACHE), (k, v, ks, vs)))
+            wsb = ops.attn_workspace_bytes(al[0][0])
+            ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+            for a_, _ in al:
+                a_.workspace, a_.ws_bytes = ws.data_ptr(), wsb
+            ctr2 = [0]
 
-        def fstep():
-            a_, (k, v, ks, vs) = al[ctr2[0] % NLAYERS]; ctr2[0] += 1
-            ops.kv_norm_rope_append(stream, qf, qw, kf, vf, kw, k, v, ks, vs, n_s=1, nh=NH, nkv=NKV, l_hd=HD, l_kvd=NKV * HD,
-                                    cache_cap=T, cache_hd=HD, base_pos=T - 1, theta=10000.0, rope_dim=HD, kv_fmt=ops.KV_I8)
-            ops.attn_fused(stream, a_)
+            def fstep():
+                a_, (k, v, ks, vs) = al[ctr2[0] % NLAYERS]; ctr2[0] += 1
+                ops.kv_norm_rope_append(stream, qf, qw, kf, vf, kw, k, v, ks, vs, n_s=1, nh=NH, nkv=NKV, l_hd=HD, l_kvd=NKV * HD,
+                                        cache_cap=T, cache_hd=HD, base_pos=T - 1, theta=10000.0, rope_dim=HD, kv_fmt=ops.KV_I8)
+                ops.attn_fused(stream, a_)
 
-        us = time_call(torch, fstep, iters)
-        out["decode_step_c2_producer_plus_attention"] = {"us_per_layer": round(us, 2), "launches": 2,
-                                                         "reference_launches": "6 + append + 2 dequant + 5 attention"}
-        del caches, ws
-    except Exception as e:
-        out["decode_step_c2_producer_plus_attention"] = {"error": str(e)}
+            us = time_call(torch, fstep, iters)
+            out["decode_step_c2_producer_plus_attention"] = {"us_per_layer": round(us, 2), "launches": 2,
+                                                             "reference_launches": "6 + append + 2 dequant + 5 attention"}
+            del caches, ws
+        except Exception as e:
+            out["decode_step_c2_producer_plus_attention"] = {"error": str(e)}
     # configuration 5a: batch 8 x 131072 keys, sharded by KV-head groups (16 / world heads per GPU, no collective)
-    try:
-        B5, T5a = 8, 131072
-        nkv5 = NKV // world
-        nh5 = nkv5 * (NH // NKV)
-        cache = make_layer_cache(torch, ops, dev, B5, nkv5, T5a, HD, 1105 + rank)
-        q = torch.randn((B5, 1, nh5, HD), device=dev).to(torch.bfloat16)
-        o = torch.zeros((B5, 1, nh5, HD), dtype=torch.bfloat16, device=dev)
-        a5 = decode_args(ops, q, cache, o, nh5, nkv5, HD, T5a, B5)
-        wsb = ops.attn_workspace_bytes(a5)
-        ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
-        a5.workspace, a5.ws_bytes = ws.data_ptr(), wsb
-        us = time_call(torch, lambda: ops.attn_fused(stream, a5), max(10, iters // 8))
-        if world > 1:
-            tt = torch.tensor([us], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX); us = float(tt.item())
-        by = algorithmic_bytes(NKV, NH // NKV, T5a, HD, B5)
-        out["c5a_batch8_131k_head_sharded"] = {"us_per_layer": round(us, 2), "GBps_aggregate": round(by / us / 1e3, 1), "gpus": world}
-        del cache, ws
-    except Exception as e:
-        out["c5a_batch8_131k_head_sharded"] = {"error": str(e)}
+    if want("c5a_batch8_131k_head_sharded"):
+        try:
+            B5, T5a = 8, 131072
+            nkv5 = NKV // world
+            nh5 = nkv5 * (NH // NKV)
+            cache = make_layer_cache(torch, ops, dev, B5, nkv5, T5a, HD, 1105 + rank)
+            q = torch.randn((B5, 1, nh5, HD), device=dev).to(torch.bfloat16)
+            o = torch.zeros((B5, 1, nh5, HD), dtype=torch.bfloat16, device=dev)
+            a5 = decode_args(ops, q, cache, o, nh5, nkv5, HD, T5a, B5)
+            wsb = ops.attn_workspace_bytes(a5)
+            ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+            a5.workspace, a5.ws_bytes = ws.data_ptr(), wsb
+            us = time_call(torch, lambda: ops.attn_fused(stream, a5), max(10, iters // 8))
+            if world > 1:
+                tt = torch.tensor([us], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX); us = float(tt.item())
+            by = algorithmic_bytes(NKV, NH // NKV, T5a, HD, B5)
+            out["c5a_batch8_131k_head_sharded"] = {"us_per_layer": round(us, 2), "GBps_aggregate": round(by / us / 1e3, 1), "gpus": world}
+            del cache, ws
+        except Exception as e:
+            out["c5a_batch8_131k_head_sharded"] = {"error": str(e)}
     # configuration 5a on PAGED caches: same bytes, pages of 128 keys behind a shuffled block table (serving layout)
-    try:
-        B5, T5a = 8, 131072
-        nkv5 = NKV // world
-        nh5 = nkv5 * (NH // NKV)
-        ppseq = T5a // 128
-        n_pages = B5 * ppseq
-        g = torch.Generator(device=dev); g.manual_seed(1205 + rank)
-        kp = torch.randint(-127, 128, (n_pages, nkv5, 128, HD), dtype=torch.int8, device=dev, generator=g)
-        vp = torch.randint(-127, 128, (n_pages, nkv5, 128, HD), dtype=torch.int8, device=dev, generator=g)
-        ksp = torch.rand((n_pages, nkv5, 128), device=dev, generator=g) * 0.02 + 0.01
-        vsp = torch.rand((n_pages, nkv5, 128), device=dev, generator=g) * 0.02 + 0.01
-        table = torch.randperm(n_pages, device=dev, generator=g).to(torch.int32).reshape(B5, ppseq).contiguous()
-        lens = torch.full((B5,), T5a, dtype=torch.int32, device=dev)
-        q = torch.randn((B5, nh5, HD), device=dev).to(torch.bfloat16)
-        o = torch.zeros((B5, nh5, HD), dtype=torch.bfloat16, device=dev)
-        wsb = ops.attn_paged_workspace_bytes(B5, nh5, nkv5, NH // NKV, HD, T5a)
-        ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+    if want("c5a_paged_batch8_131k"):
+        try:
+            B5, T5a = 8, 131072
+            nkv5 = NKV // world
+            nh5 = nkv5 * (NH // NKV)
+            ppseq = T5a // 128
+            n_pages = B5 * ppseq
+            g = torch.Generator(device=dev); g.manual_seed(1205 + rank)
+            kp = torch.randint(-127, 128, (n_pages, nkv5, 128, HD), dtype=torch.int8, device=dev, generator=g)
+            vp = torch.randint(-127, 128, (n_pages, nkv5, 128, HD), dtype=torch.int8, device=dev, generator=g)
+            ksp = torch.rand((n_pages, nkv5, 128), device=dev, generator=g) * 0.02 + 0.01
+            vsp = torch.rand((n_pages, nkv5, 128), device=dev, generator=g) * 0.02 + 0.01
+            table = torch.randperm(n_pages, device=dev, generator=g).to(torch.int32).reshape(B5, ppseq).contiguous()
+            lens = torch.full((B5,), T5a, dtype=torch.int32, device=dev)
+            q = torch.randn((B5, nh5, HD), device=dev).to(torch.bfloat16)
+            o = torch.zeros((B5, nh5, HD), dtype=torch.bfloat16, device=dev)
+            wsb = ops.attn_paged_workspace_bytes(B5, nh5, nkv5, NH // NKV, HD, T5a)
+            ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
 
-        def fnpg():
-            ops.attn_paged_decode_i8(stream, q, kp, vp, ksp, vsp, table, lens, o, ws, wsb, batch=B5, nh=nh5, nkv=nkv5, kvg=NH // NKV,
-                                     l_hd=HD, n_pages=n_pages, max_pages=ppseq, max_len=T5a, softmax_scale=SOFTMAX_SCALE,
-                                     q_type=ops.BF16, out_type=ops.BF16)
+            def fnpg():
+                ops.attn_paged_decode_i8(stream, q, kp, vp, ksp, vsp, table, lens, o, ws, wsb, batch=B5, nh=nh5, nkv=nkv5, kvg=NH // NKV,
+                                         l_hd=HD, n_pages=n_pages, max_pages=ppseq, max_len=T5a, softmax_scale=SOFTMAX_SCALE,
+                                         q_type=ops.BF16, out_type=ops.BF16)
 
-        us = time_call(torch, fnpg, max(10, iters // 8))
-        if world > 1:
-            tt = torch.tensor([us], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX); us = float(tt.item())
-        by = algorithmic_bytes(NKV, NH // NKV, T5a, HD, B5)
-        out["c5a_paged_batch8_131k"] = {"us_per_layer": round(us, 2), "GBps_aggregate": round(by / us / 1e3, 1), "gpus": world,
-                                        "page_keys": 128}
-        del kp, vp, ksp, vsp, ws
-    except Exception as e:
-        out["c5a_paged_batch8_131k"] = {"error": str(e)}
+            us = time_call(torch, fnpg, max(10, iters // 8))
+            if world > 1:
+                tt = torch.tensor([us], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX); us = float(tt.item())
+            by = algorithmic_bytes(NKV, NH // NKV, T5a, HD, B5)
+            out["c5a_paged_batch8_131k"] = {"us_per_layer": round(us, 2), "GBps_aggregate": round(by / us / 1e3, 1), "gpus": world,
+                                            "page_keys": 128}
+            del kp, vp, ksp, vsp, ws
+        except Exception as e:
+            out["c5a_paged_batch8_131k"] = {"error": str(e)}
     # configuration 5b: batch 1 x 524288 keys, sharded by sequence chunks.  Two realisations of the exchange:
     #   "nccl": attention exports (o, m, l), NCCL all-gather of 16.6 KB per rank (torch.distributed), merge kernel;
     #   "peer": nomos_attn_seq_sharded -- one launch per rank: the attention kernel stores its rows into the peers'
     #           mailboxes over NVLink, waits for theirs and merges.
     # Both are checked against the oracle: every rank computes the exact fp64 partial of its own chunk on the host,
     # the partials are gathered on the host and merged by the oracle.
-    try:
-        from nomos_nvfp4_b200.sharding import SeqShardGroup
-        T5 = 524288 // world
-        cache = make_layer_cache(torch, ops, dev, 1, NKV, T5, HD, 1005 + rank)
-        qh = np.random.default_rng(5005).standard_normal((1, 1, NH, HD), dtype=np.float32)
-        q = torch.from_numpy(qh).to(dev).to(torch.bfloat16)
-        o = torch.zeros((NH, HD), dtype=torch.bfloat16, device=dev)
-        part = torch.zeros((NH, HD + 2), dtype=torch.float32, device=dev)
-        gathered = torch.zeros((world, NH, HD + 2), dtype=torch.float32, device=dev)
-        k, v, ks, vs = cache
-        common = dict(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, kv_fmt=ops.KV_I8, q_type=ops.BF16, nh=NH, nkv=NKV,
-                      kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=T5, klen=T5, softmax_scale=SOFTMAX_SCALE, flags=ops.SETTLED_CACHE)
-        a = ops.make_args(partial_out=part, **common)
-        wsb = ops.attn_workspace_bytes(a)
-        ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
-        a.workspace, a.ws_bytes = ws.data_ptr(), wsb
+    if want("c5b_seq_sharded_512k"):
+        try:
+            from nomos_nvfp4_b200.sharding import SeqShardGroup
+            T5 = 524288 // world
+            cache = make_layer_cache(torch, ops, dev, 1, NKV, T5, HD, 1005 + rank)
+            qh = np.random.default_rng(5005).standard_normal((1, 1, NH, HD), dtype=np.float32)
+            q = torch.from_numpy(qh).to(dev).to(torch.bfloat16)
+            o = torch.zeros((NH, HD), dtype=torch.bfloat16, device=dev)
+            part = torch.zeros((NH, HD + 2), dtype=torch.float32, device=dev)
+            gathered = torch.zeros((world, NH, HD + 2), dtype=torch.float32, device=dev)
+            k, v, ks, vs = cache
+            common = dict(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, kv_fmt=ops.KV_I8, q_type=ops.BF16, nh=NH, nkv=NKV,
+                          kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=T5, klen=T5, softmax_scale=SOFTMAX_SCALE, flags=ops.SETTLED_CACHE)
+            a = ops.make_args(partial_out=part, **common)
+            wsb = ops.attn_workspace_bytes(a)
+            ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+            a.workspace, a.ws_bytes = ws.data_ptr(), wsb
 
-        def gather():
+            def gather():
+                if world > 1:
+                    dist.all_gather_into_tensor(gathered, part)
+                else:
+                    gathered.copy_(part.unsqueeze(0))
+
+            def fn():
+                ops.attn_fused(stream, a)
+                gather()
+                ops.attn_merge_partials(stream, gathered, world, NH, HD, o, ops.BF16)
+
+            n5 = max(10, iters // 4)
+            us = time_call(torch, fn, n5)
+            # the three phases bracketed by events (this serialises them; the sum can exceed the pipelined step time)
+            ph = np.zeros(3)
+            for _ in range(n5):
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+                ev[0].record(); ops.attn_fused(stream, a); ev[1].record(); gather(); ev[2].record()
+                ops.attn_merge_partials(stream, gathered, world, NH, HD, o, ops.BF16); ev[3].record()
+                torch.cuda.synchronize()
+                ph += np.array([ev[i].elapsed_time(ev[i + 1]) for i in range(3)]) * 1000.0 / n5
+            # peer-memory variant
+            o2 = torch.zeros((NH, HD), dtype=torch.bfloat16, device=dev)
+            a2 = ops.make_args(out=o2, out_type=ops.BF16, **common)
+            a2.workspace, a2.ws_bytes = ws.data_ptr(), wsb
+
+            def agb(b):
+                if world == 1:
+                    return [b]
+                lst = [None] * world
+                dist.all_gather_object(lst, b)
+                return lst
+
+            group = SeqShardGroup(rank, world, NH, HD, agb, timeout_us=200000)
             if world > 1:
-                dist.all_gather_into_tensor(gathered, part)
-            else:
-                gathered.copy_(part.unsqueeze(0))
-
-        def fn():
-            ops.attn_fused(stream, a)
-            gather()
-            ops.attn_merge_partials(stream, gathered, world, NH, HD, o, ops.BF16)
-
-        n5 = max(10, iters // 4)
-        us = time_call(torch, fn, n5)
-        # the three phases bracketed by events (this serialises them; the sum can exceed the pipelined step time)
-        ph = np.zeros(3)
-        for _ in range(n5):
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-            ev[0].record(); ops.attn_fused(stream, a); ev[1].record(); gather(); ev[2].record()
-            ops.attn_merge_partials(stream, gathered, world, NH, HD, o, ops.BF16); ev[3].record()
-            torch.cuda.synchronize()
-            ph += np.array([ev[i].elapsed_time(ev[i + 1]) for i in range(3)]) * 1000.0 / n5
-        # peer-memory variant
-        o2 = torch.zeros((NH, HD), dtype=torch.bfloat16, device=dev)
-        a2 = ops.make_args(out=o2, out_type=ops.BF16, **common)
-        a2.workspace, a2.ws_bytes = ws.data_ptr(), wsb
-
-        def agb(b):
-            if world == 1:
-                return [b]
-            lst = [None] * world
-            dist.all_gather_object(lst, b)
-            return lst
-
-        group = SeqShardGroup(rank, world, NH, HD, agb, timeout_us=200000)
-        if world > 1:
-            dist.barrier()
-        group.decode(stream, a2)                        # one step first: a group that cannot exchange is not timed
-        peer_rc = group.status(stream)
-        if world > 1:
-            tt = torch.tensor([float(peer_rc)], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MIN); peer_rc = int(tt.item())
-        us_peer = time_call(torch, lambda: group.decode(stream, a2), n5) if peer_rc == 0 else float("inf")
-        peer_rc = peer_rc or group.status(stream)
-        if world > 1:
-            tt = torch.tensor([us, us_peer, *ph], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            us, us_peer, ph = float(tt[0]), float(tt[1]), tt[2:].cpu().numpy()
-        # parity of both variants (fp32 outputs of one more step each) against the oracle
-        o32 = torch.zeros((NH, HD), dtype=torch.float32, device=dev); o32p = torch.zeros_like(o32)
-        ops.attn_fused(stream, a); gather(); ops.attn_merge_partials(stream, gathered, world, NH, HD, o32, ops.F32)
-        a2.out, a2.out_type = o32p.data_ptr(), ops.F32
-        if peer_rc == 0:
-            group.decode(stream, a2)
+                dist.barrier()
+            group.decode(stream, a2)                        # one step first: a group that cannot exchange is not timed
             peer_rc = group.status(stream)
-        from oracle import oracle as orc
-        orc.set_threads(max(1, (os.cpu_count() or 1) // world))
-        _, pe = orc.attn_exact(orc.bf16_round(qh[0]), k[0].cpu().numpy(), v[0].cpu().numpy(), ks[0].cpu().numpy(), vs[0].cpu().numpy(),
-                               orc.KV_I8, NH, NKV, HD, HD, T5, query_base_pos=T5 - 1, softmax_scale=float(SOFTMAX_SCALE), want_partial=True)
-        parts = [pe]
-        if world > 1:
-            parts = [None] * world
-            dist.all_gather_object(parts, pe)
-        want = orc.merge_partials(np.stack(parts), HD)
-        by = algorithmic_bytes(NKV, NH // NKV, 524288, HD)
-        out["c5b_seq_sharded_512k"] = {
-            "us_per_layer": round(min(us, us_peer), 2), "GBps_aggregate": round(by / min(us, us_peer) / 1e3, 1), "gpus": world,
-            "exchange": "peer stores, one launch per rank" if us_peer <= us else "NCCL all-gather + merge launch",
-            "nccl_allgather_plus_merge": {"us_per_layer": round(us, 2), "phases_us": {"attention": round(float(ph[0]), 2),
-                                          "all_gather": round(float(ph[1]), 2), "merge": round(float(ph[2]), 2)},
-                                          "parity_rel_err": float(f"{rel_err(o32.cpu().numpy(), want):.3e}")},
-            "peer_stores_one_launch": {"us_per_layer": round(us_peer, 2) if us_peer != float("inf") else None, "status": int(peer_rc),
-                                       "parity_rel_err": float(f"{rel_err(o32p.cpu().numpy(), want):.3e}")},
-            "parity_bar": 2e-3}
-        group.close()
-        del cache, ws
-    except Exception as e:
-        out["c5b_seq_sharded_512k"] = {"error": repr(e)}
+            if world > 1:
+                tt = torch.tensor([float(peer_rc)], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MIN); peer_rc = int(tt.item())
+            us_peer = time_call(torch, lambda: group.decode(stream, a2), n5) if peer_rc == 0 else float("inf")
+            peer_rc = peer_rc or group.status(stream)
+            if world > 1:
+                tt = torch.tensor([us, us_peer, *ph], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                us, us_peer, ph = float(tt[0]), float(tt[1]), tt[2:].cpu().numpy()
+            # parity of both variants (fp32 outputs of one more step each) against the oracle
+            o32 = torch.zeros((NH, HD), dtype=torch.float32, device=dev); o32p = torch.zeros_like(o32)
+            ops.attn_fused(stream, a); gather(); ops.attn_merge_partials(stream, gathered, world, NH, HD, o32, ops.F32)
+            a2.out, a2.out_type = o32p.data_ptr(), ops.F32
+            if peer_rc == 0:
+                group.decode(stream, a2)
+                peer_rc = group.status(stream)
+            from oracle import oracle as orc
+            orc.set_threads(max(1, (os.cpu_count() or 1) // world))
+            _, pe = orc.attn_exact(orc.bf16_round(qh[0]), k[0].cpu().numpy(), v[0].cpu().numpy(), ks[0].cpu().numpy(), vs[0].cpu().numpy(),
+                                   orc.KV_I8, NH, NKV, HD, HD, T5, query_base_pos=T5 - 1, softmax_scale=float(SOFTMAX_SCALE), want_partial=True)
+            parts = [pe]
+            if world > 1:
+                parts = [None] * world
+                dist.all_gather_object(parts, pe)
+            want = orc.merge_partials(np.stack(parts), HD)
+            by = algorithmic_bytes(NKV, NH // NKV, 524288, HD)
+            out["c5b_seq_sharded_512k"] = {
+                "us_per_layer": round(min(us, us_peer), 2), "GBps_aggregate": round(by / min(us, us_peer) / 1e3, 1), "gpus": world,
+                "exchange": "peer stores, one launch per rank" if us_peer <= us else "NCCL all-gather + merge launch",
+                "nccl_allgather_plus_merge": {"us_per_layer": round(us, 2), "phases_us": {"attention": round(float(ph[0]), 2),
+                                              "all_gather": round(float(ph[1]), 2), "merge": round(float(ph[2]), 2)},
+                                              "parity_rel_err": float(f"{rel_err(o32.cpu().numpy(), want):.3e}")},
+                "peer_stores_one_launch": {"us_per_layer": round(us_peer, 2) if us_peer != float("inf") else None, "status": int(peer_rc),
+                                           "parity_rel_err": float(f"{rel_err(o32p.cpu().numpy(), want):.3e}")},
+                "parity_bar": 2e-3}
+            group.close()
+            del cache, ws
+        except Exception as e:
+            out["c5b_seq_sharded_512k"] = {"error": repr(e)}
     return out
 
 
@@ -901,6 +916,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--quick", action="store_true", help="warm-up + timed steps only (for profiler captures)")
     ap.add_argument("--extras-only", action="store_true", help="run only the secondary configurations, --steps iterations each")
+    ap.add_argument("--only", default=None, help="with --extras-only: comma-separated names of the cases to run")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle comparison of the timed outputs")
     args = ap.parse_args()
@@ -909,7 +925,8 @@ def main():
         import torch.distributed as dist
         from nomos_nvfp4_b200 import ops
         torch.cuda.set_device(0)
-        print(json.dumps({"extras": extras(torch, dist, ops, "cuda:0", 0, 1, iters=args.steps)}), flush=True)
+        print(json.dumps({"extras": extras(torch, dist, ops, "cuda:0", 0, 1, iters=args.steps,
+                                            only=set(args.only.split(",")) if args.only else None)}), flush=True)
         return
     res = run_reference(args) if args.impl == "reference" else run_ours(args)
     if res:
