@@ -771,15 +771,24 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
                 dist.all_gather_object(lst, b)
                 return lst
 
-            group = SeqShardGroup(rank, world, NH, HD, agb, timeout_us=200000)
-            if world > 1:
-                dist.barrier()
-            group.decode(stream, a2)                        # one step first: a group that cannot exchange is not timed
-            peer_rc = group.status(stream)
-            if world > 1:
-                tt = torch.tensor([float(peer_rc)], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MIN); peer_rc = int(tt.item())
+            def worst(rc):
+                """Largest status over the ranks: every rank takes the same branch after a failure on one of them."""
+                if world > 1:
+                    tt = torch.tensor([float(rc)], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX); rc = int(tt.item())
+                return rc
+
+            group, peer_rc, peer_err = None, 0, None
+            try:
+                group = SeqShardGroup(rank, world, NH, HD, agb, timeout_us=200000)
+            except Exception as e:                          # e.g. no peer access between two of the GPUs
+                peer_rc, peer_err = 1, repr(e)
+            peer_rc = worst(peer_rc)
+            if peer_rc == 0:
+                group.decode(stream, a2)                    # one step first: a group that cannot exchange is not timed
+                peer_rc = worst(group.status(stream))
             us_peer = time_call(torch, lambda: group.decode(stream, a2), n5) if peer_rc == 0 else float("inf")
-            peer_rc = peer_rc or group.status(stream)
+            if peer_rc == 0:
+                peer_rc = worst(group.status(stream))
             if world > 1:
                 tt = torch.tensor([us, us_peer, *ph], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX)
                 us, us_peer, ph = float(tt[0]), float(tt[1]), tt[2:].cpu().numpy()
@@ -789,7 +798,7 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
             a2.out, a2.out_type = o32p.data_ptr(), ops.F32
             if peer_rc == 0:
                 group.decode(stream, a2)
-                peer_rc = group.status(stream)
+                peer_rc = worst(group.status(stream))
             from oracle import oracle as orc
             orc.set_threads(max(1, (os.cpu_count() or 1) // world))
             _, pe = orc.attn_exact(orc.bf16_round(qh[0]), k[0].cpu().numpy(), v[0].cpu().numpy(), ks[0].cpu().numpy(), vs[0].cpu().numpy(),
@@ -807,9 +816,11 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
                                               "all_gather": round(float(ph[1]), 2), "merge": round(float(ph[2]), 2)},
                                               "parity_rel_err": float(f"{rel_err(o32.cpu().numpy(), want):.3e}")},
                 "peer_stores_one_launch": {"us_per_layer": round(us_peer, 2) if us_peer != float("inf") else None, "status": int(peer_rc),
+                                           **({"error": peer_err} if peer_err else {}),
                                            "parity_rel_err": float(f"{rel_err(o32p.cpu().numpy(), want):.3e}")},
                 "parity_bar": 2e-3}
-            group.close()
+            if group is not None:
+                group.close()
             del cache, ws
         except Exception as e:
             out["c5b_seq_sharded_512k"] = {"error": repr(e)}

@@ -66,11 +66,27 @@ class SeqShardGroup:
         self._ops, self.rank, self.world, self.timeout_us = ops, rank, world, timeout_us
         self.step = 0
         self.mailbox_bytes = ops.attn_peer_mailbox_bytes(world, rows, l_hd)
-        self.own, handle = ops.attn_peer_mailbox_create(self.mailbox_bytes)
+        self.own, self.mailboxes = 0, []
+        try:
+            self.own, handle = ops.attn_peer_mailbox_create(self.mailbox_bytes)
+            failure = None
+        except Exception as e:                      # still take part in the exchange below: the peers are waiting in it
+            handle, failure = b"", e
         handles = all_gather_bytes(handle)
-        if len(handles) != world:
-            raise ValueError(f"expected {world} mailbox handles, got {len(handles)}")
-        self.mailboxes = [self.own if g == rank else ops.attn_peer_mailbox_open(handles[g]) for g in range(world)]
+        if failure is not None:
+            raise failure
+        if len(handles) != world or not all(handles):
+            self.close()
+            raise ValueError(f"expected {world} mailbox handles, got {sum(1 for h in handles if h)}")
+        self.mailboxes = [0] * world
+        self.mailboxes[rank] = self.own
+        try:
+            for g in range(world):
+                if g != rank:
+                    self.mailboxes[g] = ops.attn_peer_mailbox_open(handles[g])
+        except Exception:
+            self.close()
+            raise
 
     def decode(self, stream, args) -> None:
         """Attention over this rank's chunk + exchange + merge; the final output lands in ``args.out`` on every rank."""
@@ -83,6 +99,8 @@ class SeqShardGroup:
 
     def close(self) -> None:
         for g, m in enumerate(self.mailboxes):
-            if m:
-                self._ops.attn_peer_mailbox_close(m, g == self.rank)
-        self.mailboxes = []
+            if m and g != self.rank:
+                self._ops.attn_peer_mailbox_close(m, False)
+        if self.own:
+            self._ops.attn_peer_mailbox_close(self.own, True)
+        self.own, self.mailboxes = 0, []

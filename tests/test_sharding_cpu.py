@@ -96,3 +96,78 @@ def test_two_rank_shards_reproduce_full_attention(mode, oracle):
         assert p.exitcode == 0
     for rank, err in results:
         assert err < 1e-5, f"rank {rank}: {err}"
+
+
+class _FakeMailboxOps:
+    """Stand-in for the mailbox calls of the library: records what a SeqShardGroup does with them."""
+
+    def __init__(self, fail_create=False, fail_open_of=None):
+        self.fail_create, self.fail_open_of = fail_create, fail_open_of
+        self.closed, self.opened = [], []
+
+    def attn_peer_mailbox_bytes(self, world, rows, l_hd):
+        return world * (rows * (l_hd + 2) * 4 + 256)
+
+    def attn_peer_mailbox_create(self, nbytes):
+        if self.fail_create:
+            raise RuntimeError("no memory for the mailbox")
+        return 0x1000, b"handle-of-this-rank"
+
+    def attn_peer_mailbox_open(self, handle):
+        if handle == self.fail_open_of:
+            raise RuntimeError("no peer access")
+        self.opened.append(handle)
+        return 0x2000 + len(self.opened)
+
+    def attn_peer_mailbox_close(self, ptr, own):
+        self.closed.append((ptr, own))
+
+
+def _group_with(monkeypatch, fake, rank, world, gathered):
+    import nomos_nvfp4_b200.ops as ops
+    from nomos_nvfp4_b200.sharding import SeqShardGroup
+    for name in ("attn_peer_mailbox_bytes", "attn_peer_mailbox_create", "attn_peer_mailbox_open", "attn_peer_mailbox_close"):
+        monkeypatch.setattr(ops, name, getattr(fake, name))
+    calls = []
+
+    def all_gather_bytes(b):
+        calls.append(b)
+        return [b if g == rank else h for g, h in enumerate(gathered)]
+
+    return SeqShardGroup, all_gather_bytes, calls
+
+
+def test_seq_shard_group_opens_every_peer_and_closes_them(monkeypatch):
+    fake = _FakeMailboxOps()
+    cls, agb, calls = _group_with(monkeypatch, fake, 1, 3, [b"h0", None, b"h2"])
+    g = cls(1, 3, 32, 128, agb)
+    assert calls == [b"handle-of-this-rank"]
+    assert g.mailboxes[1] == 0x1000 and fake.opened == [b"h0", b"h2"]
+    g.close()
+    assert sorted(fake.closed) == sorted([(0x2001, False), (0x2002, False), (0x1000, True)])
+    g.close()                                               # idempotent
+    assert len(fake.closed) == 3
+
+
+def test_seq_shard_group_takes_part_in_the_handle_exchange_when_its_own_mailbox_fails(monkeypatch):
+    """A rank whose mailbox cannot be created must still enter the host exchange (its peers are blocked in it)
+    and every rank must then see the missing handle and give up, instead of one of them waiting for ever."""
+    fake = _FakeMailboxOps(fail_create=True)
+    cls, agb, calls = _group_with(monkeypatch, fake, 0, 2, [None, b"h1"])
+    with pytest.raises(RuntimeError, match="no memory"):
+        cls(0, 2, 32, 128, agb)
+    assert calls == [b""]
+    # the peer of that rank: it receives an empty handle
+    fake2 = _FakeMailboxOps()
+    cls, agb, calls = _group_with(monkeypatch, fake2, 1, 2, [b"", None])
+    with pytest.raises(ValueError, match="mailbox handles"):
+        cls(1, 2, 32, 128, agb)
+    assert fake2.closed == [(0x1000, True)]
+
+
+def test_seq_shard_group_releases_what_it_opened_when_a_peer_cannot_be_mapped(monkeypatch):
+    fake = _FakeMailboxOps(fail_open_of=b"h2")
+    cls, agb, _ = _group_with(monkeypatch, fake, 0, 3, [None, b"h1", b"h2"])
+    with pytest.raises(RuntimeError, match="no peer access"):
+        cls(0, 3, 32, 128, agb)
+    assert sorted(fake.closed) == sorted([(0x2001, False), (0x1000, True)])
