@@ -447,12 +447,12 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
     `only`: names of the cases to run (profiler captures run one case by itself)."""
     out = {}
 
-    def want(*names):
+    def selected(*names):
         return only is None or any(n in only for n in names)
     stream = torch.cuda.current_stream().cuda_stream
     # configuration 4: verify, VB = 9 rows against 16384 cached keys (+9 new), int8 KV.
     # Four layer caches are cycled (278 MB > L2), as a 60-layer verify pass would.
-    if want("c4_verify_vb9_16k"):
+    if selected("c4_verify_vb9_16k"):
         try:
             S, T4 = 9, 16384 + 9
             caches = [make_layer_cache(torch, ops, dev, 1, NKV, T4, HD, 1004 + i) for i in range(NLAYERS)]
@@ -491,7 +491,7 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
             out["c4_verify_vb9_16k"] = {"error": str(e)}
     # prefill: 2048 prompt tokens, 32q/16kv x 128, int8 KV already appended; causal attention over the quantised
     # cache on the query-major tcgen05 kernel (no S x S score matrix), and the same call as mma.sync row groups
-    if want("prefill_s2048_i8"):
+    if selected("prefill_s2048_i8"):
         try:
             Sp = 2048
             cache = make_layer_cache(torch, ops, dev, 1, NKV, Sp, HD, 1404)
@@ -530,7 +530,7 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
         except Exception as e:
             out["prefill_s2048_i8"] = {"error": repr(e)}
     # configuration 3: sliding-window layer, ring of 1024 at position 8191, int4 block-32, fused append
-    if want("c3_swa_ring_i4b32_fused_append"):
+    if selected("c3_swa_ring_i4b32_fused_append"):
         try:
             W, pos = 1024, 8191
             nb = HD // 32
@@ -562,7 +562,7 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
     # sliding layers 32q/16kv x 256 with a 1024-slot ring, full layers 32q/4kv x 512 at 32768 keys
     for name, nkv_g, hd_g, t_g, cap_g in (("g4_sliding_hd256_i4b32_w1024", 16, 256, 1024, 1024),
                                           ("g4_full_hd512_i4b32_32k", 4, 512, 32768, 32768)):
-        if not want(name):
+        if not selected(name):
             continue
         try:
             nb = hd_g // 32
@@ -604,7 +604,7 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
             ("producer_c2_hd128_i8", NH, NKV, HD, ops.KV_I8, 32768, 10000.0, HD),
             ("producer_g4_sliding_hd256_i4b32", NH, 16, 256, ops.KV_I4B32, 1024, 10000.0, 256),
             ("producer_g4_full_hd512_i4b32", NH, 4, 512, ops.KV_I4B32, 32768, 1000000.0, 128)):
-        if not want(name):
+        if not selected(name):
             continue
         try:
             row_b = hd_p if fmt_p == ops.KV_I8 else hd_p // 2
@@ -630,7 +630,7 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
             out[name] = {"error": str(e)}
     # one decode step of a layer's attention path at configuration 2: producer epilogue (norms, RoPE, quantize-on-write
     # of the new token) then attention over the 32768 keys -- two launches chained by programmatic dependent launch
-    if want("decode_step_c2_producer_plus_attention"):
+    if selected("decode_step_c2_producer_plus_attention"):
         try:
             caches = [make_layer_cache(torch, ops, dev, 1, NKV, T, HD, 1302 + i) for i in range(NLAYERS)]
             qf = torch.randn((1, NH, HD), device=dev); kf = torch.randn((1, NKV, HD), device=dev); vf = torch.randn((1, NKV, HD), device=dev)
@@ -660,7 +660,7 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
         except Exception as e:
             out["decode_step_c2_producer_plus_attention"] = {"error": str(e)}
     # configuration 5a: batch 8 x 131072 keys, sharded by KV-head groups (16 / world heads per GPU, no collective)
-    if want("c5a_batch8_131k_head_sharded"):
+    if selected("c5a_batch8_131k_head_sharded"):
         try:
             B5, T5a = 8, 131072
             nkv5 = NKV // world
@@ -681,7 +681,7 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
         except Exception as e:
             out["c5a_batch8_131k_head_sharded"] = {"error": str(e)}
     # configuration 5a on PAGED caches: same bytes, pages of 128 keys behind a shuffled block table (serving layout)
-    if want("c5a_paged_batch8_131k"):
+    if selected("c5a_paged_batch8_131k"):
         try:
             B5, T5a = 8, 131072
             nkv5 = NKV // world
@@ -720,7 +720,7 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
     #           mailboxes over NVLink, waits for theirs and merges.
     # Both are checked against the oracle: every rank computes the exact fp64 partial of its own chunk on the host,
     # the partials are gathered on the host and merged by the oracle.
-    if want("c5b_seq_sharded_512k"):
+    if selected("c5b_seq_sharded_512k"):
         try:
             from nomos_nvfp4_b200.sharding import SeqShardGroup
             T5 = 524288 // world

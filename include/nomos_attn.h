@@ -252,7 +252,8 @@ typedef struct nomos_attn_args {
     uint64_t k_scales, v_scales;/* per kv_fmt, see NOMOS_KV_*                             */
     uint64_t out;               /* [batch][S][nh][l_hd], out_type (may be 0 if partial_out)*/
     uint64_t partial_out;       /* 0, or fp32 [batch][S][nh][l_hd+2] = un-normalised o,
-                                   then m (natural log), then l: for cross-GPU merging     */
+                                   then m (natural log), then l: for cross-GPU merging;
+                                   a call that sets it does not write `out`                */
     uint64_t workspace;         /* split-K scratch                                        */
     int64_t ws_bytes;           /* >= nomos_attn_workspace_bytes(args)                     */
     uint64_t new_k, new_v;      /* 0, or fp32 [batch][n_new][nkv][l_hd] rows to quantize+append */

@@ -24,11 +24,11 @@
 // The cache stays int8 in device memory and on the way in: TMA boxes of 128 rows x 128 bytes, one tensor map per
 // plane over this GPU's own memory, no cluster, nothing multicast.
 //
-// Roles (384 threads): warps 0-7 softmax -- query row r = TMEM lane r is shared by two threads, lane r % 32 of warps
-// r / 32 and r / 32 + 4 (both may read that lane quarter), each taking 64 of the tile's 128 keys: two warps per
-// scheduler hide each other's latencies (one warp per scheduler measured 0.16 instructions per cycle), the row
-// maximum crosses the pair through shared memory once per tile; warps 8-9 dequant (a thread converts two key rows of
-// the V tile), warp 10 lane 0 TMA producer (+ TMEM allocation), warp 11 lane 0 MMA issuer.  The softmax threads pull
+// Roles (640 threads): warps 0-15 softmax -- query row r = TMEM lane r is shared by four threads, lane r % 32 of warps
+// r / 32 + 4 q, q = 0..3 (all may read that lane quarter), each taking 32 of the tile's 128 keys: four warps per
+// scheduler hide each other's latencies (one warp per scheduler measured 0.16 instructions per cycle, two 0.34), the
+// row maximum crosses the four through shared memory once per tile; warps 16-17 dequant (a thread converts two key rows
+// of the V tile), warp 18 lane 0 TMA producer (+ TMEM allocation), warp 19 lane 0 MMA issuer.  The softmax threads pull
 // S into registers and release it at once, so QK of tile i+1 runs while they work on tile i; O stays in tensor memory across tiles and is rescaled in
 // place only when a row's running maximum moves by more than 2^8 (a handful of times per row).  Every wait is an
 // mbarrier wait with a time limit; a wait that runs out raises the CTA's abort flag and bit 1 of the device fault
@@ -60,9 +60,15 @@ constexpr int OFF_BAR = OFF_P16 + 2 * H_TILE; // 196608
 constexpr int NBAR = 16;
 constexpr int OFF_MISC = OFF_BAR + NBAR * 8;  // tmem base, abort flag
 constexpr int OFF_SC = OFF_MISC + 64;         // [2 stages][K scales | V scales] fp32, 128 each, bulk-copied with the tile
-constexpr int OFF_XCH = OFF_SC + 2 * 2 * KT * 4;        // [3][2 halves][128 rows] fp32: row maxima by tile parity; region 2: query maxima, then denominators
-constexpr int SMEM_BYTES = 1024 + OFF_XCH + 3 * 2 * 128 * 4;
-constexpr int NTHREADS = 384;
+constexpr int TPR = 4;                        // softmax threads per query row
+constexpr int KPT = KT / TPR;                 // keys of a tile (and dims of Q / O) per softmax thread
+constexpr int NSOFT = TPR * MR;               // softmax threads
+constexpr int W_DEQ = NSOFT / 32;             // first of the two dequant warps; then the TMA producer, then the MMA issuer
+constexpr int W_TMA = W_DEQ + 2, W_MMA = W_DEQ + 3;
+constexpr int OFF_XCH = OFF_SC + 2 * 2 * KT * 4;        // [3][TPR][128 rows] fp32: row maxima by tile parity; region 2: query maxima, then denominators
+constexpr int SMEM_BYTES = 1024 + OFF_XCH + 3 * TPR * 128 * 4;
+constexpr int NTHREADS = NSOFT + 128;
+static_assert(KPT == 32, "a softmax thread moves one 32-column block of tensor memory per limb");
 constexpr int TMEM_COLS = 512;                // S_hi at column 0, S_lo at 128, O at 256
 constexpr int Q_FIX_MAX = fused::Q_FIX_MAX;   // 16-bit fixed-point query, two int8 limbs
 static_assert(OFF_V16 % 1024 == 0 && OFF_Q8 % 1024 == 0 && OFF_P16 % 1024 == 0, "operand tiles sit on swizzle-pattern boundaries");
@@ -121,14 +127,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(u[i]);
 }
-__device__ __forceinline__ void tmem_ld32i(uint32_t taddr, int (&r)[32]) {
+__device__ __forceinline__ void tmem_ld16i(uint32_t taddr, int (&r)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
-        "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&r)[32]) {
@@ -171,18 +174,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
     const uint32_t sm_u32 = smem_u32(sm);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(sm + OFF_MISC);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(sm + OFF_MISC + 4);
-    float *xch = reinterpret_cast<float *>(sm + OFF_XCH);              // [3][2][128]
+    float *xch = reinterpret_cast<float *>(sm + OFF_XCH);              // [3][TPR][128]
     const uint32_t bar0 = sm_u32 + OFF_BAR;
     auto bar_raw_full = [&](int s) { return bar0 + 8 * s; };            // TMA -> dequant and MMA (tx bytes)
-    auto bar_raw_empty = [&](int s) { return bar0 + 8 * (2 + s); };     // dequant (64, V converted) + commit after QK (1) + softmax (256, scales used) -> TMA
+    auto bar_raw_empty = [&](int s) { return bar0 + 8 * (2 + s); };     // dequant (64, V converted) + commit after QK (1) + softmax (all, scales used) -> TMA
     const uint32_t bar_v16_full = bar0 + 8 * 4;                         // dequant (64) -> MMA
     const uint32_t bar_v16_empty = bar0 + 8 * 5;                        // commit after PV -> dequant
     const uint32_t bar_s_full = bar0 + 8 * 6;                           // commit after QK -> softmax
-    const uint32_t bar_s_empty = bar0 + 8 * 7;                          // softmax (256): S is in registers -> MMA
-    const uint32_t bar_p_full = bar0 + 8 * 8;                           // softmax (256) -> MMA
+    const uint32_t bar_s_empty = bar0 + 8 * 7;                          // softmax (all): S is in registers -> MMA
+    const uint32_t bar_p_full = bar0 + 8 * 8;                           // softmax (all) -> MMA
     const uint32_t bar_o_done = bar0 + 8 * 9;                           // commit after PV -> softmax
-    const uint32_t bar_q_ready = bar0 + 8 * 10;                         // softmax (256) -> MMA
-    const uint32_t bar_xch = bar0 + 8 * 11;                             // softmax (256): the two halves of every row have written their exchange slot
+    const uint32_t bar_q_ready = bar0 + 8 * 10;                         // softmax (all) -> MMA
+    const uint32_t bar_xch = bar0 + 8 * 11;                             // softmax (all): the threads of every row have written their exchange slots
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heavy blocks (late query positions: the most key tiles) are scheduled first
@@ -200,19 +203,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         fused::mbar_init(bar_raw_full(0), 1); fused::mbar_init(bar_raw_full(1), 1);
-        fused::mbar_init(bar_raw_empty(0), 321); fused::mbar_init(bar_raw_empty(1), 321);
+        fused::mbar_init(bar_raw_empty(0), NSOFT + 65); fused::mbar_init(bar_raw_empty(1), NSOFT + 65);
         fused::mbar_init(bar_v16_full, 64); fused::mbar_init(bar_v16_empty, 1);
-        fused::mbar_init(bar_s_full, 1); fused::mbar_init(bar_s_empty, 256);
-        fused::mbar_init(bar_p_full, 256); fused::mbar_init(bar_o_done, 1);
-        fused::mbar_init(bar_q_ready, 256);
-        fused::mbar_init(bar_xch, 256);
+        fused::mbar_init(bar_s_full, 1); fused::mbar_init(bar_s_empty, NSOFT);
+        fused::mbar_init(bar_p_full, NSOFT); fused::mbar_init(bar_o_done, 1);
+        fused::mbar_init(bar_q_ready, NSOFT);
+        fused::mbar_init(bar_xch, NSOFT);
         fused::fence_mbar_init();
     }
     // the scale stages start as zeros: a partial copy at the end of the key array then leaves finite values behind
     for (int e = threadIdx.x; e < 2 * 2 * KT; e += NTHREADS) reinterpret_cast<float *>(sm + OFF_SC)[e] = 0.0f;
     fused::fence_proxy_async();
-    if (warp == 11 && lane == 0) { fused::prefetch_tensormap(&tm.k); fused::prefetch_tensormap(&tm.v); }
-    if (warp == 10) {
+    if (warp == W_MMA && lane == 0) { fused::prefetch_tensormap(&tm.k); fused::prefetch_tensormap(&tm.v); }
+    if (warp == W_TMA) {
         tc5::tmem_alloc(sm_u32 + OFF_MISC, TMEM_COLS);
         tc5::tmem_relinquish();
     }
@@ -223,7 +226,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
     fused::pdl_wait();                         // the query and the cache rows may come from the stream predecessor
     fused::pdl_launch_dependents();
 
-    if (warp == 10) {
+    if (warp == W_TMA) {
         // =========================================================== TMA producer
         if (lane == 0) {
             for (int i = 0; i < n_tiles; ++i) {
@@ -245,7 +248,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
             }
         }
         __syncwarp();
-    } else if (warp == 11) {
+    } else if (warp == W_MMA) {
         // =========================================================== MMA issuer
         if (lane == 0) {
             const uint32_t idesc_qk = tc5::make_idesc(KT, true, true, false);
@@ -294,9 +297,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
             }
         }
         __syncwarp();
-    } else if (warp >= 8) {
+    } else if (warp >= W_DEQ) {
         // =========================================================== dequant warps: a thread converts key rows t, t + 64 of the V tile
-        const int t = threadIdx.x - 256;
+        const int t = threadIdx.x - NSOFT;
         for (int i = 0; i < n_tiles; ++i) {
             const int st = i & 1;
             const uint8_t *raw = sm + OFF_RAW + st * 2 * RAW_TILE + RAW_TILE;
@@ -320,8 +323,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
             tc5::mbar_arrive(bar_raw_empty(st));
         }
     } else {
-        // =========================================================== softmax warps: two threads per query row
-        const int half = warp >> 2;                                    // which 64 keys of a tile (and which 64 dims of Q / O) this thread takes
+        // =========================================================== softmax warps: four threads per query row
+        const int qt = warp >> 2;                                      // which 32 keys of a tile (and which 32 dims of Q / O) this thread takes
         const int r = 32 * (warp & 3) + lane;                          // query row = TMEM lane
         const int s = s_first + r / p.kvg, j = r - (r / p.kvg) * p.kvg;
         const bool valid = r < p.pos_per_cta * p.kvg && s < p.S;
@@ -331,7 +334,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
         auto wait_warp = [&](uint32_t bar, uint32_t parity) {
             return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag, p.fault)) != 0;
         };
-        // Meeting point of the 256 softmax threads: an mbarrier with the same time limit as every other wait (a
+        // Meeting point of the softmax threads: an mbarrier with the same time limit as every other wait (a
         // hardware barrier would wait forever for a warp that had given up).  false = abandoned.
         uint32_t xphase = 0;
         auto pair_sync = [&]() {
@@ -341,13 +344,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
             return ok;
         };
         // ---- the query row -> 16-bit fixed point of its own maximum, two int8 limbs (q ~= sq * (256 hi + lo)),
-        // stored K-major in the 128-byte swizzle pattern; this thread converts dims 64 half .. 64 half + 63
+        // stored K-major in the 128-byte swizzle pattern; this thread converts dims 32 qt .. 32 qt + 31
         float qscale_r;                          // base-2 logit per unit of the integer dot product and of the key's scale
         {
-            const long qoff = b * p.q_batch_stride + ((long)(valid ? s : 0) * p.nh + kvh * p.kvg + (valid ? j : 0)) * HD + 64 * half;
-            float x[64];
+            const long qoff = b * p.q_batch_stride + ((long)(valid ? s : 0) * p.nh + kvh * p.kvg + (valid ? j : 0)) * HD + KPT * qt;
+            float x[KPT];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 0; c < KPT / 8; ++c) {
                 if (p.q_type == ET_BF16) {
                     const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(p.q) + qoff) + c);
                     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -362,15 +365,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
             }
             float amax = 0.0f;
 #pragma unroll
-            for (int d = 0; d < 64; ++d) amax = fmaxf(amax, fabsf(x[d]));
-            xch[(4 + half) * 128 + r] = amax;
+            for (int d = 0; d < KPT; ++d) amax = fmaxf(amax, fabsf(x[d]));
+            xch[(2 * TPR + qt) * 128 + r] = amax;
             pair_sync();
-            amax = fmaxf(amax, xch[(4 + 1 - half) * 128 + r]);
+#pragma unroll
+            for (int o = 1; o < TPR; ++o) amax = fmaxf(amax, xch[(2 * TPR + ((qt + o) & (TPR - 1))) * 128 + r]);
             const float sq = (valid && amax > 0.0f) ? amax * (1.0f / (float)Q_FIX_MAX) : 1.0f;
             const float inv = 1.0f / sq;
             qscale_r = valid ? sq * p.q_scale : 0.0f;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {                              // 16 dims per 16-byte chunk
+            for (int c = 0; c < KPT / 16; ++c) {                       // 16 dims per 16-byte chunk
                 uint32_t wh[4], wl[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -385,7 +389,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
                     }
                     wh[e] = ph; wl[e] = pl;
                 }
-                const int off = (r >> 3) * 1024 + (r & 7) * 128 + (((4 * half + c) ^ (r & 7)) << 4);
+                const int off = (r >> 3) * 1024 + (r & 7) * 128 + ((((KPT / 16) * qt + c) ^ (r & 7)) << 4);
                 *reinterpret_cast<uint4 *>(sm + OFF_Q8 + off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
                 *reinterpret_cast<uint4 *>(sm + OFF_Q8 + RAW_TILE + off) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
             }
@@ -395,60 +399,61 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
         // fp32 row scales of the keys, read per tile by every thread (the same 1 KB for the whole CTA: L1 hits)
         const float *gks = p.k_scales + b * (p.scale_batch_stride / 4) + (size_t)kvh * p.cache_cap + p.row0;
         const float *gvs = p.v_scales + b * (p.scale_batch_stride / 4) + (size_t)kvh * p.cache_cap + p.row0;
-        float m = M_INIT, l = 0.0f;              // running maximum of the row (both halves agree), this half's share of the denominator
+        float m = M_INIT, l = 0.0f;              // running maximum of the row (its threads agree), this thread's share of the denominator
         bool alive = true;
         for (int i = 0; alive && i < n_tiles; ++i) {
-            const int t0 = (tile_lo + i) * KT + 64 * half;             // first key of this thread's half of the tile
+            const int t0 = (tile_lo + i) * KT + KPT * qt;              // first key of this thread's share of the tile
             // rows outside [lo_r, hi_r] see nothing of the key (a select, never a multiply); decided per warp, so that
             // whole tiles in the middle of every row's range carry no masking instructions at all
-            const bool need_mask = __any_sync(0xffffffffu, t0 < lo_r || t0 + 63 > hi_r);
+            const bool need_mask = __any_sync(0xffffffffu, t0 < lo_r || t0 + KPT - 1 > hi_r);
             const int st = i & 1;
-            // scales of this half's keys: in shared memory when they could ride the bulk copies (the copy covers whole
+            // scales of this thread's keys: in shared memory when they could ride the bulk copies (the copy covers whole
             // 16-byte units inside the key array: a ragged tail is read from global memory), else from global memory
-            const bool whole = p.scales_vec && (((tile_lo + i) * KT + (min(KT, p.key_len - (tile_lo + i) * KT) & ~3)) >= t0 + 64);
-            const float *sks = reinterpret_cast<const float *>(sm + OFF_SC + st * 2 * KT * 4) + 64 * half - t0;      // used when `whole`
-            const float *svs = reinterpret_cast<const float *>(sm + OFF_SC + st * 2 * KT * 4 + KT * 4) + 64 * half - t0;
+            const bool whole = p.scales_vec && (((tile_lo + i) * KT + (min(KT, p.key_len - (tile_lo + i) * KT) & ~3)) >= t0 + KPT);
+            const float *sks = reinterpret_cast<const float *>(sm + OFF_SC + st * 2 * KT * 4) + KPT * qt - t0;      // used when `whole`
+            const float *svs = reinterpret_cast<const float *>(sm + OFF_SC + st * 2 * KT * 4 + KT * 4) + KPT * qt - t0;
             const int tl = p.key_len - 1;
             if (!wait_warp(bar_raw_full(st), (i >> 1) & 1)) { alive = false; break; }   // the scales have landed
             if (!wait_warp(bar_s_full, i & 1)) { alive = false; break; }
             tc5::tc_fence_after();
-            float sv[2][32];                                           // base-2 logits of this row against its 64 keys
+            float sv[KPT];                                             // base-2 logits of this row against its 32 keys
             float tmax = -CUDART_INF_F;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                int sh[32], sl[32];
-                tmem_ld32i(tmem_lane + 64 * half + 32 * c, sh);
-                tmem_ld32i(tmem_lane + 128 + 64 * half + 32 * c, sl);
+            for (int c = 0; c < KPT / 16; ++c) {                       // 16 columns of each limb at a time: registers
+                int sh[16], sl[16];
+                tmem_ld16i(tmem_lane + KPT * qt + 16 * c, sh);
+                tmem_ld16i(tmem_lane + 128 + KPT * qt + 16 * c, sl);
                 tc5::tmem_wait_ld();
 #pragma unroll
-                for (int e4 = 0; e4 < 32; e4 += 4) {
+                for (int e4 = 0; e4 < 16; e4 += 4) {
                     float4 k4;
                     if (whole) {
-                        k4 = *reinterpret_cast<const float4 *>(sks + t0 + 32 * c + e4);
+                        k4 = *reinterpret_cast<const float4 *>(sks + t0 + 16 * c + e4);
                     } else {
-                        k4 = make_float4(gks[min(t0 + 32 * c + e4, tl)], gks[min(t0 + 32 * c + e4 + 1, tl)], gks[min(t0 + 32 * c + e4 + 2, tl)],
-                                         gks[min(t0 + 32 * c + e4 + 3, tl)]);
+                        k4 = make_float4(gks[min(t0 + 16 * c + e4, tl)], gks[min(t0 + 16 * c + e4 + 1, tl)], gks[min(t0 + 16 * c + e4 + 2, tl)],
+                                         gks[min(t0 + 16 * c + e4 + 3, tl)]);
                     }
                     const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        // limb sums are below 128 * 128 * 127 < 2^22: exact in the float conversion
-                        float u = tc5::limbs2f<8>(sh[e4 + e], sl[e4 + e]) * (qscale_r * kk[e]);
+                        // limb sums are below 128 * 128 * 127 < 2^22: 256 hi + lo fits an int, one rounding in the conversion
+                        float u = (float)(sh[e4 + e] * 256 + sl[e4 + e]) * (qscale_r * kk[e]);
                         if (need_mask) {
-                            const int t = t0 + 32 * c + e4 + e;
+                            const int t = t0 + 16 * c + e4 + e;
                             u = (t >= lo_r && t <= hi_r) ? u : -CUDART_INF_F;
                         }
-                        sv[c][e4 + e] = u;
+                        sv[16 * c + e4 + e] = u;
                         tmax = fmaxf(tmax, u);
                     }
                 }
             }
             tc5::tc_fence_before();
             tc5::mbar_arrive(bar_s_empty);                             // S is in registers: QK of the next tile may overwrite it
-            // the row's tile maximum: the two halves meet through shared memory (double-buffered by tile parity)
-            xch[((i & 1) * 2 + half) * 128 + r] = tmax;
+            // the row's tile maximum: its threads meet through shared memory (double-buffered by tile parity)
+            xch[((i & 1) * TPR + qt) * 128 + r] = tmax;
             if (!pair_sync()) { alive = false; break; }
-            tmax = fmaxf(tmax, xch[((i & 1) * 2 + 1 - half) * 128 + r]);
+#pragma unroll
+            for (int o = 1; o < TPR; ++o) tmax = fmaxf(tmax, xch[((i & 1) * TPR + ((qt + o) & (TPR - 1))) * 128 + r]);
             // the running maximum only moves when the tile exceeds it by more than 2^8: the weights stay below 2^8 and
             // the accumulator in tensor memory is rescaled a handful of times per row instead of once per tile
             const bool moved = tmax > m + LAZY;
@@ -457,78 +462,72 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
             m = m_new;
             // P is single-buffered and O lives in tensor memory: both wait for the previous tile's PV product
             if (i >= 1 && !wait_warp(bar_o_done, (i - 1) & 1)) { alive = false; break; }
-            if (i >= 1 && __any_sync(0xffffffffu, moved)) {            // this thread rescales its 64 dims of O
+            if (i >= 1 && __any_sync(0xffffffffu, moved)) {            // this thread rescales its 32 dims of O
                 tc5::tc_fence_after();
-#pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    float o[32];
-                    tmem_ld32(tmem_lane + 256 + 64 * half + 32 * c, o);
+                float o[32];
+                tmem_ld32(tmem_lane + 256 + KPT * qt, o);
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) o[e] *= alpha;
-                    tmem_st32(tmem_lane + 256 + 64 * half + 32 * c, o);
-                }
+                for (int e = 0; e < 32; ++e) o[e] *= alpha;
+                tmem_st32(tmem_lane + 256 + KPT * qt, o);
                 tmem_wait_st();
             }
-            // weights of this thread's 64 keys = key block `half` of the P tiles: weight x value scale as fp16 hi + lo
-            float lsum = 0.0f;
+            // weights of this thread's 32 keys = chunks 4 qt .. 4 qt + 3 of the P tiles: weight x value scale as fp16 hi + lo
+            float lsum0 = 0.0f, lsum1 = 0.0f;
 #pragma unroll
-            for (int c = 0; c < 2; ++c)
+            for (int e8 = 0; e8 < KPT; e8 += 8) {
+                float vv[8];
+                if (whole) {
+                    const float4 a4 = *reinterpret_cast<const float4 *>(svs + t0 + e8);
+                    const float4 b4 = *reinterpret_cast<const float4 *>(svs + t0 + e8 + 4);
+                    vv[0] = a4.x; vv[1] = a4.y; vv[2] = a4.z; vv[3] = a4.w; vv[4] = b4.x; vv[5] = b4.y; vv[6] = b4.z; vv[7] = b4.w;
+                } else {
 #pragma unroll
-                for (int e8 = 0; e8 < 32; e8 += 8) {
-                    float vv[8];
-                    if (whole) {
-                        const float4 a4 = *reinterpret_cast<const float4 *>(svs + t0 + 32 * c + e8);
-                        const float4 b4 = *reinterpret_cast<const float4 *>(svs + t0 + 32 * c + e8 + 4);
-                        vv[0] = a4.x; vv[1] = a4.y; vv[2] = a4.z; vv[3] = a4.w; vv[4] = b4.x; vv[5] = b4.y; vv[6] = b4.z; vv[7] = b4.w;
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) vv[e] = gvs[min(t0 + 32 * c + e8 + e, tl)];
-                    }
-                    uint32_t wh[4], wl[4];
-#pragma unroll
-                    for (int e = 0; e < 8; e += 2) {
-                        const float p0 = ex2f(sv[c][e8 + e] - m), p1 = ex2f(sv[c][e8 + e + 1] - m);
-                        lsum += p0 + p1;
-                        const float w0 = p0 * vv[e], w1 = p1 * vv[e + 1];
-                        const __half2 h = __floats2half2_rn(w0, w1);
-                        const __half2 hl = __floats2half2_rn(w0 - __low2float(h), w1 - __high2float(h));
-                        wh[e >> 1] = *reinterpret_cast<const uint32_t *>(&h);
-                        wl[e >> 1] = *reinterpret_cast<const uint32_t *>(&hl);
-                    }
-                    const int chunk = 8 * half + 4 * c + (e8 >> 3);    // 16-byte chunk (8 keys) of the row
-                    *reinterpret_cast<uint4 *>(sm + OFF_P16 + h_off(r, chunk)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
-                    *reinterpret_cast<uint4 *>(sm + OFF_P16 + H_TILE + h_off(r, chunk)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+                    for (int e = 0; e < 8; ++e) vv[e] = gvs[min(t0 + e8 + e, tl)];
                 }
-            l = fmaf(l, alpha, lsum);
+                uint32_t wh[4], wl[4];
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                    const float p0 = ex2f(sv[e8 + e] - m), p1 = ex2f(sv[e8 + e + 1] - m);
+                    lsum0 += p0; lsum1 += p1;
+                    const float w0 = p0 * vv[e], w1 = p1 * vv[e + 1];
+                    const __half2 h = __floats2half2_rn(w0, w1);
+                    const __half2 hl = __floats2half2_rn(w0 - __low2float(h), w1 - __high2float(h));
+                    wh[e >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+                    wl[e >> 1] = *reinterpret_cast<const uint32_t *>(&hl);
+                }
+                const int chunk = (KPT / 8) * qt + (e8 >> 3);          // 16-byte chunk (8 keys) of the row
+                *reinterpret_cast<uint4 *>(sm + OFF_P16 + h_off(r, chunk)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                *reinterpret_cast<uint4 *>(sm + OFF_P16 + H_TILE + h_off(r, chunk)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+            }
+            l = fmaf(l, alpha, lsum0 + lsum1);
             tc5::mbar_arrive(bar_raw_empty(st));                       // done with the stage's scales
             fused::fence_proxy_async();
             tc5::tc_fence_before();
             tc5::mbar_arrive(bar_p_full);
         }
         // ---- output: O / l (rows without any key are exact zeros, lib/batched_attn_gpu.mojo:329-409); this thread
-        // writes dims 64 half .. 64 half + 63 of its row
+        // writes dims 32 qt .. 32 qt + 31 of its row
         if (alive && n_tiles > 0) alive = wait_warp(bar_o_done, (n_tiles - 1) & 1);
         if (alive) {
-            xch[(4 + half) * 128 + r] = l;
+            xch[(2 * TPR + qt) * 128 + r] = l;
             alive = pair_sync();
-            l += xch[(4 + 1 - half) * 128 + r];
+#pragma unroll
+            for (int o = 1; o < TPR; ++o) l += xch[(2 * TPR + ((qt + o) & (TPR - 1))) * 128 + r];
         }
         if (alive) {
             tc5::tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            const long oi = b * p.out_batch_stride + ((long)(valid ? s : 0) * p.nh + kvh * p.kvg + (valid ? j : 0)) * HD + 64 * half;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                float o[32];
-                if (n_tiles > 0) {
-                    tmem_ld32(tmem_lane + 256 + 64 * half + 32 * c, o);
-                } else {
+            const long oi = b * p.out_batch_stride + ((long)(valid ? s : 0) * p.nh + kvh * p.kvg + (valid ? j : 0)) * HD + KPT * qt;
+            float o[32];
+            if (n_tiles > 0) {
+                tmem_ld32(tmem_lane + 256 + KPT * qt, o);
+            } else {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) o[e] = 0.0f;
-                }
-                if (!valid) continue;
+                for (int e = 0; e < 32; ++e) o[e] = 0.0f;
+            }
+            if (valid) {
                 if (p.out_type == ET_BF16) {
-                    uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + oi + 32 * c);
+                    uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + oi);
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
                         uint32_t w[4];
@@ -540,7 +539,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
                         dst[q4] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 } else {
-                    float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + oi + 32 * c);
+                    float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + oi);
 #pragma unroll
                     for (int q4 = 0; q4 < 8; ++q4)
                         dst[q4] = make_float4(o[4 * q4] * inv, o[4 * q4 + 1] * inv, o[4 * q4 + 2] * inv, o[4 * q4 + 3] * inv);
@@ -552,7 +551,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
     // ------------------------------------------------------------ tear-down
     tc5::tc_fence_before();
     __syncthreads();
-    if (warp == 10) tc5::tmem_dealloc(tmem_base, TMEM_COLS);
+    if (warp == W_TMA) tc5::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 }  // namespace pf
