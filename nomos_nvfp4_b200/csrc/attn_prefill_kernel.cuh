@@ -177,15 +177,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
     float *xch = reinterpret_cast<float *>(sm + OFF_XCH);              // [3][TPR][128]
     const uint32_t bar0 = sm_u32 + OFF_BAR;
     auto bar_raw_full = [&](int s) { return bar0 + 8 * s; };            // TMA -> dequant and MMA (tx bytes)
-    auto bar_raw_empty = [&](int s) { return bar0 + 8 * (2 + s); };     // dequant (64, V converted) + commit after QK (1) + softmax (all, scales used) -> TMA
-    const uint32_t bar_v16_full = bar0 + 8 * 4;                         // dequant (64) -> MMA
+    auto bar_raw_empty = [&](int s) { return bar0 + 8 * (2 + s); };     // dequant warps (V converted) + commit after QK (1) + softmax warps (scales used) -> TMA
+    const uint32_t bar_v16_full = bar0 + 8 * 4;                         // dequant warps -> MMA
     const uint32_t bar_v16_empty = bar0 + 8 * 5;                        // commit after PV -> dequant
     const uint32_t bar_s_full = bar0 + 8 * 6;                           // commit after QK -> softmax
-    const uint32_t bar_s_empty = bar0 + 8 * 7;                          // softmax (all): S is in registers -> MMA
-    const uint32_t bar_p_full = bar0 + 8 * 8;                           // softmax (all) -> MMA
+    const uint32_t bar_s_empty = bar0 + 8 * 7;                          // softmax warps: S is in registers -> MMA
+    const uint32_t bar_p_full = bar0 + 8 * 8;                           // softmax warps -> MMA
     const uint32_t bar_o_done = bar0 + 8 * 9;                           // commit after PV -> softmax
-    const uint32_t bar_q_ready = bar0 + 8 * 10;                         // softmax (all) -> MMA
-    const uint32_t bar_xch = bar0 + 8 * 11;                             // softmax (all): the threads of every row have written their exchange slots
+    const uint32_t bar_q_ready = bar0 + 8 * 10;                         // softmax warps -> MMA
+    const uint32_t bar_xch = bar0 + 8 * 11;                             // softmax warps: the threads of every row have written their exchange slots
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heavy blocks (late query positions: the most key tiles) are scheduled first
@@ -203,12 +203,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         fused::mbar_init(bar_raw_full(0), 1); fused::mbar_init(bar_raw_full(1), 1);
-        fused::mbar_init(bar_raw_empty(0), NSOFT + 65); fused::mbar_init(bar_raw_empty(1), NSOFT + 65);
-        fused::mbar_init(bar_v16_full, 64); fused::mbar_init(bar_v16_empty, 1);
-        fused::mbar_init(bar_s_full, 1); fused::mbar_init(bar_s_empty, NSOFT);
-        fused::mbar_init(bar_p_full, NSOFT); fused::mbar_init(bar_o_done, 1);
-        fused::mbar_init(bar_q_ready, NSOFT);
-        fused::mbar_init(bar_xch, NSOFT);
+        fused::mbar_init(bar_raw_empty(0), NSOFT / 32 + 3); fused::mbar_init(bar_raw_empty(1), NSOFT / 32 + 3);
+        fused::mbar_init(bar_v16_full, 2); fused::mbar_init(bar_v16_empty, 1);
+        fused::mbar_init(bar_s_full, 1); fused::mbar_init(bar_s_empty, NSOFT / 32);
+        fused::mbar_init(bar_p_full, NSOFT / 32); fused::mbar_init(bar_o_done, 1);
+        fused::mbar_init(bar_q_ready, NSOFT / 32);
+        fused::mbar_init(bar_xch, NSOFT / 32);
         fused::fence_mbar_init();
     }
     // the scale stages start as zeros: a partial copy at the end of the key array then leaves finite values behind
@@ -252,10 +252,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
         // =========================================================== MMA issuer
         if (lane == 0) {
             const uint32_t idesc_qk = tc5::make_idesc(KT, true, true, false);
-            const uint32_t idesc_pv = make_idesc_f16(64, true);
+            const uint32_t idesc_pv = make_idesc_f16(HD, true);
             const uint64_t qdesc[2] = {tc5::smem_desc_sw128(sm_u32 + OFF_Q8), tc5::smem_desc_sw128(sm_u32 + OFF_Q8 + RAW_TILE)};
             const uint64_t pdesc[2] = {tc5::smem_desc_sw128(sm_u32 + OFF_P16), tc5::smem_desc_sw128(sm_u32 + OFF_P16 + H_TILE)};
-            const uint64_t vdesc = tc5::smem_desc_sw128(sm_u32 + OFF_V16);
+            // B of PV, MN-major: the two 64-dim blocks of V16 are one operand, the second H_BLOCK bytes after the first
+            // (leading-dimension offset); key groups of 8 rows stay 1024 bytes apart
+            const uint64_t vdesc = (tc5::smem_desc_sw128(sm_u32 + OFF_V16) & ~(0x3fffull << 16)) | ((uint64_t)(H_BLOCK >> 4) << 16);
             bool go = n_tiles > 0 && wait_or_abort(bar_q_ready, 0, abort_flag, p.fault);
             for (int i = 0; go && i <= n_tiles; ++i) {
                 if (i < n_tiles) {
@@ -274,8 +276,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
                     tc5::umma_commit(bar_raw_empty(st));
                 }
                 if (i >= 1) {
-                    // O += Phi_j x V_j + Plo_j x V_j: per weight limb and 64-dim half of V, 8 steps of 16 keys
-                    // (A: 32 bytes inside a 64-key block, then the next block; B: 16 rows of the MN-major V block = 2048 bytes)
+                    // O += Phi_j x V_j + Plo_j x V_j: per weight limb 8 steps of 16 keys against all 128 dims (an instruction
+                    // costs the issuing thread about a hundred cycles whatever its size: few and large)
+                    // (A: 32 bytes inside a 64-key block, then the next block; B: 16 rows of the MN-major V blocks = 2048 bytes)
                     const int j = i - 1;
                     if (!wait_or_abort(bar_v16_full, j & 1, abort_flag, p.fault)) break;
                     if (!wait_or_abort(bar_p_full, j & 1, abort_flag, p.fault)) break;
@@ -283,14 +286,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
 #pragma unroll
                     for (int limb = 0; limb < 2; ++limb)
 #pragma unroll
-                        for (int h = 0; h < 2; ++h)
-#pragma unroll
-                            for (int k = 0; k < 8; ++k) {
-                                const uint64_t a_adv = (uint64_t)((k >> 2) * (H_BLOCK >> 4) + (k & 3) * 2);
-                                const uint64_t b_adv = (uint64_t)(h * (H_BLOCK >> 4) + k * (2048 >> 4));
-                                umma_f16(tmem_base + 256 + 64 * h, pdesc[limb] + a_adv, vdesc + b_adv, idesc_pv,
-                                         (j > 0 || limb > 0 || k > 0) ? 1u : 0u);
-                            }
+                        for (int k = 0; k < 8; ++k) {
+                            const uint64_t a_adv = (uint64_t)((k >> 2) * (H_BLOCK >> 4) + (k & 3) * 2);
+                            const uint64_t b_adv = (uint64_t)(k * (2048 >> 4));
+                            umma_f16(tmem_base + 256, pdesc[limb] + a_adv, vdesc + b_adv, idesc_pv, (j > 0 || limb > 0 || k > 0) ? 1u : 0u);
+                        }
                     tc5::umma_commit(bar_v16_empty);
                     tc5::umma_commit(bar_o_done);
                 }
@@ -319,8 +319,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
                 }
             }
             fused::fence_proxy_async();
-            tc5::mbar_arrive(bar_v16_full);
-            tc5::mbar_arrive(bar_raw_empty(st));
+            __syncwarp();
+            if (lane == 0) { tc5::mbar_arrive(bar_v16_full); tc5::mbar_arrive(bar_raw_empty(st)); }
         }
     } else {
         // =========================================================== softmax warps: four threads per query row
@@ -336,9 +336,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
         };
         // Meeting point of the softmax threads: an mbarrier with the same time limit as every other wait (a
         // hardware barrier would wait forever for a warp that had given up).  false = abandoned.
+        // One arrival per warp: the warp's stores and fences are ordered before it by the warp barrier.
+        auto warp_arrive = [&](uint32_t bar) {
+            __syncwarp();
+            if (lane == 0) tc5::mbar_arrive(bar);
+        };
         uint32_t xphase = 0;
         auto pair_sync = [&]() {
-            tc5::mbar_arrive(bar_xch);
+            warp_arrive(bar_xch);
             const bool ok = wait_warp(bar_xch, xphase);
             xphase ^= 1u;
             return ok;
@@ -394,7 +399,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
                 *reinterpret_cast<uint4 *>(sm + OFF_Q8 + RAW_TILE + off) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
             }
             fused::fence_proxy_async();
-            tc5::mbar_arrive(bar_q_ready);
+            warp_arrive(bar_q_ready);
         }
         // fp32 row scales of the keys, read per tile by every thread (the same 1 KB for the whole CTA: L1 hits)
         const float *gks = p.k_scales + b * (p.scale_batch_stride / 4) + (size_t)kvh * p.cache_cap + p.row0;
@@ -448,7 +453,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
                 }
             }
             tc5::tc_fence_before();
-            tc5::mbar_arrive(bar_s_empty);                             // S is in registers: QK of the next tile may overwrite it
+            warp_arrive(bar_s_empty);                                  // S is in registers: QK of the next tile may overwrite it
             // the row's tile maximum: its threads meet through shared memory (double-buffered by tile parity)
             xch[((i & 1) * TPR + qt) * 128 + r] = tmax;
             if (!pair_sync()) { alive = false; break; }
@@ -500,10 +505,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_prefill_kernel(const __grid_
                 *reinterpret_cast<uint4 *>(sm + OFF_P16 + H_TILE + h_off(r, chunk)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
             }
             l = fmaf(l, alpha, lsum0 + lsum1);
-            tc5::mbar_arrive(bar_raw_empty(st));                       // done with the stage's scales
             fused::fence_proxy_async();
             tc5::tc_fence_before();
-            tc5::mbar_arrive(bar_p_full);
+            __syncwarp();
+            if (lane == 0) {
+                tc5::mbar_arrive(bar_raw_empty(st));                   // done with the stage's scales
+                tc5::mbar_arrive(bar_p_full);
+            }
         }
         // ---- output: O / l (rows without any key are exact zeros, lib/batched_attn_gpu.mojo:329-409); this thread
         // writes dims 32 qt .. 32 qt + 31 of its row
