@@ -456,7 +456,7 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
         try:
             S, T4 = 9, 16384 + 9
             caches = [make_layer_cache(torch, ops, dev, 1, NKV, T4, HD, 1004 + i) for i in range(NLAYERS)]
-            q = torch.randn((1, S, NH, HD), device=dev).to(torch.bfloat16)
+            q = torch.from_numpy(np.random.default_rng(4004 + rank).standard_normal((1, S, NH, HD), dtype=np.float32)).to(dev).to(torch.bfloat16)
             o = torch.zeros((1, S, NH, HD), dtype=torch.bfloat16, device=dev)
             al = []
             for k, v, ks, vs in caches:

@@ -146,22 +146,30 @@ static unsigned int *fault_word() {
     return cached[dev];
 }
 
+#ifndef NOMOS_COOP_LAST_K
+#define NOMOS_COOP_LAST_K 64
+#endif
+static constexpr int COOP_LAST_K = NOMOS_COOP_LAST_K;       // CTAs sharing a mid-sized unit merge
+
 struct Plan {
     int mt, row_groups, tile0, ntiles, splits, tiles_per_split, grows;
 };
 
-// Whether every CTA of a unit merges a share of the unit's rows (merge_coop) instead of the last one merging all of
-// them.  Worth it when the partials of a unit are large (a verify call: 84 KB; a 512-wide head: 600 KB through one SM
-// took several microseconds), allowed when the whole grid is resident at once (a CTA then waits for CTAs that are
-// running, not for ones that have no SM yet), the outputs take 8-byte stores and no peer exchange follows.
-static bool use_coop_merge(const AttnArgs &a, int splits, int arrivals, long ctas, int occupancy, int rows_per_unit, int hd) {
-    if (splits < 2 || splits > 64 || arrivals != splits || a.peer_world > 1) return false;
-    if (ctas > (long)device_info().sm_count * occupancy) return false;
-    // (at 84 KB -- nine splits of a verify call -- it measured a loss, 27.5 -> 34 us: every CTA then stays on its SM
-    // until the last one has arrived, which keeps the next launch's CTAs from starting under this launch's tail)
-    if ((long)splits * rows_per_unit * (hd + 2) * 4 < 256 * 1024) return false;
+// How many CTAs of a unit share its merge (0: the last one to arrive merges all of it).  The last K to arrive each
+// take 1/K of the rows once all have arrived; earlier arrivals leave at once.  Worth it when the partials of a unit
+// are large (a verify call: 84 KB, 4 us through one SM; a 512-wide head: 600 KB), allowed when the whole grid is
+// resident at once (a CTA then waits for CTAs that are running, not for ones that have no SM yet), the outputs take
+// 8-byte stores and no peer exchange follows.  Measured on the 9-split verify call (one launch after another):
+// K = 2: 27.6 us (as without), K = 4: 27.0, K = 9 (every CTA of the unit): 26.8 -- so K is the unit's CTA count.
+static int use_coop_merge(const AttnArgs &a, int splits, int arrivals, long ctas, int occupancy, int rows_per_unit, int hd) {
+    if (splits < 2 || splits > 64 || arrivals != splits || a.peer_world > 1) return 0;
+    if (ctas > (long)device_info().sm_count * occupancy) return 0;
     const bool al8 = ((reinterpret_cast<uintptr_t>(a.out) | reinterpret_cast<uintptr_t>(a.partial_out)) & 7) == 0 && (a.out_batch_stride & 3) == 0;
-    return al8;
+    if (!al8) return 0;
+    const long bytes = (long)splits * rows_per_unit * (hd + 2) * 4;
+    if (bytes >= 256 * 1024) return arrivals;
+    if (bytes >= 48 * 1024 && splits <= 12 && hd % 64 == 0) return std::min(arrivals, COOP_LAST_K);
+    return 0;
 }
 
 // Peer fields of a sequence-sharded call; returns where this rank's own merged rows go.
@@ -286,7 +294,7 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     p.splits = pl.splits;
     p.arrivals = pl.splits * DS;
     p.departures = p.counters ? p.counters + units : nullptr;
-    p.coop_merge = use_coop_merge(a, pl.splits, p.arrivals, (long)pl.splits * DS * units, occ, std::min(C::NSLOT, a.S * a.kvg), HD) ? 1 : 0;
+    p.coop_merge = use_coop_merge(a, pl.splits, p.arrivals, (long)pl.splits * DS * units, occ, std::min(C::NSLOT, a.S * a.kvg), HD);
     p.partial_export = a.partial_out;
     if (float *own = fill_peer_params(p, a, pl.grows)) p.partial_export = own;
     p.early_rows = settled_rows(a);
@@ -499,7 +507,7 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     p.splits = pl.splits;
     p.arrivals = pl.splits;
     p.departures = p.counters ? p.counters + units : nullptr;
-    p.coop_merge = (!paged && use_coop_merge(a, pl.splits, p.arrivals, (long)pl.splits * units, /* one CTA per SM, whatever the plan assumes */ 1, std::min(NS, a.S * a.kvg), a.l_hd)) ? 1 : 0;
+    p.coop_merge = paged ? 0 : use_coop_merge(a, pl.splits, p.arrivals, (long)pl.splits * units, /* one CTA per SM, whatever the plan assumes */ 1, std::min(NS, a.S * a.kvg), a.l_hd);
     p.partial_export = a.partial_out;
     if (float *own = fill_peer_params(p, a, pl.grows)) p.partial_export = own;
     p.early_rows = paged ? 0 : settled_rows(a);

@@ -119,7 +119,7 @@ struct KParams {
     int splits;
     int arrivals;                   // CTAs per unit that arrive before the merge: splits x head-dim slices
     unsigned long long *departures; // coop_merge: one more tagged word per unit, counting the CTAs that finished their share
-    int coop_merge;                 // 1: every CTA of a unit merges a share of the unit's rows once all have arrived (the whole
+    int coop_merge;                 // K > 0: the last K CTAs of a unit to arrive each merge a share of the unit's rows once all have arrived (the whole
                                     //    grid is resident at once, so waiting for the others cannot starve them)
     float *partial_export;          // optional exported (o, m, l) per row, m in natural-log units
     int early_rows;                 // window rows [0, early_rows) may be read before griddepcontrol.wait
@@ -322,13 +322,14 @@ __device__ __noinline__ void merge_small(const SmallMergeArgs a, int tid) {
 // row's weights are worked out across the warp -- lane k fetches (m, l) of split k, two warp reductions
 // give the reference and the denominator -- and handed round by shuffle.  Up to 52 independent loads per
 // thread, one round trip to L2 per round; verify needs a single round.
-template <int HD, int GC>
-__device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int nthr) {
-    constexpr int EL = 4, HP = HD / 2;
+// [begin, end) restricts the call to a share of the unit's pairs (both multiples of 32: a warp's pairs share a row).
+template <int HD, int GC, int EL = 4>
+__device__ __noinline__ void merge_medium(const SmallMergeArgs a, int tid, int nthr, int begin = 0, int end = 1 << 30) {
+    constexpr int HP = HD / 2;
     static_assert(HP % 32 == 0 && GC <= 32, "a warp's pairs share a row; one lane per split");
-    const int total = a.nrows * HP, G = a.G, lane = tid & 31;
+    const int total = min(end, a.nrows * HP), G = a.G, lane = tid & 31;
 #pragma unroll 1
-    for (int e0 = tid; e0 < total; e0 += EL * nthr) {
+    for (int e0 = begin + tid; e0 < total; e0 += EL * nthr) {
         const float *base[EL];
         long grow[EL];
         int hrow[EL], dd[EL];
@@ -450,11 +451,11 @@ __device__ __forceinline__ unsigned long long ld_acquire_gpu(const unsigned long
 // (m, l) and partial outputs of those pairs (a second round for splits 32..63), so every load of the warp is in
 // flight at once; the reference, the denominator and the sums are warp reductions.
 template <int HD>
-__device__ __noinline__ void merge_coop(const SmallMergeArgs a, int share, int tid, int nthr) {
+__device__ __noinline__ void merge_coop(const SmallMergeArgs a, int share, int nshares, int tid, int nthr) {
     constexpr int EL = 4, HP = HD / 2;
     const int G = a.G, lane = tid & 31, warp = tid >> 5, nwarp = nthr >> 5;
     const int total = a.nrows * HP;
-    const int per = (total + G - 1) / G;
+    const int per = (total + nshares - 1) / nshares;
     const int begin = share * per, end = min(total, begin + per);
 #pragma unroll 1
     for (int e0 = begin + warp * EL; e0 < end; e0 += nwarp * EL) {
@@ -524,18 +525,21 @@ __device__ __noinline__ void merge_coop(const SmallMergeArgs a, int share, int t
 }
 
 // The cooperative form of the unit merge, out of line (it runs once per CTA; p is the kernels' __grid_constant__
-// parameter block): arrive, wait -- with a time limit -- until every CTA of the unit has arrived, merge this CTA's
-// share, leave.  The whole grid is resident at once (host-checked), so the CTAs waited for are running.
+// parameter block).  The last K = p.coop_merge CTAs of the unit to arrive each merge 1/K of its rows: a CTA that
+// arrives earlier leaves at once (its SM is free for the next launch), one of the K waits -- with a time limit --
+// until every CTA of the unit has arrived, merges its share and leaves through a second tagged word; the last one
+// out resets both words.  The whole grid is resident at once (host-checked), so the CTAs waited for are running.
 template <int NSLOT, int HD, int NTHR>
 __device__ __noinline__ void coop_merge_unit(const KParams &p, int b, int kvh, int rg) {
     __shared__ int s_go, s_share;
     unsigned long long *ctr = p.counters + ((size_t)blockIdx.z * gridDim.y + blockIdx.y);
+    const int K = min(p.coop_merge, p.arrivals);
     __syncthreads();                      // all partial stores of this CTA are issued
     if (threadIdx.x == 0) {
         const int arrived = tagged_arrive(ctr);
-        s_share = arrived - 1;
+        s_share = arrived - (p.arrivals - K) - 1;
         bool all = arrived == p.arrivals;
-        if (arrived > 0 && !all) {
+        if (s_share >= 0 && !all) {
             unsigned long long t0, t1;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
             for (;;) {
@@ -546,17 +550,29 @@ __device__ __noinline__ void coop_merge_unit(const KParams &p, int b, int kvh, i
                 if (t1 - t0 > 1000000000ull) { atomicOr(p.fault, 1u); break; }
             }
         }
-        s_go = all ? 1 : 0;
+        s_go = (s_share >= 0 && all) ? 1 : 0;
     }
     __syncthreads();
     if (!s_go) return;
     SmallMergeArgs sa;
     small_merge_args<NSLOT, HD, NTHR>(p, b, kvh, rg, sa);
-    merge_coop<HD>(sa, s_share, threadIdx.x, NTHR);
+    if (p.splits <= 12) {
+        // few splits: the no-staging merge of verify calls on this CTA's share of the pairs, one pair per thread and
+        // round (shares are whole warps' worth of pairs, so a warp's pairs still share a row)
+        const int total = sa.nrows * (HD / 2);
+        const int per = ((total + K - 1) / K + 31) / 32 * 32;
+        const int begin = s_share * per, end = min(total, begin + per);
+        if (p.splits <= 4) merge_medium<HD, 4, 1>(sa, threadIdx.x, NTHR, begin, end);
+        else if (p.splits <= 8) merge_medium<HD, 8, 1>(sa, threadIdx.x, NTHR, begin, end);
+        else if (p.splits <= 10) merge_medium<HD, 10, 1>(sa, threadIdx.x, NTHR, begin, end);
+        else merge_medium<HD, 12, 1>(sa, threadIdx.x, NTHR, begin, end);
+    } else {
+        merge_coop<HD>(sa, s_share, K, threadIdx.x, NTHR);
+    }
     __syncthreads();                      // this CTA's share is stored
     if (threadIdx.x == 0) {
         unsigned long long *dep = p.departures + ((size_t)blockIdx.z * gridDim.y + blockIdx.y);
-        if (tagged_arrive(dep) == p.arrivals) {                        // the last one out leaves both words clean
+        if (tagged_arrive(dep) == K) {                                  // the last one out leaves both words clean
             *dep = ARRIVE_TAG << 16;
             *ctr = ARRIVE_TAG << 16;
         }

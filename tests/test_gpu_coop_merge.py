@@ -3,8 +3,10 @@
 When the partials of one unit of work (a KV head's query rows) are large and the whole grid is resident at once,
 the library lets every CTA of the unit merge a share of the output rows once all of them have arrived, instead of
 leaving the merge to the CTA that arrives last.  The launcher takes that route when
-    2 <= splits <= 64,  splits x rows per unit x (head_dim + 2) x 4 bytes >= 256 KiB,
-    the CTAs of the launch fit the SMs at once,  the outputs are 8-byte aligned.
+    2 <= splits <= 64,  splits x rows per unit x (head_dim + 2) x 4 bytes >= 48 KiB,
+    the CTAs of the launch fit the SMs at once,  the outputs are 8-byte aligned;
+with at most 12 splits the shares are merged by the no-staging merge of verify calls, with more by the
+lane-per-split merge.
 The cases below are sized to meet those conditions on both kernels; each runs several calls in a row on one
 workspace (the arrival and departure words must come back to their idle state) and checks every output, and the
 exported partials, against the oracle's exact attention.
@@ -27,6 +29,9 @@ CASES = [
     ("i8", 256, 2, 8, 1, 8192, 64, 0),                      # 64 x 8 x 258 x 4 = 528 KB
     ("i8", 128, 4, 2, 9, 16384, 32, ops.TCGEN05_ALWAYS),    # 32 x 18 x 130 x 4 = 300 KB, tcgen05 kernel (verify rows)
     ("i8", 128, 4, 2, 9, 16384, 32, ops.NO_TCGEN05),        # the same rows on the mma.sync kernel
+    ("i8", 128, 16, 2, 9, 16393, 9, ops.TCGEN05_ALWAYS),    # the verify configuration: 9 x 18 x 130 x 4 = 84 KB, few splits
+    ("i8", 128, 16, 2, 9, 16393, 9, ops.NO_TCGEN05),
+    ("i4b32", 256, 4, 8, 1, 4000, 12, 0),                   # 12 x 8 x 258 x 4 = 99 KB, few splits, wide head, ragged
 ]
 
 
@@ -34,8 +39,9 @@ CASES = [
 @pytest.mark.parametrize("out_type", [ops.F32, ops.BF16])
 def test_cooperative_merge_matches_oracle_on_repeated_calls(oracle, fmt, hd, nkv, kvg, S, T, splits, flags, out_type):
     sm = torch.cuda.get_device_properties(0).multi_processor_count
-    assert splits * nkv <= sm, "the case must keep its whole grid resident"
-    assert splits * min(S * kvg, 32) * (hd + 2) * 4 >= 256 * 1024
+    if flags != ops.NO_TCGEN05 or S == 1:     # (verify rows on the mma.sync kernel run as 8-row groups: whichever merge they get)
+        assert splits * nkv <= sm, "the case must keep its whole grid resident"
+        assert splits * min(S * kvg, 32) * (hd + 2) * 4 >= 48 * 1024
     rng = np.random.default_rng(hd * 7 + T + splits)
     nh = nkv * kvg
     c = build_cache(fmt, rng, T, nkv, hd, outliers=(hd == 128))
