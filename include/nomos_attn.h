@@ -292,6 +292,10 @@ typedef struct nomos_attn_args {
 /* flags bit: take the tcgen05 kernel for every call it supports, also where the library's
  * own choice would be the mma.sync kernel (for comparing the two). */
 #define NOMOS_ATTN_TCGEN05_ALWAYS 8
+/* flags bit: never run the splits of a KV head as a thread-block cluster (the mma.sync kernel then merges
+ * them through the workspace and an arrival counter, as it does whenever a cluster does not fit; same
+ * results; for comparing the two). */
+#define NOMOS_ATTN_NO_CLUSTER 16
 
 /* K / V / Q producer epilogue fused with the quantising append: from the raw projection rows of
  * n_s new tokens to cache bytes in one launch.  Replaces the sequence of lib/gemma4_layer.mojo:326-340
@@ -370,6 +374,11 @@ int64_t nomos_attn_workspace_bytes(const nomos_attn_args_t *args);
  * on the mma.sync kernel, as row groups).  No reference counterpart (lib/attention_gpu_int8.mojo has a single kernel
  * chain). */
 int32_t nomos_attn_kernel_choice(const nomos_attn_args_t *args);
+/* What the calling thread's last decode / verify launch did (for logs and tests; no counterpart in the
+ * reference): kernel 0 = mma.sync, 1 = tcgen05; sequence splits per KV head; how the splits were merged --
+ * 0 one split, 1 by the last CTA to arrive (workspace + arrival counter), 2 cooperatively by all CTAs of the
+ * head, 3 inside a thread-block cluster through distributed shared memory.  Any pointer may be NULL. */
+int32_t nomos_attn_last_launch(int32_t *kernel, int32_t *splits, int32_t *merge_route);
 /* Run it. */
 int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *args);
 

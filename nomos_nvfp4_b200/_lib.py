@@ -92,6 +92,7 @@ PROTOTYPES = {
     "nomos_attn_prefill_batched_bf16": (i32, [vp] + [u64] * 9 + [i32] * 8),
     "nomos_attn_workspace_bytes": (i64, [C.POINTER(AttnArgs)]),
     "nomos_attn_kernel_choice": (i32, [C.POINTER(AttnArgs)]),
+    "nomos_attn_last_launch": (i32, [C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "nomos_attn_fused": (i32, [vp, C.POINTER(AttnArgs)]),
     "nomos_attn_fused_static_ws": (i32, [vp, C.POINTER(AttnArgs)]),
     "nomos_attn_merge_partials": (i32, [vp, u64, i32, i32, i32, u64, i32]),

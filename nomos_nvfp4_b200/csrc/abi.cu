@@ -478,6 +478,7 @@ static int unpack_args(const nomos_attn_args_t *u, AttnArgs &a, const char *who)
     a.no_tma = (u->flags & NOMOS_ATTN_NO_TMA) ? 1 : 0;
     a.no_tcgen05 = (u->flags & NOMOS_ATTN_NO_TCGEN05) ? 1 : 0;
     a.tcgen05_always = (u->flags & NOMOS_ATTN_TCGEN05_ALWAYS) ? 1 : 0;
+    a.no_cluster = (u->flags & NOMOS_ATTN_NO_CLUSTER) ? 1 : 0;
     return NOMOS_OK;
 }
 
@@ -497,6 +498,14 @@ NOMOS_EXPORT int32_t nomos_attn_kernel_choice(const nomos_attn_args_t *args) {
     if ((rc = check_attn_geometry("nomos_attn_kernel_choice", a.nh, a.nkv, a.l_hd, a.cache_hd, a.kvg))) return rc;
     if (a.batch <= 0 || a.S <= 0 || a.klen <= 0 || a.cache_cap <= 0 || a.win_start < 0) { set_error("nomos_attn_kernel_choice: bad batch/S/klen/cache_cap/win_start"); return NOMOS_EBADARG; }
     return attn_kernel_choice(a);
+}
+
+NOMOS_EXPORT int32_t nomos_attn_last_launch(int32_t *kernel, int32_t *splits, int32_t *merge_route) {
+    const LaunchInfo li = attn_last_launch_info();
+    if (kernel) *kernel = li.kernel;
+    if (splits) *splits = li.splits;
+    if (merge_route) *merge_route = li.merge_route;
+    return NOMOS_OK;
 }
 
 NOMOS_EXPORT int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *args) {

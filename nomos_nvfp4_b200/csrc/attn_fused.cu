@@ -151,6 +151,13 @@ static unsigned int *fault_word() {
 #endif
 static constexpr int COOP_LAST_K = NOMOS_COOP_LAST_K;       // CTAs sharing a mid-sized unit merge
 
+static thread_local LaunchInfo t_last_launch = {0, 0, 0};
+static void note_launch(int kernel, const KParams &p) {
+    t_last_launch.kernel = kernel;
+    t_last_launch.splits = p.splits;
+    t_last_launch.merge_route = p.splits <= 1 ? 0 : p.cluster_merge ? 3 : p.coop_merge ? 2 : 1;
+}
+
 struct Plan {
     int mt, row_groups, tile0, ntiles, splits, tiles_per_split, grows;
 };
@@ -262,6 +269,43 @@ static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp, int d
     return pl;
 }
 
+// Whether a launch of this instance with `splits` CTAs per unit can run its units as thread-block clusters
+// (cluster x = splits, at most 16; more than 8 needs the non-portable size) with every cluster of the grid
+// resident at once.  Answered by the occupancy calculator once per (device, splits) and remembered; a launch
+// that the driver refuses switches the route off for the instance.
+template <int FMT, int HD, int MT, int DS, int QS>
+static bool cluster_route(int splits, long clusters) {
+    using C = Cfg<FMT, HD, MT, DS, QS>;
+    static std::mutex mu;
+    static int max_clusters[64][17];          // 0 = not asked yet, -1 = no
+    static bool off = false;
+    if (!C::CLUSTER_OK || splits < 2 || splits > 16) return false;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (clusters < 0) { off = true; return false; }           // (called with -1 after a refused launch)
+    if (off) return false;
+    int &n = max_clusters[dev][splits];
+    if (n == 0) {
+        n = -1;
+        if (splits <= 8 || cudaFuncSetAttribute(attn_fused_kernel<FMT, HD, MT, DS, QS>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = splits; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(splits, 1, 1); cfg.blockDim = dim3(C::NW * 32); cfg.dynamicSmemBytes = C::SMEM_BYTES;
+            cfg.attrs = at; cfg.numAttrs = 1;
+            int got = 0;
+            if (cudaOccupancyMaxActiveClusters(&got, attn_fused_kernel<FMT, HD, MT, DS, QS>, &cfg) == cudaSuccess && got > 0) n = got;
+            else cudaGetLastError();
+        } else {
+            cudaGetLastError();
+        }
+    }
+    return n > 0 && clusters <= n;
+}
+
 template <int FMT, int HD, int MT, int DS = 1, int QS = 1>
 static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *ws_needed) {
     using C = Cfg<FMT, HD, MT, DS, QS>;
@@ -297,6 +341,16 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     p.coop_merge = use_coop_merge(a, pl.splits, p.arrivals, (long)pl.splits * DS * units, occ, std::min(C::NSLOT, a.S * a.kvg), HD);
     p.partial_export = a.partial_out;
     if (float *own = fill_peer_params(p, a, pl.grows)) p.partial_export = own;
+    // splits of a unit as one thread-block cluster merging through distributed shared memory: plain calls only
+    // (final output, no export, no peer exchange), every cluster resident at once, and at least four query rows per
+    // unit.  Measured against the arrival-counter merge, launches back to back: 8 KV heads x 4 group heads, 9
+    // splits, 16384 keys 15.4 against 17.1 us; 4 x 8, 16 splits, 4096 keys 10.7 against 12.8 us; but 12 or 15 KV
+    // heads x 2 group heads, 9 splits, 32768 keys 23.1 / 26.3 against 22.8 / 26.1 us (a two-row merge is one L2
+    // round trip, and a cluster only starts when nine SMs of one GPC are free).  On B200 at most 15 clusters of 7 to
+    // 9 CTAs of this kernel are resident (74 of 2, 33 of 4, 7 of 11 to 16), so 16 KV heads x 9 splits never qualify.
+    p.cluster_merge = (!a.no_cluster && pl.splits > 1 && a.partial_out == nullptr && a.peer_world <= 1 && a.out != nullptr &&
+                       std::min(C::NSLOT, a.S * a.kvg) >= 4 && cluster_route<FMT, HD, MT, DS, QS>(pl.splits, units)) ? 1 : 0;
+    if (p.cluster_merge) p.coop_merge = 0;
     p.early_rows = settled_rows(a);
     p.new_k = a.new_k; p.new_v = a.new_v;
     p.n_new = a.new_k ? a.n_new : 0; p.new_stride = a.new_stride; p.new_base_pos = a.new_base_pos;
@@ -344,14 +398,26 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     // (another attention call of this library) the grid is set up while the predecessor drains and
     // blocks in griddepcontrol.wait before its first global access; after any other kernel it
     // starts when that kernel has completed, as usual.
-    cudaLaunchAttribute pdl[1];
+    cudaLaunchAttribute pdl[2];
     pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    pdl[1].id = cudaLaunchAttributeClusterDimension;
+    pdl[1].val.clusterDim.x = pl.splits; pdl[1].val.clusterDim.y = 1; pdl[1].val.clusterDim.z = 1;
     cudaLaunchConfig_t mcfg = {};
     mcfg.gridDim = grid; mcfg.blockDim = dim3(C::NW * 32); mcfg.dynamicSmemBytes = C::SMEM_BYTES; mcfg.stream = st;
-    mcfg.attrs = pdl; mcfg.numAttrs = 1;
+    mcfg.attrs = pdl; mcfg.numAttrs = p.cluster_merge ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&mcfg, attn_fused_kernel<FMT, HD, MT, DS, QS>, p, tm);
+    if (e != cudaSuccess && p.cluster_merge) {
+        // the driver refused the cluster shape: this instance goes back to the arrival-counter merge for good
+        cudaGetLastError();
+        cluster_route<FMT, HD, MT, DS, QS>(0, -1);
+        p.cluster_merge = 0;
+        p.coop_merge = use_coop_merge(a, pl.splits, p.arrivals, (long)pl.splits * DS * units, occ, std::min(C::NSLOT, a.S * a.kvg), HD);
+        mcfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&mcfg, attn_fused_kernel<FMT, HD, MT, DS, QS>, p, tm);
+    }
     if (e != cudaSuccess) { set_error("attn_fused launch: %s", cudaGetErrorString(e)); return NOMOS_ECUDA; }
+    note_launch(0, p);
     return NOMOS_OK;
 }
 
@@ -539,6 +605,7 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     cfg.attrs = pdl; cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, tc5::attn_tc5_kernel<NS>, p, tm);
     if (e != cudaSuccess) { set_error("attn_tc5 launch: %s", cudaGetErrorString(e)); return NOMOS_ECUDA; }
+    note_launch(1, p);
     return NOMOS_OK;
 }
 
@@ -706,6 +773,7 @@ long attn_peer_mailbox_bytes(int world, long grows, int l_hd) {
     return attn_peer_mailbox_rows_bytes(world, grows, l_hd) + 2L * world * grows * 8;
 }
 
+LaunchInfo attn_last_launch_info() { return t_last_launch; }
 int attn_kernel_choice(const AttnArgs &a) { return prefill_eligible(a) ? 2 : (tc5_eligible(a) && !prefers_mma(a) ? 1 : 0); }
 
 long attn_workspace_bytes(const AttnArgs &a) {

@@ -5,6 +5,7 @@
 #include <type_traits>
 
 #include <cuda.h>             // CUtensorMap (type only: the encoder is resolved at run time)
+#include <cooperative_groups.h>
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -89,6 +90,10 @@ struct Cfg {
     static constexpr int SCALES_BYTES = NW * NSTAGE * 2 * SC_BYTES;
     static constexpr int MERGE_BYTES = NW * NSLOT * (HDV + 2) * 4;
     static constexpr int REGION0_BYTES = ((TILES_BYTES > MERGE_BYTES ? TILES_BYTES : MERGE_BYTES) + 15) / 16 * 16;
+    // cluster merge: the CTA's own merged rows [NSLOT][HD+2] sit behind the warps' rows, where the other CTAs of the
+    // cluster read them through distributed shared memory
+    static constexpr int CPART_OFF = (MERGE_BYTES + 15) / 16 * 16;
+    static constexpr bool CLUSTER_OK = DS == 1 && CPART_OFF + NSLOT * (HD + 2) * 4 <= REGION0_BYTES;
     static constexpr int BAR_BYTES = NW * NSTAGE * 8;
     static constexpr int XCH_BYTES = NW * XCH_WARP_BYTES;                      // partial logits: [quad][tile parity][warp of the quad][MT*8][32 lanes] fp32
     static constexpr int SMEM_BYTES = 1024 + REGION0_BYTES + SCALES_BYTES + Q_BYTES + SLOT_BYTES + APPEND_BYTES + BAR_BYTES + XCH_BYTES;
@@ -121,6 +126,8 @@ struct KParams {
     unsigned long long *departures; // coop_merge: one more tagged word per unit, counting the CTAs that finished their share
     int coop_merge;                 // K > 0: the last K CTAs of a unit to arrive each merge a share of the unit's rows once all have arrived (the whole
                                     //    grid is resident at once, so waiting for the others cannot starve them)
+    int cluster_merge;              // 1: the splits of a unit are the CTAs of one thread-block cluster; they merge through
+                                    //    distributed shared memory (no partials in device memory, no arrival word)
     float *partial_export;          // optional exported (o, m, l) per row, m in natural-log units
     int early_rows;                 // window rows [0, early_rows) may be read before griddepcontrol.wait
     // fused quantize-on-write: the last n_new keys of the window are given as fp32 rows
@@ -842,6 +849,58 @@ __device__ __noinline__ void peer_exchange_and_merge(const KParams &p, int b, in
 
 // In-kernel tail of every attention CTA: the split merge and, on a sequence-sharded call, the exchange with the
 // other GPUs' shards.
+// The split merge when a unit's splits are the CTAs of one thread-block cluster (grid x = splits = cluster x).
+// Every CTA has left its own merged rows (o[HD], m, l per slot, base-2 m) at `cpart` in its shared memory; after the
+// cluster barrier CTA r takes dims [r * per, r * per + per) of every slot, reads the G rows' (m, l) and its dims
+// from the peers' shared memory, and writes the normalised output.  A second cluster barrier keeps every CTA's
+// shared memory alive until all have read it.  Both are hardware barriers over CTAs that are co-scheduled by
+// construction (a cluster starts as a whole); no CTA leaves the kernel before them.
+template <int NSLOT, int HD, int NTHR>
+__device__ __noinline__ void cluster_merge_unit(const KParams &p, float *cpart, int b, int kvh, int rg) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cl = cg::this_cluster();
+    const int G = (int)cl.num_blocks(), R = (int)cl.block_rank();
+    cl.sync();
+    const int first = rg * NSLOT;
+    const int nrows = min(NSLOT, p.S * p.kvg - first);
+    const int per = (HD + G - 1) / G;
+    for (int item = threadIdx.x; item < nrows * per; item += NTHR) {
+        const int sl = item / per, d = R * per + (item - sl * per);
+        if (d >= HD) continue;
+        float mi[16], li[16], oi[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (i < G) {
+                const float *row = cl.map_shared_rank(cpart, i) + (size_t)sl * (HD + 2);
+                mi[i] = row[HD]; li[i] = row[HD + 1]; oi[i] = row[d];
+            } else {
+                mi[i] = 0.0f; li[i] = 0.0f; oi[i] = 0.0f;
+            }
+        }
+        float m = -CUDART_INF_F;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            mi[i] = li[i] > 0.0f ? mi[i] : -CUDART_INF_F;              // a split that saw no key (or no such split)
+            m = fmaxf(m, mi[i]);
+        }
+        if (m == -CUDART_INF_F) m = 0.0f;
+        float l = 0.0f, o = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float w = ex2f(mi[i] - m);
+            l = fmaf(w, li[i], l);
+            o = fmaf(w, oi[i], o);
+        }
+        const int idx = first + sl;
+        const int r = div_kvg(p, idx);
+        const float v = l > 0.0f ? o / l : 0.0f;
+        const long oidx = b * p.out_batch_stride + ((long)r * p.nh + kvh * p.kvg + (idx - r * p.kvg)) * HD + d;
+        if (p.out_type == ET_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[oidx] = __float2bfloat16_rn(v);
+        else reinterpret_cast<float *>(p.out)[oidx] = v;
+    }
+    cl.sync();
+}
+
 template <int NSLOT, int HD, int NTHR, int GB = 8>
 __device__ __forceinline__ void merge_splits_in_kernel(const KParams &p, uint8_t *scratch, int b, int kvh, int rg) {
     const bool merged = merge_unit_splits<NSLOT, HD, NTHR, GB>(p, scratch, b, kvh, rg);
@@ -1575,7 +1634,9 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS, QS>::NW * 32)
 #pragma unroll
             for (int w = 0; w < NQ; ++w) o += wgt[w] * mbuf[((size_t)(w * QS + sj) * C::NSLOT + sl) * (HDV + 2) + d];
             if (p.write_partial) {
-                p.partial[((size_t)split * p.grows + grow) * (HD + 2) + dsl * HDV * QS + dq] = o;
+                float *dst = (C::CLUSTER_OK && p.cluster_merge) ? reinterpret_cast<float *>(pipe + C::CPART_OFF) + (size_t)sl * (HD + 2)
+                                                                : p.partial + ((size_t)split * p.grows + grow) * (HD + 2);
+                dst[dsl * HDV * QS + dq] = o;
             } else {
                 const float v = lstar > 0.0f ? o / lstar : 0.0f;
                 const long oi = b * p.out_batch_stride + ((long)r * p.nh + kvh * p.kvg + j) * HD + dsl * HDV * QS + dq;
@@ -1584,9 +1645,16 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS, QS>::NW * 32)
             }
         }
         if (p.write_partial && threadIdx.x == 0 && dsl == 0) {     // every slice computes the same (m, l)
-            float *pr = p.partial + ((size_t)split * p.grows + grow) * (HD + 2);
+            float *pr = (C::CLUSTER_OK && p.cluster_merge) ? reinterpret_cast<float *>(pipe + C::CPART_OFF) + (size_t)sl * (HD + 2)
+                                                           : p.partial + ((size_t)split * p.grows + grow) * (HD + 2);
             pr[HD] = p.export_nat ? mstar * LN2 : mstar;
             pr[HD + 1] = lstar;
+        }
+    }
+    if constexpr (C::CLUSTER_OK) {
+        if (p.cluster_merge) {
+            cluster_merge_unit<C::NSLOT, HD, NWARP * 32>(p, reinterpret_cast<float *>(pipe + C::CPART_OFF), b, kvh, rg);
+            return;
         }
     }
     merge_splits_in_kernel<C::NSLOT, HD, NWARP * 32>(p, pipe, b, kvh, rg);

@@ -71,6 +71,7 @@ struct AttnArgs {
     int d0_set, d0;
     int force_splits;       // 0 = choose; >0 = use exactly this many splits (tests)
     int no_tma;             // 1: keep every tile on the cp.async path
+    int no_cluster;         // 1: never run a unit's splits as a thread-block cluster
     int no_tcgen05;         // 1: never take the tcgen05 kernel
     int tcgen05_always;     // 1: take the tcgen05 kernel whenever it supports the call
     int settled_cache;      // 1: rows older than the S query rows may be read before the stream predecessor completes
@@ -82,6 +83,11 @@ struct AttnArgs {
 long attn_peer_mailbox_rows_bytes(int world, long grows, int l_hd);
 long attn_peer_mailbox_bytes(int world, long grows, int l_hd);
 long attn_workspace_bytes(const AttnArgs &a);
+// What the last attention launch of the calling thread did: sequence splits per unit and how they were merged
+// (0: one split, nothing to merge; 1: by the last CTA to arrive; 2: cooperatively by the unit's CTAs; 3: in a
+// thread-block cluster through distributed shared memory).
+struct LaunchInfo { int kernel, splits, merge_route; };
+LaunchInfo attn_last_launch_info();
 int attn_kernel_choice(const AttnArgs &a);     // 2: the query-major prefill kernel, 1: the tcgen05 decode / verify kernel, 0: the mma.sync kernel
 int launch_attn_fused(cudaStream_t st, const AttnArgs &a);
 long attn_paged_workspace_bytes(const AttnArgs &a);

@@ -23,6 +23,7 @@ SETTLED_CACHE = 1            # nomos_attn_args_t.flags bit, see include/nomos_at
 NO_TMA = 2                   # nomos_attn_args_t.flags bit: cp.async copies only
 NO_TCGEN05 = 4               # nomos_attn_args_t.flags bit: stay on the mma.sync kernel
 TCGEN05_ALWAYS = 8           # nomos_attn_args_t.flags bit: tcgen05 kernel wherever it supports the call
+NO_CLUSTER = 16              # nomos_attn_args_t.flags bit: splits never merged through a thread-block cluster
 
 
 class NomosError(RuntimeError):
@@ -270,6 +271,14 @@ def attn_workspace_bytes(args: AttnArgs) -> int:
     if n < 0:
         _check(int(n))
     return int(n)
+
+
+def attn_last_launch() -> tuple[int, int, int]:
+    """(kernel, splits, merge route) of this thread's last decode / verify launch; routes: 0 one split, 1 last CTA,
+    2 cooperative, 3 thread-block cluster."""
+    k, n, r = C.c_int32(0), C.c_int32(0), C.c_int32(0)
+    _check(_lib.lib().nomos_attn_last_launch(C.byref(k), C.byref(n), C.byref(r)))
+    return k.value, n.value, r.value
 
 
 def attn_kernel_choice(args: AttnArgs) -> int:
