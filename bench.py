@@ -529,6 +529,45 @@ def extras(torch, dist, ops, dev, rank, world, iters: int = 200, only=None) -> d
             del cache
         except Exception as e:
             out["prefill_s2048_i8"] = {"error": repr(e)}
+    # chunked prefill: a chunk of 2048 new positions behind a cached prefix of 6144 (keys 0..8191 in the int8 cache),
+    # the call an engine makes per prefill chunk (the reference's prefix operator, lib/attention_gpu_int8.mojo:844-887,
+    # which needs a [nkv, S*kvg, 8192] score scratch for it); and one square prefill of 8192 positions
+    if selected("prefill_chunk2048_prefix6144_i8"):
+        try:
+            Sp, Tp = 2048, 8192
+            cache = make_layer_cache(torch, ops, dev, 1, NKV, Tp, HD, 1406)
+            qh = np.random.default_rng(1406).standard_normal((1, Sp, NH, HD), dtype=np.float32)
+            q = torch.from_numpy(qh).to(dev).to(torch.bfloat16)
+            o = torch.zeros((1, Sp, NH, HD), dtype=torch.bfloat16, device=dev)
+            k, v, ks, vs = cache
+            a = ops.make_args(q=q, k_cache=k, v_cache=v, k_scales=ks, v_scales=vs, out=o, kv_fmt=ops.KV_I8, q_type=ops.BF16,
+                              out_type=ops.BF16, S=Sp, nh=NH, nkv=NKV, kvg=NH // NKV, l_hd=HD, cache_hd=HD, cache_cap=Tp, klen=Tp,
+                              softmax_scale=SOFTMAX_SCALE)
+            wsb = ops.attn_workspace_bytes(a)
+            ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+            a.workspace, a.ws_bytes = ws.data_ptr(), wsb
+            us = time_call(torch, lambda: ops.attn_fused(stream, a), max(10, iters // 16))
+            keys = sum(Tp - Sp + s + 1 for s in range(Sp))             # keys each query position attends
+            flops = 4.0 * NH * HD * keys
+            res = {"us": round(us, 1), "TFLOPs_causal": round(flops / us / 1e6, 1), "kernel_choice": ops.attn_kernel_choice(a),
+                   "tensor_peak_fraction": round(flops / us / 1e6 / measured_peak_tflops(), 4)}
+            if rank == 0:
+                from oracle import oracle as orc
+                o32 = torch.zeros((1, Sp, NH, HD), dtype=torch.float32, device=dev)
+                a.out, a.out_type = o32.data_ptr(), ops.F32
+                ops.attn_fused(stream, a); torch.cuda.synchronize()
+                got = o32[0].cpu().numpy()
+                hk, hv, hks, hvs = (t[0].cpu().numpy() for t in cache)
+                worst = 0.0
+                for srow in (0, 63, 64, 1000, 2047):
+                    want = orc.attn_exact(orc.bf16_round(qh[0, srow:srow + 1]), hk, hv, hks, hvs, orc.KV_I8, NH, NKV, HD, HD, Tp, S=1,
+                                          query_base_pos=Tp - Sp + srow, softmax_scale=float(SOFTMAX_SCALE))
+                    worst = max(worst, rel_err(got[srow], want[0]))
+                res["parity_rel_err_sampled_rows"] = float(f"{worst:.3e}")
+            out["prefill_chunk2048_prefix6144_i8"] = res
+            del cache, ws
+        except Exception as e:
+            out["prefill_chunk2048_prefix6144_i8"] = {"error": repr(e)}
     # configuration 3: sliding-window layer, ring of 1024 at position 8191, int4 block-32, fused append
     if selected("c3_swa_ring_i4b32_fused_append"):
         try:
