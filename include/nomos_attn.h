@@ -386,10 +386,11 @@ int32_t nomos_attn_fused(void *stream, const nomos_attn_args_t *args);
  * in_bytes from host_in (pinned) to dev_in on the stream, runs nomos_attn_fused(stream, args) -- args
  * point into dev_in for the query and the new K/V rows, and at dev_out for the output --, copies
  * out_bytes from dev_out back to host_out (pinned) and synchronises the stream.  The KV cache stays
- * resident on the device.  Either byte count may be 0.  When both host buffers are pinned and addressable
- * by the GPU (cudaHostAlloc / cudaHostRegister memory) and at most 64 KB each, the two copies are skipped: the
- * kernel reads the query and the new rows from host memory and writes its output there directly, and dev_in /
- * dev_out are left untouched.  No counterpart in the reference (its decode
+ * resident on the device.  Either byte count may be 0.  When host_out is pinned and addressable by the GPU
+ * (cudaHostAlloc / cudaHostRegister memory) and at most 64 KB, the copy back is skipped: the kernel writes
+ * its output into host memory directly and dev_out is left untouched.  The inputs are always staged in dev_in
+ * (every CTA of the launch reads the query): by a small copy kernel when host_in is pinned, GPU-addressable,
+ * 16-byte aligned like dev_in and at most 64 KB, else by cudaMemcpyAsync.  No counterpart in the reference (its decode
  * loop keeps activations on the device; only tokens cross the bus): it exists so that a host-side
  * caller pays one library call per step instead of three runtime calls and a synchronise. */
 int32_t nomos_attn_fused_host(void *stream, const nomos_attn_args_t *args, uint64_t host_in, uint64_t dev_in,

@@ -536,6 +536,19 @@ static uint64_t device_view_of_host(uint64_t host) {
     return 0;
 }
 
+// Copies a step's inputs from GPU-addressable host memory to the device staging buffer: a few CTAs, each thread
+// moving 16 bytes at a time (the host lines are read uncached; the ragged tail goes byte by byte).  It lets the
+// grid launched behind it be set up at once (programmatic dependent launch): the attention kernel runs its set-up
+// and, with settled cache rows, its first tile requests while these bytes cross the bus, and waits for them in
+// griddepcontrol.wait.
+__global__ void __launch_bounds__(256) stage_in_kernel(const uint8_t *src, uint8_t *dst, long bytes) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    const long n16 = bytes / 16;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long)gridDim.x * blockDim.x)
+        reinterpret_cast<uint4 *>(dst)[i] = __ldcv(reinterpret_cast<const uint4 *>(src) + i);
+    if (blockIdx.x == 0 && threadIdx.x < bytes - n16 * 16) dst[n16 * 16 + threadIdx.x] = __ldcv(src + n16 * 16 + threadIdx.x);
+}
+
 NOMOS_EXPORT int32_t nomos_attn_fused_host(void *stream, const nomos_attn_args_t *args, uint64_t host_in, uint64_t dev_in,
                                            int64_t in_bytes, uint64_t host_out, uint64_t dev_out, int64_t out_bytes) {
     const char *who = "nomos_attn_fused_host";
@@ -544,20 +557,30 @@ NOMOS_EXPORT int32_t nomos_attn_fused_host(void *stream, const nomos_attn_args_t
     REQUIRE(out_bytes == 0 || (host_out && dev_out), "%s: null output staging pointer", who);
     cudaStream_t st = as_stream(stream);
     cudaError_t e = cudaSuccess;
-    // Small steps with pinned, GPU-addressable host buffers skip the two copies: the kernel reads the query and
-    // the new rows from host memory and writes its output there (the same bytes cross the bus, inside the one
-    // launch); the staging buffers are then left untouched.
-    if (args != nullptr && args->struct_bytes == sizeof(nomos_attn_args_t) && in_bytes <= (64 << 10) && out_bytes <= (64 << 10)) {
-        const uint64_t hin = in_bytes ? device_view_of_host(host_in) : 1, hout = out_bytes ? device_view_of_host(host_out) : 1;
-        if (hin && hout) {
+    // Inputs: every CTA of the attention launch reads the query, and a hundred and more CTAs reading a few hundred
+    // bytes each straight from host memory measured 20 us slower than one 24 KB transfer, so they are staged in
+    // device memory first -- by a small copy kernel when the host buffer is pinned, GPU-addressable, 16-byte aligned
+    // and at most 64 KB (the attention grid is set up behind it while the bytes cross the bus), else by the copy
+    // engine.
+    if (in_bytes) {
+        const uint64_t hin = (in_bytes <= (64 << 10) && ((host_in | dev_in) & 15) == 0) ? device_view_of_host(host_in) : 0;
+        if (hin) {
+            const int ctas = (int)std::min<long>(8, (in_bytes / 16 + 255) / 256 + 1);
+            stage_in_kernel<<<ctas, 256, 0, st>>>(reinterpret_cast<const uint8_t *>(ptr(hin)), static_cast<uint8_t *>(ptr(dev_in)), (long)in_bytes);
+            e = cudaGetLastError();
+        } else {
+            e = cudaMemcpyAsync(ptr(dev_in), ptr(host_in), (size_t)in_bytes, cudaMemcpyHostToDevice, st);
+        }
+    }
+    if (e != cudaSuccess) { set_error("%s: host-to-device copy: %s", who, cudaGetErrorString(e)); return NOMOS_ECUDA; }
+    // A small output in pinned, GPU-addressable host memory is written there by the kernel itself (a few posted
+    // stores per KV head across the bus) instead of by a third stream operation; dev_out is then left untouched.
+    if (args != nullptr && args->struct_bytes == sizeof(nomos_attn_args_t) && out_bytes > 0 && out_bytes <= (64 << 10) &&
+        args->out >= dev_out && args->out < dev_out + (uint64_t)out_bytes) {
+        const uint64_t hout = device_view_of_host(host_out);
+        if (hout) {
             nomos_attn_args_t z = *args;
-            const auto rebase = [](uint64_t p, uint64_t from, int64_t n, uint64_t to) {
-                return (n > 0 && p >= from && p < from + (uint64_t)n) ? to + (p - from) : p;
-            };
-            z.q = rebase(z.q, dev_in, in_bytes, hin);
-            z.new_k = rebase(z.new_k, dev_in, in_bytes, hin);
-            z.new_v = rebase(z.new_v, dev_in, in_bytes, hin);
-            z.out = rebase(z.out, dev_out, out_bytes, hout);
+            z.out = hout + (z.out - dev_out);
             const int rc = nomos_attn_fused(stream, &z);
             if (rc) return rc;
             e = cudaStreamSynchronize(st);
@@ -565,8 +588,6 @@ NOMOS_EXPORT int32_t nomos_attn_fused_host(void *stream, const nomos_attn_args_t
             return NOMOS_OK;
         }
     }
-    if (in_bytes) e = cudaMemcpyAsync(ptr(dev_in), ptr(host_in), (size_t)in_bytes, cudaMemcpyHostToDevice, st);
-    if (e != cudaSuccess) { set_error("%s: host-to-device copy: %s", who, cudaGetErrorString(e)); return NOMOS_ECUDA; }
     const int rc = nomos_attn_fused(stream, args);
     if (rc) return rc;
     if (out_bytes) e = cudaMemcpyAsync(ptr(host_out), ptr(dev_out), (size_t)out_bytes, cudaMemcpyDeviceToHost, st);
