@@ -391,9 +391,13 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
         }
     }
     dim3 grid(pl.splits * DS, a.nkv, a.batch * pl.row_groups);
-    // the warming pass of the query preparation pays when CTAs start ahead of their predecessor's end and the pass
-    // is short: a single wave, and not the 512-wide heads (measured 60 -> 70 us there, 12.7 -> 11.7 us at 256)
-    p.dry_pass = (HD <= 256 && (long)grid.x * grid.y * grid.z <= (long)device_info().sm_count * occ) ? 1 : 0;
+    // The warming pass of the query preparation (run it once before the stream-order wait on whatever the buffers hold,
+    // to have the code in the instruction caches) is off for this kernel: since every load it repeats goes through
+    // L2 it no longer pays -- 27.9 against 28.2 us per launch back to back, 34.4 against 35.3 us for a launch on its
+    // own, 29.4 against 31.3 us with a fused append, and 44 against 50 us for a synchronous step that appends a row
+    // (its quantisation ran twice).  When the pass was introduced (loads through the read-only path) it took the
+    // verify call's wait -> first tile from 6.0 to 1.6 us; the kernels keep the code, nothing switches it on.
+    p.dry_pass = 0;
     // Launched with programmatic stream serialization allowed: after a grid that triggers early
     // (another attention call of this library) the grid is set up while the predecessor drains and
     // blocks in griddepcontrol.wait before its first global access; after any other kernel it
@@ -598,7 +602,8 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     pdl[0].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(pl.splits, a.nkv, a.batch * pl.row_groups);
-    p.dry_pass = (long)pl.splits * a.nkv * a.batch * pl.row_groups <= (long)device_info().sm_count * tc5_occupancy<NS>() ? 1 : 0;
+    // (the warming pass of the query preparation is off here as well: verify 26.5 against 26.8 us without it)
+    p.dry_pass = 0;
     cfg.blockDim = dim3(C::NTHREADS);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = st;
