@@ -279,13 +279,12 @@ static bool cluster_route(int splits, long clusters) {
     static std::mutex mu;
     static int max_clusters[64][17];          // 0 = not asked yet, -1 = no
     static bool off = false;
-    if (!C::CLUSTER_OK || splits < 2 || splits > 16) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (clusters < 0) { off = true; return false; }           // (called with -1 after a refused launch)
+    if (off || !C::CLUSTER_OK || splits < 2 || splits > 16) return false;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
-    std::lock_guard<std::mutex> lock(mu);
-    if (clusters < 0) { off = true; return false; }           // (called with -1 after a refused launch)
-    if (off) return false;
     int &n = max_clusters[dev][splits];
     if (n == 0) {
         n = -1;
