@@ -130,6 +130,7 @@ struct KParams {
                                     //    distributed shared memory (no partials in device memory, no arrival word)
     float *partial_export;          // optional exported (o, m, l) per row, m in natural-log units
     int early_rows;                 // window rows [0, early_rows) may be read before griddepcontrol.wait
+    int kv_read_once;               // 1: every cache byte is read by exactly one CTA of the launch (tile copies are marked evict-first in L2)
     // fused quantize-on-write: the last n_new keys of the window are given as fp32 rows
     const float *new_k, *new_v;     // [n_new][nkv][HD], row stride new_stride elements; nullptr = none
     uint8_t *k_cache_w, *v_cache_w, *k_scales_w, *v_scales_w;   // writable aliases of the cache
@@ -228,6 +229,34 @@ __device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap *m
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(dst),
         "l"(reinterpret_cast<unsigned long long>(map)), "r"(0), "r"(row), "r"(batch), "r"(bar)
         : "memory");
+}
+// The same copy for bytes that this launch reads exactly once (the cache rows of a decode call): marked evict-first
+// in L2, so that a hundred megabytes of them do not push out what the launch does come back to -- its own code, the
+// query, the split partials -- or what the next kernel in the stream needs.
+__device__ __forceinline__ void tma_load_tile_once(uint32_t dst, const CUtensorMap *map, int row, int batch, uint32_t bar) {
+    asm volatile(
+        "{\n"
+        ".reg .b64 pol;\n"
+        "createpolicy.fractional.L2::evict_first.b64 pol, 1.0;\n"
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], pol;\n"
+        "}\n" ::"r"(dst),
+        "l"(reinterpret_cast<unsigned long long>(map)), "r"(0), "r"(row), "r"(batch), "r"(bar)
+        : "memory");
+}
+// A whole 16-byte cp.async, evict-first in L2 when `once`.
+__device__ __forceinline__ void cp_async16_hint(uint32_t dst, const void *src, bool once) {
+    if (once) {
+        asm volatile(
+            "{\n"
+            ".reg .b64 pol;\n"
+            "createpolicy.fractional.L2::evict_first.b64 pol, 1.0;\n"
+            "cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, pol;\n"
+            "}\n" ::"r"(dst),
+            "l"(src)
+            : "memory");
+    } else {
+        cp_async16(dst, src, 16);
+    }
 }
 // Contiguous bytes (16-byte aligned both sides, size a multiple of 16) into shared memory.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -1004,8 +1033,13 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS, QS>::NW * 32)
                 if (lane == 0) {
                     const uint32_t bar = my_bar_u32 + 8 * stg;
                     mbar_expect_tx(bar, 2 * C::KV_BYTES + (bulk_sc ? 2 * C::SC_BYTES : 0));
-                    tma_load_tile(st, &tm.k, kvh * p.cache_cap + slot0, b, bar);
-                    tma_load_tile(st + C::KV_BYTES, &tm.v, kvh * p.cache_cap + slot0, b, bar);
+                    if (p.kv_read_once) {
+                        tma_load_tile_once(st, &tm.k, kvh * p.cache_cap + slot0, b, bar);
+                        tma_load_tile_once(st + C::KV_BYTES, &tm.v, kvh * p.cache_cap + slot0, b, bar);
+                    } else {
+                        tma_load_tile(st, &tm.k, kvh * p.cache_cap + slot0, b, bar);
+                        tma_load_tile(st + C::KV_BYTES, &tm.v, kvh * p.cache_cap + slot0, b, bar);
+                    }
                     if (bulk_sc) {
                         bulk_load(ss, ksbase + (size_t)slot0 * C::SCB, C::SC_BYTES, bar);
                         bulk_load(ss + C::SC_BYTES, vsbase + (size_t)slot0 * C::SCB, C::SC_BYTES, bar);
@@ -1018,17 +1052,19 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS, QS>::NW * 32)
                 }
                 tma_mask |= 1u << stg;
             } else if (whole) {
-                // cp.async path: 16-byte coalesced copies into the same swizzled layout
+                // cp.async path: 16-byte coalesced copies into the same swizzled layout (evict-first in L2 when the
+                // launch reads every cache byte once; only where this is the regular path, the wide heads)
                 const uint8_t *gk = kbase + (size_t)slot0 * row_stride + lane_goff;
                 const uint8_t *gv = vbase + (size_t)slot0 * row_stride + lane_goff;
+                const bool once = !C::TMA_OK && p.kv_read_once;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
 #pragma unroll
                     for (int h = 0; h < HPASS; ++h)
-                        cp_async16(st + lane_soff[h] + 8 * i * C::ROWBK, gk + (size_t)(8 * i) * row_stride + 64 * h, 16);
+                        cp_async16_hint(st + lane_soff[h] + 8 * i * C::ROWBK, gk + (size_t)(8 * i) * row_stride + 64 * h, once);
 #pragma unroll
                     for (int h = 0; h < HPASSV; ++h)
-                        cp_async16(st + C::KV_BYTES + lane_soffv[h] + 8 * i * C::ROWBV, gv + (size_t)(8 * i) * row_stride + 64 * h, 16);
+                        cp_async16_hint(st + C::KV_BYTES + lane_soffv[h] + 8 * i * C::ROWBV, gv + (size_t)(8 * i) * row_stride + 64 * h, once);
                 }
                 const size_t sg = (size_t)(slot0 + lane) * C::SCB;
                 copy_scales(ss + lane * C::SCBW, ksbase + sg, true);

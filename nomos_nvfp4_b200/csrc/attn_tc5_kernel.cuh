@@ -423,8 +423,13 @@ __global__ void __launch_bounds__(Cfg<NS>::NTHREADS, Cfg<NS>::MIN_CTAS)
                 const uint32_t sdst = sm_u32 + C::OFF_SCALES + st * 2 * SCALE_BYTES;
                 fused::mbar_expect_tx(bar_full(st), 2 * TILE_BYTES + (scales_by_tma ? 2 * SCALE_BYTES : 0));
                 const int bc = paged ? 0 : b;                    // the pools are one plane for all sequences
-                fused::tma_load_tile(kdst, &tm.k, row0, bc, bar_full(st));
-                fused::tma_load_tile(kdst + TILE_BYTES, &tm.v, row0, bc, bar_full(st));
+                if (p.kv_read_once) {            // evict-first in L2: the launch does not come back to these bytes
+                    fused::tma_load_tile_once(kdst, &tm.k, row0, bc, bar_full(st));
+                    fused::tma_load_tile_once(kdst + TILE_BYTES, &tm.v, row0, bc, bar_full(st));
+                } else {
+                    fused::tma_load_tile(kdst, &tm.k, row0, bc, bar_full(st));
+                    fused::tma_load_tile(kdst + TILE_BYTES, &tm.v, row0, bc, bar_full(st));
+                }
                 if (scales_by_tma) {
                     tma_load_2d(sdst, &tm.ks, row0, bc, bar_full(st));
                     tma_load_2d(sdst + SCALE_BYTES, &tm.vs, row0, bc, bar_full(st));
