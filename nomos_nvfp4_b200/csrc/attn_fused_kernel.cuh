@@ -1630,6 +1630,9 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS, QS>::NW * 32)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
         float *r0 = mbuf + ((size_t)warp * C::NSLOT + mt * 8 + g) * (HDV + 2);
+        // only the rows of real query rows are stored (a decode call fills 2 of a group's 8 slots): with all eight
+        // rows, 130 floats apart, every store of the warp took four shared-memory wavefronts
+        if (div_kvg(p, rg * C::NSLOT + mt * 8 + g) >= p.S) continue;
 #pragma unroll
         for (int nt = 0; nt < C::NT; ++nt) {
             // this thread has MMA columns 2t, 2t+1 of n tile nt.  int8: column c of tile nt is
