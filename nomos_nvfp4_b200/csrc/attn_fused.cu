@@ -675,8 +675,8 @@ static int dispatch_mma(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {
 // Calls both kernels can serve, decode shapes (up to 8 query rows per KV head).  Measured on B200 with both on
 // one box: the tcgen05 kernel streams faster (batch 8 x 131072 keys 619 vs 641 us, 524288 keys 325 vs 346 us:
 // about 7.0 against 6.6 TB/s), the mma.sync kernel has about 2 us less fixed cost per call (one CTA per SM, half
-// as many partials to merge: 32768 keys 26.9 vs 27.7 us, the two-launch decode step 31.5 vs 32.2 us).  Two
-// straight lines, 8.0 us + bytes / 7.0 TB/s and 5.9 us + bytes / 6.6 TB/s, cross at about 240 MB of cache.
+// as many partials to merge).  The crossing point moved from about 240 MB to about 330 MB of cache when the
+// mma.sync kernel's tile copies became evict-first in L2; the table the threshold is read from is at prefers_mma().
 // ------------------------------------------------------------------ query-major prefill (attn_prefill_kernel.cuh)
 // int8 KV, head_dim 128, more query rows per KV head than the decode / verify kernels serve in one CTA (24), a
 // window that does not wrap the ring, no fused append and no partial export.  Everything else -- int4 caches, wider
@@ -749,7 +749,9 @@ static bool prefers_mma(const AttnArgs &a) {
     if (a.tcgen05_always || a.block_table != nullptr || a.S * a.kvg > 8) return false;
     const int keys = a.window > 0 ? std::min(a.klen, a.window + a.S - 1) : a.klen;
     const double bytes = (double)a.batch * a.nkv * keys * (2.0 * a.cache_hd + 8.0);
-    return bytes < 240e6;
+    // same-box measurements, launches back to back, us (mma.sync / tcgen05): 69 MB 18.0 / 17.7, 138 MB 25.7 / 26.7,
+    // 208 MB 35.7 / 35.8, 277 MB 46.1 / 46.6, 415 MB 66.5 / 64.6, 554 MB 93.4 / 88.3
+    return bytes < 330e6;
 }
 
 static int dispatch(cudaStream_t st, const AttnArgs &a, bool q, long *ws) {

@@ -495,7 +495,7 @@ def test_query_rows_of_very_different_magnitude(oracle, S, big):
 
 def test_kernel_choice_follows_the_cost_model(kernel_path):
     """nomos_attn_kernel_choice: short decode calls go to the mma.sync kernel, verify and calls streaming more
-    than about 240 MB to the tcgen05 kernel; the flag bits override; int4 caches have one kernel."""
+    than about 330 MB to the tcgen05 kernel; the flag bits override; int4 caches have one kernel."""
     def choice(S, klen, batch=1, fmt=ops.KV_I8, flags=0, hd=128):
         a = ops.make_args(q=0x1000, k_cache=0x10000, v_cache=0x20000, k_scales=0x30000, v_scales=0x40000, out=0x50000,
                           kv_fmt=fmt, q_type=ops.BF16, out_type=ops.BF16, batch=batch, S=S, nh=32, nkv=16, kvg=2, l_hd=hd,

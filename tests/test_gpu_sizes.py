@@ -135,7 +135,7 @@ def _call(cache, q, *, batch, T, scale, flags=0, win_start=0, klen=None, partial
     return (part if partial else out), choice
 
 
-def test_library_switches_kernel_above_240_mb(oracle):
+def test_library_switches_kernel_for_large_caches(oracle):
     """Batch 2 x 65536 keys x 16 KV heads = 537 MB of cache: the cost model's own pick must be the tcgen05
     kernel, and the same call pinned to the mma.sync kernel must agree with the oracle too."""
     nh, nkv, hd, T, B = 32, 16, 128, 65536, 2
@@ -166,7 +166,7 @@ def test_config5b_shards_of_65536_keys_merge_to_the_full_answer(oracle):
     gathered = torch.empty((G, nh, hd + 2), dtype=torch.float32, device=DEV)
     for g in range(G):
         part, choice = _call(cache, q, batch=1, T=T, scale=scale, win_start=g * chunk, klen=chunk, partial=True)
-        assert choice == 1                              # 268 MB per shard: the tcgen05 kernel
+        assert choice == 0                              # 277 MB per shard: still the mma.sync kernel (it switches at 330 MB)
         gathered[g].copy_(part)
         # the shard's exported triple against the oracle's for the same keys
         _, wp = _exact_of_device_cache(oracle, cache, q, 0, T, scale, lo=g * chunk, klen=chunk, want_partial=True)
