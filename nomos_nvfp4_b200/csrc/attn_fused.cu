@@ -342,13 +342,14 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     if (float *own = fill_peer_params(p, a, pl.grows)) p.partial_export = own;
     // splits of a unit as one thread-block cluster merging through distributed shared memory: plain calls only
     // (final output, no export, no peer exchange), every cluster resident at once, and at least four query rows per
-    // unit.  Measured against the arrival-counter merge, launches back to back: 8 KV heads x 4 group heads, 9
+    // unit or at most four splits (small clusters start as easily as single CTAs: the 1024-key ring of a
+    // sliding-window layer, 16 KV heads x 3 splits, replays at 8.0 against 8.4 us per call).  Measured against the arrival-counter merge, launches back to back: 8 KV heads x 4 group heads, 9
     // splits, 16384 keys 15.4 against 17.1 us; 4 x 8, 16 splits, 4096 keys 10.7 against 12.8 us; but 12 or 15 KV
     // heads x 2 group heads, 9 splits, 32768 keys 23.1 / 26.3 against 22.8 / 26.1 us (a two-row merge is one L2
     // round trip, and a cluster only starts when nine SMs of one GPC are free).  On B200 at most 15 clusters of 7 to
     // 9 CTAs of this kernel are resident (74 of 2, 33 of 4, 7 of 11 to 16), so 16 KV heads x 9 splits never qualify.
     p.cluster_merge = (!a.no_cluster && pl.splits > 1 && a.partial_out == nullptr && a.peer_world <= 1 && a.out != nullptr &&
-                       std::min(C::NSLOT, a.S * a.kvg) >= 4 && cluster_route<FMT, HD, MT, DS, QS>(pl.splits, units)) ? 1 : 0;
+                       (std::min(C::NSLOT, a.S * a.kvg) >= 4 || pl.splits <= 4) && cluster_route<FMT, HD, MT, DS, QS>(pl.splits, units)) ? 1 : 0;
     if (p.cluster_merge) p.coop_merge = 0;
     p.early_rows = settled_rows(a);
     // (row groups and head-dim slice CTAs share their bytes through L2; configuration 2: 27.4 -> 25.6 us per launch)

@@ -21,6 +21,8 @@ CASES = [
     # fmt, hd, nkv, kvg, S, T, splits
     ("i8", 128, 16, 2, 1, 32768, 0),        # configuration 2: two rows per unit, the counter merge either way
     ("i8", 128, 4, 4, 1, 5000, 2),
+    ("i8", 128, 16, 2, 1, 1024, 3),         # a sliding-window ring: two rows per unit, small clusters
+    ("i4b32", 128, 16, 2, 1, 1024, 4),
     ("i8", 128, 4, 4, 1, 5000, 3),
     ("i8", 128, 4, 8, 1, 9001, 16),         # the largest cluster
     ("i8", 128, 2, 8, 1, 3000, 7),
