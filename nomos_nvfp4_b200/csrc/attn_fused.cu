@@ -251,7 +251,17 @@ static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp, int d
             const long fixed = 16 + 16L * units;                    // alignment slack + arrival and departure counters
             max_splits = (int)std::max<long>(1, std::min<long>(max_splits, a.workspace ? (a.ws_bytes - fixed) / per_split : 0));
         }
-        for (int n = 1; n <= max_splits; ++n) {
+        // The search costs about 3 us of host time at 1024 tiles; a decode loop asks the same question step after
+        // step (the tile count moves every 32 tokens), so the last few answers are remembered per thread.
+        struct Memo { int ntiles, units, slots_gpu, nwarp, max_splits, best; };
+        static thread_local Memo memo[4] = {};
+        static thread_local int memo_next = 0;
+        bool hit = false;
+        for (const Memo &m : memo)
+            if (m.best > 0 && m.ntiles == pl.ntiles && m.units == units && m.slots_gpu == slots_gpu && m.nwarp == nwarp && m.max_splits == max_splits) {
+                best = m.best; hit = true; break;
+            }
+        for (int n = 1; !hit && n <= max_splits; ++n) {
             const int tps = (pl.ntiles + n - 1) / n;
             const int n_eff = (pl.ntiles + tps - 1) / tps;
             if (n_eff != n) continue;
@@ -263,6 +273,7 @@ static Plan make_plan(const AttnArgs &a, int occupancy, int hd, int nwarp, int d
             const double cost = (double)waves * (per_warp + 1.5) + (n > 1 ? 1.4 + 0.02 * n : 0.0);
             if (cost < best_cost) { best_cost = cost; best = n; }
         }
+        if (!hit) { memo[memo_next] = Memo{pl.ntiles, units, slots_gpu, nwarp, max_splits, best}; memo_next = (memo_next + 1) % 4; }
     }
     pl.tiles_per_split = (pl.ntiles + best - 1) / best;
     pl.splits = (pl.ntiles + pl.tiles_per_split - 1) / pl.tiles_per_split;
@@ -519,7 +530,13 @@ static Tc5Plan tc5_plan(const AttnArgs &a, int ns, int occupancy) {
             const long fixed = 16 + 16L * units;
             max_splits = (int)std::max<long>(1, std::min<long>(max_splits, a.workspace ? (a.ws_bytes - fixed) / per_split : 0));
         }
-        for (int n = 1; n <= max_splits; ++n) {
+        struct Memo { int ntiles, units, slots_gpu, max_splits, best; };          // (as in make_plan: the last few answers, per thread)
+        static thread_local Memo memo[4] = {};
+        static thread_local int memo_next = 0;
+        bool hit = false;
+        for (const Memo &m : memo)
+            if (m.best > 0 && m.ntiles == pl.ntiles && m.units == units && m.slots_gpu == slots_gpu && m.max_splits == max_splits) { best = m.best; hit = true; break; }
+        for (int n = 1; !hit && n <= max_splits; ++n) {
             const int tps = (pl.ntiles + n - 1) / n;
             if ((pl.ntiles + tps - 1) / tps != n) continue;
             const long ctas = (long)units * n;
@@ -529,6 +546,7 @@ static Tc5Plan tc5_plan(const AttnArgs &a, int ns, int occupancy) {
             const double cost = (double)waves * (tps + 3.0) + (n > 1 ? 3.0 + 0.03 * n : 0.0);
             if (cost < best_cost) { best_cost = cost; best = n; }
         }
+        if (!hit) { memo[memo_next] = Memo{pl.ntiles, units, slots_gpu, max_splits, best}; memo_next = (memo_next + 1) % 4; }
     }
     if (paged && (pl.ntiles + best - 1) / best > tc5::MAX_PAGED_TILES) best = (pl.ntiles + tc5::MAX_PAGED_TILES - 1) / tc5::MAX_PAGED_TILES;
     pl.tiles_per_split = (pl.ntiles + best - 1) / best;
