@@ -325,7 +325,7 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     const long part_bytes = (((long)pl.splits * pl.grows * (HD + 2) * 4) + 15) / 16 * 16;
     // a sequence-sharded call always ends in the unit's merging CTA (it runs the exchange), also with one split
     const bool in_kernel_merge = pl.splits > 1 || a.peer_world > 1;
-    // two counter words per unit: arrivals, and (cooperative merge) departures
+    // 16 bytes per unit: the arrival word (count, round bit and tag) and a spare
     const long need = in_kernel_merge ? part_bytes + units * 16 : 0;
     if (query_ws) { *ws_needed = part_bytes + units * 16; return NOMOS_OK; }   // also enough for a sequence-sharded call, which merges in the kernel even with one split
     if (need > a.ws_bytes || (need > 0 && a.workspace == nullptr)) {
@@ -347,7 +347,6 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     p.counters = in_kernel_merge ? reinterpret_cast<unsigned long long *>(static_cast<char *>(a.workspace) + part_bytes) : nullptr;
     p.splits = pl.splits;
     p.arrivals = pl.splits * DS;
-    p.departures = p.counters ? p.counters + units : nullptr;
     p.coop_merge = use_coop_merge(a, pl.splits, p.arrivals, (long)pl.splits * DS * units, occ, std::min(C::NSLOT, a.S * a.kvg), HD);
     p.partial_export = a.partial_out;
     if (float *own = fill_peer_params(p, a, pl.grows)) p.partial_export = own;
@@ -596,7 +595,6 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     p.counters = in_kernel_merge ? reinterpret_cast<unsigned long long *>(static_cast<char *>(a.workspace) + part_bytes) : nullptr;
     p.splits = pl.splits;
     p.arrivals = pl.splits;
-    p.departures = p.counters ? p.counters + units : nullptr;
     p.coop_merge = paged ? 0 : use_coop_merge(a, pl.splits, p.arrivals, (long)pl.splits * units, /* one CTA per SM, whatever the plan assumes */ 1, std::min(NS, a.S * a.kvg), a.l_hd);
     p.partial_export = a.partial_out;
     if (float *own = fill_peer_params(p, a, pl.grows)) p.partial_export = own;

@@ -123,7 +123,6 @@ struct KParams {
     unsigned long long *counters;   // one word per unit: (tag << 16) | arrivals, see merge_splits_in_kernel; nullptr = no in-kernel merge
     int splits;
     int arrivals;                   // CTAs per unit that arrive before the merge: splits x head-dim slices
-    unsigned long long *departures; // coop_merge: one more tagged word per unit, counting the CTAs that finished their share
     int coop_merge;                 // K > 0: the last K CTAs of a unit to arrive each merge a share of the unit's rows once all have arrived (the whole
                                     //    grid is resident at once, so waiting for the others cannot starve them)
     int cluster_merge;              // 1: the splits of a unit are the CTAs of one thread-block cluster; they merge through
@@ -452,28 +451,37 @@ __device__ __forceinline__ bool merge_without_staging(const KParams &p, int b, i
 // arrive merges the unit's rows; the others return.  `scratch` is shared memory the CTA no
 // longer needs, at least 8 * NSLOT * splits bytes.
 // One arrival on a tagged counter word; returns how many have arrived including this one, or -1 if the word could
-// not be brought under the tag within the try limit.  The word is (tag << 16 | arrivals): the CTA that closes a round
-// leaves it tagged with zero arrivals, so the common case is a single atomic add.  A word without the tag has never
+// not be brought under the tag within the try limit.  The word is (tag << 16 | round bit << 15 | arrivals): the CTA
+// that closes a round leaves it tagged with zero arrivals, so the common case is a single atomic add.  The round bit
+// is what the cooperative merge's waiters watch: the last arrival of a round flips it (and zeroes the count in the
+// same store), so "everybody has arrived" needs no second word and nobody has to reset anything afterwards.  A word without the tag has never
 // been used by this library (the workspace is caller-owned and arrives uninitialised): the add went to garbage, and
 // the arrivals that find garbage install a tagged word with compare-and-swap, which only fails when another arrival
 // made progress.
 constexpr unsigned long long ARRIVE_TAG = 0x6e6f6d6f7341ull;
-__device__ __forceinline__ int tagged_arrive(unsigned long long *ctr) {
+__device__ __forceinline__ int tagged_arrive(unsigned long long *ctr, int *round_bit = nullptr) {
     unsigned long long old = arrive_add(ctr);
-    if ((old >> 16) == ARRIVE_TAG) return (int)(old & 0xffffull) + 1;
+    const auto done = [&](unsigned long long o) {
+        if (round_bit) *round_bit = (int)((o >> 15) & 1ull);
+        return (int)(o & 0x7fffull) + 1;
+    };
+    if ((old >> 16) == ARRIVE_TAG) return done(old);
     for (int tries = 0; tries < (1 << 16); ++tries) {            // bounded: gives up rather than spin forever
         const unsigned long long cur = *reinterpret_cast<volatile unsigned long long *>(ctr);
         if ((cur >> 16) == ARRIVE_TAG) {
             old = arrive_add(ctr);
-            if ((old >> 16) == ARRIVE_TAG) return (int)(old & 0xffffull) + 1;
+            if ((old >> 16) == ARRIVE_TAG) return done(old);
         } else {
             __threadfence();          // rare path: plain fences around the compare-and-swap
             const bool won = atomicCAS(ctr, cur, (ARRIVE_TAG << 16) | 1ull) == cur;
             __threadfence();
-            if (won) return 1;
+            if (won) { if (round_bit) *round_bit = 0; return 1; }
         }
     }
     return -1;
+}
+__device__ __forceinline__ void st_release_gpu(unsigned long long *addr, unsigned long long v) {
+    asm volatile("st.release.gpu.global.u64 [%0], %1;\n" ::"l"(addr), "l"(v) : "memory");
 }
 __device__ __forceinline__ unsigned long long ld_acquire_gpu(const unsigned long long *addr) {
     unsigned long long v;
@@ -563,8 +571,7 @@ __device__ __noinline__ void merge_coop(const SmallMergeArgs a, int share, int n
 // The cooperative form of the unit merge, out of line (it runs once per CTA; p is the kernels' __grid_constant__
 // parameter block).  The last K = p.coop_merge CTAs of the unit to arrive each merge 1/K of its rows: a CTA that
 // arrives earlier leaves at once (its SM is free for the next launch), one of the K waits -- with a time limit --
-// until every CTA of the unit has arrived, merges its share and leaves through a second tagged word; the last one
-// out resets both words.  The whole grid is resident at once (host-checked), so the CTAs waited for are running.
+// until the last arrival has flipped the word's round bit, merges its share and leaves.  The whole grid is resident at once (host-checked), so the CTAs waited for are running.
 template <int NSLOT, int HD, int NTHR>
 __device__ __noinline__ void coop_merge_unit(const KParams &p, int b, int kvh, int rg) {
     __shared__ int s_go, s_share;
@@ -572,15 +579,20 @@ __device__ __noinline__ void coop_merge_unit(const KParams &p, int b, int kvh, i
     const int K = min(p.coop_merge, p.arrivals);
     __syncthreads();                      // all partial stores of this CTA are issued
     if (threadIdx.x == 0) {
-        const int arrived = tagged_arrive(ctr);
+        int round = 0;
+        const int arrived = tagged_arrive(ctr, &round);
         s_share = arrived - (p.arrivals - K) - 1;
         bool all = arrived == p.arrivals;
-        if (s_share >= 0 && !all) {
+        if (all) {
+            // the last arrival closes the round: count back to zero, round bit flipped, in one release store (its
+            // acquire-release arrival has seen every other CTA's partial rows; the waiters acquire this store)
+            st_release_gpu(ctr, (ARRIVE_TAG << 16) | ((unsigned long long)(round ^ 1) << 15));
+        } else if (s_share >= 0) {
             unsigned long long t0, t1;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
             for (;;) {
                 const unsigned long long cur = ld_acquire_gpu(ctr);
-                if ((cur >> 16) == ARRIVE_TAG && (int)(cur & 0xffffull) == p.arrivals) { all = true; break; }
+                if ((cur >> 16) == ARRIVE_TAG && (int)((cur >> 15) & 1ull) != round) { all = true; break; }
                 __nanosleep(100);
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
                 if (t1 - t0 > 1000000000ull) { atomicOr(p.fault, 1u); break; }
@@ -604,14 +616,6 @@ __device__ __noinline__ void coop_merge_unit(const KParams &p, int b, int kvh, i
         else merge_medium<HD, 12, 1>(sa, threadIdx.x, NTHR, begin, end);
     } else {
         merge_coop<HD>(sa, s_share, K, threadIdx.x, NTHR);
-    }
-    __syncthreads();                      // this CTA's share is stored
-    if (threadIdx.x == 0) {
-        unsigned long long *dep = p.departures + ((size_t)blockIdx.z * gridDim.y + blockIdx.y);
-        if (tagged_arrive(dep) == K) {                                  // the last one out leaves both words clean
-            *dep = ARRIVE_TAG << 16;
-            *ctr = ARRIVE_TAG << 16;
-        }
     }
 }
 
