@@ -1671,7 +1671,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS, QS>::NW * 32)
         float o[NDQ], lstar = 0.0f;
 #pragma unroll
         for (int i = 0; i < NDQ; ++i) o[i] = 0.0f;
-#pragma unroll 4                                       // (four streams' loads in flight: rolled up fully the loop took 0.8 us)
+#pragma unroll                                         // (every stream's loads in flight: rolled up the loop took 0.8 us)
         for (int w = 0; w < NQ; ++w) {
             const float ww = __shfl_sync(0xffffffffu, wg, w);
             lstar = fmaf(ww, __shfl_sync(0xffffffffu, lw, w), lstar);
