@@ -363,7 +363,7 @@ static int launch_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, long *
     if (p.cluster_merge) p.coop_merge = 0;
     p.early_rows = settled_rows(a);
     // (row groups and head-dim slice CTAs share their bytes through L2; configuration 2: 27.4 -> 25.6 us per launch)
-    p.kv_read_once = (pl.row_groups == 1 && DS == 1 && (long)a.batch * a.nkv * a.klen * 2 * a.cache_hd < (512l << 20)) ? 1 : 0;
+    p.kv_read_once = (pl.row_groups == 1 && DS == 1 && (long)a.batch * a.nkv * a.klen * 2 * a.cache_hd < (1024l << 20)) ? 1 : 0;
     p.new_k = a.new_k; p.new_v = a.new_v;
     p.n_new = a.new_k ? a.n_new : 0; p.new_stride = a.new_stride; p.new_base_pos = a.new_base_pos;
     p.k_cache_w = const_cast<uint8_t *>(p.k_cache); p.v_cache_w = const_cast<uint8_t *>(p.v_cache);
@@ -601,8 +601,9 @@ static int launch_tc5_inst(cudaStream_t st, const AttnArgs &a, bool query_ws, lo
     p.early_rows = paged ? 0 : settled_rows(a);
     // evict-first tile copies protect what the launch comes back to (code, query, partials) from its own stream:
     // verify at 16393 keys 26.5 -> 25.7 us; on streams of gigabytes, where that fixed part is noise, they measured
-    // 3 % slower (C5a 612 -> 630 us, C5b 312 -> 323 us), hence the size limit
-    p.kv_read_once = (pl.row_groups == 1 && (long)a.batch * a.nkv * a.klen * 2 * a.cache_hd < (512l << 20)) ? 1 : 0;
+    // 3 % slower (C5a 612 -> 630 us, C5b 312 -> 323 us), hence the size limit (554 MB: 87.6 -> 86.8 us, 830 MB:
+    // 125.7 -> 124.9, 1107 MB: 166.5 -> 167.0; the mma.sync kernel gains 3 to 4 % at all three)
+    p.kv_read_once = (pl.row_groups == 1 && (long)a.batch * a.nkv * a.klen * 2 * a.cache_hd < (1024l << 20)) ? 1 : 0;
     p.block_table = a.block_table; p.seq_lens = a.seq_lens; p.max_pages = a.max_pages;
     p.q_type = a.q_type; p.out_type = a.out_type;
     p.S = a.S; p.nh = a.nh; p.nkv = a.nkv; p.kvg = a.kvg; p.cache_hd = a.cache_hd; p.cache_cap = a.cache_cap;
