@@ -1210,8 +1210,7 @@ __global__ void __launch_bounds__(Cfg<FMT, HD, MT, DS, QS>::NW * 32)
                     // int4 tiles hand element 32b+8t+2j+par of a row to MMA k slot 16*par+4t+j of step b
                     pos = 32 * i + ((lane & 1) << 4) + ((lane >> 3) << 2) + ((lane >> 1) & 3);
                     int bs = qf;                                        // sum of the block's fixed-point values
-    #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
+                    bs = __reduce_add_sync(0xffffffffu, bs);           // one instruction per block instead of five shuffle rounds
                     qblk[i] = bs;
                 }
                 // rows are stored with their 16-byte chunks XOR-swizzled by the slot index, so that the
